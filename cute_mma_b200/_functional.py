@@ -1,0 +1,154 @@
+"""``forward`` / ``backward``: the functional Prism API, bound to the sm_100a C-ABI library.
+
+Mirrors ``cute_prism.forward`` / ``cute_prism.backward`` of the reference
+(src/cute_prism/__init__.py:77-269 and :272-505): same positional arguments, same return
+tuples, same ``ValueError`` for invalid parameters (src/cute_prism/_validate.py:12-84).
+There is exactly one backend, so ``backend`` / ``mode`` / ``comp_params`` / ``autotuning``
+style keywords are accepted for call compatibility and otherwise ignored.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+
+import torch
+
+from . import _lib
+from ._tile_table import lookup as _tile_lookup
+
+KIND_FWD, KIND_BWD_DADR, KIND_BWD_DB = 0, 1, 2
+ACTIVATIONS = (None, "silu_gate")
+_DTYPES = {torch.float16: 0, torch.bfloat16: 1}
+
+
+def validate_kernel_params(group_size: int, reconn_sz: int) -> None:
+    """Same rules and messages as the reference's ``validate_kernel_params``."""
+    if not isinstance(group_size, int) or group_size <= 0:
+        raise ValueError(f"group_size must be a positive integer, got {group_size}")
+    if not isinstance(reconn_sz, int) or reconn_sz <= 0:
+        raise ValueError(f"reconn_sz must be a positive integer, got {reconn_sz}")
+    if reconn_sz % 8 != 0:
+        raise ValueError(f"reconn_sz must be a multiple of 8, got {reconn_sz}")
+    if group_size % 8 != 0:
+        raise ValueError(f"group_size must be a multiple of 8, got {group_size}")
+
+
+def validate_tensor_params(A, B, R, group_size, reconn_sz) -> None:
+    """Same rules as the reference's ``validate_tensor_params``."""
+    for name, t in (("A", A), ("B", B), ("R", R)):
+        if not t.is_cuda:
+            raise ValueError(f"{name} must be a CUDA tensor, got device={t.device}")
+        if t.dtype not in _DTYPES:
+            raise ValueError(f"{name} must be float16 or bfloat16, got dtype={t.dtype}")
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous (row-major)")
+        if t.dim() != 2:
+            raise ValueError(f"{name} must be 2D, got {t.dim()}D")
+    if not (A.dtype == B.dtype == R.dtype):
+        raise ValueError(f"All tensors must have the same dtype, got A={A.dtype}, B={B.dtype}, R={R.dtype}")
+    if not (A.device == B.device == R.device):
+        raise ValueError("All tensors must be on the same CUDA device")
+    M, K = A.shape
+    N = B.shape[0]
+    if B.shape[1] != K:
+        raise ValueError(f"K dimension mismatch: A has K={K} but B has K={B.shape[1]}")
+    if R.shape[1] != K:
+        raise ValueError(f"K dimension mismatch: A has K={K} but R has K={R.shape[1]}")
+    if N % group_size != 0:
+        raise ValueError(f"N ({N}) must be divisible by group_size ({group_size})")
+    if K % reconn_sz != 0:
+        raise ValueError(f"K ({K}) must be divisible by reconn_sz ({reconn_sz})")
+    rows = (N // group_size) * reconn_sz
+    if R.shape[0] != rows:
+        raise ValueError(f"R must have shape ({rows}, {K}), but got ({R.shape[0]}, {R.shape[1]})")
+
+
+# --------------------------------------------------------------------------- workspace
+class _Workspace(threading.local):
+    """One growing scratch buffer per (thread, device); its first 256 bytes are the status header."""
+
+    def __init__(self):
+        self.bufs = {}
+
+    def get(self, device: torch.device, nbytes: int) -> torch.Tensor:
+        buf = self.bufs.get(device)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+            self.bufs[device] = buf
+        return buf
+
+
+_workspace = _Workspace()
+
+
+def _cfg_array(cfg):
+    if not cfg:
+        return None
+    arr = (ctypes.c_int * 8)(*([int(x) for x in cfg] + [0] * (8 - len(cfg))))
+    return arr
+
+
+def _stream_ptr(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def check_device_status(device=None) -> None:
+    """Synchronise and raise if a kernel recorded a device-side error (bounded wait ran out)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    buf = _workspace.bufs.get(device)
+    if buf is None:
+        return
+    with torch.cuda.device(device):
+        _lib.check(_lib.lib().prism_status(ctypes.c_void_p(buf.data_ptr()), _stream_ptr(device)))
+
+
+def _gate_code(activation):
+    if activation not in ACTIVATIONS:
+        if activation == "sigmoid_gate":
+            raise ValueError("activation='sigmoid_gate' is not supported by the sm_100a kernels")
+        raise ValueError(f"Unknown activation {activation!r}, must be one of {ACTIVATIONS}")
+    return 1 if activation == "silu_gate" else 0
+
+
+def _reject_unsupported(**kw):
+    for name, val in kw.items():
+        if val is not None and val is not False and val != 0.0:
+            raise ValueError(f"{name} is not supported by the sm_100a kernels")
+
+
+def forward(A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=None, mode: str = "ar",
+            comp_params=None, activation=None, autotuning: bool = False, autotuning_search_space=None,
+            force_rebenchmark: bool = False, internal_bias=None, dropout_p: float = 0.0,
+            training: bool = False, shuffle_masks=None, *, bias=None, tile_cfg=None):
+    """C = per-group (A . blockdiag(R_g)^T) @ B_g^T, or the silu-gated form; returns ``(C, [])``.
+
+    ``bias`` (keyword-only, [N], same dtype) is added in the kernel epilogue.
+    """
+    if mode != "ar":
+        raise ValueError("The sm_100a kernels only support mode='ar'")
+    gate = _gate_code(activation)
+    validate_kernel_params(group_size, reconn_sz)
+    _reject_unsupported(internal_bias=internal_bias, shuffle_masks=shuffle_masks,
+                        dropout_p=(dropout_p if training else 0.0))
+    validate_tensor_params(A, B, R, group_size, reconn_sz)
+    M, K = A.shape
+    N = B.shape[0]
+    if bias is not None:
+        if bias.dtype != A.dtype or bias.shape != (N,) or not bias.is_contiguous() or bias.device != A.device:
+            raise ValueError("bias must be a contiguous (N,) tensor of the same dtype and device as A")
+    C = torch.empty(M, N, dtype=A.dtype, device=A.device)
+    if M == 0:
+        return C, []
+    L = _lib.lib()
+    cfg = tile_cfg if tile_cfg is not None else _tile_lookup("fwd", A.dtype, gate, M, N, K, group_size, reconn_sz)
+    cfg_arr = _cfg_array(cfg)
+    dt = _DTYPES[A.dtype]
+    with torch.cuda.device(A.device):
+        need = L.prism_workspace_bytes(KIND_FWD, M, N, K, group_size, reconn_sz, dt, cfg_arr)
+        ws = _workspace.get(A.device, need)
+        _lib.check(L.prism_fwd(
+            ctypes.c_void_p(A.data_ptr()), ctypes.c_void_p(B.data_ptr()), ctypes.c_void_p(R.data_ptr()),
+            ctypes.c_void_p(bias.data_ptr()) if bias is not None else None, ctypes.c_void_p(C.data_ptr()),
+            M, N, K, group_size, reconn_sz, dt, gate, A.stride(0), B.stride(0), R.stride(0), C.stride(0),
+            cfg_arr, ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(A.device)))
+    return C, []

@@ -1,0 +1,385 @@
+// Prism forward for sm_100a:  C[:, group g] = H_g @ B_g^T  with
+//   H_g = A . blockdiag(R_g)^T                 (plain / "ar" mode)
+//   H_g = A * silu(A . blockdiag(R_g)^T)       (silu_gate mode)
+// in one kernel; H never leaves the SM.
+//
+// Replaces the reference's prism_tn / prism_device forward kernel
+// (cute_prism_coop_pc.cu:567-804) and its binding (torch_ext/prism_fwd_torch.cu:23-196).
+//
+// Per CTA: a persistent loop over (128-row, BN-column) output tiles; per 64-wide K chunk
+//   TMA warp   : A tile [128 x 64], R_g tile [E x 64] into the "AR" ring, B_g tile [BN x 64]
+//                into the "B" ring (128-byte swizzle, zero fill outside the tensors)
+//   MMA warp   : block rotation S = A_blk . R_blk^T as tcgen05.mma M128 N=E K=16 per block into a
+//                ring of 64-column TMEM buffers; then, two chunks later, the dense product
+//                C += H . B^T as tcgen05.mma M128 N=BN K=16, accumulating in TMEM
+//   gate warps : tcgen05.ld S, read A from shared memory, H = A*silu(S) (or H = S), write H
+//                over the A tile in place (same swizzled layout), release the S buffer
+//   epilogue   : tcgen05.ld C, + bias, cast, store.
+#include "prism_host.cuh"
+#include "prism_kernels.cuh"
+
+namespace prism {
+
+namespace fwd {
+constexpr int kThreads = 448;       // warp 0 TMA, warp 1 MMA, warps 2-9 gate, warps 10-13 epilogue
+constexpr int kGateWarp0 = 2;
+constexpr int kNumGateWarps = 8;
+constexpr int kEpiWarp0 = 10;
+constexpr int kNumEpiWarps = 4;
+constexpr int kSBufs = 4;           // TMEM ring of S buffers, 64 columns each
+constexpr int kSCol0 = 256;         // S ring lives in TMEM columns [256, 512)
+constexpr int kLag = 2;             // dense MMA of chunk c is issued after the rotation of chunk c+kLag
+constexpr int kMaxStages = 8;
+constexpr int kATileBytes = 128 * 128;  // [128 rows x 64 elems] 16-bit
+}  // namespace fwd
+
+struct FwdParams {
+  int M, N, K;
+  int gs, E;            // group size, effective rotation block (16/32/64)
+  int BN;               // N tile, divides gs
+  int n_mtiles, n_ntiles, ntiles_per_group, n_tiles;
+  int PM;               // m-tiles per rasterisation panel
+  int n_kchunks;
+  int sa, sb;           // stages of the AR ring / B ring
+  int r_tile_bytes;     // bytes reserved for the R tile of one AR stage (multiple of 1024)
+  const void* bias;     // [N] or null
+  void* C;
+  long long ldc;
+  int* err;
+};
+
+struct FwdBarriers {
+  uint64_t ar_full[fwd::kMaxStages];
+  uint64_t h_full[fwd::kMaxStages];
+  uint64_t a_empty[fwd::kMaxStages];
+  uint64_t b_full[fwd::kMaxStages];
+  uint64_t b_empty[fwd::kMaxStages];
+  uint64_t s_full[fwd::kSBufs];
+  uint64_t s_empty[fwd::kSBufs];
+  uint64_t acc_full;
+  uint64_t acc_empty;
+  uint32_t tmem_base;
+};
+
+__device__ __forceinline__ void tile_coords(const FwdParams& p, int t, int& mt, int& nt) {
+  const int per_panel = p.PM * p.n_ntiles;
+  const int panel = t / per_panel;
+  const int rem = t - panel * per_panel;
+  const int m0 = panel * p.PM;
+  const int pm = min(p.PM, p.n_mtiles - m0);  // last panel may be short
+  nt = rem / pm;
+  mt = m0 + (rem - nt * pm);
+}
+
+template <int DT, int GATE>
+__global__ void __launch_bounds__(fwd::kThreads, 1)
+prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmR,
+                 const __grid_constant__ CUtensorMap tmB, const FwdParams p) {
+  using namespace fwd;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  const int ar_stage_bytes = kATileBytes + p.r_tile_bytes;
+  const int b_stage_bytes = p.BN * 128;
+  uint8_t* smemAR = smem;
+  uint8_t* smemB = smem + p.sa * ar_stage_bytes;
+  FwdBarriers* bars = reinterpret_cast<FwdBarriers*>(smemB + p.sb * b_stage_bytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kMaxStages; ++i) {
+      mbar_init(&bars->ar_full[i], 1);
+      mbar_init(&bars->h_full[i], kNumGateWarps);
+      mbar_init(&bars->a_empty[i], 1);
+      mbar_init(&bars->b_full[i], 1);
+      mbar_init(&bars->b_empty[i], 1);
+    }
+    for (int i = 0; i < kSBufs; ++i) {
+      mbar_init(&bars->s_full[i], 1);
+      mbar_init(&bars->s_empty[i], kNumGateWarps);
+    }
+    mbar_init(&bars->acc_full, 1);
+    mbar_init(&bars->acc_empty, kNumEpiWarps);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmR);
+    prefetch_tmap(&tmB);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+  const int nk = p.n_kchunks;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      // The AR ring is `ahead` chunks deeper than the B ring: A/R tiles are requested that much
+      // earlier, because the rotation + gate of a chunk must finish before its dense MMA starts.
+      const int my_tiles = (p.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+      const uint32_t total = (uint32_t)my_tiles * nk;
+      const uint32_t ahead = p.sa - p.sb;
+      bool ok = true;
+      for (uint32_t j = 0; j < total + ahead && ok; ++j) {
+        if (j < total) {
+          const uint32_t it = j;
+          int mt, nt;
+          tile_coords(p, blockIdx.x + (it / nk) * gridDim.x, mt, nt);
+          const int c = it % nk;
+          const int g = nt / p.ntiles_per_group;
+          const int sa = it % p.sa;
+          if (!mbar_wait(&bars->a_empty[sa], ((it / p.sa) & 1) ^ 1)) { ok = false; break; }
+          uint8_t* dstA = smemAR + sa * ar_stage_bytes;
+          mbar_arrive_expect_tx(&bars->ar_full[sa], kATileBytes + p.E * 128);
+          tma_load_2d(dstA, &tmA, &bars->ar_full[sa], c * 64, mt * 128);
+          tma_load_2d(dstA + kATileBytes, &tmR, &bars->ar_full[sa], c * 64, g * p.E);
+        }
+        if (j >= ahead) {
+          const uint32_t it = j - ahead;
+          int mt, nt;
+          tile_coords(p, blockIdx.x + (it / nk) * gridDim.x, mt, nt);
+          const int c = it % nk;
+          const int sb = it % p.sb;
+          if (!mbar_wait(&bars->b_empty[sb], ((it / p.sb) & 1) ^ 1)) { ok = false; break; }
+          mbar_arrive_expect_tx(&bars->b_full[sb], b_stage_bytes);
+          tma_load_2d(smemB + sb * b_stage_bytes, &tmB, &bars->b_full[sb], c * 64, nt * p.BN);
+        }
+      }
+      if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc(DT, 128, p.E, 0, 0);
+      const uint32_t idesc_c = make_idesc(DT, 128, p.BN, 0, 0);
+      const int blocks_per_chunk = 64 / p.E;
+      const int ksteps_per_block = p.E / 16;
+      const int my_tiles = (p.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+      const uint32_t total = (uint32_t)my_tiles * nk;
+      bool ok = true;
+      for (uint32_t j = 0; j < total + kLag && ok; ++j) {
+        if (j < total) {
+          // rotation of chunk j: S = A_blk . R_blk^T for every block of the chunk
+          const uint32_t it = j;
+          const int sa = it % p.sa, sbuf = it % kSBufs;
+          if (!mbar_wait(&bars->ar_full[sa], (it / p.sa) & 1)) { ok = false; break; }
+          if (!mbar_wait(&bars->s_empty[sbuf], ((it / kSBufs) & 1) ^ 1)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smemAR + sa * ar_stage_bytes);
+          const uint32_t r_addr = a_addr + kATileBytes;
+          for (int b = 0; b < blocks_per_chunk; ++b) {
+            for (int ks = 0; ks < ksteps_per_block; ++ks) {
+              const uint32_t koff = (b * p.E + ks * 16) * 2;
+              umma_f16(tmem_base + kSCol0 + sbuf * 64 + b * p.E,
+                       desc_kmajor_sw128(a_addr + koff, 1024),
+                       desc_kmajor_sw128(r_addr + koff, 1024), idesc_s, ks > 0 ? 1u : 0u);
+            }
+          }
+          umma_commit(&bars->s_full[sbuf]);
+        }
+        if (j >= kLag) {
+          // dense product of chunk j - kLag: C += H . B^T
+          const uint32_t it = j - kLag;
+          const int cm = it % nk;
+          const uint32_t tile_iter = it / nk;
+          const int sa = it % p.sa, sb = it % p.sb;
+          if (!mbar_wait(&bars->h_full[sa], (it / p.sa) & 1)) { ok = false; break; }
+          if (!mbar_wait(&bars->b_full[sb], (it / p.sb) & 1)) { ok = false; break; }
+          if (cm == 0) {
+            if (!mbar_wait(&bars->acc_empty, (tile_iter & 1) ^ 1)) { ok = false; break; }
+          }
+          tc_fence_after_sync();
+          const uint32_t h_addr = smem_u32(smemAR + sa * ar_stage_bytes);
+          const uint32_t b_addr = smem_u32(smemB + sb * b_stage_bytes);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            umma_f16(tmem_base, desc_kmajor_sw128(h_addr + ks * 32, 1024),
+                     desc_kmajor_sw128(b_addr + ks * 32, 1024), idesc_c,
+                     (cm > 0 || ks > 0) ? 1u : 0u);
+          }
+          umma_commit(&bars->a_empty[sa]);
+          umma_commit(&bars->b_empty[sb]);
+          if (cm == nk - 1) umma_commit(&bars->acc_full);
+        }
+      }
+      if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
+    }
+  } else if (warp < kEpiWarp0) {
+    // ------------------------------------------------------------------ gate warps
+    const int gw = warp - kGateWarp0;
+    const int q = warp & 3;          // TMEM lane quarter this warp may access
+    const int half = gw >> 2;        // which 32 of the chunk's 64 columns
+    const uint32_t row = q * 32 + lane;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
+      for (int c = 0; c < nk; ++c, ++it) {
+        const int sa = it % p.sa, sbuf = it % kSBufs;
+        if (!mbar_wait(&bars->s_full[sbuf], (it / kSBufs) & 1)) { ok = false; break; }
+        tc_fence_after_sync();
+        uint8_t* tile = smemAR + sa * ar_stage_bytes;
+        uint32_t s[32];
+        tmem_ld_x32(tmem_base + (uint32_t(q * 32) << 16) + kSCol0 + sbuf * 64 + half * 32, s);
+        uint4 av[4];
+        if (GATE == GATE_SILU) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            av[j] = *reinterpret_cast<const uint4*>(tile + sw128_offset(row, half * 4 + j));
+        }
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t aw[4] = {0, 0, 0, 0};
+          if (GATE == GATE_SILU) { aw[0] = av[j].x; aw[1] = av[j].y; aw[2] = av[j].z; aw[3] = av[j].w; }
+          uint32_t ow[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float s0 = __uint_as_float(s[j * 8 + e * 2]);
+            float s1 = __uint_as_float(s[j * 8 + e * 2 + 1]);
+            float h0, h1;
+            if (GATE == GATE_SILU) {
+              const float2 a2 = Elem<DT>::unpack(aw[e]);
+              h0 = a2.x * (s0 * sigmoid_fast(s0));
+              h1 = a2.y * (s1 * sigmoid_fast(s1));
+            } else {
+              h0 = s0;
+              h1 = s1;
+            }
+            ow[e] = Elem<DT>::pack(h0, h1);
+          }
+          *reinterpret_cast<uint4*>(tile + sw128_offset(row, half * 4 + j)) =
+              make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&bars->s_empty[sbuf]);
+          mbar_arrive(&bars->h_full[sa]);
+        }
+      }
+    }
+    if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int q = warp & 3;
+    const uint32_t row = q * 32 + lane;
+    uint32_t tile_iter = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++tile_iter) {
+      int mt, nt;
+      tile_coords(p, t, mt, nt);
+      if (!mbar_wait(&bars->acc_full, tile_iter & 1)) { ok = false; break; }
+      tc_fence_after_sync();
+      const long long grow = (long long)mt * 128 + row;
+      const int n0 = nt * p.BN;
+      uint16_t* crow = reinterpret_cast<uint16_t*>(p.C) + grow * p.ldc + n0;
+      const uint16_t* bias = reinterpret_cast<const uint16_t*>(p.bias);
+      for (int c0 = 0; c0 < p.BN; c0 += 32) {
+        uint32_t v[32];
+        if (p.BN - c0 >= 32) {
+          tmem_ld_x32(tmem_base + (uint32_t(q * 32) << 16) + c0, v);
+        } else {  // BN is a multiple of 16: a 16-column tail
+          uint32_t v16[16];
+          tmem_ld_x16(tmem_base + (uint32_t(q * 32) << 16) + c0, v16);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) { v[j] = v16[j]; v[16 + j] = 0; }
+        }
+        tmem_ld_wait();
+        const int ncols = min(32, p.BN - c0);
+        if (grow < p.M) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (j * 8 < ncols) {
+              uint32_t ow[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float x0 = __uint_as_float(v[j * 8 + e * 2]);
+                float x1 = __uint_as_float(v[j * 8 + e * 2 + 1]);
+                if (bias != nullptr) {
+                  const uint32_t bw = *reinterpret_cast<const uint32_t*>(bias + n0 + c0 + j * 8 + e * 2);
+                  const float2 b2 = Elem<DT>::unpack(bw);
+                  x0 += b2.x;
+                  x1 += b2.y;
+                }
+                ow[e] = Elem<DT>::pack(x0, x1);
+              }
+              *reinterpret_cast<uint4*>(crow + c0 + j * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->acc_empty);
+    }
+    if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// ----------------------------------------------------------------------------
+// host launcher
+// ----------------------------------------------------------------------------
+int launch_fwd(const FwdArgs& a) {
+  FwdParams p;
+  p.M = a.M; p.N = a.N; p.K = a.K; p.gs = a.gs; p.E = a.E; p.BN = a.BN;
+  p.n_mtiles = (a.M + 127) / 128;
+  p.n_ntiles = a.N / a.BN;
+  p.ntiles_per_group = a.gs / a.BN;
+  p.n_tiles = p.n_mtiles * p.n_ntiles;
+  p.PM = a.PM > 0 ? a.PM : 16;
+  if (p.PM > p.n_mtiles) p.PM = p.n_mtiles;
+  p.n_kchunks = (a.K + 63) / 64;
+  p.r_tile_bytes = ((a.E * 128) + 1023) / 1024 * 1024;
+  p.bias = a.bias; p.C = a.C; p.ldc = a.ldc; p.err = a.err;
+
+  const int budget = 227 * 1024 - 1024 - (int)sizeof(FwdBarriers) - 256;
+  const int ar_bytes = fwd::kATileBytes + p.r_tile_bytes;
+  const int b_bytes = a.BN * 128;
+  // AR ring runs kLag chunks ahead of the B ring: give it the deeper pipeline.
+  int sb = 3, sa = 6;
+  if (a.sa > 0) sa = a.sa;
+  if (a.sb > 0) sb = a.sb;
+  while (sa * ar_bytes + sb * b_bytes > budget && sa > 4) --sa;
+  while (sa * ar_bytes + sb * b_bytes > budget && sb > 2) --sb;
+  if (sa * ar_bytes + sb * b_bytes > budget)
+    return fail(PRISM_ERR_UNSUPPORTED, "forward tile does not fit shared memory (BN=%d E=%d)", a.BN, a.E);
+  // spend what is left on B stages, then AR stages
+  while (sb < fwd::kMaxStages && sa * ar_bytes + (sb + 1) * b_bytes <= budget && sb < 4) ++sb;
+  while (sa < fwd::kMaxStages && (sa + 1) * ar_bytes + sb * b_bytes <= budget) ++sa;
+  while (sb < fwd::kMaxStages && sa * ar_bytes + (sb + 1) * b_bytes <= budget) ++sb;
+  p.sa = sa; p.sb = sb;
+  const int smem_bytes = sa * ar_bytes + sb * b_bytes + (int)sizeof(FwdBarriers) + 1024;
+
+  CUtensorMap tmA, tmR, tmB;
+  int rc;
+  if ((rc = make_tmap_2d(&tmA, a.dtype, a.A, a.M, a.K, a.lda, 128, 64, true))) return rc;
+  if ((rc = make_tmap_2d(&tmR, a.dtype, a.R_eff, (uint64_t)(a.N / a.gs) * a.E, a.K, a.ldr, a.E, 64, true))) return rc;
+  if ((rc = make_tmap_2d(&tmB, a.dtype, a.B, a.N, a.K, a.ldb, a.BN, 64, true))) return rc;
+
+  int grid = a.num_sms;
+  if (grid > p.n_tiles) grid = p.n_tiles;
+
+  auto kern = (a.dtype == DT_BF16)
+                  ? (a.gate == GATE_SILU ? prism_fwd_kernel<DT_BF16, GATE_SILU> : prism_fwd_kernel<DT_BF16, GATE_NONE>)
+                  : (a.gate == GATE_SILU ? prism_fwd_kernel<DT_F16, GATE_SILU> : prism_fwd_kernel<DT_F16, GATE_NONE>);
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  if (e != cudaSuccess) return fail(PRISM_ERR_CUDA, "forward: cannot set %d B of shared memory: %s", smem_bytes, cudaGetErrorString(e));
+  kern<<<grid, fwd::kThreads, smem_bytes, a.stream>>>(tmA, tmR, tmB, p);
+  return check_launch("prism_fwd");
+}
+
+}  // namespace prism

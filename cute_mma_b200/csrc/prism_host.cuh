@@ -1,0 +1,81 @@
+// Host-side helpers shared by the C-ABI entry points: last-error string,
+// driver entry point for TMA descriptor encoding, launch checks.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "prism_common.cuh"
+
+namespace prism {
+
+// One message per host thread; read back through prism_last_error_string().
+inline char* last_error_buf() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+inline int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(last_error_buf(), 512, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled is fetched through the runtime so that the library
+// does not link against libcuda (it must load on a machine without a driver).
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(p);
+    (void)cudaGetLastError();
+  }
+  return fn;
+}
+
+// 2-D row-major tensor of 16-bit elements: `rows` x `cols`, leading dimension
+// `ld` elements; box = box_rows x box_cols. box_cols*2 must be 128 bytes for the
+// 128-byte swizzle. Out-of-range box parts read as zero / are not written.
+inline int make_tmap_2d(CUtensorMap* out, int dt, const void* base, uint64_t rows, uint64_t cols,
+                        uint64_t ld, uint32_t box_rows, uint32_t box_cols, bool swizzle128) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(PRISM_ERR_NO_DRIVER, "cuTensorMapEncodeTiled is not available");
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstride[1] = {ld * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType t =
+      (dt == DT_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = fn(out, t, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(PRISM_ERR_CUDA,
+                "cuTensorMapEncodeTiled failed (%d) base=%p rows=%llu cols=%llu ld=%llu box=%ux%u",
+                (int)r, base, (unsigned long long)rows, (unsigned long long)cols,
+                (unsigned long long)ld, box_rows, box_cols);
+  return PRISM_OK;
+}
+
+inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return fail(PRISM_ERR_CUDA, "%s: launch failed: %s", what, cudaGetErrorString(e));
+  return PRISM_OK;
+}
+
+}  // namespace prism

@@ -1,0 +1,31 @@
+// Host-side launch interfaces of the three Prism kernels (internal to the library;
+// the exported C ABI is declared in include/prism_b200.h).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace prism {
+
+struct FwdArgs {
+  const void* A;      // [M, K]
+  const void* B;      // [N, K]
+  const void* R_eff;  // [(N/gs)*E, K]  rotation blocks padded to E x E
+  const void* bias;   // [N] or null
+  void* C;            // [M, N]
+  int M, N, K, gs, E;
+  int dtype, gate;
+  long long lda, ldb, ldr, ldc;
+  int BN, PM, sa, sb;  // tile configuration (0 = default)
+  int num_sms;
+  int* err;           // device status word
+  cudaStream_t stream;
+};
+int launch_fwd(const FwdArgs& a);
+
+// R [(G*8), K] -> R_eff [(G*16), K]: two neighbouring 8x8 blocks become one 16x16
+// block-diagonal block, so that every rotation is a 16-wide tensor-core product.
+int launch_expand_r8(const void* R, void* R_eff, int G, int K, long long ldr, cudaStream_t stream);
+
+}  // namespace prism

@@ -1,0 +1,74 @@
+/* prism_b200 -- C ABI of the B200 (sm_100a) Prism linear-layer kernels.
+ *
+ * One shared library (libprism_b200.so) replaces the three per-variant torch
+ * extensions of the reference:
+ *   prism_fwd       <-> forward(A, B, R, group_size, reconn_sz, ...)          torch_ext/prism_fwd_bind.cpp:14-26
+ *                       (prism_forward, torch_ext/prism_fwd_torch.cu:23-196)
+ *   prism_bwd_dadr  <-> backward_dA_dR(dC, A, B, R, group_size, reconn_sz, ..) torch_ext/prism_bwd_dadr_bind.cpp:15-28
+ *                       (prism_backward_dA_dR, torch_ext/prism_bwd_dadr_torch.cu:42-210)
+ *   prism_bwd_db    <-> backward_dB(dC, A, R, group_size, reconn_sz, ...)      torch_ext/prism_bwd_db_bind.cpp:14-26
+ *                       (prism_backward_dB, torch_ext/prism_bwd_db_torch.cu:42-162)
+ *
+ * Conventions
+ *   - all matrices are row-major 16-bit (dtype 0 = fp16, 1 = bf16), device pointers,
+ *     16-byte aligned, leading dimensions in elements and multiples of 8;
+ *     A [M,K], B [N,K], R [(N/group_size)*reconn_sz, K], C/dC [M,N];
+ *   - gate 0 = plain "ar" mode (C_g = (A.blockdiag(R_g)^T) B_g^T), 1 = silu_gate
+ *     (C_g = (A * silu(A.blockdiag(R_g)^T)) B_g^T);
+ *   - the library never allocates or frees device memory: outputs and the workspace
+ *     belong to the caller.  The workspace must be 256-byte aligned, at least
+ *     prism_workspace_bytes(...) long, and its first 256 bytes (the status header)
+ *     must be zero when it is first used; the kernels write every output element;
+ *   - every call is asynchronous on `stream` (a cudaStream_t) and returns 0 on
+ *     success or a PRISM_ERR_* code; prism_last_error_string() describes the last
+ *     failure of the calling thread.  Errors detected on the device (a bounded wait
+ *     that ran out) are recorded in the workspace header and read with prism_status();
+ *   - `cfg` optionally overrides the tile configuration (null = built-in default);
+ *     its meaning per kernel is given below.
+ */
+#ifndef PRISM_B200_H
+#define PRISM_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PRISM_OK 0
+#define PRISM_ERR_BAD_ARG 1
+#define PRISM_ERR_UNSUPPORTED 2
+#define PRISM_ERR_WORKSPACE 3
+#define PRISM_ERR_CUDA 4
+#define PRISM_ERR_DEVICE_WAIT 5
+#define PRISM_ERR_NO_DRIVER 6
+
+#define PRISM_KIND_FWD 0
+#define PRISM_KIND_BWD_DADR 1
+#define PRISM_KIND_BWD_DB 2
+
+#define PRISM_WORKSPACE_HEADER_BYTES 256
+
+/* Forward.  bias: [N] in the same dtype, or NULL.  cfg (4 ints): {BN, PM, stagesAR, stagesB}. */
+int prism_fwd(const void* A, const void* B, const void* R, const void* bias, void* C,
+              int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
+              long long lda, long long ldb, long long ldr, long long ldc,
+              const int* cfg, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Bytes of workspace the given call needs (kind = PRISM_KIND_*), header included. */
+size_t prism_workspace_bytes(int kind, int M, int N, int K, int group_size, int reconn_sz,
+                             int dtype, const int* cfg);
+
+/* Synchronises `stream`, returns the device status word of the workspace header
+ * (0 = no device-side error since the header was last zero) and clears it. */
+int prism_status(void* workspace, void* stream);
+
+const char* prism_last_error_string(void);
+
+/* Library / ABI version, for the loader's sanity check. */
+int prism_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PRISM_B200_H */

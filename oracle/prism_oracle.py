@@ -1,0 +1,143 @@
+"""CPU/torch restatement of the reference Prism layer arithmetic -- TEST INFRASTRUCTURE ONLY.
+
+This file is the checker for the CUDA kernels: it is imported by the tests, by the
+smoke check and by the benchmark's CPU-baseline leg, and by nothing in the shipped
+package.  It restates, in plain torch tensor algebra, what the reference computes in
+``src/cute_prism/_pytorch_backend.py``:
+
+* forward  (``pytorch_forward``,  lines 78-176):  per output group g
+  ``S_g = A . blockdiag(R_g)^T``;  plain mode ``H_g = S_g``; gated mode
+  ``H_g = A * silu(S_g)``;  ``C[:, g] = H_g @ B_g^T``.
+* backward (``pytorch_backward``, lines 179-321):  ``dH_g = dC_g @ B_g``;
+  gated: ``dS = dH * A * silu'(S)``, ``dA += dH * silu(S) + blockdiag(dS) . R_g``,
+  ``dB_g = dC_g^T @ H_g``;  plain: ``dS = dH``, ``dA += blockdiag(dS) . R_g``, no dB;
+  both: ``dR_g[block b] = dS_b^T @ A_b``.
+
+Parity pin: ``tests/golden/make_golden.py`` imports the reference package itself,
+runs its pytorch backend on seeded inputs and stores inputs + outputs under
+``tests/golden/``; ``tests/test_oracle.py`` checks this file against those vectors
+(and against torch autograd in float64).  Only the features on the accelerated path
+are restated: modes ``ar`` / ``silu_gate``; no dropout, shuffle, internal bias or rw mode.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+
+def _blocks(R: torch.Tensor, n_groups: int, rs: int) -> torch.Tensor:
+    """R (G*rs, K) -> (G, nb, rs_i, rs_j): block b of group g is R[g*rs+i, b*rs+j]."""
+    K = R.shape[1]
+    return R.reshape(n_groups, rs, K // rs, rs).permute(0, 2, 1, 3)
+
+
+def rotate(A: torch.Tensor, Rg_blocks: torch.Tensor) -> torch.Tensor:
+    """S = A . blockdiag(R_g)^T for one group: S[:, b*rs+i] = sum_j A[:, b*rs+j] R_g[b,i,j]."""
+    M, K = A.shape
+    nb, rs, _ = Rg_blocks.shape
+    Ab = A.reshape(M, nb, rs)
+    return torch.einsum("mbj,bij->mbi", Ab, Rg_blocks).reshape(M, K)
+
+
+def rotate_t(dS: torch.Tensor, Rg_blocks: torch.Tensor) -> torch.Tensor:
+    """blockdiag(dS) . R_g: out[:, b*rs+j] = sum_i dS[:, b*rs+i] R_g[b,i,j]."""
+    M, K = dS.shape
+    nb, rs, _ = Rg_blocks.shape
+    return torch.einsum("mbi,bij->mbj", dS.reshape(M, nb, rs), Rg_blocks).reshape(M, K)
+
+
+def prism_forward(A, B, R, group_size, reconn_sz, activation=None, bias=None):
+    """C (M, N) in the dtype of A.  Follows ``pytorch_forward`` (ar mode, optional silu_gate)."""
+    if activation not in (None, "silu_gate"):
+        raise ValueError(f"oracle restates None and 'silu_gate' only, got {activation!r}")
+    M, K = A.shape
+    N = B.shape[0]
+    G = N // group_size
+    Rb = _blocks(R, G, reconn_sz)
+    C = torch.empty(M, N, dtype=A.dtype, device=A.device)
+    for g in range(G):
+        S = rotate(A, Rb[g])
+        H = A * (S * torch.sigmoid(S)) if activation == "silu_gate" else S
+        C[:, g * group_size:(g + 1) * group_size] = H @ B[g * group_size:(g + 1) * group_size].T
+    if bias is not None:
+        C = C + bias
+    return C
+
+
+def prism_backward(dC, A, B, R, group_size, reconn_sz, activation=None):
+    """(dA, dR, dB-or-None).  Follows ``pytorch_backward``."""
+    if activation not in (None, "silu_gate"):
+        raise ValueError(f"oracle restates None and 'silu_gate' only, got {activation!r}")
+    M, K = A.shape
+    N = B.shape[0]
+    G = N // group_size
+    rs = reconn_sz
+    nb = K // rs
+    gated = activation == "silu_gate"
+    Rb = _blocks(R, G, rs)
+    dA = torch.zeros_like(A)
+    dR = torch.empty_like(R)
+    dB = torch.empty_like(B) if gated else None
+    Ab = A.reshape(M, nb, rs)
+    for g in range(G):
+        sl = slice(g * group_size, (g + 1) * group_size)
+        dC_g = dC[:, sl]
+        dH = dC_g @ B[sl]
+        if gated:
+            S = rotate(A, Rb[g])
+            sig = torch.sigmoid(S)
+            gate = S * sig
+            gate_d = sig * (1.0 + S * (1.0 - sig))
+            dB[sl] = dC_g.T @ (A * gate)
+            dS = dH * A * gate_d
+            dA += dH * gate
+        else:
+            dS = dH
+        dA += rotate_t(dS, Rb[g])
+        # dR block (g, b)[i, j] = sum_m dS[m, b*rs+i] * A[m, b*rs+j]
+        dRg = torch.einsum("mbi,mbj->ibj", dS.reshape(M, nb, rs), Ab)
+        dR[g * rs:(g + 1) * rs] = dRg.reshape(rs, K)
+    return dA, dR, dB
+
+
+# ---------------------------------------------------------------------------
+# seeded synthetic inputs (shapes and value distributions of the benchmark configs)
+# ---------------------------------------------------------------------------
+def orthogonal_R(n_groups, K, rs, gen):
+    """Seeded block-orthogonal R: every rs x rs block is the Q factor of a Gaussian QR."""
+    nb = K // rs
+    Z = torch.randn(n_groups, nb, rs, rs, generator=gen, dtype=torch.float64)
+    Q, _ = torch.linalg.qr(Z)
+    return Q.permute(0, 2, 1, 3).reshape(n_groups * rs, K).to(torch.float32).contiguous()
+
+
+def make_inputs(M, K, N, group_size, reconn_sz, seed=0, a_std=1.0, b_std=1.0, dc_std=1.0,
+                r_kind="orthogonal"):
+    """fp32 CPU tensors drawn in the fixed order A, B, R, dC from one seeded generator."""
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    A = torch.randn(M, K, generator=gen) * a_std
+    B = torch.randn(N, K, generator=gen) * b_std
+    G = N // group_size
+    if r_kind == "orthogonal":
+        R = orthogonal_R(G, K, reconn_sz, gen)
+    elif r_kind == "gaussian":
+        R = torch.randn(G * reconn_sz, K, generator=gen) / math.sqrt(reconn_sz)
+    else:
+        raise ValueError(r_kind)
+    dC = torch.randn(M, N, generator=gen) * dc_std
+    return A, B, R, dC
+
+
+def rel_err(val, ref):
+    """The reference tests' metric: max|val-ref| / (max|ref| + 1e-6)  (tests/test_correctness.py:24-31)."""
+    val = val.double()
+    ref = ref.double()
+    return ((val - ref).abs().max() / (ref.abs().max() + 1e-6)).item()
+
+
+def flops(M, K, N, group_size, reconn_sz):
+    """Algorithmic work per call: (fwd, bwd_dadr, bwd_db) in FLOP; recompute is not counted."""
+    dense = 2.0 * M * N * K
+    bd = 2.0 * M * K * reconn_sz * (N // group_size)
+    return dense + bd, dense + 2 * bd, dense
