@@ -152,3 +152,23 @@ def forward(A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=None, mo
             M, N, K, group_size, reconn_sz, dt, gate, A.stride(0), B.stride(0), R.stride(0), C.stride(0),
             cfg_arr, ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(A.device)))
     return C, []
+
+
+def _backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=None):
+    """dB = dc_scale * dC^T . H  through ``prism_bwd_db`` (H recomputed on chip)."""
+    M, K = A.shape
+    N = dC.shape[1]
+    dB = torch.empty(N, K, dtype=A.dtype, device=A.device)
+    L = _lib.lib()
+    cfg = tile_cfg if tile_cfg is not None else _tile_lookup("bwd_db", A.dtype, gate, M, N, K, group_size, reconn_sz)
+    cfg_arr = _cfg_array(cfg)
+    dt = _DTYPES[A.dtype]
+    with torch.cuda.device(A.device):
+        need = L.prism_workspace_bytes(KIND_BWD_DB, M, N, K, group_size, reconn_sz, dt, cfg_arr)
+        ws = _workspace.get(A.device, need)
+        _lib.check(L.prism_bwd_db(
+            ctypes.c_void_p(dC.data_ptr()), ctypes.c_void_p(A.data_ptr()), ctypes.c_void_p(R.data_ptr()),
+            ctypes.c_void_p(dB.data_ptr()), M, N, K, group_size, reconn_sz, dt, gate,
+            ctypes.c_float(dc_scale), dC.stride(0), A.stride(0), R.stride(0), dB.stride(0),
+            cfg_arr, ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(A.device)))
+    return dB

@@ -100,6 +100,13 @@ extern "C" size_t prism_workspace_bytes(int kind, int M, int N, int K, int gs, i
   const size_t G = (size_t)(N / gs);
   if (rs == 8) bytes += align256(G * 16 * (size_t)K * 2);  // R_eff
   if (kind == PRISM_KIND_FWD) return bytes;
+  if (kind == PRISM_KIND_BWD_DB) {
+    const int bn = (cfg && cfg[0] > 0) ? cfg[0] : default_bn(gs);
+    if (bn <= 0) return bytes;
+    const int splits = (cfg && cfg[1] > 0) ? cfg[1] : db_default_splits(M, N, K, bn, num_sms());
+    if (splits > 1) bytes += align256((size_t)splits * N * K * 4);
+    return bytes;
+  }
   return bytes;
 }
 
@@ -158,4 +165,48 @@ extern "C" int prism_fwd(const void* A, const void* B, const void* R, const void
   a.err = reinterpret_cast<int*>(workspace);
   a.stream = s;
   return launch_fwd(a);
+}
+
+extern "C" int prism_bwd_db(const void* dC, const void* A, const void* R, void* dB,
+                            int M, int N, int K, int gs, int rs, int dtype, int gate, float dc_scale,
+                            long long lddc, long long lda, long long ldr, long long lddb,
+                            const int* cfg, void* workspace, size_t workspace_bytes, void* stream) {
+  const char* fn = "prism_bwd_db";
+  int rc;
+  if ((rc = check_common(fn, M, N, K, gs, rs, dtype, gate))) return rc;
+  if (K % 8 != 0) return fail(PRISM_ERR_BAD_ARG, "%s: K must be a multiple of 8", fn);
+  if ((rc = check_ptr(fn, "dB", dB, lddb, K))) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (M == 0) {  // no tokens: the gradient is zero
+    cudaError_t e = cudaMemset2DAsync(dB, lddb * 2, 0, (size_t)K * 2, N, s);
+    return e == cudaSuccess ? PRISM_OK : fail(PRISM_ERR_CUDA, "%s: %s", fn, cudaGetErrorString(e));
+  }
+  if ((rc = check_ptr(fn, "dC", dC, lddc, N))) return rc;
+  if ((rc = check_ptr(fn, "A", A, lda, K))) return rc;
+  if ((rc = check_ptr(fn, "R", R, ldr, K))) return rc;
+  const size_t need = prism_workspace_bytes(PRISM_KIND_BWD_DB, M, N, K, gs, rs, dtype, cfg);
+  if (workspace == nullptr || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+    return fail(PRISM_ERR_WORKSPACE, "%s: workspace must be 256-byte aligned and >= %zu bytes (got %zu)", fn, need, workspace_bytes);
+
+  DbArgs a;
+  a.dC = dC; a.A = A; a.dB = dB;
+  a.M = M; a.N = N; a.K = K; a.gs = gs; a.E = effective_block(rs);
+  a.dtype = dtype; a.gate = gate; a.scale = dc_scale;
+  a.lddc = lddc; a.lda = lda; a.lddb = lddb;
+  a.R_eff = R; a.ldr = ldr;
+  uint8_t* wp = reinterpret_cast<uint8_t*>(workspace) + PRISM_WORKSPACE_HEADER_BYTES;
+  if (rs == 8) {
+    if ((rc = launch_expand_r8(R, wp, N / gs, K, ldr, s))) return rc;
+    a.R_eff = wp; a.ldr = K;
+    wp += align256((size_t)(N / gs) * 16 * K * 2);
+  }
+  a.BN = (cfg && cfg[0] > 0) ? cfg[0] : default_bn(gs);
+  if (a.BN % 16 != 0 || a.BN > 256 || gs % a.BN != 0)
+    return fail(PRISM_ERR_BAD_ARG, "%s: tile BN=%d must be a multiple of 16, <= 256 and divide group_size=%d", fn, a.BN, gs);
+  a.num_sms = num_sms();
+  a.splits = (cfg && cfg[1] > 0) ? cfg[1] : db_default_splits(M, N, K, a.BN, a.num_sms);
+  a.partial = a.splits > 1 ? reinterpret_cast<float*>(wp) : nullptr;
+  a.err = reinterpret_cast<int*>(workspace);
+  a.stream = s;
+  return launch_bwd_db(a);
 }

@@ -1,0 +1,341 @@
+// Prism backward, weight gradient, for sm_100a:
+//   dB_g [gs, K] = scale * dC_g^T [gs, M] . H_g [M, K],   H_g = A * silu(A . blockdiag(R_g)^T)
+// (H_g = A . blockdiag(R_g)^T in plain mode), with H recomputed on chip.
+//
+// Replaces the reference's dB_pc_kernel / prism_backward_dB_launch
+// (cute_prism_backward_db.cu:450-582) and its binding (torch_ext/prism_bwd_db_torch.cu:42-162).
+//
+// Each CTA owns one accumulator tile D[f, n] (128 features x BN outputs of one group, fp32 in
+// TMEM) and a contiguous range of 128-token blocks.  The contraction runs over tokens, so both
+// tensor-core operands are "MN-major": H tiles [128 tokens x 64 features] and dC tiles
+// [128 tokens x 64 outputs] are used exactly as TMA / the gate warps lay them out, no transposes.
+//   TMA warp   : R_g tiles once; per token block two A tiles and ceil(BN/64) dC tiles
+//   MMA warp   : rotation S = A_blk . R_blk^T (M128 N=E K=16) into a 2-deep TMEM ring, then
+//                D += H^T . dC as 8 x tcgen05.mma M128 N=BN K=16 per token block
+//   gate warps : H = A*silu(S) written over A in place
+//   epilogue   : D -> dB (transposed store), or fp32 partials when the token range is split;
+//                a second kernel then adds the partials in a fixed order (deterministic).
+#include "prism_host.cuh"
+#include "prism_kernels.cuh"
+
+namespace prism {
+
+namespace db {
+constexpr int kThreads = 448;
+constexpr int kGateWarp0 = 2;
+constexpr int kNumGateWarps = 8;
+constexpr int kEpiWarp0 = 10;
+constexpr int kSBufs = 2;      // TMEM ring of S buffers, 128 columns each
+constexpr int kSCol0 = 256;
+constexpr int kMaxStages = 4;
+constexpr int kTile = 128 * 128;  // bytes of a [128 x 64] 16-bit tile
+}  // namespace db
+
+struct DbParams {
+  int M, N, K, gs, E, BN;
+  int ntiles_per_group;
+  int blocks_per_split, n_tokblocks;
+  int dc_tiles;       // ceil(BN / 64)
+  int r_tile_bytes;   // bytes reserved per R tile (multiple of 1024)
+  int sa, sd;         // stages of the A ring / dC ring
+  int splits;
+  float scale;
+  void* dB;
+  long long lddb;
+  float* partial;     // [splits][N][K] when splits > 1
+  int* err;
+};
+
+struct DbBarriers {
+  uint64_t r_full;
+  uint64_t a_full[db::kMaxStages];
+  uint64_t h_full[db::kMaxStages];
+  uint64_t a_empty[db::kMaxStages];
+  uint64_t dc_full[db::kMaxStages];
+  uint64_t dc_empty[db::kMaxStages];
+  uint64_t s_full[db::kSBufs];
+  uint64_t s_empty[db::kSBufs];
+  uint64_t acc_full;
+  uint32_t tmem_base;
+};
+
+template <int DT, int GATE>
+__global__ void __launch_bounds__(db::kThreads, 1)
+prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmR,
+                    const __grid_constant__ CUtensorMap tmdC, const DbParams p) {
+  using namespace db;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  const int a_stage_bytes = 2 * kTile;
+  const int dc_stage_bytes = p.dc_tiles * kTile;
+  uint8_t* smemR = smem;
+  uint8_t* smemA = smemR + 2 * p.r_tile_bytes;
+  uint8_t* smemD = smemA + p.sa * a_stage_bytes;
+  DbBarriers* bars = reinterpret_cast<DbBarriers*>(smemD + p.sd * dc_stage_bytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int f0 = blockIdx.x * 128;           // first feature (column of A / dB)
+  const int nt = blockIdx.y;
+  const int n0 = nt * p.BN;                  // first output (row of dB)
+  const int g = nt / p.ntiles_per_group;
+  const int split = blockIdx.z;
+  const int tb0 = split * p.blocks_per_split;
+  const int nb = min(p.blocks_per_split, p.n_tokblocks - tb0);  // token blocks of this CTA (>= 1)
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->r_full, 1);
+    for (int i = 0; i < kMaxStages; ++i) {
+      mbar_init(&bars->a_full[i], 1);
+      mbar_init(&bars->h_full[i], kNumGateWarps);
+      mbar_init(&bars->a_empty[i], 1);
+      mbar_init(&bars->dc_full[i], 1);
+      mbar_init(&bars->dc_empty[i], 1);
+    }
+    for (int i = 0; i < kSBufs; ++i) {
+      mbar_init(&bars->s_full[i], 1);
+      mbar_init(&bars->s_empty[i], kNumGateWarps);
+    }
+    mbar_init(&bars->acc_full, 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmR);
+    prefetch_tmap(&tmdC);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      bool ok = true;
+      mbar_arrive_expect_tx(&bars->r_full, 2 * p.E * 128);
+      tma_load_2d(smemR, &tmR, &bars->r_full, f0, g * p.E);
+      tma_load_2d(smemR + p.r_tile_bytes, &tmR, &bars->r_full, f0 + 64, g * p.E);
+      for (int j = 0; j < nb && ok; ++j) {
+        const int tok0 = (tb0 + j) * 128;
+        const int sa = j % p.sa, sd = j % p.sd;
+        if (!mbar_wait(&bars->a_empty[sa], ((j / p.sa) & 1) ^ 1)) { ok = false; break; }
+        uint8_t* dstA = smemA + sa * a_stage_bytes;
+        mbar_arrive_expect_tx(&bars->a_full[sa], 2 * kTile);
+        tma_load_2d(dstA, &tmA, &bars->a_full[sa], f0, tok0);
+        tma_load_2d(dstA + kTile, &tmA, &bars->a_full[sa], f0 + 64, tok0);
+        if (!mbar_wait(&bars->dc_empty[sd], ((j / p.sd) & 1) ^ 1)) { ok = false; break; }
+        uint8_t* dstD = smemD + sd * dc_stage_bytes;
+        mbar_arrive_expect_tx(&bars->dc_full[sd], dc_stage_bytes);
+        for (int t = 0; t < p.dc_tiles; ++t)
+          tma_load_2d(dstD + t * kTile, &tmdC, &bars->dc_full[sd], n0 + 64 * t, tok0);
+      }
+      if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc(DT, 128, p.E, 0, 0);
+      const uint32_t idesc_d = make_idesc(DT, 128, p.BN, 1, 1);
+      const int blocks_per_chunk = 64 / p.E;
+      const int ksteps_per_block = p.E / 16;
+      bool ok = mbar_wait(&bars->r_full, 0);
+      const uint32_t r_addr = smem_u32(smemR);
+      for (int j = 0; j < nb + 1 && ok; ++j) {
+        if (j < nb) {
+          const int sa = j % p.sa, sbuf = j % kSBufs;
+          if (!mbar_wait(&bars->a_full[sa], (j / p.sa) & 1)) { ok = false; break; }
+          if (!mbar_wait(&bars->s_empty[sbuf], ((j / kSBufs) & 1) ^ 1)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smemA + sa * a_stage_bytes);
+          for (int i = 0; i < 2; ++i) {
+            for (int b = 0; b < blocks_per_chunk; ++b) {
+              for (int ks = 0; ks < ksteps_per_block; ++ks) {
+                const uint32_t koff = (b * p.E + ks * 16) * 2;
+                umma_f16(tmem_base + kSCol0 + sbuf * 128 + i * 64 + b * p.E,
+                         desc_kmajor_sw128(a_addr + i * kTile + koff, 1024),
+                         desc_kmajor_sw128(r_addr + i * p.r_tile_bytes + koff, 1024), idesc_s,
+                         ks > 0 ? 1u : 0u);
+              }
+            }
+          }
+          umma_commit(&bars->s_full[sbuf]);
+        }
+        if (j >= 1) {
+          const int jm = j - 1;
+          const int sa = jm % p.sa, sd = jm % p.sd;
+          if (!mbar_wait(&bars->h_full[sa], (jm / p.sa) & 1)) { ok = false; break; }
+          if (!mbar_wait(&bars->dc_full[sd], (jm / p.sd) & 1)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t h_addr = smem_u32(smemA + sa * a_stage_bytes);
+          const uint32_t d_addr = smem_u32(smemD + sd * dc_stage_bytes);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            umma_f16(tmem_base, desc_mnmajor_sw128(h_addr + ks * 2048, kTile, 1024),
+                     desc_mnmajor_sw128(d_addr + ks * 2048, kTile, 1024), idesc_d,
+                     (jm > 0 || ks > 0) ? 1u : 0u);
+          }
+          umma_commit(&bars->a_empty[sa]);
+          umma_commit(&bars->dc_empty[sd]);
+          if (jm == nb - 1) umma_commit(&bars->acc_full);
+        }
+      }
+      if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
+    }
+  } else if (warp < kEpiWarp0) {
+    // ------------------------------------------------------------------ gate warps
+    const int gw = warp - kGateWarp0;
+    const int q = warp & 3;
+    const int chunk = gw >> 2;     // which of the two 64-feature tiles
+    const uint32_t row = q * 32 + lane;
+    bool ok = true;
+    for (int j = 0; j < nb; ++j) {
+      const int sa = j % p.sa, sbuf = j % kSBufs;
+      if (!mbar_wait(&bars->s_full[sbuf], (j / kSBufs) & 1)) { ok = false; break; }
+      tc_fence_after_sync();
+      uint8_t* tile = smemA + sa * a_stage_bytes + chunk * kTile;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t s[32];
+        tmem_ld_x32(tmem_base + (uint32_t(q * 32) << 16) + kSCol0 + sbuf * 128 + chunk * 64 + hh * 32, s);
+        uint4 av[4];
+        load_a_32cols<GATE>(tile, row, hh * 4, av);
+        tmem_ld_wait();
+        gate_h_32cols<DT, GATE>(tile, row, hh * 4, s, av);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&bars->s_empty[sbuf]);
+        mbar_arrive(&bars->h_full[sa]);
+      }
+    }
+    if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int q = warp & 3;
+    const int f = f0 + q * 32 + lane;  // feature = accumulator row
+    bool ok = mbar_wait(&bars->acc_full, 0);
+    if (ok) {
+      tc_fence_after_sync();
+      for (int c0 = 0; c0 < p.BN; c0 += 16) {
+        uint32_t v[16];
+        tmem_ld_x16(tmem_base + (uint32_t(q * 32) << 16) + c0, v);
+        tmem_ld_wait();
+        if (f < p.K) {
+          if (p.splits > 1) {
+            float* dst = p.partial + ((long long)split * p.N + n0 + c0) * p.K + f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) dst[(long long)j * p.K] = __uint_as_float(v[j]) * p.scale;
+          } else {
+            uint16_t* dst = reinterpret_cast<uint16_t*>(p.dB) + (long long)(n0 + c0) * p.lddb + f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const uint32_t w = Elem<DT>::pack(__uint_as_float(v[j]) * p.scale, 0.f);
+              dst[(long long)j * p.lddb] = static_cast<uint16_t>(w & 0xFFFFu);
+            }
+          }
+        }
+      }
+    } else if (lane == 0) {
+      atomicExch(p.err, PRISM_ERR_DEVICE_WAIT);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// dB[n, k] = cast( sum_s partial[s][n][k] ), s in increasing order.
+template <int DT>
+__global__ void db_reduce_kernel(const float* __restrict__ partial, uint16_t* __restrict__ dB, int N,
+                                 int K, long long lddb, int splits) {
+  const long long pair = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // two elements per thread
+  const long long total = (long long)N * K / 2;
+  if (pair >= total) return;
+  const long long idx = pair * 2;
+  const int n = (int)(idx / K), k = (int)(idx % K);
+  float2 acc = make_float2(0.f, 0.f);
+  for (int s = 0; s < splits; ++s) {
+    const float2 v = *reinterpret_cast<const float2*>(partial + ((long long)s * N + n) * K + k);
+    acc.x += v.x;
+    acc.y += v.y;
+  }
+  *reinterpret_cast<uint32_t*>(dB + (long long)n * lddb + k) = Elem<DT>::pack(acc.x, acc.y);
+}
+
+int db_default_splits(int M, int N, int K, int BN, int num_sms) {
+  const int base = ((K + 127) / 128) * (N / BN);
+  const int tokblocks = (M + 127) / 128;
+  if (base >= 2 * num_sms) return 1;
+  int s = (2 * num_sms + base - 1) / base;
+  if (s > tokblocks) s = tokblocks;
+  if (s > 16) s = 16;
+  return s < 1 ? 1 : s;
+}
+
+int launch_bwd_db(const DbArgs& a) {
+  DbParams p;
+  p.M = a.M; p.N = a.N; p.K = a.K; p.gs = a.gs; p.E = a.E; p.BN = a.BN;
+  p.ntiles_per_group = a.gs / a.BN;
+  p.n_tokblocks = (a.M + 127) / 128;
+  p.splits = a.splits;
+  p.blocks_per_split = (p.n_tokblocks + a.splits - 1) / a.splits;
+  // drop splits that would own no token block
+  p.splits = (p.n_tokblocks + p.blocks_per_split - 1) / p.blocks_per_split;
+  p.dc_tiles = (a.BN + 63) / 64;
+  p.r_tile_bytes = ((a.E * 128) + 1023) / 1024 * 1024;
+  p.scale = a.scale;
+  p.dB = a.dB; p.lddb = a.lddb; p.partial = a.partial; p.err = a.err;
+  if (p.splits > 1 && a.partial == nullptr)
+    return fail(PRISM_ERR_WORKSPACE, "bwd_db: split accumulation needs a partial-sum workspace");
+
+  const int budget = 227 * 1024 - 1024 - (int)sizeof(DbBarriers) - 256 - 2 * p.r_tile_bytes;
+  const int a_bytes = 2 * db::kTile, d_bytes = p.dc_tiles * db::kTile;
+  int sa = 2, sd = 2;
+  if (sa * a_bytes + sd * d_bytes > budget)
+    return fail(PRISM_ERR_UNSUPPORTED, "bwd_db tile does not fit shared memory (BN=%d E=%d)", a.BN, a.E);
+  bool grew = true;
+  while (grew) {
+    grew = false;
+    if (sd < db::kMaxStages && sa * a_bytes + (sd + 1) * d_bytes <= budget) { ++sd; grew = true; }
+    if (sa < db::kMaxStages && (sa + 1) * a_bytes + sd * d_bytes <= budget) { ++sa; grew = true; }
+  }
+  p.sa = sa; p.sd = sd;
+  const int smem_bytes = 2 * p.r_tile_bytes + sa * a_bytes + sd * d_bytes + (int)sizeof(DbBarriers) + 1024;
+
+  CUtensorMap tmA, tmR, tmdC;
+  int rc;
+  if ((rc = make_tmap_2d(&tmA, a.dtype, a.A, a.M, a.K, a.lda, 128, 64, true))) return rc;
+  if ((rc = make_tmap_2d(&tmR, a.dtype, a.R_eff, (uint64_t)(a.N / a.gs) * a.E, a.K, a.ldr, a.E, 64, true))) return rc;
+  if ((rc = make_tmap_2d(&tmdC, a.dtype, a.dC, a.M, a.N, a.lddc, 128, 64, true))) return rc;
+
+  auto kern = (a.dtype == DT_BF16)
+                  ? (a.gate == GATE_SILU ? prism_bwd_db_kernel<DT_BF16, GATE_SILU> : prism_bwd_db_kernel<DT_BF16, GATE_NONE>)
+                  : (a.gate == GATE_SILU ? prism_bwd_db_kernel<DT_F16, GATE_SILU> : prism_bwd_db_kernel<DT_F16, GATE_NONE>);
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+  if (e != cudaSuccess) return fail(PRISM_ERR_CUDA, "bwd_db: cannot set %d B of shared memory: %s", smem_bytes, cudaGetErrorString(e));
+  dim3 grid((a.K + 127) / 128, a.N / a.BN, p.splits);
+  kern<<<grid, db::kThreads, smem_bytes, a.stream>>>(tmA, tmR, tmdC, p);
+  if ((rc = check_launch("prism_bwd_db"))) return rc;
+  if (p.splits > 1) {
+    const long long pairs = (long long)a.N * a.K / 2;
+    const int threads = 256;
+    const long long blocks = (pairs + threads - 1) / threads;
+    if (a.dtype == DT_BF16)
+      db_reduce_kernel<DT_BF16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, reinterpret_cast<uint16_t*>(a.dB), a.N, a.K, a.lddb, p.splits);
+    else
+      db_reduce_kernel<DT_F16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, reinterpret_cast<uint16_t*>(a.dB), a.N, a.K, a.lddb, p.splits);
+    if ((rc = check_launch("prism_bwd_db reduce"))) return rc;
+  }
+  return PRISM_OK;
+}
+
+}  // namespace prism

@@ -296,4 +296,49 @@ __device__ __forceinline__ float sigmoid_fast(float x) {
   return fmaf(tanh_approx(0.5f * x), 0.5f, 0.5f);
 }
 
+// ----------------------------------------------------------------------------
+// The gate producer step shared by the forward and dB kernels: 32 consecutive
+// columns of one row.  s[] holds S = (A . blockdiag(R_g)^T)[row, cols] in fp32
+// (read from TMEM); the matching 16-bit A values sit in the swizzled tile in
+// shared memory at 16-byte chunks chunk0..chunk0+3 of `row`; H = A * silu(S)
+// (or H = S in plain mode) is written over them in place.
+// ----------------------------------------------------------------------------
+template <int DT, int GATE>
+__device__ __forceinline__ void gate_h_32cols(uint8_t* tile, uint32_t row, uint32_t chunk0,
+                                              const uint32_t (&s)[32], const uint4 (&av)[4]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t aw[4] = {av[j].x, av[j].y, av[j].z, av[j].w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float s0 = __uint_as_float(s[j * 8 + e * 2]);
+      const float s1 = __uint_as_float(s[j * 8 + e * 2 + 1]);
+      float h0, h1;
+      if (GATE == GATE_SILU) {
+        const float2 a2 = Elem<DT>::unpack(aw[e]);
+        h0 = a2.x * (s0 * sigmoid_fast(s0));
+        h1 = a2.y * (s1 * sigmoid_fast(s1));
+      } else {
+        h0 = s0;
+        h1 = s1;
+      }
+      ow[e] = Elem<DT>::pack(h0, h1);
+    }
+    *reinterpret_cast<uint4*>(tile + sw128_offset(row, chunk0 + j)) =
+        make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  }
+}
+template <int GATE>
+__device__ __forceinline__ void load_a_32cols(const uint8_t* tile, uint32_t row, uint32_t chunk0,
+                                              uint4 (&av)[4]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (GATE == GATE_SILU)
+      av[j] = *reinterpret_cast<const uint4*>(tile + sw128_offset(row, chunk0 + j));
+    else
+      av[j] = make_uint4(0, 0, 0, 0);
+  }
+}
+
 }  // namespace prism

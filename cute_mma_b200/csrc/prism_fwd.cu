@@ -229,35 +229,9 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint32_t s[32];
         tmem_ld_x32(tmem_base + (uint32_t(q * 32) << 16) + kSCol0 + sbuf * 64 + half * 32, s);
         uint4 av[4];
-        if (GATE == GATE_SILU) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            av[j] = *reinterpret_cast<const uint4*>(tile + sw128_offset(row, half * 4 + j));
-        }
+        load_a_32cols<GATE>(tile, row, half * 4, av);
         tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint32_t aw[4] = {0, 0, 0, 0};
-          if (GATE == GATE_SILU) { aw[0] = av[j].x; aw[1] = av[j].y; aw[2] = av[j].z; aw[3] = av[j].w; }
-          uint32_t ow[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float s0 = __uint_as_float(s[j * 8 + e * 2]);
-            float s1 = __uint_as_float(s[j * 8 + e * 2 + 1]);
-            float h0, h1;
-            if (GATE == GATE_SILU) {
-              const float2 a2 = Elem<DT>::unpack(aw[e]);
-              h0 = a2.x * (s0 * sigmoid_fast(s0));
-              h1 = a2.y * (s1 * sigmoid_fast(s1));
-            } else {
-              h0 = s0;
-              h1 = s1;
-            }
-            ow[e] = Elem<DT>::pack(h0, h1);
-          }
-          *reinterpret_cast<uint4*>(tile + sw128_offset(row, half * 4 + j)) =
-              make_uint4(ow[0], ow[1], ow[2], ow[3]);
-        }
+        gate_h_32cols<DT, GATE>(tile, row, half * 4, s, av);
         fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncwarp();

@@ -28,4 +28,22 @@ int launch_fwd(const FwdArgs& a);
 // block-diagonal block, so that every rotation is a 16-wide tensor-core product.
 int launch_expand_r8(const void* R, void* R_eff, int G, int K, long long ldr, cudaStream_t stream);
 
+struct DbArgs {
+  const void* dC;     // [M, N]
+  const void* A;      // [M, K]
+  const void* R_eff;  // [(N/gs)*E, K]
+  void* dB;           // [N, K]
+  int M, N, K, gs, E;
+  int dtype, gate;
+  float scale;        // dB = scale * dC^T H
+  long long lddc, lda, ldr, lddb;
+  int BN, splits;
+  float* partial;     // [splits][N][K] fp32 scratch when splits > 1
+  int num_sms;
+  int* err;
+  cudaStream_t stream;
+};
+int launch_bwd_db(const DbArgs& a);
+int db_default_splits(int M, int N, int K, int BN, int num_sms);
+
 }  // namespace prism

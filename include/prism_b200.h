@@ -55,6 +55,14 @@ int prism_fwd(const void* A, const void* B, const void* R, const void* bias, voi
               long long lda, long long ldb, long long ldr, long long ldc,
               const int* cfg, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Weight gradient dB [N,K] = dc_scale * dC^T . H (H recomputed from A and R; B is not needed).
+ * cfg (2 ints): {BN, splits} -- splits > 1 divides the token range over several CTAs whose fp32
+ * partial sums (in the workspace) are added in a fixed order, so the result is deterministic. */
+int prism_bwd_db(const void* dC, const void* A, const void* R, void* dB,
+                 int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
+                 float dc_scale, long long lddc, long long lda, long long ldr, long long lddb,
+                 const int* cfg, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Bytes of workspace the given call needs (kind = PRISM_KIND_*), header included. */
 size_t prism_workspace_bytes(int kind, int M, int N, int K, int group_size, int reconn_sz,
                              int dtype, const int* cfg);
