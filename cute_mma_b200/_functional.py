@@ -172,3 +172,54 @@ def _backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=N
             ctypes.c_float(dc_scale), dC.stride(0), A.stride(0), R.stride(0), dB.stride(0),
             cfg_arr, ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(A.device)))
     return dB
+
+
+def _backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=None):
+    """(dA, dR), both scaled by ``dc_scale``, through ``prism_bwd_dadr``."""
+    M, K = A.shape
+    N = B.shape[0]
+    dA = torch.empty(M, K, dtype=A.dtype, device=A.device)
+    dR = torch.empty_like(R)
+    L = _lib.lib()
+    cfg = tile_cfg if tile_cfg is not None else _tile_lookup("bwd_dadr", A.dtype, gate, M, N, K, group_size, reconn_sz)
+    cfg_arr = _cfg_array(cfg)
+    dt = _DTYPES[A.dtype]
+    with torch.cuda.device(A.device):
+        need = L.prism_workspace_bytes(KIND_BWD_DADR, M, N, K, group_size, reconn_sz, dt, cfg_arr)
+        ws = _workspace.get(A.device, need)
+        _lib.check(L.prism_bwd_dadr(
+            ctypes.c_void_p(dC.data_ptr()), ctypes.c_void_p(A.data_ptr()), ctypes.c_void_p(B.data_ptr()),
+            ctypes.c_void_p(R.data_ptr()), ctypes.c_void_p(dA.data_ptr()), ctypes.c_void_p(dR.data_ptr()),
+            M, N, K, group_size, reconn_sz, dt, gate, ctypes.c_float(dc_scale),
+            dC.stride(0), A.stride(0), B.stride(0), R.stride(0), dA.stride(0), dR.stride(0),
+            cfg_arr, ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(A.device)))
+    return dA, dR
+
+
+def backward(dC, A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=None, activation=None,
+             comp_params=None, autotuning: bool = False, autotuning_search_space_dadr=None,
+             autotuning_search_space_db=None, bwd_dadr_params=None, bwd_db_params=None,
+             force_rebenchmark: bool = False, dR_dtype=None, dB_dtype=None, internal_bias=None,
+             dropout_seeds=None, dropout_p: float = 0.0, shuffle_masks=None, *, dc_scale: float = 1.0,
+             tile_cfg_dadr=None, tile_cfg_db=None):
+    """Gradients ``(dA, dR, dB, d_internal_bias)``; ``dB`` is None in plain mode and
+    ``d_internal_bias`` is always None (internal bias is not part of the accelerated path).
+
+    ``dc_scale`` (keyword-only) multiplies dC on the fly, i.e. scales every returned gradient.
+    """
+    gate = _gate_code(activation)
+    validate_kernel_params(group_size, reconn_sz)
+    _reject_unsupported(internal_bias=internal_bias, shuffle_masks=shuffle_masks,
+                        dropout_seeds=dropout_seeds if dropout_p > 0.0 else None)
+    validate_tensor_params(A, B, R, group_size, reconn_sz)
+    M, K = A.shape
+    N = B.shape[0]
+    if dC.shape != (M, N) or dC.dtype != A.dtype or dC.device != A.device or not dC.is_contiguous():
+        raise ValueError(f"dC must be a contiguous ({M}, {N}) tensor of the same dtype and device as A")
+    dA, dR = _backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, dc_scale, tile_cfg_dadr)
+    dB = _backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale, tile_cfg_db) if gate else None
+    if dR_dtype is not None and dR_dtype != dR.dtype:
+        dR = dR.to(dR_dtype)
+    if dB is not None and dB_dtype is not None and dB_dtype != dB.dtype:
+        dB = dB.to(dB_dtype)
+    return dA, dR, dB, None

@@ -107,6 +107,16 @@ extern "C" size_t prism_workspace_bytes(int kind, int M, int N, int K, int gs, i
     if (splits > 1) bytes += align256((size_t)splits * N * K * 4);
     return bytes;
   }
+  if (kind == PRISM_KIND_BWD_DADR) {
+    const int E = effective_block(rs);
+    if (E == 0) return bytes;
+    int runs = (cfg && cfg[0] > 0) ? cfg[0] : dadr_default_runs(M, K, num_sms());
+    const int n_mt = (M + 127) / 128;
+    if (runs > n_mt) runs = n_mt;
+    if (runs < 1) runs = 1;
+    bytes += align256((size_t)runs * G * E * (size_t)K * 4);
+    return bytes;
+  }
   return bytes;
 }
 
@@ -209,4 +219,48 @@ extern "C" int prism_bwd_db(const void* dC, const void* A, const void* R, void* 
   a.err = reinterpret_cast<int*>(workspace);
   a.stream = s;
   return launch_bwd_db(a);
+}
+
+extern "C" int prism_bwd_dadr(const void* dC, const void* A, const void* B, const void* R, void* dA,
+                              void* dR, int M, int N, int K, int gs, int rs, int dtype, int gate,
+                              float dc_scale, long long lddc, long long lda, long long ldb,
+                              long long ldr, long long ldda, long long lddr, const int* cfg,
+                              void* workspace, size_t workspace_bytes, void* stream) {
+  const char* fn = "prism_bwd_dadr";
+  int rc;
+  if ((rc = check_common(fn, M, N, K, gs, rs, dtype, gate))) return rc;
+  if (K % 8 != 0) return fail(PRISM_ERR_BAD_ARG, "%s: K must be a multiple of 8", fn);
+  if ((rc = check_ptr(fn, "dR", dR, lddr, K))) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (M == 0) {  // no tokens: dA is empty and dR is zero
+    cudaError_t e = cudaMemset2DAsync(dR, lddr * 2, 0, (size_t)K * 2, (size_t)(N / gs) * rs, s);
+    return e == cudaSuccess ? PRISM_OK : fail(PRISM_ERR_CUDA, "%s: %s", fn, cudaGetErrorString(e));
+  }
+  if ((rc = check_ptr(fn, "dC", dC, lddc, N))) return rc;
+  if ((rc = check_ptr(fn, "A", A, lda, K))) return rc;
+  if ((rc = check_ptr(fn, "B", B, ldb, K))) return rc;
+  if ((rc = check_ptr(fn, "R", R, ldr, K))) return rc;
+  if ((rc = check_ptr(fn, "dA", dA, ldda, K))) return rc;
+  const size_t need = prism_workspace_bytes(PRISM_KIND_BWD_DADR, M, N, K, gs, rs, dtype, cfg);
+  if (workspace == nullptr || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+    return fail(PRISM_ERR_WORKSPACE, "%s: workspace must be 256-byte aligned and >= %zu bytes (got %zu)", fn, need, workspace_bytes);
+
+  DadrArgs a;
+  a.dC = dC; a.A = A; a.B = B; a.dA = dA; a.dR = dR;
+  a.M = M; a.N = N; a.K = K; a.gs = gs; a.rs = rs; a.E = effective_block(rs);
+  a.dtype = dtype; a.gate = gate; a.scale = dc_scale;
+  a.lddc = lddc; a.lda = lda; a.ldb = ldb; a.ldda = ldda; a.lddr = lddr;
+  a.R_eff = R; a.ldr = ldr;
+  uint8_t* wp = reinterpret_cast<uint8_t*>(workspace) + PRISM_WORKSPACE_HEADER_BYTES;
+  if (rs == 8) {
+    if ((rc = launch_expand_r8(R, wp, N / gs, K, ldr, s))) return rc;
+    a.R_eff = wp; a.ldr = K;
+    wp += align256((size_t)(N / gs) * 16 * K * 2);
+  }
+  a.num_sms = num_sms();
+  a.runs = (cfg && cfg[0] > 0) ? cfg[0] : dadr_default_runs(M, K, a.num_sms);
+  a.partial = reinterpret_cast<float*>(wp);
+  a.err = reinterpret_cast<int*>(workspace);
+  a.stream = s;
+  return launch_bwd_dadr(a);
 }

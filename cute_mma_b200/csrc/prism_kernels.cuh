@@ -46,4 +46,24 @@ struct DbArgs {
 int launch_bwd_db(const DbArgs& a);
 int db_default_splits(int M, int N, int K, int BN, int num_sms);
 
+struct DadrArgs {
+  const void* dC;     // [M, N]
+  const void* A;      // [M, K]
+  const void* B;      // [N, K]
+  const void* R_eff;  // [(N/gs)*E, K]
+  void* dA;           // [M, K]
+  void* dR;           // [(N/gs)*rs, K]
+  int M, N, K, gs, rs, E;
+  int dtype, gate;
+  float scale;
+  long long lddc, lda, ldb, ldr, ldda, lddr;
+  int runs;           // CTAs per 128-feature column; each owns one fp32 partial dR buffer
+  float* partial;     // [runs][(N/gs)*E][K]
+  int num_sms;
+  int* err;
+  cudaStream_t stream;
+};
+int launch_bwd_dadr(const DadrArgs& a);
+int dadr_default_runs(int M, int K, int num_sms);
+
 }  // namespace prism

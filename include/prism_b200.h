@@ -55,6 +55,16 @@ int prism_fwd(const void* A, const void* B, const void* R, const void* bias, voi
               long long lda, long long ldb, long long ldr, long long ldc,
               const int* cfg, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Input and rotation gradients: dA [M,K] and dR [(N/group_size)*reconn_sz, K], both scaled by
+ * dc_scale.  cfg (1 int): {runs} -- the number of CTAs that share one 128-feature column of dA;
+ * each accumulates dR into its own fp32 buffer in the workspace in a fixed order and a second
+ * kernel adds the buffers in a fixed order: dR is bit-identical from run to run. */
+int prism_bwd_dadr(const void* dC, const void* A, const void* B, const void* R, void* dA, void* dR,
+                   int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
+                   float dc_scale, long long lddc, long long lda, long long ldb, long long ldr,
+                   long long ldda, long long lddr,
+                   const int* cfg, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Weight gradient dB [N,K] = dc_scale * dC^T . H (H recomputed from A and R; B is not needed).
  * cfg (2 ints): {BN, splits} -- splits > 1 divides the token range over several CTAs whose fp32
  * partial sums (in the workspace) are added in a fixed order, so the result is deterministic. */
