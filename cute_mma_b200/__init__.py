@@ -1,4 +1,12 @@
-"""prism-b200: the Prism linear layer (forward + backward) as hand-written sm_100a kernels."""
-from ._functional import forward, backward, check_device_status  # noqa: F401
+"""prism-b200: the Prism linear layer (forward + backward) as hand-written sm_100a kernels.
 
-__all__ = ["forward", "backward", "check_device_status"]
+Public surface (same names and argument meaning as the reference package ``cute_prism``):
+``forward``, ``backward``, ``PrismLinear``; plus ``prism_linear`` (differentiable functional
+form), ``check_device_status`` and the data-parallel helpers in ``cute_mma_b200._dp``.
+"""
+from ._functional import forward, backward, check_device_status  # noqa: F401
+from ._module import PrismLinear, prism_linear  # noqa: F401
+from ._dp import allreduce_grads, shard_rows, sync_module_grads  # noqa: F401
+
+__all__ = ["forward", "backward", "PrismLinear", "prism_linear", "check_device_status",
+           "allreduce_grads", "shard_rows", "sync_module_grads"]

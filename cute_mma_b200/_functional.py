@@ -112,7 +112,7 @@ def _gate_code(activation):
 
 def _reject_unsupported(**kw):
     for name, val in kw.items():
-        if val is not None and val is not False and val != 0.0:
+        if isinstance(val, torch.Tensor) or (val is not None and val is not False and val != 0.0):
             raise ValueError(f"{name} is not supported by the sm_100a kernels")
 
 

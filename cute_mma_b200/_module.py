@@ -1,0 +1,232 @@
+"""``PrismLinear`` and the autograd wiring of the sm_100a Prism kernels.
+
+Mirrors the reference module (src/cute_prism/_module.py): the custom ops with fake
+implementations (lines 38-141), the constant backward rescale of the gated layer
+(``_BwdScaleFn``, lines 20-30 and 462-470), parameter names / shapes / initialisation
+(lines 415-532), the Cayley construction of R in fine-tuning mode (lines 534-577),
+``load_pretrained_weight`` / ``from_linear`` (lines 599-688) and ``forward`` (lines 690-739).
+
+Differences, all on the fast path:
+* the output bias is added in the forward kernel's epilogue instead of a separate op;
+* the backward rescale is passed to the backward kernels as ``dc_scale`` instead of an extra
+  pass over dC (the bias gradient, taken after the rescale point, stays unscaled as in the
+  reference);
+* in plain mode a frozen ``weight`` gets no gradient tensor at all; a trainable ``weight``
+  in plain mode gets exact zeros, which is the reference's contract
+  (src/cute_prism/_module.py:92-104);
+* the exact Cayley transform is solved in fp32 for fp16/bf16 parameters (``torch.linalg.solve``
+  has no 16-bit kernels) and cast back;
+* input shuffle, internal bias, dropout and ``sigmoid_gate`` are not part of the accelerated
+  path and raise ``ValueError`` at construction.
+"""
+from __future__ import annotations
+
+import math
+from typing import Literal
+
+import torch
+import torch.nn as nn
+
+from . import _functional as F
+
+_GATED_SILU_BWD_GAIN = 1.437  # same constant as the reference (src/cute_prism/_module.py:16)
+
+
+# ---------------------------------------------------------------------------
+# custom ops: opaque to torch.compile, with fake-tensor and autograd support
+# ---------------------------------------------------------------------------
+@torch.library.custom_op("prism_b200::forward", mutates_args=())
+def _prism_forward_op(A: torch.Tensor, B: torch.Tensor, R: torch.Tensor, bias: torch.Tensor | None,
+                      group_size: int, reconn_sz: int, activation: str, bwd_scale: float) -> torch.Tensor:
+    C, _ = F.forward(A.contiguous(), B.contiguous(), R.contiguous(), group_size, reconn_sz,
+                     activation=activation or None, bias=bias)
+    return C
+
+
+@_prism_forward_op.register_fake
+def _(A, B, R, bias, group_size, reconn_sz, activation, bwd_scale):
+    return A.new_empty(A.shape[0], B.shape[0])
+
+
+@torch.library.custom_op("prism_b200::backward", mutates_args=())
+def _prism_backward_op(dC: torch.Tensor, A: torch.Tensor, B: torch.Tensor, R: torch.Tensor,
+                       group_size: int, reconn_sz: int, activation: str, bwd_scale: float,
+                       need_dB: bool) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    dC = dC.contiguous()
+    A, B, R = A.contiguous(), B.contiguous(), R.contiguous()
+    gate = 1 if activation else 0
+    dA, dR = F._backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, bwd_scale)
+    if not need_dB:
+        dB = B.new_empty(0)
+    elif gate:
+        dB = F._backward_db(dC, A, R, group_size, reconn_sz, gate, bwd_scale)
+    else:
+        dB = torch.zeros_like(B)  # frozen-B contract of the reference's plain mode
+    return dA, dR, dB
+
+
+@_prism_backward_op.register_fake
+def _(dC, A, B, R, group_size, reconn_sz, activation, bwd_scale, need_dB):
+    return A.new_empty(A.shape), R.new_empty(R.shape), (B.new_empty(B.shape) if need_dB else B.new_empty(0))
+
+
+def _setup_context(ctx, inputs, output):
+    A, B, R, bias, group_size, reconn_sz, activation, bwd_scale = inputs
+    ctx.save_for_backward(A, B, R)
+    ctx.has_bias = bias is not None
+    ctx.group_size, ctx.reconn_sz = group_size, reconn_sz
+    ctx.activation, ctx.bwd_scale = activation, bwd_scale
+
+
+def _backward(ctx, dC):
+    A, B, R = ctx.saved_tensors
+    need_dB = bool(ctx.needs_input_grad[1])
+    dA, dR, dB = _prism_backward_op(dC, A, B, R, ctx.group_size, ctx.reconn_sz, ctx.activation,
+                                    ctx.bwd_scale, need_dB)
+    dbias = dC.sum(dim=0) if (ctx.has_bias and ctx.needs_input_grad[3]) else None
+    return dA, (dB if need_dB else None), dR, dbias, None, None, None, None
+
+
+_prism_forward_op.register_autograd(_backward, setup_context=_setup_context)
+
+
+def prism_linear(A, B, R, bias=None, group_size=256, reconn_sz=8, activation=None, bwd_scale=1.0):
+    """Differentiable functional form: C = prism(A, B, R) + bias; gradients of A/B/R are
+    multiplied by ``bwd_scale`` (the bias gradient is not)."""
+    return _prism_forward_op(A, B, R, bias, group_size, reconn_sz, activation or "", float(bwd_scale))
+
+
+# ---------------------------------------------------------------------------
+# module
+# ---------------------------------------------------------------------------
+class PrismLinear(nn.Module):
+    """Drop-in for the reference ``cute_prism.PrismLinear`` on the accelerated path.
+
+    ``C = (A . blockdiag(R_g)^T) @ B_g^T`` per output group (``activation=None``: B frozen, R is
+    the Cayley transform of the skew-symmetric part of ``reconn``), or
+    ``C = (A * silu(A . blockdiag(R_g)^T)) @ B_g^T`` (``activation="silu_gate"``: B and R trained,
+    R = ``reconn``).  Parameter names and shapes match the reference, so its checkpoints load:
+    ``weight (N, K)``, ``reconn (N/group_size*reconn_sz, K)``, ``bias (N)``, optional ``ar_scale``.
+    """
+
+    def __init__(self, in_features: int, out_features: int, group_size: int = 256, reconn_sz: int = 8,
+                 bias: bool = True, activation: Literal["silu_gate"] | None = None,
+                 cayley_order: int | float = float("inf"), input_shuffle: bool = False,
+                 shuffle_blk_k: int = 64, backend: str | None = None, autotuning: bool = False,
+                 force_rebenchmark: bool = False, comp_params=None, bwd_dadr_params=None,
+                 bwd_db_params=None, internal_bias: bool = False, dropout: float = 0.0,
+                 r_init_scale=1.0, ar_scale_init: float | None = None):
+        super().__init__()
+        if activation not in (None, "silu_gate"):
+            if activation == "sigmoid_gate":
+                raise ValueError("activation='sigmoid_gate' is not supported by the sm_100a kernels")
+            raise ValueError(f"Unknown activation {activation!r}, must be one of (None, 'silu_gate')")
+        if input_shuffle or internal_bias or dropout > 0.0:
+            raise ValueError("input_shuffle, internal_bias and dropout are not supported by the sm_100a kernels")
+        if out_features % group_size != 0:
+            raise ValueError(f"out_features ({out_features}) must be divisible by group_size ({group_size})")
+        if in_features % reconn_sz != 0:
+            raise ValueError(f"in_features ({in_features}) must be divisible by reconn_sz ({reconn_sz})")
+        F.validate_kernel_params(group_size, reconn_sz)
+
+        self.in_features, self.out_features = in_features, out_features
+        self.group_size, self.reconn_sz = group_size, reconn_sz
+        self.activation = activation
+        self.cayley_order = cayley_order
+        self.r_init_scale = r_init_scale
+        # accepted for signature compatibility; there is one backend and no autotuner
+        self.backend, self.autotuning, self.force_rebenchmark = backend, autotuning, force_rebenchmark
+
+        gated = activation == "silu_gate"
+        n_groups = out_features // group_size
+        self.weight = nn.Parameter(torch.empty(out_features, in_features), requires_grad=gated)
+        self.reconn = nn.Parameter(torch.empty(n_groups * reconn_sz, in_features))
+        if ar_scale_init is not None:
+            self.ar_scale = nn.Parameter(torch.tensor(float(ar_scale_init)))
+        else:
+            self.register_parameter("ar_scale", None)
+        if bias:
+            self.bias = nn.Parameter(torch.empty(out_features))
+        else:
+            self.register_parameter("bias", None)
+        self._bwd_scale = 1.0 / _GATED_SILU_BWD_GAIN if gated else 1.0
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        """Same initialisation as the reference (src/cute_prism/_module.py:474-532)."""
+        K, r = self.in_features, self.reconn_sz
+        nn.init.normal_(self.weight, std=1.0 / math.sqrt(K))
+        if self.activation == "silu_gate":
+            n_groups = self.out_features // self.group_size
+            sigma = 4.0 / math.sqrt(2 * (r - 1)) * self.r_init_scale
+            Mb = torch.randn(n_groups, K // r, r, r, device=self.reconn.device, dtype=self.reconn.dtype) * sigma
+            S = Mb - Mb.transpose(-1, -2)
+            with torch.no_grad():
+                self.reconn.copy_(S.permute(0, 2, 1, 3).reshape(n_groups * r, K))
+        else:
+            nn.init.zeros_(self.reconn)
+        if self.bias is not None:
+            bound = 1 / math.sqrt(K) if K > 0 else 0
+            nn.init.uniform_(self.bias, -bound, bound)
+
+    def _build_R(self) -> torch.Tensor:
+        """R from the stored parameter (reference: src/cute_prism/_module.py:534-577)."""
+        if self.activation == "silu_gate":
+            return self.reconn if self.ar_scale is None else self.ar_scale * self.reconn
+        n_groups = self.out_features // self.group_size
+        r = self.reconn_sz
+        nb = self.in_features // r
+        out_dtype = self.reconn.dtype
+        Mb = self.reconn.reshape(n_groups, r, nb, r).permute(0, 2, 1, 3)
+        if out_dtype in (torch.float16, torch.bfloat16):
+            Mb = Mb.float()
+        S = Mb - Mb.transpose(-1, -2)
+        eye = torch.eye(r, device=S.device, dtype=S.dtype).expand_as(S)
+        if self.cayley_order == float("inf"):
+            Rb = torch.linalg.solve(eye - S, eye + S)
+        else:
+            Rb = eye.clone()
+            Sp = S
+            for _ in range(int(self.cayley_order)):
+                Rb = Rb + 2 * Sp
+                Sp = Sp @ S
+        return Rb.permute(0, 2, 1, 3).reshape(n_groups * r, self.in_features).to(out_dtype)
+
+    def load_pretrained_weight(self, weight: torch.Tensor, bias: torch.Tensor | None = None) -> None:
+        if weight.shape != self.weight.shape:
+            raise ValueError(f"Weight shape mismatch: expected {self.weight.shape}, got {weight.shape}")
+        with torch.no_grad():
+            self.weight.copy_(weight)
+        if bias is not None:
+            if self.bias is None:
+                raise ValueError("This layer has no bias, but bias was provided")
+            if bias.shape != self.bias.shape:
+                raise ValueError(f"Bias shape mismatch: expected {self.bias.shape}, got {bias.shape}")
+            with torch.no_grad():
+                self.bias.copy_(bias)
+
+    @classmethod
+    def from_linear(cls, linear: nn.Linear, group_size: int = 256, reconn_sz: int = 8, activation=None,
+                    backend=None, autotuning: bool = False, **kwargs) -> "PrismLinear":
+        layer = cls(linear.in_features, linear.out_features, group_size=group_size, reconn_sz=reconn_sz,
+                    bias=linear.bias is not None, activation=activation, backend=backend,
+                    autotuning=autotuning, **kwargs)
+        layer.to(device=linear.weight.device, dtype=linear.weight.dtype)
+        layer.load_pretrained_weight(linear.weight.data, linear.bias.data if linear.bias is not None else None)
+        return layer
+
+    def forward(self, input: torch.Tensor) -> torch.Tensor:
+        A = input.reshape(-1, self.in_features)
+        C = _prism_forward_op(A, self.weight, self._build_R(), self.bias, self.group_size, self.reconn_sz,
+                              self.activation or "", float(self._bwd_scale))
+        return C.reshape(input.shape[:-1] + (self.out_features,))
+
+    def extra_repr(self) -> str:
+        parts = [f"in_features={self.in_features}", f"out_features={self.out_features}",
+                 f"group_size={self.group_size}", f"reconn_sz={self.reconn_sz}",
+                 f"bias={self.bias is not None}"]
+        if self.activation is not None:
+            parts.append(f"activation={self.activation!r}")
+        else:
+            parts.append(f"cayley_order={self.cayley_order}")
+        return ", ".join(parts)

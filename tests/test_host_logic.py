@@ -1,0 +1,161 @@
+"""Host-side logic that needs no GPU: argument validation (same rules as the reference's
+src/cute_prism/_validate.py), the tile table, PrismLinear construction / state / R construction,
+and the token-sharded gradient all-reduce on two gloo ranks."""
+import json
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import cute_mma_b200 as cp
+from cute_mma_b200 import _functional as F
+from cute_mma_b200 import _tile_table
+
+
+def test_validate_kernel_params():
+    F.validate_kernel_params(256, 8)
+    for gs, rs in ((0, 8), (256, 0), (256, 12), (100, 8), (2.5, 8)):
+        with pytest.raises(ValueError):
+            F.validate_kernel_params(gs, rs)
+
+
+def test_forward_rejects_cpu_and_bad_options():
+    A, B, R = torch.randn(8, 64), torch.randn(64, 64), torch.randn(16, 64)
+    with pytest.raises(ValueError, match="CUDA"):
+        cp.forward(A.half(), B.half(), R.half(), 32, 8)
+    with pytest.raises(ValueError, match="activation"):
+        cp.forward(A, B, R, 32, 8, activation="relu")
+    with pytest.raises(ValueError, match="sigmoid_gate"):
+        cp.forward(A, B, R, 32, 8, activation="sigmoid_gate")
+    with pytest.raises(ValueError, match="mode"):
+        cp.forward(A, B, R, 32, 8, mode="rw")
+    with pytest.raises(ValueError, match="internal_bias"):
+        cp.forward(A, B, R, 32, 8, activation="silu_gate", internal_bias=torch.zeros(2, 64))
+    with pytest.raises(ValueError):
+        cp.backward(torch.randn(8, 64), A, B, R, 32, 12)
+
+
+def test_tile_table_lookup(tmp_path):
+    path = tmp_path / "tt.json"
+    path.write_text(json.dumps({"entries": [
+        {"kernel": "fwd", "dtype": "bf16", "gate": 1, "M": 0, "N": 14336, "K": 4096, "gs": 256, "rs": 16, "cfg": [64, 16]},
+        {"kernel": "fwd", "dtype": "bf16", "gate": 1, "M": 1024, "N": 14336, "K": 4096, "gs": 256, "rs": 16, "cfg": [256, 16]},
+        {"kernel": "bwd_db", "dtype": "*", "gate": "*", "M": 0, "N": "*", "K": "*", "gs": "*", "rs": "*", "cfg": [128, 2]},
+    ]}))
+    _tile_table.load(str(path))
+    try:
+        look = _tile_table.lookup
+        assert look("fwd", torch.bfloat16, 1, 16, 14336, 4096, 256, 16) == [64, 16]
+        assert look("fwd", torch.bfloat16, 1, 16384, 14336, 4096, 256, 16) == [256, 16]
+        assert look("fwd", torch.float16, 1, 16384, 14336, 4096, 256, 16) is None
+        assert look("bwd_db", torch.float16, 1, 77, 512, 512, 64, 8) == [128, 2]
+        assert look("bwd_dadr", torch.float16, 1, 77, 512, 512, 64, 8) is None
+    finally:
+        _tile_table.load()  # restore the shipped table
+    assert isinstance(_tile_table.load(), list)
+
+
+def test_prism_linear_construction_and_state():
+    m = cp.PrismLinear(64, 128, group_size=32, reconn_sz=8)
+    assert sorted(m.state_dict()) == ["bias", "reconn", "weight"]
+    assert m.weight.shape == (128, 64) and m.reconn.shape == (32, 64) and m.bias.shape == (128,)
+    assert not m.weight.requires_grad and m.reconn.requires_grad
+    assert m._bwd_scale == 1.0
+    g = cp.PrismLinear(64, 128, group_size=32, reconn_sz=16, activation="silu_gate", bias=False)
+    assert g.weight.requires_grad and g.bias is None
+    assert abs(g._bwd_scale - 1 / 1.437) < 1e-12
+    # gated R is block skew-symmetric at init
+    Rb = g._build_R().reshape(4, 16, 4, 16).permute(0, 2, 1, 3)
+    assert torch.allclose(Rb, -Rb.transpose(-1, -2))
+    m2 = cp.PrismLinear(64, 128, group_size=32, reconn_sz=8)
+    m2.load_state_dict(m.state_dict())
+    assert torch.equal(m2.weight, m.weight)
+    for bad in (dict(activation="sigmoid_gate"), dict(input_shuffle=True), dict(dropout=0.1),
+                dict(internal_bias=True), dict(activation="tanh")):
+        with pytest.raises(ValueError):
+            cp.PrismLinear(64, 128, 32, 16, **bad)
+    with pytest.raises(ValueError):
+        cp.PrismLinear(64, 100, 32, 8)
+
+
+def test_build_R_identity_and_orthogonal():
+    m = cp.PrismLinear(64, 64, group_size=32, reconn_sz=8)
+    R = m._build_R()
+    assert torch.allclose(R, torch.eye(8).repeat(2, 8))  # reconn = 0  ->  identity blocks
+    with torch.no_grad():
+        m.reconn.normal_(0, 0.3)
+    for order in (float("inf"), 2):
+        m.cayley_order = order
+        Rb = m._build_R().reshape(2, 8, 8, 8).permute(0, 2, 1, 3)
+        if order == float("inf"):
+            assert torch.allclose(Rb @ Rb.transpose(-1, -2), torch.eye(8).expand_as(Rb), atol=1e-5)
+    # 16-bit parameters: solved in fp32, returned in the parameter dtype
+    mb = cp.PrismLinear(64, 64, group_size=32, reconn_sz=8).to(torch.bfloat16)
+    assert mb._build_R().dtype == torch.bfloat16
+
+
+def test_from_linear_copies_weights():
+    lin = torch.nn.Linear(64, 128)
+    m = cp.PrismLinear.from_linear(lin, group_size=32, reconn_sz=8)
+    assert torch.equal(m.weight, lin.weight) and torch.equal(m.bias, lin.bias)
+
+
+def test_shard_rows():
+    assert [cp.shard_rows(10, r, 4) for r in range(4)] == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    assert cp.shard_rows(65536, 7, 8) == (57344, 65536)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _dp_worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import prism_oracle as O
+        M, K, N, gs, rs = 64, 64, 64, 32, 8
+        A, B, R, dC = O.make_inputs(M, K, N, gs, rs, seed=2)
+        lo, hi = cp.shard_rows(M, rank, world)
+        # each rank computes the gradients of its token rows (here with the CPU oracle standing in
+        # for the kernels), then the parameter gradients are summed over ranks
+        dA, dR, dB = O.prism_backward(dC[lo:hi], A[lo:hi], B, R, gs, rs, "silu_gate")
+        dbias = dC[lo:hi].sum(0)
+        cp.allreduce_grads([dR, dB, dbias, dR.double()])
+        fA, fR, fB = O.prism_backward(dC, A, B, R, gs, rs, "silu_gate")
+        ok = (torch.allclose(dR, fR, atol=1e-4) and torch.allclose(dB, fB, atol=1e-4)
+              and torch.allclose(dbias, dC.sum(0), atol=1e-4) and torch.allclose(dA, fA[lo:hi], atol=1e-4))
+        # async form
+        t = torch.full((5,), float(rank + 1))
+        fin = cp.allreduce_grads([t], average=True, async_op=True)
+        fin()
+        ok = ok and torch.allclose(t, torch.full((5,), (1 + world) / 2))
+        out[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_token_sharded_gradients_two_gloo_ranks():
+    world = 2
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    out = ctx.Manager().dict()
+    procs = [ctx.Process(target=_dp_worker, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert dict(out) == {0: True, 1: True}
+
+
+def test_allreduce_is_a_noop_without_process_group():
+    t = torch.ones(3)
+    assert cp.allreduce_grads([t]) is None
+    assert torch.equal(t, torch.ones(3))

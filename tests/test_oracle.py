@@ -1,0 +1,93 @@
+"""The oracle (oracle/prism_oracle.py) against the reference's own outputs (golden vectors made
+by tests/golden/make_golden.py from the reference package), against torch autograd in float64
+(the reference's own self-check, tests/test_pytorch_backend.py:184-239) and against the
+structural known answers the reference relies on."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import prism_oracle as O
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _t(x):
+    return torch.from_numpy(np.ascontiguousarray(x))
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLD, "small_*.npz"))), ids=os.path.basename)
+def test_oracle_matches_reference_small(path):
+    z = np.load(path)
+    M, K, N, gs, rs = [int(v) for v in z["meta"]]
+    A, B, R, dC = _t(z["A"]), _t(z["B"]), _t(z["R"]), _t(z["dC"])
+    tol = 1e-12 if A.dtype == torch.float64 else 2e-5
+    for act, tag in ((None, "plain"), ("silu_gate", "gated")):
+        C = O.prism_forward(A, B, R, gs, rs, act)
+        dA, dR, dB = O.prism_backward(dC, A, B, R, gs, rs, act)
+        assert O.rel_err(C, _t(z[f"C_{tag}"])) < tol
+        assert O.rel_err(dA, _t(z[f"dA_{tag}"])) < tol
+        assert O.rel_err(dR, _t(z[f"dR_{tag}"])) < tol
+        if act is None:
+            assert dB is None and f"dB_{tag}" not in z.files
+        else:
+            assert O.rel_err(dB, _t(z[f"dB_{tag}"])) < tol
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_oracle_matches_reference_config0(seed):
+    z = np.load(os.path.join(GOLD, f"config0_seed{seed}.npz"))
+    M, K, N, gs, rs, s = [int(v) for v in z["meta"]]
+    assert s == seed
+    A, B, R, dC = O.make_inputs(M, K, N, gs, rs, seed=seed)
+    chk = np.array([A.double().sum().item(), B.double().sum().item(), R.double().sum().item(),
+                    dC.double().sum().item()])
+    np.testing.assert_allclose(chk, z["input_checksum"], rtol=1e-9, atol=1e-9)
+    for act, tag in ((None, "plain"), ("silu_gate", "gated")):
+        C = O.prism_forward(A, B, R, gs, rs, act)
+        dA, dR, dB = O.prism_backward(dC, A, B, R, gs, rs, act)
+        assert O.rel_err(C[::16, ::16], _t(z[f"C_{tag}"])) < 2e-5
+        assert O.rel_err(dA[::16, ::4], _t(z[f"dA_{tag}"])) < 2e-5
+        assert O.rel_err(dR, _t(z[f"dR_{tag}"])) < 2e-5
+        if act is not None:
+            assert O.rel_err(dB[::16, ::4], _t(z[f"dB_{tag}"])) < 2e-5
+
+
+@pytest.mark.parametrize("act", [None, "silu_gate"])
+@pytest.mark.parametrize("rs", [8, 16])
+def test_oracle_backward_matches_autograd_fp64(act, rs):
+    M, K, N, gs = 32, 128, 128, 32
+    A, B, R, dC = [t.double() for t in O.make_inputs(M, K, N, gs, rs, seed=3, r_kind="gaussian")]
+    A.requires_grad_(True); B.requires_grad_(True); R.requires_grad_(True)
+    C = O.prism_forward(A, B, R, gs, rs, act)
+    C.backward(dC)
+    dA, dR, dB = O.prism_backward(dC, A.detach(), B.detach(), R.detach(), gs, rs, act)
+    # only the entries of R inside the diagonal blocks take part; compare those
+    assert (dA - A.grad).abs().max() < 1e-9
+    assert (dR - R.grad).abs().max() < 1e-9
+    if act is not None:
+        assert (dB - B.grad).abs().max() < 1e-9
+
+
+def test_known_answers():
+    M, K, N, gs, rs = 16, 64, 64, 32, 8
+    A, B, _, _ = O.make_inputs(M, K, N, gs, rs, seed=5)
+    G, nb = N // gs, K // rs
+    eye = torch.eye(rs).repeat(G, nb)  # identity blocks
+    # identity R: plain forward is a dense linear layer
+    assert torch.allclose(O.prism_forward(A, B, eye, gs, rs), A @ B.T, atol=1e-5)
+    # R = 0: gated forward is exactly zero
+    assert O.prism_forward(A, B, torch.zeros_like(eye), gs, rs, "silu_gate").abs().max() == 0
+    # permutation blocks: S is a column permutation of A inside each block
+    perm = torch.randperm(rs, generator=torch.Generator().manual_seed(0))
+    P = torch.eye(rs)[perm]
+    Rp = P.repeat(G, nb)
+    S = O.rotate(A, O._blocks(Rp, G, rs)[0])
+    assert torch.equal(S.reshape(M, nb, rs), A.reshape(M, nb, rs)[:, :, perm])
+
+
+def test_flop_model():
+    f, d, b = O.flops(16384, 4096, 14336, 256, 16)
+    assert abs(f / 1e9 - 2044.4) < 0.5 and abs(d / 1e9 - 2164.7) < 0.5 and abs(b / 1e9 - 1924.2) < 0.5
