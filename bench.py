@@ -1,0 +1,341 @@
+#!/usr/bin/env python
+"""Benchmark of the Prism hot path: one step = forward + full backward (dA+dR, dB) of one Prism
+linear layer on one batch of synthetic tokens.
+
+Workload (default ``cfg2_m16384``): K=4096, N=14336, group_size=256, reconn_sz=16, bf16,
+silu_gate, M=16384 tokens per GPU -- the configuration the headline metric is quoted on.
+With N > 1 GPUs every rank processes its own batch of M tokens (weak scaling) and the parameter
+gradients dR and dB are summed over ranks with an NCCL all-reduce inside the timed step.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
+    python bench.py --impl reference            # CPU arm: the oracle restatement on the host cores
+
+Rank 0 prints ONE JSON line.  ``value`` = algorithmic TFLOP/s of the whole job with inputs resident
+in HBM; ``e2e`` = the same through the public API with the step's inputs (A, dC) coming from pinned
+host memory and its results (C, dA, dR, dB) copied back, copies inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (M per GPU, K, N, gs, rs, dtype, activation, a_std, b_std(K), dc_std)
+    "cfg2_m16384": dict(M=16384, K=4096, N=14336, gs=256, rs=16, dtype="bf16", act="silu_gate", dc_std=1.0),
+    "cfg2_m2048": dict(M=2048, K=4096, N=14336, gs=256, rs=16, dtype="bf16", act="silu_gate", dc_std=1.0),
+    "cfg3_m8192": dict(M=8192, K=1024, N=16384, gs=256, rs=8, dtype="fp16", act="silu_gate", dc_std=0.1),
+    "cfg1": dict(M=1024, K=256, N=1024, gs=256, rs=8, dtype="fp16", act="silu_gate", dc_std=1.0),
+}
+NOMINAL_TFLOPS = 2250.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture
+# summarised under profiles/ (null until captured for the workload)
+NCU_TRAFFIC_BYTES = {}
+
+
+def flops(w):
+    dense = 2.0 * w["M"] * w["N"] * w["K"]
+    bd = 2.0 * w["M"] * w["K"] * w["rs"] * (w["N"] // w["gs"])
+    gated = w["act"] is not None
+    return {"fwd": dense + bd, "dadr": dense + 2 * bd, "db": dense if gated else 0.0}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return json.load(f), "measured"
+    except (OSError, ValueError):
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+               0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, device_index):
+        super().__init__(daemon=True)
+        self.samples, self.reasons, self.max_mhz, self.power = [], set(), None, []
+        self._stop_evt = threading.Event()
+        self.handle = None
+        try:
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            try:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.handle = None
+
+    def run(self):
+        if self.handle is None:
+            return
+        nv = self.nv
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for b, name in self.REASONS.items():
+                    if bits & b:
+                        self.reasons.add(name)
+                self.power.append(nv.nvmlDeviceGetPowerUsage(self.handle) / 1000.0)
+            except Exception:
+                pass
+            self._stop_evt.wait(0.05)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(2.0)
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s),
+                "power_w_max": (max(self.power) if self.power else None)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_oracle_step(w, m_rows, threads):
+    """One bounded sample of the workload on the host cores: fwd + bwd of the oracle on m_rows tokens."""
+    from oracle import prism_oracle as O
+    torch.set_num_threads(threads)
+    A, B, R, dC = O.make_inputs(m_rows, w["K"], w["N"], w["gs"], w["rs"], seed=0, b_std=w["K"] ** -0.5,
+                                dc_std=w["dc_std"])
+
+    def step():
+        O.prism_forward(A, B, R, w["gs"], w["rs"], w["act"])
+        O.prism_backward(dC, A, B, R, w["gs"], w["rs"], w["act"])
+
+    return step
+
+
+def cpu_baseline(w, budget_s=12.0):
+    """Oracle (a port of the reference's pytorch backend) timed on the host cores on a bounded sample."""
+    threads = os.cpu_count() or 1
+    m_rows = 64
+    step = cpu_oracle_step(w, m_rows, threads)
+    step()
+    t0 = time.perf_counter(); step(); t1 = time.perf_counter() - t0
+    # grow the sample towards the budget (cost is linear in rows), at most 1024 rows
+    scale = max(1, min(16, int(budget_s / 3 / max(t1, 1e-3))))
+    m_rows = min(1024, m_rows * scale, w["M"])
+    step = cpu_oracle_step(w, m_rows, threads)
+    step()
+    ts = []
+    for _ in range(3):
+        t0 = time.perf_counter(); step(); ts.append(time.perf_counter() - t0)
+    ww = dict(w, M=m_rows)
+    f = sum(flops(ww).values())
+    return {"value": f / min(ts) / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": f"fwd+bwd of the fp32 oracle on {m_rows} of {w['M']} tokens, best of 3"}, m_rows
+
+
+def run_reference_arm(args, w, wname):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    base, m_rows = cpu_baseline(w, budget_s=6.0)
+    step = cpu_oracle_step(w, m_rows, threads)
+    for _ in range(min(args.warmup, 2)):
+        step()
+    steps = min(args.steps, 5)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    f = sum(flops(dict(w, M=m_rows)).values())
+    val = f / dt / 1e12
+    line = {
+        "impl": "reference", "metric": "prism_fwd_bwd_tflops", "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wname, **{k: w[k] for k in ("M", "K", "N", "gs", "rs", "act")},
+                   "sample_rows": m_rows},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": f"each step = fwd+bwd of the fp32 oracle on {m_rows} of {w['M']} tokens"},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--workload", default="cfg2_m16384", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference_arm(args, w, args.workload)
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch.distributed as dist
+    import cute_mma_b200 as cp
+    from cute_mma_b200 import _functional as F
+    from cute_mma_b200 import _lib
+    from oracle import prism_oracle as O  # seeded input generator only
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    dt = torch.bfloat16 if w["dtype"] == "bf16" else torch.float16
+    M, K, N, gs, rs, act = w["M"], w["K"], w["N"], w["gs"], w["rs"], w["act"]
+    gate = 1 if act else 0
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    A = torch.randn(M, K, device=dev, generator=gen).to(dt)
+    B = (torch.randn(N, K, device=dev, generator=torch.Generator(device=dev).manual_seed(7)) * K ** -0.5).to(dt)
+    R = O.orthogonal_R(N // gs, K, rs, torch.Generator().manual_seed(0)).to(dt).to(dev)
+    dC = (torch.randn(M, N, device=dev, generator=gen) * w["dc_std"]).to(dt)
+    fl = flops(w)
+    step_flops = sum(fl.values())
+
+    def step(ev=None):
+        if ev: ev[0].record()
+        C, _ = cp.forward(A, B, R, gs, rs, activation=act)
+        if ev: ev[1].record()
+        # weight gradient first so that its all-reduce overlaps the dA+dR kernel
+        dB = F._backward_db(dC, A, R, gs, rs, gate) if gate else None
+        fin_b = cp.allreduce_grads([dB], async_op=True) if world > 1 else None
+        if ev: ev[2].record()
+        dA, dR = F._backward_dadr(dC, A, B, R, gs, rs, gate)
+        if ev: ev[3].record()
+        if world > 1:
+            fin_r = cp.allreduce_grads([dR], async_op=True)
+            fin_b(); fin_r()
+        return C, dA, dR, dB
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    cp.check_device_status()
+
+    sampler = ClockSampler(local_rank)
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    launches0 = _lib.lib().prism_launch_count()
+    e0.record()
+    for i in range(args.steps):
+        step(evs[i])
+    e1.record()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    launches = _lib.lib().prism_launch_count() - launches0
+    clocks = sampler.stop()
+    cp.check_device_status()
+    ms = e0.elapsed_time(e1) / args.steps
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    k_fwd = sum(e[0].elapsed_time(e[1]) for e in evs) / args.steps
+    k_db = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
+    k_dadr = sum(e[2].elapsed_time(e[3]) for e in evs) / args.steps
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    value = world * step_flops / (ms * 1e-3) / 1e12
+    peaks, peak_kind = measured_peaks()
+    # dominant kernel = the one with the largest share of the step
+    parts = {"prism_bwd_dadr": (k_dadr, fl["dadr"]), "prism_fwd": (k_fwd, fl["fwd"]), "prism_bwd_db": (k_db, fl["db"])}
+    dom = max(parts, key=lambda k: parts[k][0])
+    dom_ms, dom_flops = parts[dom]
+    achieved = dom_flops / (dom_ms * 1e-3) / 1e12
+    peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+    roofline = {"bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get((dom, args.workload)),
+                "peak_source": f"{peak_kind} bf16_tflops_sustained (kernels timed inside a long step)",
+                "ms_per_launch": dom_ms,
+                "kernels_ms": {"prism_fwd": k_fwd, "prism_bwd_db": k_db, "prism_bwd_dadr": k_dadr},
+                "kernels_tflops": {k: (v[1] / (v[0] * 1e-3) / 1e12 if v[0] > 0 else None) for k, v in parts.items()}}
+
+    line = {
+        "metric": "prism_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "config": {"workload": args.workload, "M_per_gpu": M, "K": K, "N": N, "group_size": gs, "reconn_sz": rs,
+                   "activation": act, "step": "forward + backward(dA+dR, dB)" + (" + NCCL all-reduce(dR, dB)" if world > 1 else ""),
+                   "l2": "inputs larger than L2 (A+B+dC = %.0f MB per step), no flush" % ((A.numel() + B.numel() + dC.numel()) * 2 / 1e6)},
+        "tokens_per_s": world * M / (ms * 1e-3),
+        "frac_of_nominal_peak": value / world / NOMINAL_TFLOPS,
+        "frac_of_measured_peak": value / world / peak,
+        "roofline": roofline, "clocks": clocks, "gpu_launches": int(launches),
+    }
+
+    # ---- end-to-end through the public API with host buffers (rank-local; N ranks do the same)
+    if not args.no_e2e:
+        e_steps = max(2, min(args.steps, 5))
+        A_h, dC_h = A.cpu().pin_memory(), dC.cpu().pin_memory()
+        outs_h = None
+        def e2e_step():
+            nonlocal outs_h
+            A_d = A_h.to(dev, non_blocking=True)
+            dC_d = dC_h.to(dev, non_blocking=True)
+            C, _ = cp.forward(A_d, B, R, gs, rs, activation=act)
+            dA, dR, dB, _ = cp.backward(dC_d, A_d, B, R, gs, rs, activation=act)
+            res = [C, dA, dR] + ([dB] if dB is not None else [])
+            if outs_h is None:
+                outs_h = [torch.empty(r.shape, dtype=r.dtype, pin_memory=True) for r in res]
+            for h, r in zip(outs_h, res):
+                h.copy_(r, non_blocking=True)
+            torch.cuda.synchronize()
+        e2e_step()
+        t0 = time.perf_counter()
+        for _ in range(e_steps):
+            e2e_step()
+        e_ms = (time.perf_counter() - t0) / e_steps * 1e3
+        line["e2e"] = {"value": world * step_flops / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                       "h2d_bytes_per_step": int((A_h.numel() + dC_h.numel()) * 2),
+                       "d2h_bytes_per_step": int(sum(h.numel() * h.element_size() for h in outs_h)),
+                       "ms_per_step": e_ms, "steps": e_steps,
+                       "note": "cute_mma_b200.forward/backward with A, dC from pinned host memory and C, dA, dR, dB copied back"}
+        del A_h, dC_h, outs_h
+
+    if not args.no_cpu_baseline:
+        line["cpu_baseline"], _ = cpu_baseline(w)
+
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

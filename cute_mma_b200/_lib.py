@@ -26,7 +26,7 @@ NVCC_FLAGS = [
 # every symbol include/prism_b200.h declares
 EXPORTS = [
     "prism_fwd", "prism_bwd_dadr", "prism_bwd_db", "prism_workspace_bytes", "prism_status",
-    "prism_last_error_string", "prism_abi_version",
+    "prism_last_error_string", "prism_abi_version", "prism_launch_count",
 ]
 
 _lock = threading.Lock()
@@ -96,6 +96,7 @@ def lib() -> ctypes.CDLL:
             L.prism_last_error_string.restype = ctypes.c_char_p
             L.prism_last_error_string.argtypes = []
             L.prism_abi_version.restype = i
+            L.prism_launch_count.restype = ll
             _lib = L
         return _lib
 

@@ -90,6 +90,8 @@ using namespace prism;
 
 extern "C" int prism_abi_version(void) { return 1; }
 
+extern "C" long long prism_launch_count(void) { return launch_counter(); }
+
 extern "C" const char* prism_last_error_string(void) { return last_error_buf(); }
 
 extern "C" size_t prism_workspace_bytes(int kind, int M, int N, int K, int gs, int rs, int dtype,

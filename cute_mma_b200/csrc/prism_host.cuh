@@ -71,7 +71,14 @@ inline int make_tmap_2d(CUtensorMap* out, int dt, const void* base, uint64_t row
   return PRISM_OK;
 }
 
+// Number of kernels this library has launched in this process (for benchmarks and tests).
+inline long long& launch_counter() {
+  static long long n = 0;
+  return n;
+}
+
 inline int check_launch(const char* what) {
+  ++launch_counter();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess)
     return fail(PRISM_ERR_CUDA, "%s: launch failed: %s", what, cudaGetErrorString(e));

@@ -83,6 +83,9 @@ int prism_status(void* workspace, void* stream);
 
 const char* prism_last_error_string(void);
 
+/* Number of CUDA kernels the library has launched so far in this process. */
+long long prism_launch_count(void);
+
 /* Library / ABI version, for the loader's sanity check. */
 int prism_abi_version(void);
 
