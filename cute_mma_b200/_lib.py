@@ -14,7 +14,7 @@ import threading
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.path.join(_HERE, "libprism_b200.so")
-SOURCES = ["prism_abi.cu", "prism_fwd.cu", "prism_bwd_db.cu", "prism_bwd_dadr.cu"]
+SOURCES = ["prism_abi.cu", "prism_fwd.cu", "prism_bwd_db.cu", "prism_bwd_dadr.cu", "prism_fwd_noalloc.cu"]
 HEADERS = ["prism_common.cuh", "prism_host.cuh", "prism_kernels.cuh"]
 PUBLIC_HEADER = os.path.join(os.path.dirname(_HERE), "include", "prism_b200.h")
 
@@ -25,7 +25,7 @@ NVCC_FLAGS = [
 
 # every symbol include/prism_b200.h declares
 EXPORTS = [
-    "prism_fwd", "prism_bwd_dadr", "prism_bwd_db", "prism_workspace_bytes", "prism_status",
+    "prism_fwd", "prism_fwd_noalloc", "prism_bwd_dadr", "prism_bwd_db", "prism_workspace_bytes", "prism_status",
     "prism_last_error_string", "prism_abi_version", "prism_launch_count",
 ]
 
@@ -81,6 +81,8 @@ def lib() -> ctypes.CDLL:
             ip = ctypes.POINTER(ctypes.c_int)
             L.prism_fwd.restype = i
             L.prism_fwd.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, i, ll, ll, ll, ll, ip, vp, sz, vp]
+            L.prism_fwd_noalloc.restype = i
+            L.prism_fwd_noalloc.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, i, ll, ll, ll, ll, ip, vp, vp]
             if hasattr(L, "prism_bwd_dadr"):
                 L.prism_bwd_dadr.restype = i
                 L.prism_bwd_dadr.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, ctypes.c_float,

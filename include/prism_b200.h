@@ -48,12 +48,31 @@ extern "C" {
 #define PRISM_KIND_BWD_DB 2
 
 #define PRISM_WORKSPACE_HEADER_BYTES 256
+/* size of the library's built-in scratch array used by prism_fwd_noalloc: 8 MiB + the status header */
+#define PRISM_NOALLOC_SCRATCH_BYTES (8 * 1024 * 1024 + 256)
 
 /* Forward.  bias: [N] in the same dtype, or NULL.  cfg (4 ints): {BN, PM, stagesAR, stagesB}. */
 int prism_fwd(const void* A, const void* B, const void* R, const void* bias, void* C,
               int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
               long long lda, long long ldb, long long ldr, long long ldc,
               const int* cfg, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Forward for callers that cannot allocate device memory and therefore cannot supply a workspace.
+ * (No counterpart in the reference: its bindings allocate outputs and scratch themselves.)
+ * Same arguments and results as prism_fwd, except that the scratch is a fixed array of
+ * PRISM_NOALLOC_SCRATCH_BYTES inside the library (resident on every GPU that loads the library
+ * until the process exits).  The call fails with PRISM_ERR_WORKSPACE when the shape needs more:
+ * 256 bytes, plus (N/group_size)*16*K*2 bytes when reconn_sz = 8.  It calls no cudaMalloc / cudaFree
+ * and no allocating library routine.  All calls on a GPU share the array: calls ordered on one
+ * stream are independent (each rewrites what it reads and clears the status word first), calls
+ * that can overlap on the GPU race and give undefined results.  The first call on each GPU looks
+ * up the array's device address; make that call outside any stream capture.
+ * device_status: NULL, or where the 4-byte device status word of this call is copied
+ * (stream-ordered; device or pinned host memory). */
+int prism_fwd_noalloc(const void* A, const void* B, const void* R, const void* bias, void* C,
+                      int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
+                      long long lda, long long ldb, long long ldr, long long ldc,
+                      const int* cfg, int* device_status, void* stream);
 
 /* Input and rotation gradients: dA [M,K] and dR [(N/group_size)*reconn_sz, K], both scaled by
  * dc_scale.  cfg (1 int): {runs} -- the number of CTAs that share one 128-feature column of dA;
