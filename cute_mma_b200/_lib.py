@@ -13,7 +13,7 @@ import threading
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_HERE, "csrc")
-LIB_PATH = os.path.join(_HERE, "libprism_b200.so")
+LIB_PATH = os.environ.get("PRISM_B200_LIB", os.path.join(_HERE, "libprism_b200.so"))
 SOURCES = ["prism_abi.cu", "prism_fwd.cu", "prism_bwd_db.cu", "prism_bwd_dadr.cu", "prism_fwd_noalloc.cu"]
 HEADERS = ["prism_common.cuh", "prism_host.cuh", "prism_kernels.cuh"]
 PUBLIC_HEADER = os.path.join(os.path.dirname(_HERE), "include", "prism_b200.h")

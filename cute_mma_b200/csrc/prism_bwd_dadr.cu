@@ -147,23 +147,24 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       bool ok = true;
-      uint32_t tile_iter = 0, gg = 0, sc = 0;
+      uint32_t tile_iter = 0;
+      Ring rr(p.rb), rst(p.ns);
       for (int mt = run; mt < p.n_mtiles && ok; mt += p.runs, ++tile_iter) {
         const int m0 = mt * 128;
         if (!mbar_wait(&bars->a_empty, (tile_iter & 1) ^ 1)) { ok = false; break; }
         mbar_arrive_expect_tx(&bars->a_full, 2 * kTile);
         tma_load_2d(smemA, &tmA, &bars->a_full, f0, m0);
         tma_load_2d(smemA + kTile, &tmA, &bars->a_full, f0 + 64, m0);
-        for (int g = 0; g < G && ok; ++g, ++gg) {
-          const int rb = gg % p.rb;
-          if (!mbar_wait(&bars->r_empty[rb], ((gg / p.rb) & 1) ^ 1)) { ok = false; break; }
+        for (int g = 0; g < G && ok; ++g, rr.next()) {
+          const int rb = rr.idx;
+          if (!mbar_wait(&bars->r_empty[rb], rr.phase ^ 1)) { ok = false; break; }
           uint8_t* dstR = smemR + rb * r_buf_bytes;
           mbar_arrive_expect_tx(&bars->r_full[rb], 2 * p.E * 128);
           tma_load_2d(dstR, &tmR, &bars->r_full[rb], f0, g * p.E);
           tma_load_2d(dstR + p.r_tile_bytes, &tmR, &bars->r_full[rb], f0 + 64, g * p.E);
-          for (int s = 0; s < nstg; ++s, ++sc) {
-            const int st = sc % p.ns;
-            if (!mbar_wait(&bars->st_empty[st], ((sc / p.ns) & 1) ^ 1)) { ok = false; break; }
+          for (int s = 0; s < nstg; ++s, rst.next()) {
+            const int st = rst.idx;
+            if (!mbar_wait(&bars->st_empty[st], rst.phase ^ 1)) { ok = false; break; }
             uint8_t* dst = smemSt + st * kStageBytes;
             const int n0 = g * p.gs + s * 64;
             mbar_arrive_expect_tx(&bars->st_full[st], kStageBytes);
@@ -185,12 +186,14 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const int ksteps_per_block = p.E / 16;
       const uint32_t a_addr = smem_u32(smemA);
       bool ok = true;
-      uint32_t tile_iter = 0, gg = 0, sc = 0;
+      uint32_t tile_iter = 0, gg = 0;
+      Ring rr(p.rb), rr_dsr(p.rb), rst(p.ns);
 
-      // dA += dS(x) . R(x) for the group with global index x
+      // dA += dS(x) . R(x) for the group with global index x (called once per group, in order)
       auto issue_dsr = [&](uint32_t x, bool first_of_tile, bool last_of_tile, uint32_t titer) -> bool {
         const int buf = x & 1;
-        const int rbx = x % p.rb;
+        const int rbx = rr_dsr.idx;
+        rr_dsr.next();
         if (!mbar_wait(&bars->ds_full[buf], (x >> 1) & 1)) return false;
         if (first_of_tile) {
           if (!mbar_wait(&bars->da_empty, (titer & 1) ^ 1)) return false;
@@ -220,10 +223,10 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
       for (int mt = run; mt < p.n_mtiles && ok; mt += p.runs, ++tile_iter) {
         if (!mbar_wait(&bars->a_full, tile_iter & 1)) { ok = false; break; }
-        for (int g = 0; g < G && ok; ++g, ++gg) {
-          const int rb = gg % p.rb;
+        for (int g = 0; g < G && ok; ++g, ++gg, rr.next()) {
+          const int rb = rr.idx;
           const int hb = gg & 1;
-          if (!mbar_wait(&bars->r_full[rb], (gg / p.rb) & 1)) { ok = false; break; }
+          if (!mbar_wait(&bars->r_full[rb], rr.phase)) { ok = false; break; }
           if (GATE == GATE_SILU) {
             if (!mbar_wait(&bars->s_empty, (gg & 1) ^ 1)) { ok = false; break; }
             tc_fence_after_sync();
@@ -242,9 +245,9 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             umma_commit(&bars->s_full);
           }
           if (!mbar_wait(&bars->dh_empty[hb], ((gg >> 1) & 1) ^ 1)) { ok = false; break; }
-          for (int s = 0; s < nstg; ++s, ++sc) {
-            const int st = sc % p.ns;
-            if (!mbar_wait(&bars->st_full[st], (sc / p.ns) & 1)) { ok = false; break; }
+          for (int s = 0; s < nstg; ++s, rst.next()) {
+            const int st = rst.idx;
+            if (!mbar_wait(&bars->st_full[st], rst.phase)) { ok = false; break; }
             tc_fence_after_sync();
             const uint32_t dc_addr = smem_u32(smemSt + st * kStageBytes);
             const uint32_t b_addr = dc_addr + kTile;

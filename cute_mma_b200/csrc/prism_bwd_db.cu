@@ -121,15 +121,16 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       mbar_arrive_expect_tx(&bars->r_full, 2 * p.E * 128);
       tma_load_2d(smemR, &tmR, &bars->r_full, f0, g * p.E);
       tma_load_2d(smemR + p.r_tile_bytes, &tmR, &bars->r_full, f0 + 64, g * p.E);
-      for (int j = 0; j < nb && ok; ++j) {
+      Ring ra(p.sa), rd(p.sd);
+      for (int j = 0; j < nb && ok; ++j, ra.next(), rd.next()) {
         const int tok0 = (tb0 + j) * 128;
-        const int sa = j % p.sa, sd = j % p.sd;
-        if (!mbar_wait(&bars->a_empty[sa], ((j / p.sa) & 1) ^ 1)) { ok = false; break; }
+        const int sa = ra.idx, sd = rd.idx;
+        if (!mbar_wait(&bars->a_empty[sa], ra.phase ^ 1)) { ok = false; break; }
         uint8_t* dstA = smemA + sa * a_stage_bytes;
         mbar_arrive_expect_tx(&bars->a_full[sa], 2 * kTile);
         tma_load_2d(dstA, &tmA, &bars->a_full[sa], f0, tok0);
         tma_load_2d(dstA + kTile, &tmA, &bars->a_full[sa], f0 + 64, tok0);
-        if (!mbar_wait(&bars->dc_empty[sd], ((j / p.sd) & 1) ^ 1)) { ok = false; break; }
+        if (!mbar_wait(&bars->dc_empty[sd], rd.phase ^ 1)) { ok = false; break; }
         uint8_t* dstD = smemD + sd * dc_stage_bytes;
         mbar_arrive_expect_tx(&bars->dc_full[sd], dc_stage_bytes);
         for (int t = 0; t < p.dc_tiles; ++t)
@@ -146,11 +147,13 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int ksteps_per_block = p.E / 16;
       bool ok = mbar_wait(&bars->r_full, 0);
       const uint32_t r_addr = smem_u32(smemR);
+      Ring rs_a(p.sa), rm_a(p.sa), rm_d(p.sd);
       for (int j = 0; j < nb + 1 && ok; ++j) {
         if (j < nb) {
-          const int sa = j % p.sa, sbuf = j % kSBufs;
-          if (!mbar_wait(&bars->a_full[sa], (j / p.sa) & 1)) { ok = false; break; }
+          const int sa = rs_a.idx, sbuf = j & (kSBufs - 1);
+          if (!mbar_wait(&bars->a_full[sa], rs_a.phase)) { ok = false; break; }
           if (!mbar_wait(&bars->s_empty[sbuf], ((j / kSBufs) & 1) ^ 1)) { ok = false; break; }
+          rs_a.next();
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smemA + sa * a_stage_bytes);
           for (int i = 0; i < 2; ++i) {
@@ -168,9 +171,11 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         if (j >= 1) {
           const int jm = j - 1;
-          const int sa = jm % p.sa, sd = jm % p.sd;
-          if (!mbar_wait(&bars->h_full[sa], (jm / p.sa) & 1)) { ok = false; break; }
-          if (!mbar_wait(&bars->dc_full[sd], (jm / p.sd) & 1)) { ok = false; break; }
+          const int sa = rm_a.idx, sd = rm_d.idx;
+          if (!mbar_wait(&bars->h_full[sa], rm_a.phase)) { ok = false; break; }
+          if (!mbar_wait(&bars->dc_full[sd], rm_d.phase)) { ok = false; break; }
+          rm_a.next();
+          rm_d.next();
           tc_fence_after_sync();
           const uint32_t h_addr = smem_u32(smemA + sa * a_stage_bytes);
           const uint32_t d_addr = smem_u32(smemD + sd * dc_stage_bytes);
@@ -194,8 +199,9 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int chunk = gw >> 2;     // which of the two 64-feature tiles
     const uint32_t row = q * 32 + lane;
     bool ok = true;
-    for (int j = 0; j < nb; ++j) {
-      const int sa = j % p.sa, sbuf = j % kSBufs;
+    Ring ra(p.sa);
+    for (int j = 0; j < nb; ++j, ra.next()) {
+      const int sa = ra.idx, sbuf = j & (kSBufs - 1);
       if (!mbar_wait(&bars->s_full[sbuf], (j / kSBufs) & 1)) { ok = false; break; }
       tc_fence_after_sync();
       uint8_t* tile = smemA + sa * a_stage_bytes + chunk * kTile;

@@ -97,6 +97,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   }
 }
 
+// Position in a ring of n buffers plus the mbarrier phase parity of the current pass.
+// Advancing is an increment and a compare: the single-thread producer / MMA-issuer roles are
+// latency-bound, and a runtime division per stage would cost more than the work they hand out.
+struct Ring {
+  uint32_t idx, phase, n;
+  __device__ __forceinline__ explicit Ring(uint32_t n_) : idx(0), phase(0), n(n_) {}
+  __device__ __forceinline__ void next() {
+    if (++idx == n) { idx = 0; phase ^= 1u; }
+  }
+};
+
 // Make generic-proxy writes to shared memory visible to the async proxy
 // (TMA stores, tcgen05.mma operand reads).
 __device__ __forceinline__ void fence_proxy_async_smem() {
@@ -297,6 +308,71 @@ __device__ __forceinline__ float sigmoid_fast(float x) {
 }
 
 // ----------------------------------------------------------------------------
+// Packed two-element arithmetic in the data's own 16-bit type (one instruction per pair).
+// ----------------------------------------------------------------------------
+#ifndef PRISM_GATE_PACKED
+#define PRISM_GATE_PACKED 1   // 1: gate math on f16x2 / bf16x2 pairs, 0: fp32 per element
+#endif
+
+template <int DT>
+struct Pk;
+template <>
+struct Pk<DT_F16> {
+  static constexpr uint32_t kHalf = 0x38003800u;  // (0.5, 0.5)
+  __device__ __forceinline__ static uint32_t cvt(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+  }
+  __device__ __forceinline__ static uint32_t mul(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+  }
+  __device__ __forceinline__ static uint32_t fma(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+  }
+  __device__ __forceinline__ static uint32_t tanh(uint32_t a) {
+    uint32_t d;
+    asm("tanh.approx.f16x2 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+  }
+};
+template <>
+struct Pk<DT_BF16> {
+  static constexpr uint32_t kHalf = 0x3F003F00u;
+  __device__ __forceinline__ static uint32_t cvt(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+  }
+  __device__ __forceinline__ static uint32_t mul(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+  }
+  __device__ __forceinline__ static uint32_t fma(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+  }
+  __device__ __forceinline__ static uint32_t tanh(uint32_t a) {
+    uint32_t d;
+    asm("tanh.approx.bf16x2 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+  }
+};
+
+// silu(s) for a pair, from fp32 s: with hs = s/2, silu(s) = hs + hs*tanh(hs).
+template <int DT>
+__device__ __forceinline__ uint32_t silu_pair(float s0, float s1) {
+  const uint32_t hs = Pk<DT>::mul(Pk<DT>::cvt(s0, s1), Pk<DT>::kHalf);
+  return Pk<DT>::fma(hs, Pk<DT>::tanh(hs), hs);
+}
+
+// ----------------------------------------------------------------------------
 // The gate producer step shared by the forward and dB kernels: 32 consecutive
 // columns of one row.  s[] holds S = (A . blockdiag(R_g)^T)[row, cols] in fp32
 // (read from TMEM); the matching 16-bit A values sit in the swizzled tile in
@@ -314,6 +390,13 @@ __device__ __forceinline__ void gate_h_32cols(uint8_t* tile, uint32_t row, uint3
     for (int e = 0; e < 4; ++e) {
       const float s0 = __uint_as_float(s[j * 8 + e * 2]);
       const float s1 = __uint_as_float(s[j * 8 + e * 2 + 1]);
+#if PRISM_GATE_PACKED
+      if (GATE == GATE_SILU) {
+        ow[e] = Pk<DT>::mul(aw[e], silu_pair<DT>(s0, s1));
+      } else {
+        ow[e] = Pk<DT>::cvt(s0, s1);
+      }
+#else
       float h0, h1;
       if (GATE == GATE_SILU) {
         const float2 a2 = Elem<DT>::unpack(aw[e]);
@@ -324,6 +407,7 @@ __device__ __forceinline__ void gate_h_32cols(uint8_t* tile, uint32_t row, uint3
         h1 = s1;
       }
       ow[e] = Elem<DT>::pack(h0, h1);
+#endif
     }
     *reinterpret_cast<uint4*>(tile + sw128_offset(row, chunk0 + j)) =
         make_uint4(ow[0], ow[1], ow[2], ow[3]);

@@ -7,30 +7,36 @@
 // (cute_prism_coop_pc.cu:567-804) and its binding (torch_ext/prism_fwd_torch.cu:23-196).
 //
 // Per CTA: a persistent loop over (128-row, BN-column) output tiles; per 64-wide K chunk
-//   TMA warp   : A tile [128 x 64], R_g tile [E x 64] into the "AR" ring, B_g tile [BN x 64]
-//                into the "B" ring (128-byte swizzle, zero fill outside the tensors)
-//   MMA warp   : block rotation S = A_blk . R_blk^T as tcgen05.mma M128 N=E K=16 per block into a
-//                ring of 64-column TMEM buffers; then, two chunks later, the dense product
-//                C += H . B^T as tcgen05.mma M128 N=BN K=16, accumulating in TMEM
-//   gate warps : tcgen05.ld S, read A from shared memory, H = A*silu(S) (or H = S), write H
-//                over the A tile in place (same swizzled layout), release the S buffer
-//   epilogue   : tcgen05.ld C, + bias, cast, store.
+//   warp 0      TMA producer: A tile [128 x 64] + R_g tile [E x 64] into the "AR" ring, B_g tile
+//               [BN x 64] into the "B" ring (128-byte swizzle, zero fill outside the tensors)
+//   warp 2      rotation issuer: S = A_blk . R_blk^T as tcgen05.mma M128 N=E K=16 per block into
+//               a ring of four 64-column TMEM buffers
+//   warps 4-11  gate warps, two groups of four that take alternate chunks: tcgen05.ld S, read A
+//               from shared memory, H = A*silu(S) (or H = S) written over the A tile in place
+//   warp 1      dense issuer: C += H . B^T as 4 x tcgen05.mma M128 N=BN K=16, fp32 in TMEM
+//   warps 12-15 epilogue: tcgen05.ld C, + bias, cast, swizzled staging tile, TMA store.
+// Every role keeps its ring positions as counters; the single-thread roles do no division.
 #include "prism_host.cuh"
 #include "prism_kernels.cuh"
+
+#ifndef PRISM_DBG
+#define PRISM_DBG 0   // debugging aid: bit 0 skips the gate math, bit 1 the output stores, bit 2 the rotation MMAs
+#endif
 
 namespace prism {
 
 namespace fwd {
-constexpr int kThreads = 448;       // warp 0 TMA, warp 1 MMA, warps 2-9 gate, warps 10-13 epilogue
-constexpr int kGateWarp0 = 2;
-constexpr int kNumGateWarps = 8;
-constexpr int kEpiWarp0 = 10;
+constexpr int kThreads = 512;
+constexpr int kWarpTma = 0, kWarpMma = 1, kWarpRot = 2;
+constexpr int kGateWarp0 = 4;
+constexpr int kNumGateWarps = 8;      // two groups of four
+constexpr int kEpiWarp0 = 12;
 constexpr int kNumEpiWarps = 4;
-constexpr int kSBufs = 4;           // TMEM ring of S buffers, 64 columns each
-constexpr int kSCol0 = 256;         // S ring lives in TMEM columns [256, 512)
-constexpr int kLag = 2;             // dense MMA of chunk c is issued after the rotation of chunk c+kLag
+constexpr int kSBufs = 4;             // TMEM ring of S buffers, 64 columns each (power of two)
+constexpr int kSCol0 = 256;           // S ring lives in TMEM columns [256, 512)
 constexpr int kMaxStages = 8;
-constexpr int kATileBytes = 128 * 128;  // [128 rows x 64 elems] 16-bit
+constexpr int kATileBytes = 128 * 128;   // [128 rows x 64 elems] 16-bit
+constexpr int kEpiStageBytes = 32 * 128; // per epilogue warp: [32 rows x 64 elems]
 }  // namespace fwd
 
 struct FwdParams {
@@ -42,6 +48,7 @@ struct FwdParams {
   int n_kchunks;
   int sa, sb;           // stages of the AR ring / B ring
   int r_tile_bytes;     // bytes reserved for the R tile of one AR stage (multiple of 1024)
+  int tma_store;        // 1: epilogue goes through TMA stores (BN multiple of 64)
   const void* bias;     // [N] or null
   void* C;
   long long ldc;
@@ -74,7 +81,8 @@ __device__ __forceinline__ void tile_coords(const FwdParams& p, int t, int& mt, 
 template <int DT, int GATE>
 __global__ void __launch_bounds__(fwd::kThreads, 1)
 prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmR,
-                 const __grid_constant__ CUtensorMap tmB, const FwdParams p) {
+                 const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
+                 const FwdParams p) {
   using namespace fwd;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -82,8 +90,9 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int ar_stage_bytes = kATileBytes + p.r_tile_bytes;
   const int b_stage_bytes = p.BN * 128;
   uint8_t* smemAR = smem;
-  uint8_t* smemB = smem + p.sa * ar_stage_bytes;
-  FwdBarriers* bars = reinterpret_cast<FwdBarriers*>(smemB + p.sb * b_stage_bytes);
+  uint8_t* smemB = smemAR + p.sa * ar_stage_bytes;
+  uint8_t* smemEpi = smemB + p.sb * b_stage_bytes;
+  FwdBarriers* bars = reinterpret_cast<FwdBarriers*>(smemEpi + kNumEpiWarps * kEpiStageBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -91,188 +100,239 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int i = 0; i < kMaxStages; ++i) {
       mbar_init(&bars->ar_full[i], 1);
-      mbar_init(&bars->h_full[i], kNumGateWarps);
+      mbar_init(&bars->h_full[i], kNumGateWarps / 2);
       mbar_init(&bars->a_empty[i], 1);
       mbar_init(&bars->b_full[i], 1);
       mbar_init(&bars->b_empty[i], 1);
     }
     for (int i = 0; i < kSBufs; ++i) {
       mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->s_empty[i], kNumGateWarps);
+      mbar_init(&bars->s_empty[i], kNumGateWarps / 2);
     }
     mbar_init(&bars->acc_full, 1);
     mbar_init(&bars->acc_empty, kNumEpiWarps);
     fence_mbar_init();
   }
-  if (warp == 1) {
+  if (warp == kWarpMma) {
     tmem_alloc(&bars->tmem_base, 512);
     tmem_relinquish();
   }
-  if (warp == 0 && lane == 0) {
+  if (warp == kWarpTma && lane == 0) {
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmR);
     prefetch_tmap(&tmB);
+    prefetch_tmap(&tmC);
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
   const int nk = p.n_kchunks;
+  const int my_tiles = (p.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  const uint32_t total = (uint32_t)my_tiles * nk;   // chunks this CTA processes
 
-  if (warp == 0) {
+  if (warp == kWarpTma) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       // The AR ring is `ahead` chunks deeper than the B ring: A/R tiles are requested that much
-      // earlier, because the rotation + gate of a chunk must finish before its dense MMA starts.
-      const int my_tiles = (p.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-      const uint32_t total = (uint32_t)my_tiles * nk;
+      // earlier, because rotation + gate of a chunk must finish before its dense MMA starts.
+      // Two cursors (tile, chunk) walk the same sequence, the B cursor `ahead` chunks behind.
       const uint32_t ahead = p.sa - p.sb;
+      Ring ra(p.sa), rb(p.sb);
+      int ta = blockIdx.x, ca = 0, mta, nta, tb = blockIdx.x, cb = 0, mtb, ntb;
+      tile_coords(p, ta, mta, nta);
+      tile_coords(p, tb, mtb, ntb);
+      int ga = nta / p.ntiles_per_group;
       bool ok = true;
       for (uint32_t j = 0; j < total + ahead && ok; ++j) {
         if (j < total) {
-          const uint32_t it = j;
-          int mt, nt;
-          tile_coords(p, blockIdx.x + (it / nk) * gridDim.x, mt, nt);
-          const int c = it % nk;
-          const int g = nt / p.ntiles_per_group;
-          const int sa = it % p.sa;
-          if (!mbar_wait(&bars->a_empty[sa], ((it / p.sa) & 1) ^ 1)) { ok = false; break; }
-          uint8_t* dstA = smemAR + sa * ar_stage_bytes;
-          mbar_arrive_expect_tx(&bars->ar_full[sa], kATileBytes + p.E * 128);
-          tma_load_2d(dstA, &tmA, &bars->ar_full[sa], c * 64, mt * 128);
-          tma_load_2d(dstA + kATileBytes, &tmR, &bars->ar_full[sa], c * 64, g * p.E);
+          if (!mbar_wait(&bars->a_empty[ra.idx], ra.phase ^ 1)) { ok = false; break; }
+          uint8_t* dstA = smemAR + ra.idx * ar_stage_bytes;
+          mbar_arrive_expect_tx(&bars->ar_full[ra.idx], kATileBytes + p.E * 128);
+          tma_load_2d(dstA, &tmA, &bars->ar_full[ra.idx], ca * 64, mta * 128);
+          tma_load_2d(dstA + kATileBytes, &tmR, &bars->ar_full[ra.idx], ca * 64, ga * p.E);
+          ra.next();
+          if (++ca == nk) {
+            ca = 0;
+            ta += gridDim.x;
+            if (ta < p.n_tiles) { tile_coords(p, ta, mta, nta); ga = nta / p.ntiles_per_group; }
+          }
         }
         if (j >= ahead) {
-          const uint32_t it = j - ahead;
-          int mt, nt;
-          tile_coords(p, blockIdx.x + (it / nk) * gridDim.x, mt, nt);
-          const int c = it % nk;
-          const int sb = it % p.sb;
-          if (!mbar_wait(&bars->b_empty[sb], ((it / p.sb) & 1) ^ 1)) { ok = false; break; }
-          mbar_arrive_expect_tx(&bars->b_full[sb], b_stage_bytes);
-          tma_load_2d(smemB + sb * b_stage_bytes, &tmB, &bars->b_full[sb], c * 64, nt * p.BN);
+          if (!mbar_wait(&bars->b_empty[rb.idx], rb.phase ^ 1)) { ok = false; break; }
+          mbar_arrive_expect_tx(&bars->b_full[rb.idx], b_stage_bytes);
+          tma_load_2d(smemB + rb.idx * b_stage_bytes, &tmB, &bars->b_full[rb.idx], cb * 64, ntb * p.BN);
+          rb.next();
+          if (++cb == nk) {
+            cb = 0;
+            tb += gridDim.x;
+            if (tb < p.n_tiles) tile_coords(p, tb, mtb, ntb);
+          }
         }
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == kWarpRot) {
+    // ------------------------------------------------------------------ rotation issuer
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(DT, 128, p.E, 0, 0);
-      const uint32_t idesc_c = make_idesc(DT, 128, p.BN, 0, 0);
       const int blocks_per_chunk = 64 / p.E;
       const int ksteps_per_block = p.E / 16;
-      const int my_tiles = (p.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-      const uint32_t total = (uint32_t)my_tiles * nk;
+      Ring ra(p.sa);
       bool ok = true;
-      for (uint32_t j = 0; j < total + kLag && ok; ++j) {
-        if (j < total) {
-          // rotation of chunk j: S = A_blk . R_blk^T for every block of the chunk
-          const uint32_t it = j;
-          const int sa = it % p.sa, sbuf = it % kSBufs;
-          if (!mbar_wait(&bars->ar_full[sa], (it / p.sa) & 1)) { ok = false; break; }
-          if (!mbar_wait(&bars->s_empty[sbuf], ((it / kSBufs) & 1) ^ 1)) { ok = false; break; }
-          tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(smemAR + sa * ar_stage_bytes);
-          const uint32_t r_addr = a_addr + kATileBytes;
-          for (int b = 0; b < blocks_per_chunk; ++b) {
-            for (int ks = 0; ks < ksteps_per_block; ++ks) {
-              const uint32_t koff = (b * p.E + ks * 16) * 2;
-              umma_f16(tmem_base + kSCol0 + sbuf * 64 + b * p.E,
-                       desc_kmajor_sw128(a_addr + koff, 1024),
-                       desc_kmajor_sw128(r_addr + koff, 1024), idesc_s, ks > 0 ? 1u : 0u);
-            }
+      for (uint32_t j = 0; j < total; ++j) {
+        const uint32_t sbuf = j & (kSBufs - 1), sphase = (j / kSBufs) & 1;
+        if (!mbar_wait(&bars->ar_full[ra.idx], ra.phase)) { ok = false; break; }
+        if (!mbar_wait(&bars->s_empty[sbuf], sphase ^ 1)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_u32(smemAR + ra.idx * ar_stage_bytes);
+        const uint32_t r_addr = a_addr + kATileBytes;
+        for (int b = 0; b < blocks_per_chunk; ++b) {
+          for (int ks = 0; ks < ksteps_per_block; ++ks) {
+            if (PRISM_DBG & 4) break;
+            const uint32_t koff = (b * p.E + ks * 16) * 2;
+            umma_f16(tmem_base + kSCol0 + sbuf * 64 + b * p.E, desc_kmajor_sw128(a_addr + koff, 1024),
+                     desc_kmajor_sw128(r_addr + koff, 1024), idesc_s, ks > 0 ? 1u : 0u);
           }
-          umma_commit(&bars->s_full[sbuf]);
         }
-        if (j >= kLag) {
-          // dense product of chunk j - kLag: C += H . B^T
-          const uint32_t it = j - kLag;
-          const int cm = it % nk;
-          const uint32_t tile_iter = it / nk;
-          const int sa = it % p.sa, sb = it % p.sb;
-          if (!mbar_wait(&bars->h_full[sa], (it / p.sa) & 1)) { ok = false; break; }
-          if (!mbar_wait(&bars->b_full[sb], (it / p.sb) & 1)) { ok = false; break; }
-          if (cm == 0) {
-            if (!mbar_wait(&bars->acc_empty, (tile_iter & 1) ^ 1)) { ok = false; break; }
-          }
-          tc_fence_after_sync();
-          const uint32_t h_addr = smem_u32(smemAR + sa * ar_stage_bytes);
-          const uint32_t b_addr = smem_u32(smemB + sb * b_stage_bytes);
+        umma_commit(&bars->s_full[sbuf]);
+        ra.next();
+      }
+      if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
+    }
+  } else if (warp == kWarpMma) {
+    // ------------------------------------------------------------------ dense issuer
+    if (lane == 0) {
+      const uint32_t idesc_c = make_idesc(DT, 128, p.BN, 0, 0);
+      Ring ra(p.sa), rb(p.sb);
+      int cm = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (uint32_t j = 0; j < total; ++j) {
+        if (!mbar_wait(&bars->h_full[ra.idx], ra.phase)) { ok = false; break; }
+        if (!mbar_wait(&bars->b_full[rb.idx], rb.phase)) { ok = false; break; }
+        if (cm == 0) {
+          if (!mbar_wait(&bars->acc_empty, acc_phase ^ 1)) { ok = false; break; }
+        }
+        tc_fence_after_sync();
+        const uint32_t h_addr = smem_u32(smemAR + ra.idx * ar_stage_bytes);
+        const uint32_t b_addr = smem_u32(smemB + rb.idx * b_stage_bytes);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            umma_f16(tmem_base, desc_kmajor_sw128(h_addr + ks * 32, 1024),
-                     desc_kmajor_sw128(b_addr + ks * 32, 1024), idesc_c,
-                     (cm > 0 || ks > 0) ? 1u : 0u);
-          }
-          umma_commit(&bars->a_empty[sa]);
-          umma_commit(&bars->b_empty[sb]);
-          if (cm == nk - 1) umma_commit(&bars->acc_full);
+        for (int ks = 0; ks < 4; ++ks) {
+          umma_f16(tmem_base, desc_kmajor_sw128(h_addr + ks * 32, 1024),
+                   desc_kmajor_sw128(b_addr + ks * 32, 1024), idesc_c, (cm > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(&bars->a_empty[ra.idx]);
+        umma_commit(&bars->b_empty[rb.idx]);
+        ra.next();
+        rb.next();
+        if (++cm == nk) {
+          cm = 0;
+          umma_commit(&bars->acc_full);
+          acc_phase ^= 1u;
         }
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
-  } else if (warp < kEpiWarp0) {
+  } else if (warp >= kGateWarp0 && warp < kEpiWarp0) {
     // ------------------------------------------------------------------ gate warps
     const int gw = warp - kGateWarp0;
     const int q = warp & 3;          // TMEM lane quarter this warp may access
-    const int half = gw >> 2;        // which 32 of the chunk's 64 columns
+    const uint32_t group = gw >> 2;  // group 0 takes even chunks, group 1 odd chunks
     const uint32_t row = q * 32 + lane;
-    uint32_t it = 0;
+    const uint32_t lane_base = uint32_t(q * 32) << 16;
+    Ring ra(p.sa);
+    if (group == 1) ra.next();
     bool ok = true;
-    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
-      for (int c = 0; c < nk; ++c, ++it) {
-        const int sa = it % p.sa, sbuf = it % kSBufs;
-        if (!mbar_wait(&bars->s_full[sbuf], (it / kSBufs) & 1)) { ok = false; break; }
-        tc_fence_after_sync();
-        uint8_t* tile = smemAR + sa * ar_stage_bytes;
-        uint32_t s[32];
-        tmem_ld_x32(tmem_base + (uint32_t(q * 32) << 16) + kSCol0 + sbuf * 64 + half * 32, s);
-        uint4 av[4];
-        load_a_32cols<GATE>(tile, row, half * 4, av);
-        tmem_ld_wait();
-        gate_h_32cols<DT, GATE>(tile, row, half * 4, s, av);
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(&bars->s_empty[sbuf]);
-          mbar_arrive(&bars->h_full[sa]);
-        }
+    for (uint32_t j = group; j < total; j += 2) {
+      const uint32_t sbuf = j & (kSBufs - 1), sphase = (j / kSBufs) & 1;
+      const int sa = ra.idx;
+      if (!mbar_wait(&bars->s_full[sbuf], sphase)) { ok = false; break; }
+      tc_fence_after_sync();
+      uint8_t* tile = smemAR + sa * ar_stage_bytes;
+#if !(PRISM_DBG & 1)
+      uint32_t s0[32], s1[32];
+      uint4 av[4];
+      tmem_ld_x32(tmem_base + lane_base + kSCol0 + sbuf * 64, s0);
+      load_a_32cols<GATE>(tile, row, 0, av);
+      tmem_ld_wait();
+      tmem_ld_x32(tmem_base + lane_base + kSCol0 + sbuf * 64 + 32, s1);
+      gate_h_32cols<DT, GATE>(tile, row, 0, s0, av);
+      load_a_32cols<GATE>(tile, row, 4, av);
+      tmem_ld_wait();
+      gate_h_32cols<DT, GATE>(tile, row, 4, s1, av);
+#endif
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&bars->s_empty[sbuf]);
+        mbar_arrive(&bars->h_full[sa]);
       }
+      ra.next();
+      ra.next();
     }
     if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
-  } else {
+  } else if (warp >= kEpiWarp0) {
     // ------------------------------------------------------------------ epilogue warps
     const int q = warp & 3;
     const uint32_t row = q * 32 + lane;
-    uint32_t tile_iter = 0;
+    const uint32_t lane_base = uint32_t(q * 32) << 16;
+    uint8_t* stage = smemEpi + (warp - kEpiWarp0) * kEpiStageBytes;
+    const uint16_t* bias = reinterpret_cast<const uint16_t*>(p.bias);
+    uint32_t acc_phase = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, ++tile_iter) {
+    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, acc_phase ^= 1u) {
       int mt, nt;
       tile_coords(p, t, mt, nt);
-      if (!mbar_wait(&bars->acc_full, tile_iter & 1)) { ok = false; break; }
+      if (!mbar_wait(&bars->acc_full, acc_phase)) { ok = false; break; }
       tc_fence_after_sync();
       const long long grow = (long long)mt * 128 + row;
       const int n0 = nt * p.BN;
-      uint16_t* crow = reinterpret_cast<uint16_t*>(p.C) + grow * p.ldc + n0;
-      const uint16_t* bias = reinterpret_cast<const uint16_t*>(p.bias);
-      for (int c0 = 0; c0 < p.BN; c0 += 32) {
-        uint32_t v[32];
-        if (p.BN - c0 >= 32) {
-          tmem_ld_x32(tmem_base + (uint32_t(q * 32) << 16) + c0, v);
-        } else {  // BN is a multiple of 16: a 16-column tail
-          uint32_t v16[16];
-          tmem_ld_x16(tmem_base + (uint32_t(q * 32) << 16) + c0, v16);
+      if (p.tma_store) {
+        // 64 columns at a time: TMEM -> registers -> swizzled staging tile -> TMA store
+        for (int c0 = 0; c0 < p.BN; c0 += 64) {
+          if (lane == 0) tma_store_wait_read<0>();   // the staging tile is free again
+          __syncwarp();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) { v[j] = v16[j]; v[16 + j] = 0; }
+          for (int hh = 0; hh < 2; ++hh) {
+            uint32_t v[32];
+            tmem_ld_x32(tmem_base + lane_base + c0 + hh * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t ow[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float x0 = __uint_as_float(v[j * 8 + e * 2]);
+                float x1 = __uint_as_float(v[j * 8 + e * 2 + 1]);
+                if (bias != nullptr) {
+                  const uint32_t bw = *reinterpret_cast<const uint32_t*>(bias + n0 + c0 + hh * 32 + j * 8 + e * 2);
+                  const float2 b2 = Elem<DT>::unpack(bw);
+                  x0 += b2.x;
+                  x1 += b2.y;
+                }
+                ow[e] = Elem<DT>::pack(x0, x1);
+              }
+              *reinterpret_cast<uint4*>(stage + sw128_offset(lane, hh * 4 + j)) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && !(PRISM_DBG & 2) && mt * 128 + q * 32 < p.M) {
+            tma_store_2d(&tmC, stage, n0 + c0, mt * 128 + q * 32);
+            tma_store_commit();
+          }
         }
-        tmem_ld_wait();
-        const int ncols = min(32, p.BN - c0);
-        if (grow < p.M) {
+      } else {
+        uint16_t* crow = reinterpret_cast<uint16_t*>(p.C) + grow * p.ldc + n0;
+        for (int c0 = 0; c0 < p.BN; c0 += 16) {   // BN is a multiple of 16
+          uint32_t v[16];
+          tmem_ld_x16(tmem_base + lane_base + c0, v);
+          tmem_ld_wait();
+          if (grow < p.M && !(PRISM_DBG & 2)) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (j * 8 < ncols) {
+            for (int j = 0; j < 2; ++j) {
               uint32_t ow[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
@@ -295,13 +355,14 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->acc_empty);
     }
+    if (lane == 0) tma_store_wait_all<0>();   // outstanding stores read shared memory
     if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
   }
 
   // ------------------------------------------------------------------ teardown
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, 512);
+  if (warp == kWarpMma) tmem_dealloc(tmem_base, 512);
 }
 
 // ----------------------------------------------------------------------------
@@ -318,31 +379,39 @@ int launch_fwd(const FwdArgs& a) {
   if (p.PM > p.n_mtiles) p.PM = p.n_mtiles;
   p.n_kchunks = (a.K + 63) / 64;
   p.r_tile_bytes = ((a.E * 128) + 1023) / 1024 * 1024;
+  p.tma_store = (a.BN % 64 == 0) ? 1 : 0;
   p.bias = a.bias; p.C = a.C; p.ldc = a.ldc; p.err = a.err;
 
-  const int budget = 227 * 1024 - 1024 - (int)sizeof(FwdBarriers) - 256;
+  const int budget = 227 * 1024 - 1024 - (int)sizeof(FwdBarriers) - 256 - fwd::kNumEpiWarps * fwd::kEpiStageBytes;
   const int ar_bytes = fwd::kATileBytes + p.r_tile_bytes;
   const int b_bytes = a.BN * 128;
-  // AR ring runs kLag chunks ahead of the B ring: give it the deeper pipeline.
-  int sb = 3, sa = 6;
-  if (a.sa > 0) sa = a.sa;
-  if (a.sb > 0) sb = a.sb;
+  // the AR ring feeds rotation + gate, which run ahead of the dense product: give it the deeper pipeline
+  int sb = a.sb > 0 ? a.sb : 3;
+  int sa = a.sa > 0 ? a.sa : 6;
+  if (sa > fwd::kMaxStages) sa = fwd::kMaxStages;
+  if (sb > fwd::kMaxStages) sb = fwd::kMaxStages;
   while (sa * ar_bytes + sb * b_bytes > budget && sa > 4) --sa;
   while (sa * ar_bytes + sb * b_bytes > budget && sb > 2) --sb;
   if (sa * ar_bytes + sb * b_bytes > budget)
     return fail(PRISM_ERR_UNSUPPORTED, "forward tile does not fit shared memory (BN=%d E=%d)", a.BN, a.E);
-  // spend what is left on B stages, then AR stages
-  while (sb < fwd::kMaxStages && sa * ar_bytes + (sb + 1) * b_bytes <= budget && sb < 4) ++sb;
-  while (sa < fwd::kMaxStages && (sa + 1) * ar_bytes + sb * b_bytes <= budget) ++sa;
-  while (sb < fwd::kMaxStages && sa * ar_bytes + (sb + 1) * b_bytes <= budget) ++sb;
+  if (a.sa <= 0 && a.sb <= 0) {  // spend what is left
+    while (sb < 4 && sa * ar_bytes + (sb + 1) * b_bytes <= budget) ++sb;
+    while (sa < fwd::kMaxStages && (sa + 1) * ar_bytes + sb * b_bytes <= budget) ++sa;
+    while (sb < fwd::kMaxStages && sa * ar_bytes + (sb + 1) * b_bytes <= budget) ++sb;
+  }
+  if (sa < sb) sa = sb;  // the producer assumes the AR ring is at least as deep as the B ring
+  if (sa * ar_bytes + sb * b_bytes > budget) sb = sa = (budget / (ar_bytes + b_bytes));
+  if (sa < 2) return fail(PRISM_ERR_UNSUPPORTED, "forward tile does not fit shared memory (BN=%d E=%d)", a.BN, a.E);
   p.sa = sa; p.sb = sb;
-  const int smem_bytes = sa * ar_bytes + sb * b_bytes + (int)sizeof(FwdBarriers) + 1024;
+  const int smem_bytes = sa * ar_bytes + sb * b_bytes + fwd::kNumEpiWarps * fwd::kEpiStageBytes +
+                         (int)sizeof(FwdBarriers) + 1024;
 
-  CUtensorMap tmA, tmR, tmB;
+  CUtensorMap tmA, tmR, tmB, tmC;
   int rc;
   if ((rc = make_tmap_2d(&tmA, a.dtype, a.A, a.M, a.K, a.lda, 128, 64, true))) return rc;
   if ((rc = make_tmap_2d(&tmR, a.dtype, a.R_eff, (uint64_t)(a.N / a.gs) * a.E, a.K, a.ldr, a.E, 64, true))) return rc;
   if ((rc = make_tmap_2d(&tmB, a.dtype, a.B, a.N, a.K, a.ldb, a.BN, 64, true))) return rc;
+  if ((rc = make_tmap_2d(&tmC, a.dtype, a.C, a.M, a.N, a.ldc, 32, 64, true))) return rc;
 
   int grid = a.num_sms;
   if (grid > p.n_tiles) grid = p.n_tiles;
@@ -352,7 +421,7 @@ int launch_fwd(const FwdArgs& a) {
                   : (a.gate == GATE_SILU ? prism_fwd_kernel<DT_F16, GATE_SILU> : prism_fwd_kernel<DT_F16, GATE_NONE>);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return fail(PRISM_ERR_CUDA, "forward: cannot set %d B of shared memory: %s", smem_bytes, cudaGetErrorString(e));
-  kern<<<grid, fwd::kThreads, smem_bytes, a.stream>>>(tmA, tmR, tmB, p);
+  kern<<<grid, fwd::kThreads, smem_bytes, a.stream>>>(tmA, tmR, tmB, tmC, p);
   return check_launch("prism_fwd");
 }
 
