@@ -10,9 +10,9 @@
 // tensor-core operands are "MN-major": H tiles [128 tokens x 64 features] and dC tiles
 // [128 tokens x 64 outputs] are used exactly as TMA / the gate warps lay them out, no transposes.
 //   TMA warp   : R_g tiles once; per token block two A tiles and ceil(BN/64) dC tiles
-//   MMA warp   : rotation S = A_blk . R_blk^T (M128 N=E K=16) into a 2-deep TMEM ring, then
-//                D += H^T . dC as 8 x tcgen05.mma M128 N=BN K=16 per token block
-//   gate warps : H = A*silu(S) written over A in place
+//   rot issuer : rotation S = A_blk . R_blk^T (M128 N=E K=16) into a 2-deep TMEM ring
+//   gate warps : two groups taking alternate token blocks; H = A*silu(S) written over A in place
+//   MMA issuer : D += H^T . dC as 8 x tcgen05.mma M128 N=BN K=16 per token block
 //   epilogue   : D -> dB (transposed store), or fp32 partials when the token range is split;
 //                a second kernel then adds the partials in a fixed order (deterministic).
 #include "prism_host.cuh"
@@ -21,10 +21,11 @@
 namespace prism {
 
 namespace db {
-constexpr int kThreads = 448;
-constexpr int kGateWarp0 = 2;
-constexpr int kNumGateWarps = 8;
-constexpr int kEpiWarp0 = 10;
+constexpr int kThreads = 512;     // warp 0 TMA, 1 dense issuer, 2 rotation issuer, 4-11 gate, 12-15 epilogue
+constexpr int kWarpTma = 0, kWarpMma = 1, kWarpRot = 2;
+constexpr int kGateWarp0 = 4;
+constexpr int kNumGateWarps = 8;  // two groups of four that take alternate token blocks
+constexpr int kEpiWarp0 = 12;
 constexpr int kSBufs = 2;      // TMEM ring of S buffers, 128 columns each
 constexpr int kSCol0 = 256;
 constexpr int kMaxStages = 4;
@@ -88,23 +89,23 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     mbar_init(&bars->r_full, 1);
     for (int i = 0; i < kMaxStages; ++i) {
       mbar_init(&bars->a_full[i], 1);
-      mbar_init(&bars->h_full[i], kNumGateWarps);
+      mbar_init(&bars->h_full[i], kNumGateWarps / 2);
       mbar_init(&bars->a_empty[i], 1);
       mbar_init(&bars->dc_full[i], 1);
       mbar_init(&bars->dc_empty[i], 1);
     }
     for (int i = 0; i < kSBufs; ++i) {
       mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->s_empty[i], kNumGateWarps);
+      mbar_init(&bars->s_empty[i], kNumGateWarps / 2);
     }
     mbar_init(&bars->acc_full, 1);
     fence_mbar_init();
   }
-  if (warp == 1) {
+  if (warp == kWarpMma) {
     tmem_alloc(&bars->tmem_base, 512);
     tmem_relinquish();
   }
-  if (warp == 0 && lane == 0) {
+  if (warp == kWarpTma && lane == 0) {
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmR);
     prefetch_tmap(&tmdC);
@@ -114,7 +115,7 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
 
-  if (warp == 0) {
+  if (warp == kWarpTma) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       bool ok = true;
@@ -138,81 +139,87 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == kWarpRot) {
+    // ------------------------------------------------------------------ rotation issuer
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(DT, 128, p.E, 0, 0);
-      const uint32_t idesc_d = make_idesc(DT, 128, p.BN, 1, 1);
       const int blocks_per_chunk = 64 / p.E;
       const int ksteps_per_block = p.E / 16;
       bool ok = mbar_wait(&bars->r_full, 0);
       const uint32_t r_addr = smem_u32(smemR);
-      Ring rs_a(p.sa), rm_a(p.sa), rm_d(p.sd);
-      for (int j = 0; j < nb + 1 && ok; ++j) {
-        if (j < nb) {
-          const int sa = rs_a.idx, sbuf = j & (kSBufs - 1);
-          if (!mbar_wait(&bars->a_full[sa], rs_a.phase)) { ok = false; break; }
-          if (!mbar_wait(&bars->s_empty[sbuf], ((j / kSBufs) & 1) ^ 1)) { ok = false; break; }
-          rs_a.next();
-          tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(smemA + sa * a_stage_bytes);
-          for (int i = 0; i < 2; ++i) {
-            for (int b = 0; b < blocks_per_chunk; ++b) {
-              for (int ks = 0; ks < ksteps_per_block; ++ks) {
-                const uint32_t koff = (b * p.E + ks * 16) * 2;
-                umma_f16(tmem_base + kSCol0 + sbuf * 128 + i * 64 + b * p.E,
-                         desc_kmajor_sw128(a_addr + i * kTile + koff, 1024),
-                         desc_kmajor_sw128(r_addr + i * p.r_tile_bytes + koff, 1024), idesc_s,
-                         ks > 0 ? 1u : 0u);
-              }
+      Ring ra(p.sa);
+      for (int j = 0; j < nb && ok; ++j, ra.next()) {
+        const int sbuf = j & (kSBufs - 1);
+        if (!mbar_wait(&bars->a_full[ra.idx], ra.phase)) { ok = false; break; }
+        if (!mbar_wait(&bars->s_empty[sbuf], ((j / kSBufs) & 1) ^ 1)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_u32(smemA + ra.idx * a_stage_bytes);
+        for (int i = 0; i < 2; ++i) {
+          for (int b = 0; b < blocks_per_chunk; ++b) {
+            for (int ks = 0; ks < ksteps_per_block; ++ks) {
+              const uint32_t koff = (b * p.E + ks * 16) * 2;
+              umma_f16(tmem_base + kSCol0 + sbuf * 128 + i * 64 + b * p.E,
+                       desc_kmajor_sw128(a_addr + i * kTile + koff, 1024),
+                       desc_kmajor_sw128(r_addr + i * p.r_tile_bytes + koff, 1024), idesc_s,
+                       ks > 0 ? 1u : 0u);
             }
           }
-          umma_commit(&bars->s_full[sbuf]);
         }
-        if (j >= 1) {
-          const int jm = j - 1;
-          const int sa = rm_a.idx, sd = rm_d.idx;
-          if (!mbar_wait(&bars->h_full[sa], rm_a.phase)) { ok = false; break; }
-          if (!mbar_wait(&bars->dc_full[sd], rm_d.phase)) { ok = false; break; }
-          rm_a.next();
-          rm_d.next();
-          tc_fence_after_sync();
-          const uint32_t h_addr = smem_u32(smemA + sa * a_stage_bytes);
-          const uint32_t d_addr = smem_u32(smemD + sd * dc_stage_bytes);
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            umma_f16(tmem_base, desc_mnmajor_sw128(h_addr + ks * 2048, kTile, 1024),
-                     desc_mnmajor_sw128(d_addr + ks * 2048, kTile, 1024), idesc_d,
-                     (jm > 0 || ks > 0) ? 1u : 0u);
-          }
-          umma_commit(&bars->a_empty[sa]);
-          umma_commit(&bars->dc_empty[sd]);
-          if (jm == nb - 1) umma_commit(&bars->acc_full);
-        }
+        umma_commit(&bars->s_full[sbuf]);
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
-  } else if (warp < kEpiWarp0) {
+  } else if (warp == kWarpMma) {
+    // ------------------------------------------------------------------ dense issuer
+    if (lane == 0) {
+      const uint32_t idesc_d = make_idesc(DT, 128, p.BN, 1, 1);
+      bool ok = true;
+      Ring ra(p.sa), rd(p.sd);
+      for (int j = 0; j < nb && ok; ++j, ra.next(), rd.next()) {
+        if (!mbar_wait(&bars->h_full[ra.idx], ra.phase)) { ok = false; break; }
+        if (!mbar_wait(&bars->dc_full[rd.idx], rd.phase)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t h_addr = smem_u32(smemA + ra.idx * a_stage_bytes);
+        const uint32_t d_addr = smem_u32(smemD + rd.idx * dc_stage_bytes);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          umma_f16(tmem_base, desc_mnmajor_sw128(h_addr + ks * 2048, kTile, 1024),
+                   desc_mnmajor_sw128(d_addr + ks * 2048, kTile, 1024), idesc_d,
+                   (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(&bars->a_empty[ra.idx]);
+        umma_commit(&bars->dc_empty[rd.idx]);
+        if (j == nb - 1) umma_commit(&bars->acc_full);
+      }
+      if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
+    }
+  } else if (warp >= kGateWarp0 && warp < kEpiWarp0) {
     // ------------------------------------------------------------------ gate warps
     const int gw = warp - kGateWarp0;
     const int q = warp & 3;
-    const int chunk = gw >> 2;     // which of the two 64-feature tiles
+    const int group = gw >> 2;     // group 0 takes even token blocks, group 1 odd ones
     const uint32_t row = q * 32 + lane;
+    const uint32_t lane_base = uint32_t(q * 32) << 16;
     bool ok = true;
     Ring ra(p.sa);
-    for (int j = 0; j < nb; ++j, ra.next()) {
+    if (group == 1) ra.next();
+    for (int j = group; j < nb; j += 2) {
       const int sa = ra.idx, sbuf = j & (kSBufs - 1);
       if (!mbar_wait(&bars->s_full[sbuf], (j / kSBufs) & 1)) { ok = false; break; }
       tc_fence_after_sync();
-      uint8_t* tile = smemA + sa * a_stage_bytes + chunk * kTile;
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        uint32_t s[32];
-        tmem_ld_x32(tmem_base + (uint32_t(q * 32) << 16) + kSCol0 + sbuf * 128 + chunk * 64 + hh * 32, s);
+      for (int chunk = 0; chunk < 2; ++chunk) {
+        uint8_t* tile = smemA + sa * a_stage_bytes + chunk * kTile;
+        uint32_t s0[32], s1[32];
         uint4 av[4];
-        load_a_32cols<GATE>(tile, row, hh * 4, av);
+        tmem_ld_x32(tmem_base + lane_base + kSCol0 + sbuf * 128 + chunk * 64, s0);
+        load_a_32cols<GATE>(tile, row, 0, av);
         tmem_ld_wait();
-        gate_h_32cols<DT, GATE>(tile, row, hh * 4, s, av);
+        tmem_ld_x32(tmem_base + lane_base + kSCol0 + sbuf * 128 + chunk * 64 + 32, s1);
+        gate_h_32cols<DT, GATE>(tile, row, 0, s0, av);
+        load_a_32cols<GATE>(tile, row, 4, av);
+        tmem_ld_wait();
+        gate_h_32cols<DT, GATE>(tile, row, 4, s1, av);
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
@@ -221,9 +228,11 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         mbar_arrive(&bars->s_empty[sbuf]);
         mbar_arrive(&bars->h_full[sa]);
       }
+      ra.next();
+      ra.next();
     }
     if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
-  } else {
+  } else if (warp >= kEpiWarp0) {
     // ------------------------------------------------------------------ epilogue warps
     const int q = warp & 3;
     const int f = f0 + q * 32 + lane;  // feature = accumulator row
@@ -256,7 +265,7 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, 512);
+  if (warp == kWarpMma) tmem_dealloc(tmem_base, 512);
 }
 
 // dB[n, k] = cast( sum_s partial[s][n][k] ), s in increasing order.
