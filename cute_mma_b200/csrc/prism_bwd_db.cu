@@ -10,8 +10,8 @@
 // tensor-core operands are "MN-major": H tiles [128 tokens x 64 features] and dC tiles
 // [128 tokens x 64 outputs] are used exactly as TMA / the gate warps lay them out, no transposes.
 //   TMA warp   : R_g tiles once; per token block two A tiles and ceil(BN/64) dC tiles
-//   rot issuer : rotation S = A_blk . R_blk^T (M128 N=E K=16) into a 2-deep TMEM ring
-//   gate warps : two groups taking alternate token blocks; H = A*silu(S) written over A in place
+//   gate warps : 16 token rows each; block rotation S = A_blk . R_blk^T by mma.sync on ldmatrix
+//                fragments, H = A*silu(S) on registers, stmatrix of H over the A tiles in place
 //   MMA issuer : D += H^T . dC as 8 x tcgen05.mma M128 N=BN K=16 per token block
 //   epilogue   : D -> dB (transposed store), or fp32 partials when the token range is split;
 //                a second kernel then adds the partials in a fixed order (deterministic).
@@ -21,13 +21,11 @@
 namespace prism {
 
 namespace db {
-constexpr int kThreads = 512;     // warp 0 TMA, 1 dense issuer, 2 rotation issuer, 4-11 gate, 12-15 epilogue
-constexpr int kWarpTma = 0, kWarpMma = 1, kWarpRot = 2;
-constexpr int kGateWarp0 = 4;
-constexpr int kNumGateWarps = 8;  // two groups of four that take alternate token blocks
-constexpr int kEpiWarp0 = 12;
-constexpr int kSBufs = 2;      // TMEM ring of S buffers, 128 columns each
-constexpr int kSCol0 = 256;
+constexpr int kThreads = 448;     // warp 0 TMA, 1 dense issuer, 2-9 gate (16 rows each), 10-13 epilogue
+constexpr int kWarpTma = 0, kWarpMma = 1;
+constexpr int kGateWarp0 = 2;
+constexpr int kNumGateWarps = 8;
+constexpr int kEpiWarp0 = 10;
 constexpr int kMaxStages = 4;
 constexpr int kTile = 128 * 128;  // bytes of a [128 x 64] 16-bit tile
 }  // namespace db
@@ -54,13 +52,11 @@ struct DbBarriers {
   uint64_t a_empty[db::kMaxStages];
   uint64_t dc_full[db::kMaxStages];
   uint64_t dc_empty[db::kMaxStages];
-  uint64_t s_full[db::kSBufs];
-  uint64_t s_empty[db::kSBufs];
   uint64_t acc_full;
   uint32_t tmem_base;
 };
 
-template <int DT, int GATE>
+template <int DT, int GATE, int E>
 __global__ void __launch_bounds__(db::kThreads, 1)
 prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmR,
                     const __grid_constant__ CUtensorMap tmdC, const DbParams p) {
@@ -89,14 +85,10 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     mbar_init(&bars->r_full, 1);
     for (int i = 0; i < kMaxStages; ++i) {
       mbar_init(&bars->a_full[i], 1);
-      mbar_init(&bars->h_full[i], kNumGateWarps / 2);
+      mbar_init(&bars->h_full[i], kNumGateWarps);
       mbar_init(&bars->a_empty[i], 1);
       mbar_init(&bars->dc_full[i], 1);
       mbar_init(&bars->dc_empty[i], 1);
-    }
-    for (int i = 0; i < kSBufs; ++i) {
-      mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->s_empty[i], kNumGateWarps / 2);
     }
     mbar_init(&bars->acc_full, 1);
     fence_mbar_init();
@@ -139,36 +131,6 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
-  } else if (warp == kWarpRot) {
-    // ------------------------------------------------------------------ rotation issuer
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc(DT, 128, p.E, 0, 0);
-      const int blocks_per_chunk = 64 / p.E;
-      const int ksteps_per_block = p.E / 16;
-      bool ok = mbar_wait(&bars->r_full, 0);
-      const uint32_t r_addr = smem_u32(smemR);
-      Ring ra(p.sa);
-      for (int j = 0; j < nb && ok; ++j, ra.next()) {
-        const int sbuf = j & (kSBufs - 1);
-        if (!mbar_wait(&bars->a_full[ra.idx], ra.phase)) { ok = false; break; }
-        if (!mbar_wait(&bars->s_empty[sbuf], ((j / kSBufs) & 1) ^ 1)) { ok = false; break; }
-        tc_fence_after_sync();
-        const uint32_t a_addr = smem_u32(smemA + ra.idx * a_stage_bytes);
-        for (int i = 0; i < 2; ++i) {
-          for (int b = 0; b < blocks_per_chunk; ++b) {
-            for (int ks = 0; ks < ksteps_per_block; ++ks) {
-              const uint32_t koff = (b * p.E + ks * 16) * 2;
-              umma_f16(tmem_base + kSCol0 + sbuf * 128 + i * 64 + b * p.E,
-                       desc_kmajor_sw128(a_addr + i * kTile + koff, 1024),
-                       desc_kmajor_sw128(r_addr + i * p.r_tile_bytes + koff, 1024), idesc_s,
-                       ks > 0 ? 1u : 0u);
-            }
-          }
-        }
-        umma_commit(&bars->s_full[sbuf]);
-      }
-      if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
-    }
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ dense issuer
     if (lane == 0) {
@@ -195,41 +157,18 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else if (warp >= kGateWarp0 && warp < kEpiWarp0) {
     // ------------------------------------------------------------------ gate warps
-    const int gw = warp - kGateWarp0;
-    const int q = warp & 3;
-    const int group = gw >> 2;     // group 0 takes even token blocks, group 1 odd ones
-    const uint32_t row = q * 32 + lane;
-    const uint32_t lane_base = uint32_t(q * 32) << 16;
-    bool ok = true;
+    const uint32_t r0 = (warp - kGateWarp0) * 16;   // this warp's 16 token rows of the block
+    bool ok = mbar_wait(&bars->r_full, 0);
+    const uint32_t r_addr = smem_u32(smemR);
     Ring ra(p.sa);
-    if (group == 1) ra.next();
-    for (int j = group; j < nb; j += 2) {
-      const int sa = ra.idx, sbuf = j & (kSBufs - 1);
-      if (!mbar_wait(&bars->s_full[sbuf], (j / kSBufs) & 1)) { ok = false; break; }
-      tc_fence_after_sync();
-#pragma unroll
-      for (int chunk = 0; chunk < 2; ++chunk) {
-        uint8_t* tile = smemA + sa * a_stage_bytes + chunk * kTile;
-        uint32_t s0[32], s1[32];
-        uint4 av[4];
-        tmem_ld_x32(tmem_base + lane_base + kSCol0 + sbuf * 128 + chunk * 64, s0);
-        load_a_32cols<GATE>(tile, row, 0, av);
-        tmem_ld_wait();
-        tmem_ld_x32(tmem_base + lane_base + kSCol0 + sbuf * 128 + chunk * 64 + 32, s1);
-        gate_h_32cols<DT, GATE>(tile, row, 0, s0, av);
-        load_a_32cols<GATE>(tile, row, 4, av);
-        tmem_ld_wait();
-        gate_h_32cols<DT, GATE>(tile, row, 4, s1, av);
-      }
+    for (int j = 0; j < nb && ok; ++j, ra.next()) {
+      if (!mbar_wait(&bars->a_full[ra.idx], ra.phase)) { ok = false; break; }
+      const uint32_t tile = smem_u32(smemA + ra.idx * a_stage_bytes);
+      rotate_gate_rows16<DT, GATE, E>(tile, r_addr, r0, lane);
+      rotate_gate_rows16<DT, GATE, E>(tile + kTile, r_addr + p.r_tile_bytes, r0, lane);
       fence_proxy_async_smem();
-      tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&bars->s_empty[sbuf]);
-        mbar_arrive(&bars->h_full[sa]);
-      }
-      ra.next();
-      ra.next();
+      if (lane == 0) mbar_arrive(&bars->h_full[ra.idx]);
     }
     if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
   } else if (warp >= kEpiWarp0) {
@@ -332,9 +271,14 @@ int launch_bwd_db(const DbArgs& a) {
   if ((rc = make_tmap_2d(&tmR, a.dtype, a.R_eff, (uint64_t)(a.N / a.gs) * a.E, a.K, a.ldr, a.E, 64, true))) return rc;
   if ((rc = make_tmap_2d(&tmdC, a.dtype, a.dC, a.M, a.N, a.lddc, 128, 64, true))) return rc;
 
-  auto kern = (a.dtype == DT_BF16)
-                  ? (a.gate == GATE_SILU ? prism_bwd_db_kernel<DT_BF16, GATE_SILU> : prism_bwd_db_kernel<DT_BF16, GATE_NONE>)
-                  : (a.gate == GATE_SILU ? prism_bwd_db_kernel<DT_F16, GATE_SILU> : prism_bwd_db_kernel<DT_F16, GATE_NONE>);
+  using KernT = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, DbParams);
+  KernT kern = nullptr;
+#define PRISM_PICK(E_)                                                                               \
+  kern = (a.dtype == DT_BF16)                                                                        \
+             ? (a.gate == GATE_SILU ? (KernT)prism_bwd_db_kernel<DT_BF16, GATE_SILU, E_> : (KernT)prism_bwd_db_kernel<DT_BF16, GATE_NONE, E_>) \
+             : (a.gate == GATE_SILU ? (KernT)prism_bwd_db_kernel<DT_F16, GATE_SILU, E_> : (KernT)prism_bwd_db_kernel<DT_F16, GATE_NONE, E_>)
+  if (a.E == 16) { PRISM_PICK(16); } else if (a.E == 32) { PRISM_PICK(32); } else { PRISM_PICK(64); }
+#undef PRISM_PICK
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return fail(PRISM_ERR_CUDA, "bwd_db: cannot set %d B of shared memory: %s", smem_bytes, cudaGetErrorString(e));
   dim3 grid((a.K + 127) / 128, a.N / a.BN, p.splits);

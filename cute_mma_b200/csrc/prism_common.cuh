@@ -425,4 +425,97 @@ __device__ __forceinline__ void load_a_32cols(const uint8_t* tile, uint32_t row,
   }
 }
 
+// ----------------------------------------------------------------------------
+// Warp-level matrix fragments (ldmatrix / stmatrix / mma.sync m16n8k16).
+// The block rotation S = A_blk . R_blk^T runs here, on the legacy warp MMA path: measured on
+// B200 it sustains ~1000 FMA/clk/SM next to a saturated tcgen05 pipe and slows that pipe by
+// less than 10 %, whereas a 16-wide tcgen05.mma occupies the pipe for the ~46 clocks that
+// fetching its 128x16 A operand from shared memory takes, whatever its N.
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ void ldmatrix_x4(uint32_t saddr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(saddr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t saddr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(saddr));
+}
+__device__ __forceinline__ void stmatrix_x4(uint32_t saddr, const uint32_t (&r)[4]) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(saddr),
+               "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3])
+               : "memory");
+}
+template <int DT>
+__device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                             uint32_t b1) {
+  if (DT == DT_BF16) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+        "{%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  } else {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+        "{%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+}
+
+// H for one pair of elements from fp32 S and packed 16-bit A: A*silu(S), or S in plain mode.
+template <int DT, int GATE>
+__device__ __forceinline__ uint32_t gate_pair(uint32_t a2, float s0, float s1) {
+#if PRISM_GATE_PACKED
+  if (GATE == GATE_SILU) return Pk<DT>::mul(a2, silu_pair<DT>(s0, s1));
+  return Pk<DT>::cvt(s0, s1);
+#else
+  if (GATE == GATE_SILU) {
+    const float2 a = Elem<DT>::unpack(a2);
+    return Elem<DT>::pack(a.x * (s0 * sigmoid_fast(s0)), a.y * (s1 * sigmoid_fast(s1)));
+  }
+  return Elem<DT>::pack(s0, s1);
+#endif
+}
+
+// One warp turns its 16 rows of a [rows x 64] swizzled A tile into H in place.
+//   tile   : shared-memory address of the A tile (1024-byte aligned), r0 = first of the warp's 16 rows
+//   rtile  : shared-memory address of the R_g tile [E x 64] of the same 64 columns
+// Per rotation block: A fragments by ldmatrix, S by mma.sync against R fragments; an A fragment
+// and the S accumulators of the same 16 columns hold the same (row, column) elements in the same
+// lanes, so the gate is elementwise on registers and H goes back with stmatrix to where A came from.
+template <int DT, int GATE, int E>
+__device__ __forceinline__ void rotate_gate_rows16(uint32_t tile, uint32_t rtile, uint32_t r0, int lane) {
+  constexpr int KS = E / 16;           // 16-wide k-steps (= 16-column output pairs) per block
+  const uint32_t mat = lane >> 3, l8 = lane & 7;
+  const uint32_t a_row = r0 + l8 + (mat & 1) * 8;   // A operand: matrices (r-lo,k-lo) (r-hi,k-lo) (r-lo,k-hi) (r-hi,k-hi)
+  const uint32_t r_row = l8 + (mat >> 1) * 8;       // B operand: matrices (n-lo,k-lo) (n-lo,k-hi) (n-hi,k-lo) (n-hi,k-hi)
+#pragma unroll
+  for (int b = 0; b < 64 / E; ++b) {
+    uint32_t af[KS][4];
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+      ldmatrix_x4(tile + sw128_offset(a_row, b * (E / 8) + ks * 2 + (mat >> 1)), af[ks]);
+#pragma unroll
+    for (int np = 0; np < KS; ++np) {
+      float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        uint32_t rf[4];
+        ldmatrix_x4(rtile + sw128_offset(np * 16 + r_row, b * (E / 8) + ks * 2 + (mat & 1)), rf);
+        mma_m16n8k16<DT>(c0, af[ks], rf[0], rf[1]);
+        mma_m16n8k16<DT>(c1, af[ks], rf[2], rf[3]);
+      }
+      uint32_t h[4];
+      h[0] = gate_pair<DT, GATE>(af[np][0], c0[0], c0[1]);
+      h[1] = gate_pair<DT, GATE>(af[np][1], c0[2], c0[3]);
+      h[2] = gate_pair<DT, GATE>(af[np][2], c1[0], c1[1]);
+      h[3] = gate_pair<DT, GATE>(af[np][3], c1[2], c1[3]);
+      stmatrix_x4(tile + sw128_offset(a_row, b * (E / 8) + np * 2 + (mat >> 1)), h);
+    }
+  }
+}
+
 }  // namespace prism

@@ -9,12 +9,12 @@
 // Per CTA: a persistent loop over (128-row, BN-column) output tiles; per 64-wide K chunk
 //   warp 0      TMA producer: A tile [128 x 64] + R_g tile [E x 64] into the "AR" ring, B_g tile
 //               [BN x 64] into the "B" ring (128-byte swizzle, zero fill outside the tensors)
-//   warp 2      rotation issuer: S = A_blk . R_blk^T as tcgen05.mma M128 N=E K=16 per block into
-//               a ring of four 64-column TMEM buffers
-//   warps 4-11  gate warps, two groups of four that take alternate chunks: tcgen05.ld S, read A
-//               from shared memory, H = A*silu(S) (or H = S) written over the A tile in place
-//   warp 1      dense issuer: C += H . B^T as 4 x tcgen05.mma M128 N=BN K=16, fp32 in TMEM
-//   warps 12-15 epilogue: tcgen05.ld C, + bias, cast, swizzled staging tile, TMA store.
+//   warps 2-17  gate warps, two groups of eight that take alternate chunks, 16 rows per warp: A and R fragments by ldmatrix, block rotation
+//               S = A_blk . R_blk^T by mma.sync (fp32), H = A*silu(S) (or H = S) on registers,
+//               stmatrix of H over the A tile in place
+//   warp 1      dense issuer: C += H . B^T as 4 x tcgen05.mma M128 N=BN K=16, fp32 in TMEM,
+//               two accumulators so that the epilogue of a tile overlaps the next tile
+//   warps 18-21 epilogue: tcgen05.ld C, + bias, cast, swizzled staging tile, TMA store.
 // Every role keeps its ring positions as counters; the single-thread roles do no division.
 #include "prism_host.cuh"
 #include "prism_kernels.cuh"
@@ -26,14 +26,14 @@
 namespace prism {
 
 namespace fwd {
-constexpr int kThreads = 512;
-constexpr int kWarpTma = 0, kWarpMma = 1, kWarpRot = 2;
-constexpr int kGateWarp0 = 4;
-constexpr int kNumGateWarps = 8;      // two groups of four
-constexpr int kEpiWarp0 = 12;
+constexpr int kThreads = 704;
+constexpr int kWarpTma = 0, kWarpMma = 1;
+constexpr int kGateWarp0 = 2;
+constexpr int kGateGroups = 2;        // groups take alternate chunks ...
+constexpr int kWarpsPerGroup = 8;     // ... with 16 rows per warp
+constexpr int kNumGateWarps = kGateGroups * kWarpsPerGroup;
+constexpr int kEpiWarp0 = kGateWarp0 + kNumGateWarps;   // 18: (warp & 3) of warps 18..21 covers 2,3,0,1
 constexpr int kNumEpiWarps = 4;
-constexpr int kSBufs = 4;             // TMEM ring of S buffers, 64 columns each (power of two)
-constexpr int kSCol0 = 256;           // S ring lives in TMEM columns [256, 512)
 constexpr int kMaxStages = 8;
 constexpr int kATileBytes = 128 * 128;   // [128 rows x 64 elems] 16-bit
 constexpr int kEpiStageBytes = 32 * 128; // per epilogue warp: [32 rows x 64 elems]
@@ -61,10 +61,8 @@ struct FwdBarriers {
   uint64_t a_empty[fwd::kMaxStages];
   uint64_t b_full[fwd::kMaxStages];
   uint64_t b_empty[fwd::kMaxStages];
-  uint64_t s_full[fwd::kSBufs];
-  uint64_t s_empty[fwd::kSBufs];
-  uint64_t acc_full;
-  uint64_t acc_empty;
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
   uint32_t tmem_base;
 };
 
@@ -78,7 +76,7 @@ __device__ __forceinline__ void tile_coords(const FwdParams& p, int t, int& mt, 
   mt = m0 + (rem - nt * pm);
 }
 
-template <int DT, int GATE>
+template <int DT, int GATE, int E>
 __global__ void __launch_bounds__(fwd::kThreads, 1)
 prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmR,
                  const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
@@ -100,17 +98,15 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int i = 0; i < kMaxStages; ++i) {
       mbar_init(&bars->ar_full[i], 1);
-      mbar_init(&bars->h_full[i], kNumGateWarps / 2);
+      mbar_init(&bars->h_full[i], kWarpsPerGroup);
       mbar_init(&bars->a_empty[i], 1);
       mbar_init(&bars->b_full[i], 1);
       mbar_init(&bars->b_empty[i], 1);
     }
-    for (int i = 0; i < kSBufs; ++i) {
-      mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->s_empty[i], kNumGateWarps / 2);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->acc_full[i], 1);
+      mbar_init(&bars->acc_empty[i], kNumEpiWarps);
     }
-    mbar_init(&bars->acc_full, 1);
-    mbar_init(&bars->acc_empty, kNumEpiWarps);
     fence_mbar_init();
   }
   if (warp == kWarpMma) {
@@ -172,54 +168,26 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
-  } else if (warp == kWarpRot) {
-    // ------------------------------------------------------------------ rotation issuer
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc(DT, 128, p.E, 0, 0);
-      const int blocks_per_chunk = 64 / p.E;
-      const int ksteps_per_block = p.E / 16;
-      Ring ra(p.sa);
-      bool ok = true;
-      for (uint32_t j = 0; j < total; ++j) {
-        const uint32_t sbuf = j & (kSBufs - 1), sphase = (j / kSBufs) & 1;
-        if (!mbar_wait(&bars->ar_full[ra.idx], ra.phase)) { ok = false; break; }
-        if (!mbar_wait(&bars->s_empty[sbuf], sphase ^ 1)) { ok = false; break; }
-        tc_fence_after_sync();
-        const uint32_t a_addr = smem_u32(smemAR + ra.idx * ar_stage_bytes);
-        const uint32_t r_addr = a_addr + kATileBytes;
-        for (int b = 0; b < blocks_per_chunk; ++b) {
-          for (int ks = 0; ks < ksteps_per_block; ++ks) {
-            if (PRISM_DBG & 4) break;
-            const uint32_t koff = (b * p.E + ks * 16) * 2;
-            umma_f16(tmem_base + kSCol0 + sbuf * 64 + b * p.E, desc_kmajor_sw128(a_addr + koff, 1024),
-                     desc_kmajor_sw128(r_addr + koff, 1024), idesc_s, ks > 0 ? 1u : 0u);
-          }
-        }
-        umma_commit(&bars->s_full[sbuf]);
-        ra.next();
-      }
-      if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
-    }
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ dense issuer
     if (lane == 0) {
       const uint32_t idesc_c = make_idesc(DT, 128, p.BN, 0, 0);
       Ring ra(p.sa), rb(p.sb);
       int cm = 0;
-      uint32_t acc_phase = 0;
+      uint32_t acc = 0, acc_phase = 0;   // accumulator buffer (TMEM columns acc*256) and its phase
       bool ok = true;
       for (uint32_t j = 0; j < total; ++j) {
         if (!mbar_wait(&bars->h_full[ra.idx], ra.phase)) { ok = false; break; }
         if (!mbar_wait(&bars->b_full[rb.idx], rb.phase)) { ok = false; break; }
         if (cm == 0) {
-          if (!mbar_wait(&bars->acc_empty, acc_phase ^ 1)) { ok = false; break; }
+          if (!mbar_wait(&bars->acc_empty[acc], acc_phase ^ 1)) { ok = false; break; }
         }
         tc_fence_after_sync();
         const uint32_t h_addr = smem_u32(smemAR + ra.idx * ar_stage_bytes);
         const uint32_t b_addr = smem_u32(smemB + rb.idx * b_stage_bytes);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-          umma_f16(tmem_base, desc_kmajor_sw128(h_addr + ks * 32, 1024),
+          umma_f16(tmem_base + acc * 256, desc_kmajor_sw128(h_addr + ks * 32, 1024),
                    desc_kmajor_sw128(b_addr + ks * 32, 1024), idesc_c, (cm > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(&bars->a_empty[ra.idx]);
@@ -228,49 +196,30 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         rb.next();
         if (++cm == nk) {
           cm = 0;
-          umma_commit(&bars->acc_full);
-          acc_phase ^= 1u;
+          umma_commit(&bars->acc_full[acc]);
+          acc ^= 1u;
+          if (acc == 0) acc_phase ^= 1u;
         }
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
   } else if (warp >= kGateWarp0 && warp < kEpiWarp0) {
     // ------------------------------------------------------------------ gate warps
-    const int gw = warp - kGateWarp0;
-    const int q = warp & 3;          // TMEM lane quarter this warp may access
-    const uint32_t group = gw >> 2;  // group 0 takes even chunks, group 1 odd chunks
-    const uint32_t row = q * 32 + lane;
-    const uint32_t lane_base = uint32_t(q * 32) << 16;
+    const uint32_t gw = warp - kGateWarp0;
+    const uint32_t group = gw / kWarpsPerGroup;               // which chunks (j mod kGateGroups)
+    const uint32_t r0 = (gw % kWarpsPerGroup) * 16;           // this warp's 16 rows of the tile
     Ring ra(p.sa);
-    if (group == 1) ra.next();
+    for (uint32_t i = 0; i < group; ++i) ra.next();
     bool ok = true;
-    for (uint32_t j = group; j < total; j += 2) {
-      const uint32_t sbuf = j & (kSBufs - 1), sphase = (j / kSBufs) & 1;
-      const int sa = ra.idx;
-      if (!mbar_wait(&bars->s_full[sbuf], sphase)) { ok = false; break; }
-      tc_fence_after_sync();
-      uint8_t* tile = smemAR + sa * ar_stage_bytes;
+    for (uint32_t j = group; j < total; j += kGateGroups, ra.next(), ra.next()) {
+      if (!mbar_wait(&bars->ar_full[ra.idx], ra.phase)) { ok = false; break; }
+      const uint32_t tile = smem_u32(smemAR + ra.idx * ar_stage_bytes);
 #if !(PRISM_DBG & 1)
-      uint32_t s0[32], s1[32];
-      uint4 av[4];
-      tmem_ld_x32(tmem_base + lane_base + kSCol0 + sbuf * 64, s0);
-      load_a_32cols<GATE>(tile, row, 0, av);
-      tmem_ld_wait();
-      tmem_ld_x32(tmem_base + lane_base + kSCol0 + sbuf * 64 + 32, s1);
-      gate_h_32cols<DT, GATE>(tile, row, 0, s0, av);
-      load_a_32cols<GATE>(tile, row, 4, av);
-      tmem_ld_wait();
-      gate_h_32cols<DT, GATE>(tile, row, 4, s1, av);
+      rotate_gate_rows16<DT, GATE, E>(tile, tile + kATileBytes, r0, lane);
 #endif
       fence_proxy_async_smem();
-      tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&bars->s_empty[sbuf]);
-        mbar_arrive(&bars->h_full[sa]);
-      }
-      ra.next();
-      ra.next();
+      if (lane == 0) mbar_arrive(&bars->h_full[ra.idx]);
     }
     if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
   } else if (warp >= kEpiWarp0) {
@@ -280,12 +229,13 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t lane_base = uint32_t(q * 32) << 16;
     uint8_t* stage = smemEpi + (warp - kEpiWarp0) * kEpiStageBytes;
     const uint16_t* bias = reinterpret_cast<const uint16_t*>(p.bias);
-    uint32_t acc_phase = 0;
+    uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, acc_phase ^= 1u) {
+    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
       int mt, nt;
       tile_coords(p, t, mt, nt);
-      if (!mbar_wait(&bars->acc_full, acc_phase)) { ok = false; break; }
+      if (!mbar_wait(&bars->acc_full[acc], acc_phase)) { ok = false; break; }
+      const uint32_t tacc = tmem_base + lane_base + acc * 256;
       tc_fence_after_sync();
       const long long grow = (long long)mt * 128 + row;
       const int n0 = nt * p.BN;
@@ -297,7 +247,7 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) {
             uint32_t v[32];
-            tmem_ld_x32(tmem_base + lane_base + c0 + hh * 32, v);
+            tmem_ld_x32(tacc + c0 + hh * 32, v);
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -328,7 +278,7 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         uint16_t* crow = reinterpret_cast<uint16_t*>(p.C) + grow * p.ldc + n0;
         for (int c0 = 0; c0 < p.BN; c0 += 16) {   // BN is a multiple of 16
           uint32_t v[16];
-          tmem_ld_x16(tmem_base + lane_base + c0, v);
+          tmem_ld_x16(tacc + c0, v);
           tmem_ld_wait();
           if (grow < p.M && !(PRISM_DBG & 2)) {
 #pragma unroll
@@ -353,7 +303,9 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->acc_empty);
+      if (lane == 0) mbar_arrive(&bars->acc_empty[acc]);
+      acc ^= 1u;
+      if (acc == 0) acc_phase ^= 1u;
     }
     if (lane == 0) tma_store_wait_all<0>();   // outstanding stores read shared memory
     if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
@@ -416,9 +368,14 @@ int launch_fwd(const FwdArgs& a) {
   int grid = a.num_sms;
   if (grid > p.n_tiles) grid = p.n_tiles;
 
-  auto kern = (a.dtype == DT_BF16)
-                  ? (a.gate == GATE_SILU ? prism_fwd_kernel<DT_BF16, GATE_SILU> : prism_fwd_kernel<DT_BF16, GATE_NONE>)
-                  : (a.gate == GATE_SILU ? prism_fwd_kernel<DT_F16, GATE_SILU> : prism_fwd_kernel<DT_F16, GATE_NONE>);
+  using KernT = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, FwdParams);
+  KernT kern = nullptr;
+#define PRISM_PICK(E_)                                                                               \
+  kern = (a.dtype == DT_BF16)                                                                        \
+             ? (a.gate == GATE_SILU ? (KernT)prism_fwd_kernel<DT_BF16, GATE_SILU, E_> : (KernT)prism_fwd_kernel<DT_BF16, GATE_NONE, E_>) \
+             : (a.gate == GATE_SILU ? (KernT)prism_fwd_kernel<DT_F16, GATE_SILU, E_> : (KernT)prism_fwd_kernel<DT_F16, GATE_NONE, E_>)
+  if (a.E == 16) { PRISM_PICK(16); } else if (a.E == 32) { PRISM_PICK(32); } else { PRISM_PICK(64); }
+#undef PRISM_PICK
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return fail(PRISM_ERR_CUDA, "forward: cannot set %d B of shared memory: %s", smem_bytes, cudaGetErrorString(e));
   kern<<<grid, fwd::kThreads, smem_bytes, a.stream>>>(tmA, tmR, tmB, tmC, p);
