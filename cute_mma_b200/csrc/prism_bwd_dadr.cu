@@ -1,9 +1,9 @@
 // Prism backward, input and rotation gradients, for sm_100a:
-//   dH_g = dC_g . B_g                                   (dense, tcgen05)
-//   S_g  = A . blockdiag(R_g)^T                         (recomputed, tcgen05 M128 N=E K=16)
+//   dH_g = dC_g . B_g                                   (dense, tcgen05, fp32 in TMEM)
+//   S_g  = A . blockdiag(R_g)^T                         (recomputed, mma.sync)
 //   gated:  dS = dH * A * silu'(S),  dA += dH * silu(S) + blockdiag(dS) . R_g
 //   plain:  dS = dH,                 dA += blockdiag(dS) . R_g
-//   dR_g[block b] = dS_b^T . A_b                        (mma.sync on ldmatrix.trans fragments)
+//   dR_g[block b] = dS_b^T . A_b
 // summed over groups g for dA and over tokens for dR.
 //
 // Replaces the reference's bwd_dadr_kernel + dR_reduce_kernel + prism_backward_dA_dR_launch
@@ -13,13 +13,16 @@
 // kernel adds the buffers in a fixed order, so dR is bit-stable from run to run.
 //
 // One CTA works on a [128 tokens x 128 features] tile of dA and walks over all groups:
-//   TMA warp   : A tiles once per tile; per group the R_g tiles and, per 64 outputs, a dC tile
-//                [128 x 64] and two B_g tiles [64 x 64]
-//   MMA warp   : S_g, dH_g (two TMEM buffers), and one group later dA += dS . R_g (TMEM)
-//   gate warps : read S, dH (TMEM) and A (smem); keep sum_g dH*silu(S) in registers; write dS
-//                (16-bit, swizzled) to shared memory; at the end of the tile add the TMEM part
-//                and store dA
-//   dR warps   : ldmatrix.trans of dS and A tiles, mma.sync m16n8k16 over the 128 tokens, then
+//   warp 0       TMA producer: A tiles once per tile; per group the R_g tiles and, per 64 outputs,
+//                a dC tile [128 x 64] and two B_g tiles [64 x 64]
+//   warp 1       dense issuer: dH_g = dC_g . B_g as tcgen05.mma M128 N128 K16 (dC K-major, B_g
+//                MN-major) into a ring of four 128-column TMEM buffers
+//   warps 4-19   gate warps, 16 tokens x 64 features each: dH fragments straight from TMEM
+//                (tcgen05.ld.16x256b delivers the mma.sync accumulator layout), A and R fragments by
+//                ldmatrix, S by mma.sync; dS on registers -> stmatrix to shared memory for the dR
+//                warps and, as the A operand of a second mma.sync, dA += dS . R_g; dA lives in
+//                fp32 accumulator fragments for the whole tile
+//   warps 2,3,20,21  dR warps: ldmatrix.trans of the dS and A tiles, mma.sync over the 128 tokens,
 //                read-modify-write of this CTA's fp32 partial buffer.
 #include "prism_host.cuh"
 #include "prism_kernels.cuh"
@@ -27,16 +30,14 @@
 namespace prism {
 
 namespace dadr {
-constexpr int kThreads = 448;     // warp 0 TMA, warp 1 MMA, warps 2-9 gate, warps 10-13 dR
-constexpr int kGateWarp0 = 2;
-constexpr int kNumGateWarps = 8;
-constexpr int kDrWarp0 = 10;
-constexpr int kNumDrWarps = 4;
-constexpr int kDhCol0 = 0;        // two dH buffers of 128 columns
-constexpr int kSCol0 = 256;       // S buffer, 128 columns
-constexpr int kDaCol0 = 384;      // dA accumulator, 128 columns
-constexpr int kTile = 128 * 128;  // bytes of a [128 x 64] 16-bit tile
-constexpr int kBTile = 64 * 128;  // bytes of a [64 x 64] 16-bit tile
+constexpr int kThreads = 704;
+constexpr int kWarpTma = 0, kWarpMma = 1;
+constexpr int kGateWarp0 = 4;      // multiple of 4: (warp & 3) is the TMEM lane quarter
+constexpr int kNumGateWarps = 16;
+constexpr int kNumDrWarps = 4;     // warps 2, 3, 20, 21
+constexpr int kDhBufs = 4;         // TMEM ring of dH buffers, 128 columns each
+constexpr int kTile = 128 * 128;   // bytes of a [128 x 64] 16-bit tile
+constexpr int kBTile = 64 * 128;   // bytes of a [64 x 64] 16-bit tile
 constexpr int kStageBytes = kTile + 2 * kBTile;
 constexpr int kMaxStages = 4;
 constexpr int kMaxRBufs = 4;
@@ -58,19 +59,56 @@ struct DadrBarriers {
   uint64_t a_full, a_empty;
   uint64_t r_full[dadr::kMaxRBufs], r_empty[dadr::kMaxRBufs];
   uint64_t st_full[dadr::kMaxStages], st_empty[dadr::kMaxStages];
-  uint64_t s_full, s_empty;
-  uint64_t dh_full[2], dh_empty[2];
+  uint64_t dh_full[dadr::kDhBufs], dh_empty[dadr::kDhBufs];
   uint64_t ds_full[2], ds_empty[2];
-  uint64_t da_full, da_empty;
   uint32_t tmem_base;
 };
 
-template <int DT, int GATE>
+// TMEM -> registers in the mma.sync accumulator layout: 16 lanes x 16 columns; thread t gets
+// r[0..1] = (lane t/4, cols 2(t%4)+{0,1}), r[2..3] = (lane t/4+8, same cols), r[4..7] = cols + 8.
+__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+
+__device__ __forceinline__ void dr_accumulate(float* addr, float x, float y, bool first) {
+  if (first) {
+    *reinterpret_cast<float2*>(addr) = make_float2(x, y);
+  } else {
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(x), "f"(y) : "memory");
+  }
+}
+
+template <int DT> struct NegHalf;
+template <> struct NegHalf<DT_F16> { static constexpr uint32_t v = 0xB800B800u; };
+template <> struct NegHalf<DT_BF16> { static constexpr uint32_t v = 0xBF00BF00u; };
+
+// One pair of elements of the gated backward: returns dS (packed) and adds dh*silu(s) to acc0/acc1.
+template <int DT>
+__device__ __forceinline__ uint32_t gate_bwd_pair(uint32_t a2, float s0, float s1, float dh0, float dh1,
+                                                  float& acc0, float& acc1) {
+  const uint32_t hs = Pk<DT>::mul(Pk<DT>::cvt(s0, s1), Pk<DT>::kHalf);
+  const uint32_t t = Pk<DT>::tanh(hs);
+  const uint32_t g = Pk<DT>::fma(hs, t, hs);                          // silu(s)
+  const uint32_t sg = Pk<DT>::fma(t, Pk<DT>::kHalf, Pk<DT>::kHalf);   // sigmoid(s)
+  const uint32_t oms = Pk<DT>::fma(t, NegHalf<DT>::v, Pk<DT>::kHalf); // 1 - sigmoid(s)
+  const uint32_t gp = Pk<DT>::fma(g, oms, sg);                        // silu'(s) = sg + silu*(1 - sg)
+  const float2 gf = Elem<DT>::unpack(g);
+  acc0 = fmaf(dh0, gf.x, acc0);
+  acc1 = fmaf(dh1, gf.y, acc1);
+  return Pk<DT>::mul(Pk<DT>::mul(Pk<DT>::cvt(dh0, dh1), a2), gp);
+}
+
+template <int DT, int GATE, int E>
 __global__ void __launch_bounds__(dadr::kThreads, 1)
 prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmR,
                       const __grid_constant__ CUtensorMap tmdC, const __grid_constant__ CUtensorMap tmB,
                       const DadrParams p) {
   using namespace dadr;
+  constexpr int KS = E / 16;       // 16-wide steps per rotation block
+  constexpr int NB = 64 / E;       // rotation blocks per 64-column tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -87,29 +125,23 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int run = blockIdx.y;
   const int G = p.G;
   const int nstg = (p.gs + 63) / 64;  // 64-output slices per group
+  const bool is_gate = warp >= kGateWarp0 && warp < kGateWarp0 + kNumGateWarps;
+  const bool is_dr = warp == 2 || warp == 3 || warp >= kGateWarp0 + kNumGateWarps;
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->a_full, 1);
-    mbar_init(&bars->a_empty, 1 + kNumDrWarps);
-    for (int i = 0; i < kMaxRBufs; ++i) { mbar_init(&bars->r_full[i], 1); mbar_init(&bars->r_empty[i], 1); }
+    mbar_init(&bars->a_empty, kNumGateWarps + kNumDrWarps);
+    for (int i = 0; i < kMaxRBufs; ++i) { mbar_init(&bars->r_full[i], 1); mbar_init(&bars->r_empty[i], kNumGateWarps); }
     for (int i = 0; i < kMaxStages; ++i) { mbar_init(&bars->st_full[i], 1); mbar_init(&bars->st_empty[i], 1); }
-    mbar_init(&bars->s_full, 1);
-    mbar_init(&bars->s_empty, kNumGateWarps);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars->dh_full[i], 1);
-      mbar_init(&bars->dh_empty[i], kNumGateWarps);
-      mbar_init(&bars->ds_full[i], kNumGateWarps);
-      mbar_init(&bars->ds_empty[i], 1 + kNumDrWarps);
-    }
-    mbar_init(&bars->da_full, 1);
-    mbar_init(&bars->da_empty, kNumGateWarps);
+    for (int i = 0; i < kDhBufs; ++i) { mbar_init(&bars->dh_full[i], 1); mbar_init(&bars->dh_empty[i], kNumGateWarps); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&bars->ds_full[i], kNumGateWarps); mbar_init(&bars->ds_empty[i], kNumDrWarps); }
     fence_mbar_init();
   }
-  if (warp == 1) {
+  if (warp == kWarpMma) {
     tmem_alloc(&bars->tmem_base, 512);
     tmem_relinquish();
   }
-  if (warp == 0 && lane == 0) {
+  if (warp == kWarpTma && lane == 0) {
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmR);
     prefetch_tmap(&tmdC);
@@ -120,7 +152,7 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
 
-  if (warp == 0) {
+  if (warp == kWarpTma) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       bool ok = true;
@@ -136,9 +168,9 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           const int rb = rr.idx;
           if (!mbar_wait(&bars->r_empty[rb], rr.phase ^ 1)) { ok = false; break; }
           uint8_t* dstR = smemR + rb * r_buf_bytes;
-          mbar_arrive_expect_tx(&bars->r_full[rb], 2 * p.E * 128);
-          tma_load_2d(dstR, &tmR, &bars->r_full[rb], f0, g * p.E);
-          tma_load_2d(dstR + p.r_tile_bytes, &tmR, &bars->r_full[rb], f0 + 64, g * p.E);
+          mbar_arrive_expect_tx(&bars->r_full[rb], 2 * E * 128);
+          tma_load_2d(dstR, &tmR, &bars->r_full[rb], f0, g * E);
+          tma_load_2d(dstR + p.r_tile_bytes, &tmR, &bars->r_full[rb], f0 + 64, g * E);
           for (int s = 0; s < nstg; ++s, rst.next()) {
             const int st = rst.idx;
             if (!mbar_wait(&bars->st_empty[st], rst.phase ^ 1)) { ok = false; break; }
@@ -153,75 +185,17 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == kWarpMma) {
+    // ------------------------------------------------------------------ dense issuer: dH = dC . B
     if (lane == 0) {
-      const uint32_t idesc_s = make_idesc(DT, 128, p.E, 0, 0);    // S  = A . R^T      (both K-major)
-      const uint32_t idesc_h = make_idesc(DT, 128, 128, 0, 1);    // dH = dC . B       (B MN-major)
-      const uint32_t idesc_r = make_idesc(DT, 128, p.E, 0, 1);    // dA += dS . R      (R MN-major)
-      const int blocks_per_chunk = 64 / p.E;
-      const int ksteps_per_block = p.E / 16;
-      const uint32_t a_addr = smem_u32(smemA);
+      const uint32_t idesc_h = make_idesc(DT, 128, 128, 0, 1);   // dC K-major, B_g MN-major
       bool ok = true;
-      uint32_t tile_iter = 0, gg = 0;
-      Ring rr(p.rb), rr_dsr(p.rb), rst(p.ns);
-
-      // dA += dS(x) . R(x) for the group with global index x (called once per group, in order)
-      auto issue_dsr = [&](uint32_t x, bool first_of_tile, bool last_of_tile, uint32_t titer) -> bool {
-        const int buf = x & 1;
-        const int rbx = rr_dsr.idx;
-        rr_dsr.next();
-        if (!mbar_wait(&bars->ds_full[buf], (x >> 1) & 1)) return false;
-        if (first_of_tile) {
-          if (!mbar_wait(&bars->da_empty, (titer & 1) ^ 1)) return false;
-        }
-        tc_fence_after_sync();
-        const uint32_t ds_addr = smem_u32(smemDS + buf * 2 * kTile);
-        const uint32_t r_addr = smem_u32(smemR + rbx * r_buf_bytes);
-        for (int i = 0; i < 2; ++i) {
-          for (int b = 0; b < blocks_per_chunk; ++b) {
-            for (int ks = 0; ks < ksteps_per_block; ++ks) {
-              umma_f16(tmem_base + kDaCol0 + i * 64 + b * p.E,
-                       desc_kmajor_sw128(ds_addr + i * kTile + (b * p.E + ks * 16) * 2, 1024),
-                       desc_mnmajor_sw128(r_addr + i * p.r_tile_bytes + b * p.E * 2 + ks * 2048,
-                                          p.r_tile_bytes, 1024),
-                       idesc_r, (!first_of_tile || ks > 0) ? 1u : 0u);
-            }
-          }
-        }
-        umma_commit(&bars->ds_empty[buf]);
-        umma_commit(&bars->r_empty[rbx]);
-        if (last_of_tile) {
-          umma_commit(&bars->a_empty);
-          umma_commit(&bars->da_full);
-        }
-        return true;
-      };
-
-      for (int mt = run; mt < p.n_mtiles && ok; mt += p.runs, ++tile_iter) {
-        if (!mbar_wait(&bars->a_full, tile_iter & 1)) { ok = false; break; }
-        for (int g = 0; g < G && ok; ++g, ++gg, rr.next()) {
-          const int rb = rr.idx;
-          const int hb = gg & 1;
-          if (!mbar_wait(&bars->r_full[rb], rr.phase)) { ok = false; break; }
-          if (GATE == GATE_SILU) {
-            if (!mbar_wait(&bars->s_empty, (gg & 1) ^ 1)) { ok = false; break; }
-            tc_fence_after_sync();
-            const uint32_t r_addr = smem_u32(smemR + rb * r_buf_bytes);
-            for (int i = 0; i < 2; ++i) {
-              for (int b = 0; b < blocks_per_chunk; ++b) {
-                for (int ks = 0; ks < ksteps_per_block; ++ks) {
-                  const uint32_t koff = (b * p.E + ks * 16) * 2;
-                  umma_f16(tmem_base + kSCol0 + i * 64 + b * p.E,
-                           desc_kmajor_sw128(a_addr + i * kTile + koff, 1024),
-                           desc_kmajor_sw128(r_addr + i * p.r_tile_bytes + koff, 1024), idesc_s,
-                           ks > 0 ? 1u : 0u);
-                }
-              }
-            }
-            umma_commit(&bars->s_full);
-          }
-          if (!mbar_wait(&bars->dh_empty[hb], ((gg >> 1) & 1) ^ 1)) { ok = false; break; }
+      uint32_t gg = 0;
+      Ring rst(p.ns);
+      for (int mt = run; mt < p.n_mtiles && ok; mt += p.runs) {
+        for (int g = 0; g < G && ok; ++g, ++gg) {
+          const uint32_t hb = gg & (kDhBufs - 1);
+          if (!mbar_wait(&bars->dh_empty[hb], ((gg / kDhBufs) & 1) ^ 1)) { ok = false; break; }
           for (int s = 0; s < nstg; ++s, rst.next()) {
             const int st = rst.idx;
             if (!mbar_wait(&bars->st_full[st], rst.phase)) { ok = false; break; }
@@ -230,7 +204,7 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             const uint32_t b_addr = dc_addr + kTile;
             const int ksteps = min(4, (p.gs - s * 64) / 16);
             for (int ks = 0; ks < ksteps; ++ks) {
-              umma_f16(tmem_base + kDhCol0 + hb * 128, desc_kmajor_sw128(dc_addr + ks * 32, 1024),
+              umma_f16(tmem_base + hb * 128, desc_kmajor_sw128(dc_addr + ks * 32, 1024),
                        desc_mnmajor_sw128(b_addr + ks * 2048, kBTile, 1024), idesc_h,
                        (s > 0 || ks > 0) ? 1u : 0u);
             }
@@ -238,130 +212,122 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           }
           if (!ok) break;
           umma_commit(&bars->dh_full[hb]);
-          if (g > 0) {
-            if (!issue_dsr(gg - 1, g == 1, false, tile_iter)) { ok = false; break; }
-          }
         }
-        if (!ok) break;
-        if (!issue_dsr(gg - 1, G == 1, true, tile_iter)) { ok = false; break; }
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
-  } else if (warp < kDrWarp0) {
-    // ------------------------------------------------------------------ gate warps (+ dA epilogue)
+  } else if (is_gate) {
+    // ------------------------------------------------------------------ gate warps
     const int gw = warp - kGateWarp0;
-    const int q = warp & 3;
-    const int chunk = gw >> 2;
-    const uint32_t row = q * 32 + lane;
-    const uint32_t lane_base = uint32_t(q * 32) << 16;
-    const uint8_t* tileA = smemA + chunk * kTile;
-    float pacc[64];
+    const int q = gw & 3, half = (gw >> 2) & 1, ch = gw >> 3;   // lane quarter, 16-row half, 64-column tile
+    const uint32_t r0 = q * 32 + half * 16;                    // first of this warp's 16 token rows
+    const uint32_t lane_base = r0 << 16;                       // TMEM lane window [r0, r0+16)
+    const uint32_t mat = lane >> 3, l8 = lane & 7;
+    const uint32_t a_row = r0 + l8 + (mat & 1) * 8;            // A-operand fragments (also dS stores)
+    const uint32_t rn_row = l8 + (mat >> 1) * 8;               // R as B operand of S = A . R^T (rows = i)
+    const uint32_t rt_row = l8 + (mat & 1) * 8;                // R as B operand of dS . R (rows = i, transposed load)
+    const uint32_t tileA = smem_u32(smemA + ch * kTile);
+    float dacc[8][4];   // dA accumulator fragments: 16 rows x 64 columns of this warp, whole tile
 #pragma unroll
-    for (int i = 0; i < 64; ++i) pacc[i] = 0.f;
+    for (int i = 0; i < 8; ++i) { dacc[i][0] = dacc[i][1] = dacc[i][2] = dacc[i][3] = 0.f; }
     bool ok = true;
     uint32_t tile_iter = 0, gg = 0;
+    Ring rr(p.rb);
     for (int mt = run; mt < p.n_mtiles && ok; mt += p.runs, ++tile_iter) {
-      for (int g = 0; g < G && ok; ++g, ++gg) {
-        const int hb = gg & 1;
-        if (GATE == GATE_SILU) {
-          if (!mbar_wait(&bars->s_full, gg & 1)) { ok = false; break; }
-        }
-        if (!mbar_wait(&bars->dh_full[hb], (gg >> 1) & 1)) { ok = false; break; }
-        if (!mbar_wait(&bars->ds_empty[hb], ((gg >> 1) & 1) ^ 1)) { ok = false; break; }
+      if (!mbar_wait(&bars->a_full, tile_iter & 1)) { ok = false; break; }
+      for (int g = 0; g < G && ok; ++g, ++gg, rr.next()) {
+        const uint32_t hb = gg & (kDhBufs - 1), db = gg & 1;
+        if (!mbar_wait(&bars->r_full[rr.idx], rr.phase)) { ok = false; break; }
+        if (!mbar_wait(&bars->dh_full[hb], (gg / kDhBufs) & 1)) { ok = false; break; }
+        if (!mbar_wait(&bars->ds_empty[db], ((gg >> 1) & 1) ^ 1)) { ok = false; break; }
         tc_fence_after_sync();
-        uint8_t* tileDS = smemDS + hb * 2 * kTile + chunk * kTile;
+        const uint32_t tileDS = smem_u32(smemDS + db * 2 * kTile + ch * kTile);
+        const uint32_t rtile = smem_u32(smemR + rr.idx * r_buf_bytes + ch * p.r_tile_bytes);
+        const uint32_t tdh = tmem_base + lane_base + hb * 128 + ch * 64;
 #pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 16) {
-          uint32_t dh[16], s[16];
-          tmem_ld_x16(tmem_base + lane_base + kDhCol0 + hb * 128 + chunk * 64 + c0, dh);
-          uint4 av[2];
+        for (int b = 0; b < NB; ++b) {
+          uint32_t af[KS][4], dsf[KS][4];
           if (GATE == GATE_SILU) {
-            tmem_ld_x16(tmem_base + lane_base + kSCol0 + chunk * 64 + c0, s);
-            av[0] = *reinterpret_cast<const uint4*>(tileA + sw128_offset(row, c0 / 8));
-            av[1] = *reinterpret_cast<const uint4*>(tileA + sw128_offset(row, c0 / 8 + 1));
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks)
+              ldmatrix_x4(tileA + sw128_offset(a_row, b * (E / 8) + ks * 2 + (mat >> 1)), af[ks]);
           }
-          tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            uint32_t aw[4] = {0, 0, 0, 0};
-            if (GATE == GATE_SILU) { aw[0] = av[j].x; aw[1] = av[j].y; aw[2] = av[j].z; aw[3] = av[j].w; }
-            uint32_t ow[4];
+          for (int np = 0; np < KS; ++np) {
+            uint32_t dh[8];
+            tmem_ld_16x256b_x2(tdh + b * E + np * 16, dh);
+            float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+            if (GATE == GATE_SILU) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int c = j * 8 + e * 2;
-              float d0 = __uint_as_float(dh[c]), d1 = __uint_as_float(dh[c + 1]);
-              float ds0, ds1;
-              if (GATE == GATE_SILU) {
-                const float s0 = __uint_as_float(s[c]), s1 = __uint_as_float(s[c + 1]);
-                const float2 a2 = Elem<DT>::unpack(aw[e]);
-                const float sg0 = sigmoid_fast(s0), sg1 = sigmoid_fast(s1);
-                const float t0 = s0 * sg0, t1 = s1 * sg1;            // silu(S)
-                const float gp0 = fmaf(t0, 1.f - sg0, sg0);          // silu'(S) = sg + silu*(1-sg)
-                const float gp1 = fmaf(t1, 1.f - sg1, sg1);
-                pacc[c0 + c] = fmaf(d0, t0, pacc[c0 + c]);
-                pacc[c0 + c + 1] = fmaf(d1, t1, pacc[c0 + c + 1]);
-                ds0 = d0 * a2.x * gp0;
-                ds1 = d1 * a2.y * gp1;
-              } else {
-                ds0 = d0;
-                ds1 = d1;
+              for (int ks = 0; ks < KS; ++ks) {
+                uint32_t rf[4];
+                ldmatrix_x4(rtile + sw128_offset(np * 16 + rn_row, b * (E / 8) + ks * 2 + (mat & 1)), rf);
+                mma_m16n8k16<DT>(c0, af[ks], rf[0], rf[1]);
+                mma_m16n8k16<DT>(c1, af[ks], rf[2], rf[3]);
               }
-              ow[e] = Elem<DT>::pack(ds0, ds1);
             }
-            *reinterpret_cast<uint4*>(tileDS + sw128_offset(row, c0 / 8 + j)) =
-                make_uint4(ow[0], ow[1], ow[2], ow[3]);
+            tmem_ld_wait();
+            float* d0 = dacc[(b * KS + np) * 2];
+            float* d1 = dacc[(b * KS + np) * 2 + 1];
+            if (GATE == GATE_SILU) {
+              dsf[np][0] = gate_bwd_pair<DT>(af[np][0], c0[0], c0[1], __uint_as_float(dh[0]), __uint_as_float(dh[1]), d0[0], d0[1]);
+              dsf[np][1] = gate_bwd_pair<DT>(af[np][1], c0[2], c0[3], __uint_as_float(dh[2]), __uint_as_float(dh[3]), d0[2], d0[3]);
+              dsf[np][2] = gate_bwd_pair<DT>(af[np][2], c1[0], c1[1], __uint_as_float(dh[4]), __uint_as_float(dh[5]), d1[0], d1[1]);
+              dsf[np][3] = gate_bwd_pair<DT>(af[np][3], c1[2], c1[3], __uint_as_float(dh[6]), __uint_as_float(dh[7]), d1[2], d1[3]);
+            } else {
+              dsf[np][0] = Pk<DT>::cvt(__uint_as_float(dh[0]), __uint_as_float(dh[1]));
+              dsf[np][1] = Pk<DT>::cvt(__uint_as_float(dh[2]), __uint_as_float(dh[3]));
+              dsf[np][2] = Pk<DT>::cvt(__uint_as_float(dh[4]), __uint_as_float(dh[5]));
+              dsf[np][3] = Pk<DT>::cvt(__uint_as_float(dh[6]), __uint_as_float(dh[7]));
+            }
+            stmatrix_x4(tileDS + sw128_offset(a_row, b * (E / 8) + np * 2 + (mat >> 1)), dsf[np]);
+          }
+          // dA[:, block b] += dS[:, block b] . R_g[block b]   (contraction over the block's i)
+#pragma unroll
+          for (int jp = 0; jp < KS; ++jp) {
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+              uint32_t rt[4];
+              ldmatrix_x4_trans(rtile + sw128_offset(ks * 16 + rt_row, b * (E / 8) + jp * 2 + (mat >> 1)), rt);
+              mma_m16n8k16<DT>(dacc[(b * KS + jp) * 2], dsf[ks], rt[0], rt[1]);
+              mma_m16n8k16<DT>(dacc[(b * KS + jp) * 2 + 1], dsf[ks], rt[2], rt[3]);
+            }
           }
         }
-        fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
-          mbar_arrive(&bars->ds_full[hb]);
+          mbar_arrive(&bars->ds_full[db]);
           mbar_arrive(&bars->dh_empty[hb]);
-          if (GATE == GATE_SILU) mbar_arrive(&bars->s_empty);
+          mbar_arrive(&bars->r_empty[rr.idx]);
         }
       }
       if (!ok) break;
-      // tile epilogue: dA = scale * (register part + tensor-core part)
-      if (!mbar_wait(&bars->da_full, tile_iter & 1)) { ok = false; break; }
-      tc_fence_after_sync();
-      const long long grow = (long long)mt * 128 + row;
-      uint16_t* drow = reinterpret_cast<uint16_t*>(p.dA) + grow * p.ldda + f0 + chunk * 64;
-#pragma unroll
-      for (int c0 = 0; c0 < 64; c0 += 16) {
-        uint32_t v[16];
-        tmem_ld_x16(tmem_base + lane_base + kDaCol0 + chunk * 64 + c0, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          uint32_t ow[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int c = j * 8 + e * 2;
-            const float x0 = (__uint_as_float(v[c]) + pacc[c0 + c]) * p.scale;
-            const float x1 = (__uint_as_float(v[c + 1]) + pacc[c0 + c + 1]) * p.scale;
-            ow[e] = Elem<DT>::pack(x0, x1);
-            pacc[c0 + c] = 0.f;
-            pacc[c0 + c + 1] = 0.f;
-          }
-          if (grow < p.M && f0 + chunk * 64 + c0 + j * 8 < p.K)
-            *reinterpret_cast<uint4*>(drow + c0 + j * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-        }
-      }
-      tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->da_empty);
+      if (lane == 0) mbar_arrive(&bars->a_empty);   // this warp no longer reads the A tile
+      // tile epilogue: dA = scale * accumulators, written straight from the fragments
+      const long long grow = (long long)mt * 128 + r0 + (lane >> 2);
+      uint16_t* out = reinterpret_cast<uint16_t*>(p.dA);
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const int col = f0 + ch * 64 + nt * 8 + (lane & 3) * 2;
+        if (col < p.K) {
+          if (grow < p.M)
+            *reinterpret_cast<uint32_t*>(out + grow * p.ldda + col) = Elem<DT>::pack(dacc[nt][0] * p.scale, dacc[nt][1] * p.scale);
+          if (grow + 8 < p.M)
+            *reinterpret_cast<uint32_t*>(out + (grow + 8) * p.ldda + col) = Elem<DT>::pack(dacc[nt][2] * p.scale, dacc[nt][3] * p.scale);
+        }
+        dacc[nt][0] = dacc[nt][1] = dacc[nt][2] = dacc[nt][3] = 0.f;
+      }
     }
     if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
-  } else {
+  } else if (is_dr) {
     // ------------------------------------------------------------------ dR warps
-    const int w = warp - kDrWarp0;
-    const int sub_e = p.E / 16;                  // 16x16 sub-tiles per block edge
-    const int spb = sub_e * sub_e;               // sub-tiles per block
-    const int n_sub = (128 / p.E) * spb;         // sub-tiles of this CTA's 128 features
-    const int bpc = 64 / p.E;
+    const int w = (warp < kGateWarp0) ? (warp - 2) : (warp - kGateWarp0 - kNumGateWarps + 2);
+    constexpr int spb = KS * KS;                 // 16x16 sub-tiles per rotation block
+    constexpr int n_sub = (128 / E) * spb;       // sub-tiles of this CTA's 128 features
     const int mat = lane >> 3, l8 = lane & 7;
-    const long long GE = (long long)G * p.E;
+    const long long GE = (long long)G * E;
     float* part = p.partial + (long long)run * GE * p.K;
     bool ok = true;
     uint32_t tile_iter = 0, gg = 0;
@@ -372,12 +338,12 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         if (!mbar_wait(&bars->ds_full[buf], (gg >> 1) & 1)) { ok = false; break; }
         for (int u = w; u < n_sub; u += kNumDrWarps) {
           const int block = u / spb, rem = u - block * spb;
-          const int is = rem / sub_e, js = rem - is * sub_e;
-          const int chunk = block / bpc, b = block - chunk * bpc;
+          const int is = rem / KS, js = rem - is * KS;
+          const int chunk = block / NB, b = block - chunk * NB;
           const uint32_t ds_tile = smem_u32(smemDS + buf * 2 * kTile + chunk * kTile);
           const uint32_t a_tile = smem_u32(smemA + chunk * kTile);
-          const uint32_t ci = (b * p.E + is * 16) / 8;   // 16-byte chunk of the dS columns (i)
-          const uint32_t cj = (b * p.E + js * 16) / 8;   // 16-byte chunk of the A columns (j)
+          const uint32_t ci = (b * E + is * 16) / 8;   // 16-byte chunk of the dS columns (i)
+          const uint32_t cj = (b * E + js * 16) / 8;   // 16-byte chunk of the A columns (j)
           float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
@@ -392,28 +358,19 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             mma_m16n8k16<DT>(d0, af, bf[0], bf[1]);
             mma_m16n8k16<DT>(d1, af, bf[2], bf[3]);
           }
-          // accumulate into this CTA's partial buffer (fixed order: m-tiles ascending)
-          const int r0 = g * p.E + is * 16 + (lane >> 2);
-          const int col = f0 + chunk * 64 + b * p.E + js * 16 + (lane & 3) * 2;
+          // Accumulate into this CTA's partial buffer.  Every address has exactly one writer thread,
+          // which stores on its first token tile and afterwards issues fire-and-forget fp32 reductions
+          // in token-tile order: same-address operations of one thread stay ordered, so the sum is
+          // formed in a fixed order (bit-stable) without waiting for a read-modify-write round trip.
+          const int rr0 = g * E + is * 16 + (lane >> 2);
+          const int col = f0 + chunk * 64 + b * E + js * 16 + (lane & 3) * 2;
           if (col < p.K) {
-            float2* p00 = reinterpret_cast<float2*>(part + (long long)r0 * p.K + col);
-            float2* p10 = reinterpret_cast<float2*>(part + (long long)(r0 + 8) * p.K + col);
-            float2 v00 = make_float2(d0[0], d0[1]), v10 = make_float2(d0[2], d0[3]);
-            if (tile_iter > 0) {
-              const float2 o00 = *p00, o10 = *p10;
-              v00.x += o00.x; v00.y += o00.y; v10.x += o10.x; v10.y += o10.y;
-            }
-            *p00 = v00; *p10 = v10;
+            dr_accumulate(part + (long long)rr0 * p.K + col, d0[0], d0[1], tile_iter == 0);
+            dr_accumulate(part + (long long)(rr0 + 8) * p.K + col, d0[2], d0[3], tile_iter == 0);
           }
           if (col + 8 < p.K) {
-            float2* p01 = reinterpret_cast<float2*>(part + (long long)r0 * p.K + col + 8);
-            float2* p11 = reinterpret_cast<float2*>(part + (long long)(r0 + 8) * p.K + col + 8);
-            float2 v01 = make_float2(d1[0], d1[1]), v11 = make_float2(d1[2], d1[3]);
-            if (tile_iter > 0) {
-              const float2 o01 = *p01, o11 = *p11;
-              v01.x += o01.x; v01.y += o01.y; v11.x += o11.x; v11.y += o11.y;
-            }
-            *p01 = v01; *p11 = v11;
+            dr_accumulate(part + (long long)rr0 * p.K + col + 8, d1[0], d1[1], tile_iter == 0);
+            dr_accumulate(part + (long long)(rr0 + 8) * p.K + col + 8, d1[2], d1[3], tile_iter == 0);
           }
         }
         __syncwarp();
@@ -428,7 +385,7 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, 512);
+  if (warp == kWarpMma) tmem_dealloc(tmem_base, 512);
 }
 
 // dR[g*rs + i, k] = cast( scale * sum_run partial[run][g*E + i'][k] ), runs in increasing order.
@@ -436,8 +393,7 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 // the block in the upper 8 columns of each 16-column pair sits in rows 8..15.
 template <int DT>
 __global__ void dr_reduce_kernel(const float* __restrict__ partial, uint16_t* __restrict__ dR, int G,
-                                 int rs, int E, int K, long long lddr, int runs, int runs_alloc_rows,
-                                 float scale) {
+                                 int rs, int E, int K, long long lddr, int runs, float scale) {
   const long long pair = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long total = (long long)G * rs * K / 2;
   if (pair >= total) return;
@@ -448,7 +404,6 @@ __global__ void dr_reduce_kernel(const float* __restrict__ partial, uint16_t* __
   int ip = i;
   if (rs == 8) ip = i + (((k & 15) >= 8) ? 8 : 0);
   const long long GE = (long long)G * E;
-  (void)runs_alloc_rows;
   float2 acc = make_float2(0.f, 0.f);
   for (int r = 0; r < runs; ++r) {
     const float2 v = *reinterpret_cast<const float2*>(partial + ((long long)r * GE + (long long)g * E + ip) * K + k);
@@ -494,9 +449,14 @@ int launch_bwd_dadr(const DadrArgs& a) {
   if ((rc = make_tmap_2d(&tmdC, a.dtype, a.dC, a.M, a.N, a.lddc, 128, 64, true))) return rc;
   if ((rc = make_tmap_2d(&tmB, a.dtype, a.B, a.N, a.K, a.ldb, 64, 64, true))) return rc;
 
-  auto kern = (a.dtype == DT_BF16)
-                  ? (a.gate == GATE_SILU ? prism_bwd_dadr_kernel<DT_BF16, GATE_SILU> : prism_bwd_dadr_kernel<DT_BF16, GATE_NONE>)
-                  : (a.gate == GATE_SILU ? prism_bwd_dadr_kernel<DT_F16, GATE_SILU> : prism_bwd_dadr_kernel<DT_F16, GATE_NONE>);
+  using KernT = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, DadrParams);
+  KernT kern = nullptr;
+#define PRISM_PICK(E_)                                                                               \
+  kern = (a.dtype == DT_BF16)                                                                        \
+             ? (a.gate == GATE_SILU ? (KernT)prism_bwd_dadr_kernel<DT_BF16, GATE_SILU, E_> : (KernT)prism_bwd_dadr_kernel<DT_BF16, GATE_NONE, E_>) \
+             : (a.gate == GATE_SILU ? (KernT)prism_bwd_dadr_kernel<DT_F16, GATE_SILU, E_> : (KernT)prism_bwd_dadr_kernel<DT_F16, GATE_NONE, E_>)
+  if (a.E == 16) { PRISM_PICK(16); } else if (a.E == 32) { PRISM_PICK(32); } else { PRISM_PICK(64); }
+#undef PRISM_PICK
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return fail(PRISM_ERR_CUDA, "bwd_dadr: cannot set %d B of shared memory: %s", smem_bytes, cudaGetErrorString(e));
   dim3 grid((a.K + 127) / 128, p.runs, 1);
@@ -507,9 +467,9 @@ int launch_bwd_dadr(const DadrArgs& a) {
   const int threads = 256;
   const long long blocks = (pairs + threads - 1) / threads;
   if (a.dtype == DT_BF16)
-    dr_reduce_kernel<DT_BF16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, reinterpret_cast<uint16_t*>(a.dR), p.G, a.rs, a.E, a.K, a.lddr, p.runs, 0, a.scale);
+    dr_reduce_kernel<DT_BF16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, reinterpret_cast<uint16_t*>(a.dR), p.G, a.rs, a.E, a.K, a.lddr, p.runs, a.scale);
   else
-    dr_reduce_kernel<DT_F16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, reinterpret_cast<uint16_t*>(a.dR), p.G, a.rs, a.E, a.K, a.lddr, p.runs, 0, a.scale);
+    dr_reduce_kernel<DT_F16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, reinterpret_cast<uint16_t*>(a.dR), p.G, a.rs, a.E, a.K, a.lddr, p.runs, a.scale);
   return check_launch("prism_bwd_dadr reduce");
 }
 
