@@ -6,13 +6,16 @@
 // Replaces the reference's prism_tn / prism_device forward kernel
 // (cute_prism_coop_pc.cu:567-804) and its binding (torch_ext/prism_fwd_torch.cu:23-196).
 //
-// Per CTA: a persistent loop over (128-row, BN-column) output tiles; per 64-wide K chunk
+// CTAs work in pairs (cluster of 2, tcgen05 cta_group::2) on (256-row, BN-column) output tiles: each CTA
+// owns 128 of the rows and loads half of the B tile, which halves the L2 traffic per flop.  Per CTA a
+// persistent loop over the pair's tiles; per 64-wide K chunk
 //   warp 0      TMA producer: A tile [128 x 64] + R_g tile [E x 64] into the "AR" ring, B_g tile
 //               [BN x 64] into the "B" ring (128-byte swizzle, zero fill outside the tensors)
 //   warps 2-17  gate warps, two groups of eight that take alternate chunks, 16 rows per warp: A and R fragments by ldmatrix, block rotation
 //               S = A_blk . R_blk^T by mma.sync (fp32), H = A*silu(S) (or H = S) on registers,
 //               stmatrix of H over the A tile in place
-//   warp 1      dense issuer: C += H . B^T as 4 x tcgen05.mma M128 N=BN K=16, fp32 in TMEM,
+//   warp 1      dense issuer (leader CTA only): C += H . B^T as 4 x tcgen05.mma M256 N=BN K=16 spanning
+//               both CTAs, fp32 in TMEM,
 //               two accumulators so that the epilogue of a tile overlaps the next tile
 //   warps 18-21 epilogue: tcgen05.ld C, + bias, cast, swizzled staging tile, TMA store.
 // Every role keeps its ring positions as counters; the single-thread roles do no division.
@@ -77,7 +80,7 @@ __device__ __forceinline__ void tile_coords(const FwdParams& p, int t, int& mt, 
 }
 
 template <int DT, int GATE, int E>
-__global__ void __launch_bounds__(fwd::kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(fwd::kThreads, 1)
 prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmR,
                  const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
                  const FwdParams p) {
@@ -86,7 +89,7 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
   const int ar_stage_bytes = kATileBytes + p.r_tile_bytes;
-  const int b_stage_bytes = p.BN * 128;
+  const int b_stage_bytes = p.BN * 64;   // this CTA's half of the B tile: BN/2 rows of 128 bytes
   uint8_t* smemAR = smem;
   uint8_t* smemB = smemAR + p.sa * ar_stage_bytes;
   uint8_t* smemEpi = smemB + p.sb * b_stage_bytes;
@@ -95,23 +98,27 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  const uint32_t rank = cluster_ctarank();          // 0 = leader (issues the MMAs), 1 = peer
+  const int cid = blockIdx.x >> 1;                  // cluster index
+  const int n_clusters = gridDim.x >> 1;
+
   if (threadIdx.x == 0) {
     for (int i = 0; i < kMaxStages; ++i) {
-      mbar_init(&bars->ar_full[i], 1);
-      mbar_init(&bars->h_full[i], kWarpsPerGroup);
-      mbar_init(&bars->a_empty[i], 1);
-      mbar_init(&bars->b_full[i], 1);
+      mbar_init(&bars->ar_full[i], 1);                    // local: this CTA's A and R tiles landed
+      mbar_init(&bars->h_full[i], 2 * kWarpsPerGroup);    // leader's copy is used: gate warps of both CTAs
+      mbar_init(&bars->a_empty[i], 1);                    // local, arrived by the multicast commit
+      mbar_init(&bars->b_full[i], 2);                     // leader's copy is used: both CTAs' B halves
       mbar_init(&bars->b_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars->acc_full[i], 1);
-      mbar_init(&bars->acc_empty[i], kNumEpiWarps);
+      mbar_init(&bars->acc_full[i], 1);                   // local, arrived by the multicast commit
+      mbar_init(&bars->acc_empty[i], 2 * kNumEpiWarps);   // leader's copy is used
     }
     fence_mbar_init();
   }
   if (warp == kWarpMma) {
-    tmem_alloc(&bars->tmem_base, 512);
-    tmem_relinquish();
+    tmem_alloc_pair(&bars->tmem_base, 512);
+    tmem_relinquish_pair();
   }
   if (warp == kWarpTma && lane == 0) {
     prefetch_tmap(&tmA);
@@ -119,13 +126,16 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     prefetch_tmap(&tmB);
     prefetch_tmap(&tmC);
   }
+  // the peer's barriers must be initialised before anything arrives on them remotely
   tc_fence_before_sync();
   __syncthreads();
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
   const int nk = p.n_kchunks;
-  const int my_tiles = (p.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-  const uint32_t total = (uint32_t)my_tiles * nk;   // chunks this CTA processes
+  const int my_tiles = (p.n_tiles - cid + n_clusters - 1) / n_clusters;
+  const uint32_t total = (uint32_t)my_tiles * nk;   // chunks this CTA pair processes
 
   if (warp == kWarpTma) {
     // ------------------------------------------------------------------ TMA producer
@@ -135,7 +145,7 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // Two cursors (tile, chunk) walk the same sequence, the B cursor `ahead` chunks behind.
       const uint32_t ahead = p.sa - p.sb;
       Ring ra(p.sa), rb(p.sb);
-      int ta = blockIdx.x, ca = 0, mta, nta, tb = blockIdx.x, cb = 0, mtb, ntb;
+      int ta = cid, ca = 0, mta, nta, tb = cid, cb = 0, mtb, ntb;
       tile_coords(p, ta, mta, nta);
       tile_coords(p, tb, mtb, ntb);
       int ga = nta / p.ntiles_per_group;
@@ -145,23 +155,25 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (!mbar_wait(&bars->a_empty[ra.idx], ra.phase ^ 1)) { ok = false; break; }
           uint8_t* dstA = smemAR + ra.idx * ar_stage_bytes;
           mbar_arrive_expect_tx(&bars->ar_full[ra.idx], kATileBytes + p.E * 128);
-          tma_load_2d(dstA, &tmA, &bars->ar_full[ra.idx], ca * 64, mta * 128);
+          tma_load_2d(dstA, &tmA, &bars->ar_full[ra.idx], ca * 64, mta * 256 + (int)rank * 128);
           tma_load_2d(dstA + kATileBytes, &tmR, &bars->ar_full[ra.idx], ca * 64, ga * p.E);
           ra.next();
           if (++ca == nk) {
             ca = 0;
-            ta += gridDim.x;
+            ta += n_clusters;
             if (ta < p.n_tiles) { tile_coords(p, ta, mta, nta); ga = nta / p.ntiles_per_group; }
           }
         }
         if (j >= ahead) {
           if (!mbar_wait(&bars->b_empty[rb.idx], rb.phase ^ 1)) { ok = false; break; }
-          mbar_arrive_expect_tx(&bars->b_full[rb.idx], b_stage_bytes);
-          tma_load_2d(smemB + rb.idx * b_stage_bytes, &tmB, &bars->b_full[rb.idx], cb * 64, ntb * p.BN);
+          // this CTA's half of the B tile; completion is counted on the leader's barrier
+          const uint32_t bfull = mapa_shared(smem_u32(&bars->b_full[rb.idx]), 0);
+          mbar_arrive_expect_tx_cluster(bfull, b_stage_bytes);
+          tma_load_2d_pair(smemB + rb.idx * b_stage_bytes, &tmB, bfull, cb * 64, ntb * p.BN + (int)rank * (p.BN / 2));
           rb.next();
           if (++cb == nk) {
             cb = 0;
-            tb += gridDim.x;
+            tb += n_clusters;
             if (tb < p.n_tiles) tile_coords(p, tb, mtb, ntb);
           }
         }
@@ -170,33 +182,33 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ dense issuer
-    if (lane == 0) {
-      const uint32_t idesc_c = make_idesc(DT, 128, p.BN, 0, 0);
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc_c = make_idesc(DT, 256, p.BN, 0, 0);   // M = 256: 128 rows in each CTA
       Ring ra(p.sa), rb(p.sb);
       int cm = 0;
       uint32_t acc = 0, acc_phase = 0;   // accumulator buffer (TMEM columns acc*256) and its phase
       bool ok = true;
       for (uint32_t j = 0; j < total; ++j) {
-        if (!mbar_wait(&bars->h_full[ra.idx], ra.phase)) { ok = false; break; }
-        if (!mbar_wait(&bars->b_full[rb.idx], rb.phase)) { ok = false; break; }
+        if (!mbar_wait_cluster(&bars->h_full[ra.idx], ra.phase)) { ok = false; break; }
+        if (!mbar_wait_cluster(&bars->b_full[rb.idx], rb.phase)) { ok = false; break; }
         if (cm == 0) {
-          if (!mbar_wait(&bars->acc_empty[acc], acc_phase ^ 1)) { ok = false; break; }
+          if (!mbar_wait_cluster(&bars->acc_empty[acc], acc_phase ^ 1)) { ok = false; break; }
         }
         tc_fence_after_sync();
         const uint32_t h_addr = smem_u32(smemAR + ra.idx * ar_stage_bytes);
         const uint32_t b_addr = smem_u32(smemB + rb.idx * b_stage_bytes);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-          umma_f16(tmem_base + acc * 256, desc_kmajor_sw128(h_addr + ks * 32, 1024),
-                   desc_kmajor_sw128(b_addr + ks * 32, 1024), idesc_c, (cm > 0 || ks > 0) ? 1u : 0u);
+          umma_f16_pair(tmem_base + acc * 256, desc_kmajor_sw128(h_addr + ks * 32, 1024),
+                        desc_kmajor_sw128(b_addr + ks * 32, 1024), idesc_c, (cm > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit(&bars->a_empty[ra.idx]);
-        umma_commit(&bars->b_empty[rb.idx]);
+        umma_commit_pair(&bars->a_empty[ra.idx], 0x3);   // both CTAs' rings move on
+        umma_commit_pair(&bars->b_empty[rb.idx], 0x3);
         ra.next();
         rb.next();
         if (++cm == nk) {
           cm = 0;
-          umma_commit(&bars->acc_full[acc]);
+          umma_commit_pair(&bars->acc_full[acc], 0x3);
           acc ^= 1u;
           if (acc == 0) acc_phase ^= 1u;
         }
@@ -219,7 +231,7 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #endif
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->h_full[ra.idx]);
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars->h_full[ra.idx]), 0));
     }
     if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
   } else if (warp >= kEpiWarp0) {
@@ -231,9 +243,10 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint16_t* bias = reinterpret_cast<const uint16_t*>(p.bias);
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
-      int mt, nt;
-      tile_coords(p, t, mt, nt);
+    for (int t = cid; t < p.n_tiles && ok; t += n_clusters) {
+      int mp, nt;
+      tile_coords(p, t, mp, nt);
+      const int mt = mp * 2 + (int)rank;   // this CTA's 128-row block
       if (!mbar_wait(&bars->acc_full[acc], acc_phase)) { ok = false; break; }
       const uint32_t tacc = tmem_base + lane_base + acc * 256;
       tc_fence_after_sync();
@@ -303,7 +316,7 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->acc_empty[acc]);
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars->acc_empty[acc]), 0));
       acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
     }
@@ -312,9 +325,12 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 
   // ------------------------------------------------------------------ teardown
+  // neither CTA may leave (or free TMEM) while its peer can still reach its barriers or shared memory
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == kWarpMma) tmem_dealloc(tmem_base, 512);
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+  if (warp == kWarpMma) tmem_dealloc_pair(tmem_base, 512);
 }
 
 // ----------------------------------------------------------------------------
@@ -323,11 +339,11 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 int launch_fwd(const FwdArgs& a) {
   FwdParams p;
   p.M = a.M; p.N = a.N; p.K = a.K; p.gs = a.gs; p.E = a.E; p.BN = a.BN;
-  p.n_mtiles = (a.M + 127) / 128;
+  p.n_mtiles = (a.M + 255) / 256;   // row blocks of a CTA pair
   p.n_ntiles = a.N / a.BN;
   p.ntiles_per_group = a.gs / a.BN;
   p.n_tiles = p.n_mtiles * p.n_ntiles;
-  p.PM = a.PM > 0 ? a.PM : 16;
+  p.PM = a.PM > 0 ? a.PM : 8;
   if (p.PM > p.n_mtiles) p.PM = p.n_mtiles;
   p.n_kchunks = (a.K + 63) / 64;
   p.r_tile_bytes = ((a.E * 128) + 1023) / 1024 * 1024;
@@ -336,9 +352,9 @@ int launch_fwd(const FwdArgs& a) {
 
   const int budget = 227 * 1024 - 1024 - (int)sizeof(FwdBarriers) - 256 - fwd::kNumEpiWarps * fwd::kEpiStageBytes;
   const int ar_bytes = fwd::kATileBytes + p.r_tile_bytes;
-  const int b_bytes = a.BN * 128;
+  const int b_bytes = a.BN * 64;   // per CTA: half of the B tile
   // the AR ring feeds rotation + gate, which run ahead of the dense product: give it the deeper pipeline
-  int sb = a.sb > 0 ? a.sb : 3;
+  int sb = a.sb > 0 ? a.sb : 4;
   int sa = a.sa > 0 ? a.sa : 6;
   if (sa > fwd::kMaxStages) sa = fwd::kMaxStages;
   if (sb > fwd::kMaxStages) sb = fwd::kMaxStages;
@@ -362,11 +378,12 @@ int launch_fwd(const FwdArgs& a) {
   int rc;
   if ((rc = make_tmap_2d(&tmA, a.dtype, a.A, a.M, a.K, a.lda, 128, 64, true))) return rc;
   if ((rc = make_tmap_2d(&tmR, a.dtype, a.R_eff, (uint64_t)(a.N / a.gs) * a.E, a.K, a.ldr, a.E, 64, true))) return rc;
-  if ((rc = make_tmap_2d(&tmB, a.dtype, a.B, a.N, a.K, a.ldb, a.BN, 64, true))) return rc;
+  if ((rc = make_tmap_2d(&tmB, a.dtype, a.B, a.N, a.K, a.ldb, a.BN / 2, 64, true))) return rc;
   if ((rc = make_tmap_2d(&tmC, a.dtype, a.C, a.M, a.N, a.ldc, 32, 64, true))) return rc;
 
-  int grid = a.num_sms;
-  if (grid > p.n_tiles) grid = p.n_tiles;
+  int n_clusters = a.num_sms / 2;
+  if (n_clusters > p.n_tiles) n_clusters = p.n_tiles;
+  const int grid = 2 * n_clusters;
 
   using KernT = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, FwdParams);
   KernT kern = nullptr;
