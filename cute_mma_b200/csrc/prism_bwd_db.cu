@@ -5,12 +5,13 @@
 // Replaces the reference's dB_pc_kernel / prism_backward_dB_launch
 // (cute_prism_backward_db.cu:450-582) and its binding (torch_ext/prism_bwd_db_torch.cu:42-162).
 //
-// Each CTA owns one accumulator tile D[f, n] (128 features x BN outputs of one group, fp32 in
-// TMEM) and a contiguous range of 128-token blocks.  The contraction runs over tokens, so both
+// CTAs work in pairs (cluster of 2, tcgen05 cta_group::2).  A pair owns one accumulator tile
+// D[f, n] (256 features x BN outputs of one group; each CTA holds its 128 features in its own TMEM
+// and loads half of the dC columns) and a contiguous range of 128-token blocks.  The contraction runs over tokens, so both
 // tensor-core operands are "MN-major": H tiles [128 tokens x 64 features] and dC tiles
 // [128 tokens x 64 outputs] are used exactly as TMA / the gate warps lay them out, no transposes.
 //   TMA warp   : R_g tiles once; per token block two A tiles and ceil(BN/64) dC tiles
-//   gate warps : 16 token rows each; block rotation S = A_blk . R_blk^T by mma.sync on ldmatrix
+//   gate warps : two groups taking alternate token blocks, 16 token rows per warp; block rotation S = A_blk . R_blk^T by mma.sync on ldmatrix
 //                fragments, H = A*silu(S) on registers, stmatrix of H over the A tiles in place
 //   MMA issuer : D += H^T . dC as 8 x tcgen05.mma M128 N=BN K=16 per token block
 //   epilogue   : D -> dB (transposed store), or fp32 partials when the token range is split;
@@ -21,11 +22,13 @@
 namespace prism {
 
 namespace db {
-constexpr int kThreads = 448;     // warp 0 TMA, 1 dense issuer, 2-9 gate (16 rows each), 10-13 epilogue
+constexpr int kThreads = 704;     // warp 0 TMA, 1 dense issuer, 2-17 gate, 18-21 epilogue
 constexpr int kWarpTma = 0, kWarpMma = 1;
 constexpr int kGateWarp0 = 2;
-constexpr int kNumGateWarps = 8;
-constexpr int kEpiWarp0 = 10;
+constexpr int kGateGroups = 2;    // groups take alternate token blocks ...
+constexpr int kWarpsPerGroup = 8; // ... with 16 token rows per warp
+constexpr int kNumGateWarps = kGateGroups * kWarpsPerGroup;
+constexpr int kEpiWarp0 = kGateWarp0 + kNumGateWarps;   // (warp & 3) of warps 18..21 covers 2,3,0,1
 constexpr int kMaxStages = 4;
 constexpr int kTile = 128 * 128;  // bytes of a [128 x 64] 16-bit tile
 }  // namespace db
@@ -57,7 +60,7 @@ struct DbBarriers {
 };
 
 template <int DT, int GATE, int E>
-__global__ void __launch_bounds__(db::kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(db::kThreads, 1)
 prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmR,
                     const __grid_constant__ CUtensorMap tmdC, const DbParams p) {
   using namespace db;
@@ -73,7 +76,8 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int f0 = blockIdx.x * 128;           // first feature (column of A / dB)
+  const uint32_t rank = cluster_ctarank();   // 0 = leader (issues the MMAs), 1 = peer
+  const int f0 = blockIdx.x * 128;           // first of this CTA's 128 features (column of A / dB)
   const int nt = blockIdx.y;
   const int n0 = nt * p.BN;                  // first output (row of dB)
   const int g = nt / p.ntiles_per_group;
@@ -84,26 +88,29 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(&bars->r_full, 1);
     for (int i = 0; i < kMaxStages; ++i) {
-      mbar_init(&bars->a_full[i], 1);
-      mbar_init(&bars->h_full[i], kNumGateWarps);
-      mbar_init(&bars->a_empty[i], 1);
-      mbar_init(&bars->dc_full[i], 1);
+      mbar_init(&bars->a_full[i], 1);                  // local: this CTA's A tiles landed
+      mbar_init(&bars->h_full[i], 2 * kWarpsPerGroup); // leader's copy is used: gate warps of both CTAs
+      mbar_init(&bars->a_empty[i], 1);                 // local, arrived by the multicast commit
+      mbar_init(&bars->dc_full[i], 2);                 // leader's copy is used: both CTAs' dC halves
       mbar_init(&bars->dc_empty[i], 1);
     }
     mbar_init(&bars->acc_full, 1);
     fence_mbar_init();
   }
   if (warp == kWarpMma) {
-    tmem_alloc(&bars->tmem_base, 512);
-    tmem_relinquish();
+    tmem_alloc_pair(&bars->tmem_base, 512);
+    tmem_relinquish_pair();
   }
   if (warp == kWarpTma && lane == 0) {
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmR);
     prefetch_tmap(&tmdC);
   }
+  // the peer's barriers must be initialised before anything arrives on them remotely
   tc_fence_before_sync();
   __syncthreads();
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
 
@@ -125,50 +132,55 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tma_load_2d(dstA + kTile, &tmA, &bars->a_full[sa], f0 + 64, tok0);
         if (!mbar_wait(&bars->dc_empty[sd], rd.phase ^ 1)) { ok = false; break; }
         uint8_t* dstD = smemD + sd * dc_stage_bytes;
-        mbar_arrive_expect_tx(&bars->dc_full[sd], dc_stage_bytes);
+        // this CTA's half of the dC columns; completion is counted on the leader's barrier
+        const uint32_t dcfull = mapa_shared(smem_u32(&bars->dc_full[sd]), 0);
+        mbar_arrive_expect_tx_cluster(dcfull, dc_stage_bytes);
         for (int t = 0; t < p.dc_tiles; ++t)
-          tma_load_2d(dstD + t * kTile, &tmdC, &bars->dc_full[sd], n0 + 64 * t, tok0);
+          tma_load_2d_pair(dstD + t * kTile, &tmdC, dcfull, n0 + (int)rank * (p.BN / 2) + 64 * t, tok0);
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ dense issuer
-    if (lane == 0) {
-      const uint32_t idesc_d = make_idesc(DT, 128, p.BN, 1, 1);
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc_d = make_idesc(DT, 256, p.BN, 1, 1);   // M = 256: 128 features in each CTA
       bool ok = true;
       Ring ra(p.sa), rd(p.sd);
       for (int j = 0; j < nb && ok; ++j, ra.next(), rd.next()) {
-        if (!mbar_wait(&bars->h_full[ra.idx], ra.phase)) { ok = false; break; }
-        if (!mbar_wait(&bars->dc_full[rd.idx], rd.phase)) { ok = false; break; }
+        if (!mbar_wait_cluster(&bars->h_full[ra.idx], ra.phase)) { ok = false; break; }
+        if (!mbar_wait_cluster(&bars->dc_full[rd.idx], rd.phase)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t h_addr = smem_u32(smemA + ra.idx * a_stage_bytes);
         const uint32_t d_addr = smem_u32(smemD + rd.idx * dc_stage_bytes);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          umma_f16(tmem_base, desc_mnmajor_sw128(h_addr + ks * 2048, kTile, 1024),
-                   desc_mnmajor_sw128(d_addr + ks * 2048, kTile, 1024), idesc_d,
-                   (j > 0 || ks > 0) ? 1u : 0u);
+          umma_f16_pair(tmem_base, desc_mnmajor_sw128(h_addr + ks * 2048, kTile, 1024),
+                        desc_mnmajor_sw128(d_addr + ks * 2048, kTile, 1024), idesc_d,
+                        (j > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit(&bars->a_empty[ra.idx]);
-        umma_commit(&bars->dc_empty[rd.idx]);
-        if (j == nb - 1) umma_commit(&bars->acc_full);
+        umma_commit_pair(&bars->a_empty[ra.idx], 0x3);
+        umma_commit_pair(&bars->dc_empty[rd.idx], 0x3);
+        if (j == nb - 1) umma_commit_pair(&bars->acc_full, 0x3);
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
   } else if (warp >= kGateWarp0 && warp < kEpiWarp0) {
     // ------------------------------------------------------------------ gate warps
-    const uint32_t r0 = (warp - kGateWarp0) * 16;   // this warp's 16 token rows of the block
+    const int gw = warp - kGateWarp0;
+    const int group = gw / kWarpsPerGroup;            // which token blocks (j mod kGateGroups)
+    const uint32_t r0 = (gw % kWarpsPerGroup) * 16;   // this warp's 16 token rows of the block
     bool ok = mbar_wait(&bars->r_full, 0);
     const uint32_t r_addr = smem_u32(smemR);
     Ring ra(p.sa);
-    for (int j = 0; j < nb && ok; ++j, ra.next()) {
+    for (int i = 0; i < group; ++i) ra.next();
+    for (int j = group; j < nb && ok; j += kGateGroups, ra.next(), ra.next()) {
       if (!mbar_wait(&bars->a_full[ra.idx], ra.phase)) { ok = false; break; }
       const uint32_t tile = smem_u32(smemA + ra.idx * a_stage_bytes);
       rotate_gate_rows16<DT, GATE, E>(tile, r_addr, r0, lane);
       rotate_gate_rows16<DT, GATE, E>(tile + kTile, r_addr + p.r_tile_bytes, r0, lane);
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->h_full[ra.idx]);
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars->h_full[ra.idx]), 0));
     }
     if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
   } else if (warp >= kEpiWarp0) {
@@ -202,9 +214,12 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   }
 
+  // neither CTA may leave (or free TMEM) while its peer can still reach its barriers or shared memory
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == kWarpMma) tmem_dealloc(tmem_base, 512);
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+  if (warp == kWarpMma) tmem_dealloc_pair(tmem_base, 512);
 }
 
 // dB[n, k] = cast( sum_s partial[s][n][k] ), s in increasing order.
@@ -226,7 +241,7 @@ __global__ void db_reduce_kernel(const float* __restrict__ partial, uint16_t* __
 }
 
 int db_default_splits(int M, int N, int K, int BN, int num_sms) {
-  const int base = ((K + 127) / 128) * (N / BN);
+  const int base = 2 * ((K + 255) / 256) * (N / BN);
   const int tokblocks = (M + 127) / 128;
   if (base >= 2 * num_sms) return 1;
   int s = (2 * num_sms + base - 1) / base;
@@ -244,7 +259,7 @@ int launch_bwd_db(const DbArgs& a) {
   p.blocks_per_split = (p.n_tokblocks + a.splits - 1) / a.splits;
   // drop splits that would own no token block
   p.splits = (p.n_tokblocks + p.blocks_per_split - 1) / p.blocks_per_split;
-  p.dc_tiles = (a.BN + 63) / 64;
+  p.dc_tiles = (a.BN / 2 + 63) / 64;   // per CTA: half of the tile's dC columns
   p.r_tile_bytes = ((a.E * 128) + 1023) / 1024 * 1024;
   p.scale = a.scale;
   p.dB = a.dB; p.lddb = a.lddb; p.partial = a.partial; p.err = a.err;
@@ -281,7 +296,7 @@ int launch_bwd_db(const DbArgs& a) {
 #undef PRISM_PICK
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return fail(PRISM_ERR_CUDA, "bwd_db: cannot set %d B of shared memory: %s", smem_bytes, cudaGetErrorString(e));
-  dim3 grid((a.K + 127) / 128, a.N / a.BN, p.splits);
+  dim3 grid(2 * ((a.K + 255) / 256), a.N / a.BN, p.splits);   // x: CTA pairs of 2 x 128 features
   kern<<<grid, db::kThreads, smem_bytes, a.stream>>>(tmA, tmR, tmdC, p);
   if ((rc = check_launch("prism_bwd_db"))) return rc;
   if (p.splits > 1) {
