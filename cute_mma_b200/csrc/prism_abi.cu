@@ -113,10 +113,10 @@ extern "C" size_t prism_workspace_bytes(int kind, int M, int N, int K, int gs, i
     const int E = effective_block(rs);
     if (E == 0) return bytes;
     int runs = (cfg && cfg[0] > 0) ? cfg[0] : dadr_default_runs(M, K, num_sms());
-    const int n_mt = (M + 127) / 128;
-    if (runs > n_mt) runs = n_mt;
+    const int n_mp = (M + 255) / 256;
+    if (runs > n_mp) runs = n_mp;
     if (runs < 1) runs = 1;
-    bytes += align256((size_t)runs * G * E * (size_t)K * 4);
+    bytes += align256((size_t)2 * runs * G * E * (size_t)K * 4);   // one buffer per CTA of every pair
     return bytes;
   }
   return bytes;

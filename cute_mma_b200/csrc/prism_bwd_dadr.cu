@@ -12,10 +12,12 @@
 // every CTA owns one exclusive partial buffer that it updates in a fixed order, and a second
 // kernel adds the buffers in a fixed order, so dR is bit-stable from run to run.
 //
-// One CTA works on a [128 tokens x 128 features] tile of dA and walks over all groups:
+// CTAs work in pairs (cluster of 2, tcgen05 cta_group::2) on [256 tokens x 128 features]: each CTA
+// owns 128 of the tokens and loads half of the B_g features, which cuts the L2 traffic per flop.
+// One CTA works on its [128 tokens x 128 features] tile of dA and walks over all groups:
 //   warp 0       TMA producer: A tiles once per tile; per group the R_g tiles and, per 64 outputs,
 //                a dC tile [128 x 64] and two B_g tiles [64 x 64]
-//   warp 1       dense issuer: dH_g = dC_g . B_g as tcgen05.mma M128 N128 K16 (dC K-major, B_g
+//   warp 1       dense issuer (leader CTA): dH_g = dC_g . B_g as tcgen05.mma M256 N128 K16 (dC K-major, B_g
 //                MN-major) into a ring of four 128-column TMEM buffers
 //   warps 4-19   gate warps, 16 tokens x 64 features each: dH fragments straight from TMEM
 //                (tcgen05.ld.16x256b delivers the mma.sync accumulator layout), A and R fragments by
@@ -38,7 +40,7 @@ constexpr int kNumDrWarps = 4;     // warps 2, 3, 20, 21
 constexpr int kDhBufs = 4;         // TMEM ring of dH buffers, 128 columns each
 constexpr int kTile = 128 * 128;   // bytes of a [128 x 64] 16-bit tile
 constexpr int kBTile = 64 * 128;   // bytes of a [64 x 64] 16-bit tile
-constexpr int kStageBytes = kTile + 2 * kBTile;
+constexpr int kStageBytes = kTile + kBTile;   // dC tile of this CTA's tokens + its half of the B_g features
 constexpr int kMaxStages = 4;
 constexpr int kMaxRBufs = 4;
 }  // namespace dadr
@@ -51,7 +53,7 @@ struct DadrParams {
   float scale;
   void* dA;
   long long ldda;
-  float* partial;      // [runs][G*E][K] fp32
+  float* partial;      // [2*runs][G*E][K] fp32: one buffer per CTA of every pair
   int* err;
 };
 
@@ -102,7 +104,7 @@ __device__ __forceinline__ uint32_t gate_bwd_pair(uint32_t a2, float s0, float s
 }
 
 template <int DT, int GATE, int E>
-__global__ void __launch_bounds__(dadr::kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(dadr::kThreads, 1)
 prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmR,
                       const __grid_constant__ CUtensorMap tmdC, const __grid_constant__ CUtensorMap tmB,
                       const DadrParams p) {
@@ -121,8 +123,10 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int f0 = blockIdx.x * 128;
-  const int run = blockIdx.y;
+  const uint32_t rank = cluster_ctarank();   // 0 = leader (issues the MMAs), 1 = peer
+  const int f0 = (blockIdx.x >> 1) * 128;    // the pair's 128 features
+  const int run = blockIdx.y;                // the pair walks token-tile pairs run, run + runs, ...
+  const int n_mpairs = (p.n_mtiles + 1) / 2;
   const int G = p.G;
   const int nstg = (p.gs + 63) / 64;  // 64-output slices per group
   const bool is_gate = warp >= kGateWarp0 && warp < kGateWarp0 + kNumGateWarps;
@@ -132,14 +136,15 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     mbar_init(&bars->a_full, 1);
     mbar_init(&bars->a_empty, kNumGateWarps + kNumDrWarps);
     for (int i = 0; i < kMaxRBufs; ++i) { mbar_init(&bars->r_full[i], 1); mbar_init(&bars->r_empty[i], kNumGateWarps); }
-    for (int i = 0; i < kMaxStages; ++i) { mbar_init(&bars->st_full[i], 1); mbar_init(&bars->st_empty[i], 1); }
-    for (int i = 0; i < kDhBufs; ++i) { mbar_init(&bars->dh_full[i], 1); mbar_init(&bars->dh_empty[i], kNumGateWarps); }
+    // st_full and dh_empty are used in the leader's copy only and count both CTAs
+    for (int i = 0; i < kMaxStages; ++i) { mbar_init(&bars->st_full[i], 2); mbar_init(&bars->st_empty[i], 1); }
+    for (int i = 0; i < kDhBufs; ++i) { mbar_init(&bars->dh_full[i], 1); mbar_init(&bars->dh_empty[i], 2 * kNumGateWarps); }
     for (int i = 0; i < 2; ++i) { mbar_init(&bars->ds_full[i], kNumGateWarps); mbar_init(&bars->ds_empty[i], kNumDrWarps); }
     fence_mbar_init();
   }
   if (warp == kWarpMma) {
-    tmem_alloc(&bars->tmem_base, 512);
-    tmem_relinquish();
+    tmem_alloc_pair(&bars->tmem_base, 512);
+    tmem_relinquish_pair();
   }
   if (warp == kWarpTma && lane == 0) {
     prefetch_tmap(&tmA);
@@ -147,8 +152,11 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     prefetch_tmap(&tmdC);
     prefetch_tmap(&tmB);
   }
+  // the peer's barriers must be initialised before anything arrives on them remotely
   tc_fence_before_sync();
   __syncthreads();
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
 
@@ -158,8 +166,8 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       bool ok = true;
       uint32_t tile_iter = 0;
       Ring rr(p.rb), rst(p.ns);
-      for (int mt = run; mt < p.n_mtiles && ok; mt += p.runs, ++tile_iter) {
-        const int m0 = mt * 128;
+      for (int mp = run; mp < n_mpairs && ok; mp += p.runs, ++tile_iter) {
+        const int m0 = (mp * 2 + (int)rank) * 128;
         if (!mbar_wait(&bars->a_empty, (tile_iter & 1) ^ 1)) { ok = false; break; }
         mbar_arrive_expect_tx(&bars->a_full, 2 * kTile);
         tma_load_2d(smemA, &tmA, &bars->a_full, f0, m0);
@@ -176,10 +184,11 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             if (!mbar_wait(&bars->st_empty[st], rst.phase ^ 1)) { ok = false; break; }
             uint8_t* dst = smemSt + st * kStageBytes;
             const int n0 = g * p.gs + s * 64;
-            mbar_arrive_expect_tx(&bars->st_full[st], kStageBytes);
-            tma_load_2d(dst, &tmdC, &bars->st_full[st], n0, m0);
-            tma_load_2d(dst + kTile, &tmB, &bars->st_full[st], f0, n0);
-            tma_load_2d(dst + kTile + kBTile, &tmB, &bars->st_full[st], f0 + 64, n0);
+            // completion is counted on the leader's barrier: its MMAs read both CTAs' tiles
+            const uint32_t stfull = mapa_shared(smem_u32(&bars->st_full[st]), 0);
+            mbar_arrive_expect_tx_cluster(stfull, kStageBytes);
+            tma_load_2d_pair(dst, &tmdC, stfull, n0, m0);
+            tma_load_2d_pair(dst + kTile, &tmB, stfull, f0 + (int)rank * 64, n0);
           }
         }
       }
@@ -187,31 +196,31 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     }
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ dense issuer: dH = dC . B
-    if (lane == 0) {
-      const uint32_t idesc_h = make_idesc(DT, 128, 128, 0, 1);   // dC K-major, B_g MN-major
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc_h = make_idesc(DT, 256, 128, 0, 1);   // M = 256 tokens; dC K-major, B_g MN-major
       bool ok = true;
       uint32_t gg = 0;
       Ring rst(p.ns);
-      for (int mt = run; mt < p.n_mtiles && ok; mt += p.runs) {
+      for (int mp = run; mp < n_mpairs && ok; mp += p.runs) {
         for (int g = 0; g < G && ok; ++g, ++gg) {
           const uint32_t hb = gg & (kDhBufs - 1);
-          if (!mbar_wait(&bars->dh_empty[hb], ((gg / kDhBufs) & 1) ^ 1)) { ok = false; break; }
+          if (!mbar_wait_cluster(&bars->dh_empty[hb], ((gg / kDhBufs) & 1) ^ 1)) { ok = false; break; }
           for (int s = 0; s < nstg; ++s, rst.next()) {
             const int st = rst.idx;
-            if (!mbar_wait(&bars->st_full[st], rst.phase)) { ok = false; break; }
+            if (!mbar_wait_cluster(&bars->st_full[st], rst.phase)) { ok = false; break; }
             tc_fence_after_sync();
             const uint32_t dc_addr = smem_u32(smemSt + st * kStageBytes);
             const uint32_t b_addr = dc_addr + kTile;
             const int ksteps = min(4, (p.gs - s * 64) / 16);
             for (int ks = 0; ks < ksteps; ++ks) {
-              umma_f16(tmem_base + hb * 128, desc_kmajor_sw128(dc_addr + ks * 32, 1024),
-                       desc_mnmajor_sw128(b_addr + ks * 2048, kBTile, 1024), idesc_h,
-                       (s > 0 || ks > 0) ? 1u : 0u);
+              umma_f16_pair(tmem_base + hb * 128, desc_kmajor_sw128(dc_addr + ks * 32, 1024),
+                            desc_mnmajor_sw128(b_addr + ks * 2048, kBTile, 1024), idesc_h,
+                            (s > 0 || ks > 0) ? 1u : 0u);
             }
-            umma_commit(&bars->st_empty[st]);
+            umma_commit_pair(&bars->st_empty[st], 0x3);
           }
           if (!ok) break;
-          umma_commit(&bars->dh_full[hb]);
+          umma_commit_pair(&bars->dh_full[hb], 0x3);
         }
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
@@ -233,7 +242,8 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     bool ok = true;
     uint32_t tile_iter = 0, gg = 0;
     Ring rr(p.rb);
-    for (int mt = run; mt < p.n_mtiles && ok; mt += p.runs, ++tile_iter) {
+    for (int mp = run; mp < n_mpairs && ok; mp += p.runs, ++tile_iter) {
+      const int mt = mp * 2 + (int)rank;
       if (!mbar_wait(&bars->a_full, tile_iter & 1)) { ok = false; break; }
       for (int g = 0; g < G && ok; ++g, ++gg, rr.next()) {
         const uint32_t hb = gg & (kDhBufs - 1), db = gg & 1;
@@ -298,7 +308,7 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(&bars->ds_full[db]);
-          mbar_arrive(&bars->dh_empty[hb]);
+          mbar_arrive_cluster(mapa_shared(smem_u32(&bars->dh_empty[hb]), 0));
           mbar_arrive(&bars->r_empty[rr.idx]);
         }
       }
@@ -328,10 +338,10 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     constexpr int n_sub = (128 / E) * spb;       // sub-tiles of this CTA's 128 features
     const int mat = lane >> 3, l8 = lane & 7;
     const long long GE = (long long)G * E;
-    float* part = p.partial + (long long)run * GE * p.K;
+    float* part = p.partial + (long long)(run * 2 + (int)rank) * GE * p.K;
     bool ok = true;
     uint32_t tile_iter = 0, gg = 0;
-    for (int mt = run; mt < p.n_mtiles && ok; mt += p.runs, ++tile_iter) {
+    for (int mp = run; mp < n_mpairs && ok; mp += p.runs, ++tile_iter) {
       if (!mbar_wait(&bars->a_full, tile_iter & 1)) { ok = false; break; }
       for (int g = 0; g < G && ok; ++g, ++gg) {
         const int buf = gg & 1;
@@ -383,9 +393,12 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
   }
 
+  // neither CTA may leave (or free TMEM) while its peer can still reach its barriers or shared memory
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == kWarpMma) tmem_dealloc(tmem_base, 512);
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+  if (warp == kWarpMma) tmem_dealloc_pair(tmem_base, 512);
 }
 
 // dR[g*rs + i, k] = cast( scale * sum_run partial[run][g*E + i'][k] ), runs in increasing order.
@@ -413,15 +426,21 @@ __global__ void dr_reduce_kernel(const float* __restrict__ partial, uint16_t* __
   *reinterpret_cast<uint32_t*>(dR + (long long)row * lddr + k) = Elem<DT>::pack(acc.x * scale, acc.y * scale);
 }
 
+// Number of CTA pairs that share one 128-feature column of dA (each pair walks every runs-th
+// 256-token tile).  Picks the count that minimises (waves of pairs over the SM pairs) x (tiles per
+// pair); ties go to the smaller count, which needs less workspace.
 int dadr_default_runs(int M, int K, int num_sms) {
   const int n_ft = (K + 127) / 128;
-  const int n_mt = (M + 127) / 128;
-  // about two CTAs' worth of work per SM, but never more runs than token tiles
-  int runs = (2 * num_sms + n_ft - 1) / n_ft;
-  if (n_ft >= num_sms) runs = 1;
-  if (runs > n_mt) runs = n_mt;
-  if (runs > 64) runs = 64;
-  return runs < 1 ? 1 : runs;
+  const int n_mp = (M + 255) / 256;
+  const int slots = num_sms / 2 > 0 ? num_sms / 2 : 1;
+  int best = 1;
+  long long best_cost = -1;
+  for (int r = 1; r <= n_mp && r <= 32; ++r) {
+    const long long waves = ((long long)n_ft * r + slots - 1) / slots;
+    const long long cost = waves * ((n_mp + r - 1) / r);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = r; }
+  }
+  return best;
 }
 
 int launch_bwd_dadr(const DadrArgs& a) {
@@ -429,7 +448,7 @@ int launch_bwd_dadr(const DadrArgs& a) {
   p.M = a.M; p.N = a.N; p.K = a.K; p.gs = a.gs; p.E = a.E; p.G = a.N / a.gs;
   p.n_mtiles = (a.M + 127) / 128;
   p.runs = a.runs < 1 ? 1 : a.runs;
-  if (p.runs > p.n_mtiles) p.runs = p.n_mtiles;
+  if (p.runs > (p.n_mtiles + 1) / 2) p.runs = (p.n_mtiles + 1) / 2;
   p.r_tile_bytes = ((a.E * 128) + 1023) / 1024 * 1024;
   p.scale = a.scale;
   p.dA = a.dA; p.ldda = a.ldda; p.partial = a.partial; p.err = a.err;
@@ -459,7 +478,7 @@ int launch_bwd_dadr(const DadrArgs& a) {
 #undef PRISM_PICK
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return fail(PRISM_ERR_CUDA, "bwd_dadr: cannot set %d B of shared memory: %s", smem_bytes, cudaGetErrorString(e));
-  dim3 grid((a.K + 127) / 128, p.runs, 1);
+  dim3 grid(2 * ((a.K + 127) / 128), p.runs, 1);   // x: the two CTAs of a pair
   kern<<<grid, dadr::kThreads, smem_bytes, a.stream>>>(tmA, tmR, tmdC, tmB, p);
   if ((rc = check_launch("prism_bwd_dadr"))) return rc;
 
@@ -467,9 +486,9 @@ int launch_bwd_dadr(const DadrArgs& a) {
   const int threads = 256;
   const long long blocks = (pairs + threads - 1) / threads;
   if (a.dtype == DT_BF16)
-    dr_reduce_kernel<DT_BF16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, reinterpret_cast<uint16_t*>(a.dR), p.G, a.rs, a.E, a.K, a.lddr, p.runs, a.scale);
+    dr_reduce_kernel<DT_BF16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, reinterpret_cast<uint16_t*>(a.dR), p.G, a.rs, a.E, a.K, a.lddr, 2 * p.runs, a.scale);
   else
-    dr_reduce_kernel<DT_F16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, reinterpret_cast<uint16_t*>(a.dR), p.G, a.rs, a.E, a.K, a.lddr, p.runs, a.scale);
+    dr_reduce_kernel<DT_F16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, reinterpret_cast<uint16_t*>(a.dR), p.G, a.rs, a.E, a.K, a.lddr, 2 * p.runs, a.scale);
   return check_launch("prism_bwd_dadr reduce");
 }
 

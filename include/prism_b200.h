@@ -75,9 +75,9 @@ int prism_fwd_noalloc(const void* A, const void* B, const void* R, const void* b
                       const int* cfg, int* device_status, void* stream);
 
 /* Input and rotation gradients: dA [M,K] and dR [(N/group_size)*reconn_sz, K], both scaled by
- * dc_scale.  cfg (1 int): {runs} -- the number of CTAs that share one 128-feature column of dA;
- * each accumulates dR into its own fp32 buffer in the workspace in a fixed order and a second
- * kernel adds the buffers in a fixed order: dR is bit-identical from run to run. */
+ * dc_scale.  cfg (1 int): {runs} -- the number of CTA pairs that share one 128-feature column of
+ * dA; each CTA accumulates dR into its own fp32 buffer in the workspace in a fixed order and a
+ * second kernel adds the buffers in a fixed order: dR is bit-identical from run to run. */
 int prism_bwd_dadr(const void* dC, const void* A, const void* B, const void* R, void* dA, void* dR,
                    int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
                    float dc_scale, long long lddc, long long lda, long long ldb, long long ldr,
