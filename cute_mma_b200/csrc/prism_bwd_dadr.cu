@@ -29,6 +29,10 @@
 #include "prism_host.cuh"
 #include "prism_kernels.cuh"
 
+#ifndef PRISM_DBG
+#define PRISM_DBG 0   // debugging aid: bit 0 skips the gate warps' work, bit 1 the dR warps' work
+#endif
+
 namespace prism {
 
 namespace dadr {
@@ -255,7 +259,7 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         const uint32_t rtile = smem_u32(smemR + rr.idx * r_buf_bytes + ch * p.r_tile_bytes);
         const uint32_t tdh = tmem_base + lane_base + hb * 128 + ch * 64;
 #pragma unroll
-        for (int b = 0; b < NB; ++b) {
+        for (int b = 0; b < ((PRISM_DBG & 1) ? 0 : NB); ++b) {
           uint32_t af[KS][4], dsf[KS][4];
           if (GATE == GATE_SILU) {
 #pragma unroll
@@ -346,7 +350,7 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       for (int g = 0; g < G && ok; ++g, ++gg) {
         const int buf = gg & 1;
         if (!mbar_wait(&bars->ds_full[buf], (gg >> 1) & 1)) { ok = false; break; }
-        for (int u = w; u < n_sub; u += kNumDrWarps) {
+        for (int u = w; u < ((PRISM_DBG & 2) ? 0 : n_sub); u += kNumDrWarps) {
           const int block = u / spb, rem = u - block * spb;
           const int is = rem / KS, js = rem - is * KS;
           const int chunk = block / NB, b = block - chunk * NB;
