@@ -16,7 +16,7 @@
 // owns 128 of the tokens and loads half of the B_g features, which cuts the L2 traffic per flop.
 // One CTA works on its [128 tokens x 128 features] tile of dA and walks over all groups:
 //   warp 0       TMA producer: A tiles once per tile; per group the R_g tiles and, per 64 outputs,
-//                a dC tile [128 x 64] and two B_g tiles [64 x 64]
+//                two dC tiles [128 x 64] and this CTA's B_g tile [128 x 64]
 //   warp 1       dense issuer (leader CTA): dH_g = dC_g . B_g as tcgen05.mma M256 N128 K16 (dC K-major, B_g
 //                MN-major) into a ring of four 128-column TMEM buffers
 //   warps 4-19   gate warps, 16 tokens x 64 features each: dH fragments straight from TMEM
@@ -43,8 +43,9 @@ constexpr int kNumGateWarps = 16;
 constexpr int kNumDrWarps = 4;     // warps 2, 3, 20, 21
 constexpr int kDhBufs = 4;         // TMEM ring of dH buffers, 128 columns each
 constexpr int kTile = 128 * 128;   // bytes of a [128 x 64] 16-bit tile
-constexpr int kBTile = 64 * 128;   // bytes of a [64 x 64] 16-bit tile
-constexpr int kStageBytes = kTile + kBTile;   // dC tile of this CTA's tokens + its half of the B_g features
+constexpr int kBTile = 128 * 128;  // bytes of a [128 outputs x 64 features] 16-bit tile
+// one stage = 128 outputs of the group: two dC tiles [128 tokens x 64] and this CTA's half of the B_g features
+constexpr int kStageBytes = 2 * kTile + kBTile;
 constexpr int kMaxStages = 4;
 constexpr int kMaxRBufs = 4;
 }  // namespace dadr
@@ -132,7 +133,7 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int run = blockIdx.y;                // the pair walks token-tile pairs run, run + runs, ...
   const int n_mpairs = (p.n_mtiles + 1) / 2;
   const int G = p.G;
-  const int nstg = (p.gs + 63) / 64;  // 64-output slices per group
+  const int nstg = (p.gs + 127) / 128;  // 128-output slices per group
   const bool is_gate = warp >= kGateWarp0 && warp < kGateWarp0 + kNumGateWarps;
   const bool is_dr = warp == 2 || warp == 3 || warp >= kGateWarp0 + kNumGateWarps;
 
@@ -187,12 +188,14 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             const int st = rst.idx;
             if (!mbar_wait(&bars->st_empty[st], rst.phase ^ 1)) { ok = false; break; }
             uint8_t* dst = smemSt + st * kStageBytes;
-            const int n0 = g * p.gs + s * 64;
+            const int n0 = g * p.gs + s * 128;
+            const bool two = p.gs - s * 128 > 64;   // the slice has more than 64 outputs
             // completion is counted on the leader's barrier: its MMAs read both CTAs' tiles
             const uint32_t stfull = mapa_shared(smem_u32(&bars->st_full[st]), 0);
-            mbar_arrive_expect_tx_cluster(stfull, kStageBytes);
+            mbar_arrive_expect_tx_cluster(stfull, (two ? 2 : 1) * kTile + kBTile);
             tma_load_2d_pair(dst, &tmdC, stfull, n0, m0);
-            tma_load_2d_pair(dst + kTile, &tmB, stfull, f0 + (int)rank * 64, n0);
+            if (two) tma_load_2d_pair(dst + kTile, &tmdC, stfull, n0 + 64, m0);
+            tma_load_2d_pair(dst + 2 * kTile, &tmB, stfull, f0 + (int)rank * 64, n0);
           }
         }
       }
@@ -214,10 +217,10 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             if (!mbar_wait_cluster(&bars->st_full[st], rst.phase)) { ok = false; break; }
             tc_fence_after_sync();
             const uint32_t dc_addr = smem_u32(smemSt + st * kStageBytes);
-            const uint32_t b_addr = dc_addr + kTile;
-            const int ksteps = min(4, (p.gs - s * 64) / 16);
+            const uint32_t b_addr = dc_addr + 2 * kTile;
+            const int ksteps = min(8, (p.gs - s * 128) / 16);
             for (int ks = 0; ks < ksteps; ++ks) {
-              umma_f16_pair(tmem_base + hb * 128, desc_kmajor_sw128(dc_addr + ks * 32, 1024),
+              umma_f16_pair(tmem_base + hb * 128, desc_kmajor_sw128(dc_addr + (ks >> 2) * kTile + (ks & 3) * 32, 1024),
                             desc_mnmajor_sw128(b_addr + ks * 2048, kBTile, 1024), idesc_h,
                             (s > 0 || ks > 0) ? 1u : 0u);
             }
@@ -470,7 +473,7 @@ int launch_bwd_dadr(const DadrArgs& a) {
   if ((rc = make_tmap_2d(&tmA, a.dtype, a.A, a.M, a.K, a.lda, 128, 64, true))) return rc;
   if ((rc = make_tmap_2d(&tmR, a.dtype, a.R_eff, (uint64_t)p.G * a.E, a.K, a.ldr, a.E, 64, true))) return rc;
   if ((rc = make_tmap_2d(&tmdC, a.dtype, a.dC, a.M, a.N, a.lddc, 128, 64, true))) return rc;
-  if ((rc = make_tmap_2d(&tmB, a.dtype, a.B, a.N, a.K, a.ldb, 64, 64, true))) return rc;
+  if ((rc = make_tmap_2d(&tmB, a.dtype, a.B, a.N, a.K, a.ldb, 128, 64, true))) return rc;
 
   using KernT = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, DadrParams);
   KernT kern = nullptr;
