@@ -92,11 +92,12 @@ template <int DT> struct NegHalf;
 template <> struct NegHalf<DT_F16> { static constexpr uint32_t v = 0xB800B800u; };
 template <> struct NegHalf<DT_BF16> { static constexpr uint32_t v = 0xBF00BF00u; };
 
-// One pair of elements of the gated backward: returns dS (packed) and adds dh*silu(s) to acc0/acc1.
+// One pair of elements of the gated backward (sp = packed S): returns dS (packed) and adds
+// dh*silu(s) to acc0/acc1.
 template <int DT>
-__device__ __forceinline__ uint32_t gate_bwd_pair(uint32_t a2, float s0, float s1, float dh0, float dh1,
+__device__ __forceinline__ uint32_t gate_bwd_pair(uint32_t a2, uint32_t sp, float dh0, float dh1,
                                                   float& acc0, float& acc1) {
-  const uint32_t hs = Pk<DT>::mul(Pk<DT>::cvt(s0, s1), Pk<DT>::kHalf);
+  const uint32_t hs = Pk<DT>::mul(sp, Pk<DT>::kHalf);
   const uint32_t t = Pk<DT>::tanh(hs);
   const uint32_t g = Pk<DT>::fma(hs, t, hs);                          // silu(s)
   const uint32_t sg = Pk<DT>::fma(t, Pk<DT>::kHalf, Pk<DT>::kHalf);   // sigmoid(s)
@@ -273,24 +274,39 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           for (int np = 0; np < KS; ++np) {
             uint32_t dh[8];
             tmem_ld_16x256b_x2(tdh + b * E + np * 16, dh);
-            float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t sp[4] = {0u, 0u, 0u, 0u};   // packed S of this thread's four pairs
             if (GATE == GATE_SILU) {
+              if (DT == DT_F16) {
+                uint32_t c0[2] = {0u, 0u}, c1[2] = {0u, 0u};   // fp16 accumulation: packed result
 #pragma unroll
-              for (int ks = 0; ks < KS; ++ks) {
-                uint32_t rf[4];
-                ldmatrix_x4(rtile + sw128_offset(np * 16 + rn_row, b * (E / 8) + ks * 2 + (mat & 1)), rf);
-                mma_m16n8k16<DT>(c0, af[ks], rf[0], rf[1]);
-                mma_m16n8k16<DT>(c1, af[ks], rf[2], rf[3]);
+                for (int ks = 0; ks < KS; ++ks) {
+                  uint32_t rf[4];
+                  ldmatrix_x4(rtile + sw128_offset(np * 16 + rn_row, b * (E / 8) + ks * 2 + (mat & 1)), rf);
+                  mma_m16n8k16_f16acc(c0, af[ks], rf[0], rf[1]);
+                  mma_m16n8k16_f16acc(c1, af[ks], rf[2], rf[3]);
+                }
+                sp[0] = c0[0]; sp[1] = c0[1]; sp[2] = c1[0]; sp[3] = c1[1];
+              } else {
+                float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks) {
+                  uint32_t rf[4];
+                  ldmatrix_x4(rtile + sw128_offset(np * 16 + rn_row, b * (E / 8) + ks * 2 + (mat & 1)), rf);
+                  mma_m16n8k16<DT>(c0, af[ks], rf[0], rf[1]);
+                  mma_m16n8k16<DT>(c1, af[ks], rf[2], rf[3]);
+                }
+                sp[0] = Pk<DT>::cvt(c0[0], c0[1]); sp[1] = Pk<DT>::cvt(c0[2], c0[3]);
+                sp[2] = Pk<DT>::cvt(c1[0], c1[1]); sp[3] = Pk<DT>::cvt(c1[2], c1[3]);
               }
             }
             tmem_ld_wait();
             float* d0 = dacc[(b * KS + np) * 2];
             float* d1 = dacc[(b * KS + np) * 2 + 1];
             if (GATE == GATE_SILU) {
-              dsf[np][0] = gate_bwd_pair<DT>(af[np][0], c0[0], c0[1], __uint_as_float(dh[0]), __uint_as_float(dh[1]), d0[0], d0[1]);
-              dsf[np][1] = gate_bwd_pair<DT>(af[np][1], c0[2], c0[3], __uint_as_float(dh[2]), __uint_as_float(dh[3]), d0[2], d0[3]);
-              dsf[np][2] = gate_bwd_pair<DT>(af[np][2], c1[0], c1[1], __uint_as_float(dh[4]), __uint_as_float(dh[5]), d1[0], d1[1]);
-              dsf[np][3] = gate_bwd_pair<DT>(af[np][3], c1[2], c1[3], __uint_as_float(dh[6]), __uint_as_float(dh[7]), d1[2], d1[3]);
+              dsf[np][0] = gate_bwd_pair<DT>(af[np][0], sp[0], __uint_as_float(dh[0]), __uint_as_float(dh[1]), d0[0], d0[1]);
+              dsf[np][1] = gate_bwd_pair<DT>(af[np][1], sp[1], __uint_as_float(dh[2]), __uint_as_float(dh[3]), d0[2], d0[3]);
+              dsf[np][2] = gate_bwd_pair<DT>(af[np][2], sp[2], __uint_as_float(dh[4]), __uint_as_float(dh[5]), d1[0], d1[1]);
+              dsf[np][3] = gate_bwd_pair<DT>(af[np][3], sp[3], __uint_as_float(dh[6]), __uint_as_float(dh[7]), d1[2], d1[3]);
             } else {
               dsf[np][0] = Pk<DT>::cvt(__uint_as_float(dh[0]), __uint_as_float(dh[1]));
               dsf[np][1] = Pk<DT>::cvt(__uint_as_float(dh[2]), __uint_as_float(dh[3]));

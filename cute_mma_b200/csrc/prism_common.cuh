@@ -441,10 +441,13 @@ struct Pk<DT_F16> {
 template <>
 struct Pk<DT_BF16> {
   static constexpr uint32_t kHalf = 0x3F003F00u;
+  // fp32 pair -> bf16x2 with integer ops: add half an ulp to the bit patterns and keep the upper
+  // halves (round to nearest, ties away from zero).  The cvt.rn.bf16x2.f32 instruction runs on the
+  // 16-lane/clk special-function pipe (measured: as expensive as a tanh), these three ALU ops do not.
   __device__ __forceinline__ static uint32_t cvt(float lo, float hi) {
-    uint32_t d;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
-    return d;
+    const uint32_t ulo = __float_as_uint(lo) + 0x8000u;
+    const uint32_t uhi = __float_as_uint(hi) + 0x8000u;
+    return __byte_perm(ulo, uhi, 0x7632);
   }
   __device__ __forceinline__ static uint32_t mul(uint32_t a, uint32_t b) {
     uint32_t d;
@@ -563,6 +566,23 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[
   }
 }
 
+// fp16 operands with fp16 accumulation: the accumulator comes out as packed pairs, ready for the
+// packed gate math without an f32 -> f16 conversion (special-function pipe).  The reference's own
+// fp16 kernels accumulate the rotation in fp16 as well (cute_prism_dtype.hpp:55-66).
+__device__ __forceinline__ void mma_m16n8k16_f16acc(uint32_t (&d)[2], const uint32_t (&a)[4], uint32_t b0,
+                                                    uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f16.f16.f16.f16 {%0, %1}, {%2, %3, %4, %5}, {%6, %7}, {%0, %1};"
+      : "+r"(d[0]), "+r"(d[1])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// silu of a packed pair: with hs = s/2, silu(s) = hs + hs*tanh(hs)
+template <int DT>
+__device__ __forceinline__ uint32_t silu_packed(uint32_t sp) {
+  const uint32_t hs = Pk<DT>::mul(sp, Pk<DT>::kHalf);
+  return Pk<DT>::fma(hs, Pk<DT>::tanh(hs), hs);
+}
+
 // H for one pair of elements from fp32 S and packed 16-bit A: A*silu(S), or S in plain mode.
 template <int DT, int GATE>
 __device__ __forceinline__ uint32_t gate_pair(uint32_t a2, float s0, float s1) {
@@ -598,19 +618,38 @@ __device__ __forceinline__ void rotate_gate_rows16(uint32_t tile, uint32_t rtile
       ldmatrix_x4(tile + sw128_offset(a_row, b * (E / 8) + ks * 2 + (mat >> 1)), af[ks]);
 #pragma unroll
     for (int np = 0; np < KS; ++np) {
-      float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int ks = 0; ks < KS; ++ks) {
-        uint32_t rf[4];
-        ldmatrix_x4(rtile + sw128_offset(np * 16 + r_row, b * (E / 8) + ks * 2 + (mat & 1)), rf);
-        mma_m16n8k16<DT>(c0, af[ks], rf[0], rf[1]);
-        mma_m16n8k16<DT>(c1, af[ks], rf[2], rf[3]);
-      }
       uint32_t h[4];
-      h[0] = gate_pair<DT, GATE>(af[np][0], c0[0], c0[1]);
-      h[1] = gate_pair<DT, GATE>(af[np][1], c0[2], c0[3]);
-      h[2] = gate_pair<DT, GATE>(af[np][2], c1[0], c1[1]);
-      h[3] = gate_pair<DT, GATE>(af[np][3], c1[2], c1[3]);
+      if (DT == DT_F16) {
+        uint32_t c0[2] = {0u, 0u}, c1[2] = {0u, 0u};   // packed fp16 accumulators
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          uint32_t rf[4];
+          ldmatrix_x4(rtile + sw128_offset(np * 16 + r_row, b * (E / 8) + ks * 2 + (mat & 1)), rf);
+          mma_m16n8k16_f16acc(c0, af[ks], rf[0], rf[1]);
+          mma_m16n8k16_f16acc(c1, af[ks], rf[2], rf[3]);
+        }
+        if (GATE == GATE_SILU) {
+          h[0] = Pk<DT>::mul(af[np][0], silu_packed<DT>(c0[0]));
+          h[1] = Pk<DT>::mul(af[np][1], silu_packed<DT>(c0[1]));
+          h[2] = Pk<DT>::mul(af[np][2], silu_packed<DT>(c1[0]));
+          h[3] = Pk<DT>::mul(af[np][3], silu_packed<DT>(c1[1]));
+        } else {
+          h[0] = c0[0]; h[1] = c0[1]; h[2] = c1[0]; h[3] = c1[1];
+        }
+      } else {
+        float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          uint32_t rf[4];
+          ldmatrix_x4(rtile + sw128_offset(np * 16 + r_row, b * (E / 8) + ks * 2 + (mat & 1)), rf);
+          mma_m16n8k16<DT>(c0, af[ks], rf[0], rf[1]);
+          mma_m16n8k16<DT>(c1, af[ks], rf[2], rf[3]);
+        }
+        h[0] = gate_pair<DT, GATE>(af[np][0], c0[0], c0[1]);
+        h[1] = gate_pair<DT, GATE>(af[np][1], c0[2], c0[3]);
+        h[2] = gate_pair<DT, GATE>(af[np][2], c1[0], c1[1]);
+        h[3] = gate_pair<DT, GATE>(af[np][3], c1[2], c1[3]);
+      }
       stmatrix_x4(tile + sw128_offset(a_row, b * (E / 8) + np * 2 + (mat >> 1)), h);
     }
   }
