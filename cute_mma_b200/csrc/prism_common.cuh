@@ -306,6 +306,19 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, u
       : "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same, with the A operand read from TMEM (lane = row, each 32-bit column = two K elements).
+__device__ __forceinline__ void umma_f16_pair_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive (count 1) on the barrier at this shared-memory offset in every CTA of `cta_mask`
 // once all MMAs issued so far by this thread are complete.
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
@@ -318,6 +331,17 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mas
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// registers -> TMEM: an mma.sync A-operand fragment (16 rows x 16 K elements of 16-bit data, four
+// registers) lands as [lane = row][column = k/2]; taddr's lane field is the first of the 16 rows.
+__device__ __forceinline__ void tmem_st_frag16x16(uint32_t taddr, const uint32_t (&r)[4]) {
+  asm volatile("tcgen05.st.sync.aligned.16x128b.x2.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+               "r"(r[2]), "r"(r[3])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
 // ----------------------------------------------------------------------------
@@ -604,53 +628,91 @@ __device__ __forceinline__ uint32_t gate_pair(uint32_t a2, float s0, float s1) {
 // Per rotation block: A fragments by ldmatrix, S by mma.sync against R fragments; an A fragment
 // and the S accumulators of the same 16 columns hold the same (row, column) elements in the same
 // lanes, so the gate is elementwise on registers and H goes back with stmatrix to where A came from.
-template <int DT, int GATE, int E>
-__device__ __forceinline__ void rotate_gate_rows16(uint32_t tile, uint32_t rtile, uint32_t r0, int lane) {
-  constexpr int KS = E / 16;           // 16-wide k-steps (= 16-column output pairs) per block
+// h_tmem = 0: H goes back into the A tile (stmatrix); otherwise H is written to TMEM at h_tmem
+// (lane field = r0) as the A operand of the dense tcgen05.mma, 8 columns per 16 K elements.
+// The 64 columns are four 16-wide pieces; PP of them are processed together, phase by phase (all
+// loads, all MMAs, all gate math, all stores), so that a warp has PP independent dependency chains
+// in flight: with one chain per warp the gate warps are latency-bound.
+template <int DT, int GATE, int E, int PP = 4>
+__device__ __forceinline__ void rotate_gate_rows16(uint32_t tile, uint32_t rtile, uint32_t r0, int lane,
+                                                   uint32_t h_tmem = 0) {
+  constexpr int KS = E / 16;           // 16-wide k-steps (= 16-column output pieces) per rotation block
+  static_assert(PP == 2 || PP == 4, "pieces per pass");
+  static_assert(PP % KS == 0 || KS % PP == 0, "a pass must not straddle rotation blocks unevenly");
   const uint32_t mat = lane >> 3, l8 = lane & 7;
   const uint32_t a_row = r0 + l8 + (mat & 1) * 8;   // A operand: matrices (r-lo,k-lo) (r-hi,k-lo) (r-lo,k-hi) (r-hi,k-hi)
   const uint32_t r_row = l8 + (mat >> 1) * 8;       // B operand: matrices (n-lo,k-lo) (n-lo,k-hi) (n-hi,k-lo) (n-hi,k-hi)
 #pragma unroll
-  for (int b = 0; b < 64 / E; ++b) {
-    uint32_t af[KS][4];
+  for (int pass = 0; pass < 4 / PP; ++pass) {
+    // A fragments of every 16-wide piece that this pass reads: the pieces of the blocks it covers
+    constexpr int NA = (PP > KS) ? PP : KS;          // pieces of A needed (whole rotation blocks)
+    const int pa0 = (pass * PP / NA) * NA;           // first A piece (block aligned)
+    uint32_t af[NA][4];
 #pragma unroll
-    for (int ks = 0; ks < KS; ++ks)
-      ldmatrix_x4(tile + sw128_offset(a_row, b * (E / 8) + ks * 2 + (mat >> 1)), af[ks]);
+    for (int i = 0; i < NA; ++i)
+      ldmatrix_x4(tile + sw128_offset(a_row, (pa0 + i) * 2 + (mat >> 1)), af[i]);
+    float c[PP][2][4];
+    uint32_t ch[PP][2][2];
 #pragma unroll
-    for (int np = 0; np < KS; ++np) {
-      uint32_t h[4];
-      if (DT == DT_F16) {
-        uint32_t c0[2] = {0u, 0u}, c1[2] = {0u, 0u};   // packed fp16 accumulators
+    for (int i = 0; i < PP; ++i) {
 #pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-          uint32_t rf[4];
-          ldmatrix_x4(rtile + sw128_offset(np * 16 + r_row, b * (E / 8) + ks * 2 + (mat & 1)), rf);
-          mma_m16n8k16_f16acc(c0, af[ks], rf[0], rf[1]);
-          mma_m16n8k16_f16acc(c1, af[ks], rf[2], rf[3]);
-        }
-        if (GATE == GATE_SILU) {
-          h[0] = Pk<DT>::mul(af[np][0], silu_packed<DT>(c0[0]));
-          h[1] = Pk<DT>::mul(af[np][1], silu_packed<DT>(c0[1]));
-          h[2] = Pk<DT>::mul(af[np][2], silu_packed<DT>(c1[0]));
-          h[3] = Pk<DT>::mul(af[np][3], silu_packed<DT>(c1[1]));
+      for (int t = 0; t < 2; ++t) {
+        c[i][t][0] = c[i][t][1] = c[i][t][2] = c[i][t][3] = 0.f;
+        ch[i][t][0] = ch[i][t][1] = 0u;
+      }
+    }
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      uint32_t rf[PP][4];
+#pragma unroll
+      for (int i = 0; i < PP; ++i) {
+        const int pc = pass * PP + i;                // output piece: block b, 16-column part np
+        const int b = pc / KS, np = pc % KS;
+        ldmatrix_x4(rtile + sw128_offset(np * 16 + r_row, b * (E / 8) + ks * 2 + (mat & 1)), rf[i]);
+      }
+#pragma unroll
+      for (int i = 0; i < PP; ++i) {
+        const int pc = pass * PP + i;
+        const int b = pc / KS;
+        const uint32_t (&a)[4] = af[b * KS + ks - pa0];
+        if (DT == DT_F16) {
+          mma_m16n8k16_f16acc(ch[i][0], a, rf[i][0], rf[i][1]);
+          mma_m16n8k16_f16acc(ch[i][1], a, rf[i][2], rf[i][3]);
         } else {
-          h[0] = c0[0]; h[1] = c0[1]; h[2] = c1[0]; h[3] = c1[1];
+          mma_m16n8k16<DT>(c[i][0], a, rf[i][0], rf[i][1]);
+          mma_m16n8k16<DT>(c[i][1], a, rf[i][2], rf[i][3]);
+        }
+      }
+    }
+    uint32_t h[PP][4];
+#pragma unroll
+    for (int i = 0; i < PP; ++i) {
+      const int pc = pass * PP + i;
+      const uint32_t (&a)[4] = af[pc - pa0];         // the A values of this output piece's columns
+      if (DT == DT_F16) {
+        if (GATE == GATE_SILU) {
+          h[i][0] = Pk<DT>::mul(a[0], silu_packed<DT>(ch[i][0][0]));
+          h[i][1] = Pk<DT>::mul(a[1], silu_packed<DT>(ch[i][0][1]));
+          h[i][2] = Pk<DT>::mul(a[2], silu_packed<DT>(ch[i][1][0]));
+          h[i][3] = Pk<DT>::mul(a[3], silu_packed<DT>(ch[i][1][1]));
+        } else {
+          h[i][0] = ch[i][0][0]; h[i][1] = ch[i][0][1]; h[i][2] = ch[i][1][0]; h[i][3] = ch[i][1][1];
         }
       } else {
-        float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-          uint32_t rf[4];
-          ldmatrix_x4(rtile + sw128_offset(np * 16 + r_row, b * (E / 8) + ks * 2 + (mat & 1)), rf);
-          mma_m16n8k16<DT>(c0, af[ks], rf[0], rf[1]);
-          mma_m16n8k16<DT>(c1, af[ks], rf[2], rf[3]);
-        }
-        h[0] = gate_pair<DT, GATE>(af[np][0], c0[0], c0[1]);
-        h[1] = gate_pair<DT, GATE>(af[np][1], c0[2], c0[3]);
-        h[2] = gate_pair<DT, GATE>(af[np][2], c1[0], c1[1]);
-        h[3] = gate_pair<DT, GATE>(af[np][3], c1[2], c1[3]);
+        h[i][0] = gate_pair<DT, GATE>(a[0], c[i][0][0], c[i][0][1]);
+        h[i][1] = gate_pair<DT, GATE>(a[1], c[i][0][2], c[i][0][3]);
+        h[i][2] = gate_pair<DT, GATE>(a[2], c[i][1][0], c[i][1][1]);
+        h[i][3] = gate_pair<DT, GATE>(a[3], c[i][1][2], c[i][1][3]);
       }
-      stmatrix_x4(tile + sw128_offset(a_row, b * (E / 8) + np * 2 + (mat >> 1)), h);
+    }
+#pragma unroll
+    for (int i = 0; i < PP; ++i) {
+      const int pc = pass * PP + i;
+      if (h_tmem != 0) {
+        tmem_st_frag16x16(h_tmem + pc * 8, h[i]);
+      } else {
+        stmatrix_x4(tile + sw128_offset(a_row, pc * 2 + (mat >> 1)), h[i]);
+      }
     }
   }
 }

@@ -9,15 +9,16 @@
 // CTAs work in pairs (cluster of 2, tcgen05 cta_group::2) on (256-row, BN-column) output tiles: each CTA
 // owns 128 of the rows and loads half of the B tile, which halves the L2 traffic per flop.  Per CTA a
 // persistent loop over the pair's tiles; per 64-wide K chunk
-//   warp 0      TMA producer: A tile [128 x 64] + R_g tile [E x 64] into the "AR" ring, B_g tile
-//               [BN x 64] into the "B" ring (128-byte swizzle, zero fill outside the tensors)
-//   warps 2-17  gate warps, two groups of eight that take alternate chunks, 16 rows per warp: A and R fragments by ldmatrix, block rotation
+//   warps 0, 2  TMA producers: A tile [128 x 64] + R_g tile [E x 64] into the "AR" ring (warp 0), this
+//               CTA's half of the B_g tile [BN/2 x 64] into the "B" ring (warp 2); 128-byte swizzle,
+//               zero fill outside the tensors
+//   warps 4-19  gate warps, two groups of eight that take alternate chunks, 16 rows per warp: A and R fragments by ldmatrix, block rotation
 //               S = A_blk . R_blk^T by mma.sync (fp32), H = A*silu(S) (or H = S) on registers,
-//               stmatrix of H over the A tile in place
+//               H written to TMEM (tcgen05.st) as the A operand of the dense MMA: H never goes
+//               through shared memory, which is the scarce resource of this kernel
 //   warp 1      dense issuer (leader CTA only): C += H . B^T as 4 x tcgen05.mma M256 N=BN K=16 spanning
-//               both CTAs, fp32 in TMEM,
-//               two accumulators so that the epilogue of a tile overlaps the next tile
-//   warps 18-21 epilogue: tcgen05.ld C, + bias, cast, swizzled staging tile, TMA store.
+//               both CTAs (A = H from TMEM, B = B_g from shared memory), fp32 accumulator in TMEM
+//   warps 20-23 epilogue: tcgen05.ld C, + bias, cast, swizzled staging tile, TMA store.
 // Every role keeps its ring positions as counters; the single-thread roles do no division.
 #include "prism_host.cuh"
 #include "prism_kernels.cuh"
@@ -29,13 +30,15 @@
 namespace prism {
 
 namespace fwd {
-constexpr int kThreads = 704;
-constexpr int kWarpTma = 0, kWarpMma = 1;
-constexpr int kGateWarp0 = 2;
+constexpr int kThreads = 768;
+constexpr int kWarpTma = 0, kWarpMma = 1, kWarpTmaB = 2;
+constexpr int kGateWarp0 = 4;         // multiple of 4: (warp & 3) is the TMEM lane quarter a warp may touch
 constexpr int kGateGroups = 2;        // groups take alternate chunks ...
 constexpr int kWarpsPerGroup = 8;     // ... with 16 rows per warp
 constexpr int kNumGateWarps = kGateGroups * kWarpsPerGroup;
-constexpr int kEpiWarp0 = kGateWarp0 + kNumGateWarps;   // 18: (warp & 3) of warps 18..21 covers 2,3,0,1
+constexpr int kEpiWarp0 = kGateWarp0 + kNumGateWarps;   // 20
+constexpr int kHBufs = 4;             // TMEM ring of H chunks (power of two), 32 columns each
+constexpr int kHCol0 = 256;           // accumulator: TMEM columns [0, 256); H ring: [256, 384)
 constexpr int kNumEpiWarps = 4;
 constexpr int kMaxStages = 8;
 constexpr int kATileBytes = 128 * 128;   // [128 rows x 64 elems] 16-bit
@@ -60,12 +63,11 @@ struct FwdParams {
 
 struct FwdBarriers {
   uint64_t ar_full[fwd::kMaxStages];
-  uint64_t h_full[fwd::kMaxStages];
   uint64_t a_empty[fwd::kMaxStages];
-  uint64_t b_full[fwd::kMaxStages];
-  uint64_t b_empty[fwd::kMaxStages];
-  uint64_t acc_full[2];
-  uint64_t acc_empty[2];
+  uint64_t hb_full[fwd::kHBufs];    // H chunk in TMEM (both CTAs' gate warps) and both B halves in shared memory
+  uint64_t hb_empty[fwd::kHBufs];   // the dense MMAs of the chunk are done: H buffer and B stage are free
+  uint64_t acc_full;
+  uint64_t acc_empty;
   uint32_t tmem_base;
 };
 
@@ -105,15 +107,15 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int i = 0; i < kMaxStages; ++i) {
       mbar_init(&bars->ar_full[i], 1);                    // local: this CTA's A and R tiles landed
-      mbar_init(&bars->h_full[i], 2 * kWarpsPerGroup);    // leader's copy is used: gate warps of both CTAs
-      mbar_init(&bars->a_empty[i], 1);                    // local, arrived by the multicast commit
-      mbar_init(&bars->b_full[i], 2);                     // leader's copy is used: both CTAs' B halves
-      mbar_init(&bars->b_empty[i], 1);
+      mbar_init(&bars->a_empty[i], kWarpsPerGroup);       // local: the gate warps have read the tiles
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars->acc_full[i], 1);                   // local, arrived by the multicast commit
-      mbar_init(&bars->acc_empty[i], 2 * kNumEpiWarps);   // leader's copy is used
+    for (int i = 0; i < kHBufs; ++i) {
+      // leader's copy is used: gate warps of both CTAs + the two B producers (with their byte counts)
+      mbar_init(&bars->hb_full[i], 2 * kWarpsPerGroup + 2);
+      mbar_init(&bars->hb_empty[i], 1);                   // local, arrived by the multicast commit
     }
+    mbar_init(&bars->acc_full, 1);                        // local, arrived by the multicast commit
+    mbar_init(&bars->acc_empty, 2 * kNumEpiWarps);        // leader's copy is used
     fence_mbar_init();
   }
   if (warp == kWarpMma) {
@@ -138,44 +140,45 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t total = (uint32_t)my_tiles * nk;   // chunks this CTA pair processes
 
   if (warp == kWarpTma) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ TMA producer: A and R tiles
     if (lane == 0) {
-      // The AR ring is `ahead` chunks deeper than the B ring: A/R tiles are requested that much
-      // earlier, because rotation + gate of a chunk must finish before its dense MMA starts.
-      // Two cursors (tile, chunk) walk the same sequence, the B cursor `ahead` chunks behind.
-      const uint32_t ahead = p.sa - p.sb;
-      Ring ra(p.sa), rb(p.sb);
-      int ta = cid, ca = 0, mta, nta, tb = cid, cb = 0, mtb, ntb;
+      Ring ra(p.sa);
+      int ta = cid, ca = 0, mta, nta;
       tile_coords(p, ta, mta, nta);
-      tile_coords(p, tb, mtb, ntb);
       int ga = nta / p.ntiles_per_group;
       bool ok = true;
-      for (uint32_t j = 0; j < total + ahead && ok; ++j) {
-        if (j < total) {
-          if (!mbar_wait(&bars->a_empty[ra.idx], ra.phase ^ 1)) { ok = false; break; }
-          uint8_t* dstA = smemAR + ra.idx * ar_stage_bytes;
-          mbar_arrive_expect_tx(&bars->ar_full[ra.idx], kATileBytes + p.E * 128);
-          tma_load_2d(dstA, &tmA, &bars->ar_full[ra.idx], ca * 64, mta * 256 + (int)rank * 128);
-          tma_load_2d(dstA + kATileBytes, &tmR, &bars->ar_full[ra.idx], ca * 64, ga * p.E);
-          ra.next();
-          if (++ca == nk) {
-            ca = 0;
-            ta += n_clusters;
-            if (ta < p.n_tiles) { tile_coords(p, ta, mta, nta); ga = nta / p.ntiles_per_group; }
-          }
+      for (uint32_t j = 0; j < total; ++j) {
+        if (!mbar_wait(&bars->a_empty[ra.idx], ra.phase ^ 1)) { ok = false; break; }
+        uint8_t* dstA = smemAR + ra.idx * ar_stage_bytes;
+        mbar_arrive_expect_tx(&bars->ar_full[ra.idx], kATileBytes + p.E * 128);
+        tma_load_2d(dstA, &tmA, &bars->ar_full[ra.idx], ca * 64, mta * 256 + (int)rank * 128);
+        tma_load_2d(dstA + kATileBytes, &tmR, &bars->ar_full[ra.idx], ca * 64, ga * p.E);
+        ra.next();
+        if (++ca == nk) {
+          ca = 0;
+          ta += n_clusters;
+          if (ta < p.n_tiles) { tile_coords(p, ta, mta, nta); ga = nta / p.ntiles_per_group; }
         }
-        if (j >= ahead) {
-          if (!mbar_wait(&bars->b_empty[rb.idx], rb.phase ^ 1)) { ok = false; break; }
-          // this CTA's half of the B tile; completion is counted on the leader's barrier
-          const uint32_t bfull = mapa_shared(smem_u32(&bars->b_full[rb.idx]), 0);
-          mbar_arrive_expect_tx_cluster(bfull, b_stage_bytes);
-          tma_load_2d_pair(smemB + rb.idx * b_stage_bytes, &tmB, bfull, cb * 64, ntb * p.BN + (int)rank * (p.BN / 2));
-          rb.next();
-          if (++cb == nk) {
-            cb = 0;
-            tb += n_clusters;
-            if (tb < p.n_tiles) tile_coords(p, tb, mtb, ntb);
-          }
+      }
+      if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
+    }
+  } else if (warp == kWarpTmaB) {
+    // ------------------------------------------------------------------ TMA producer: this CTA's half of the B tiles
+    if (lane == 0) {
+      int tb = cid, cb = 0, mtb, ntb;
+      tile_coords(p, tb, mtb, ntb);
+      bool ok = true;
+      for (uint32_t j = 0; j < total; ++j) {
+        const uint32_t hb = j & (kHBufs - 1), hphase = (j / kHBufs) & 1;   // B stage = H buffer index
+        if (!mbar_wait(&bars->hb_empty[hb], hphase ^ 1)) { ok = false; break; }
+        // completion is counted on the leader's barrier
+        const uint32_t bfull = mapa_shared(smem_u32(&bars->hb_full[hb]), 0);
+        mbar_arrive_expect_tx_cluster(bfull, b_stage_bytes);
+        tma_load_2d_pair(smemB + hb * b_stage_bytes, &tmB, bfull, cb * 64, ntb * p.BN + (int)rank * (p.BN / 2));
+        if (++cb == nk) {
+          cb = 0;
+          tb += n_clusters;
+          if (tb < p.n_tiles) tile_coords(p, tb, mtb, ntb);
         }
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
@@ -184,33 +187,29 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------------ dense issuer
     if (lane == 0 && rank == 0) {
       const uint32_t idesc_c = make_idesc(DT, 256, p.BN, 0, 0);   // M = 256: 128 rows in each CTA
-      Ring ra(p.sa), rb(p.sb);
       int cm = 0;
-      uint32_t acc = 0, acc_phase = 0;   // accumulator buffer (TMEM columns acc*256) and its phase
+      uint32_t acc_phase = 0;
       bool ok = true;
+      // one wait and one commit per chunk: while this thread does anything else the tensor pipe drains
       for (uint32_t j = 0; j < total; ++j) {
-        if (!mbar_wait_cluster(&bars->h_full[ra.idx], ra.phase)) { ok = false; break; }
-        if (!mbar_wait_cluster(&bars->b_full[rb.idx], rb.phase)) { ok = false; break; }
+        const uint32_t hb = j & (kHBufs - 1), hphase = (j / kHBufs) & 1;
+        if (!mbar_wait_cluster(&bars->hb_full[hb], hphase)) { ok = false; break; }
         if (cm == 0) {
-          if (!mbar_wait_cluster(&bars->acc_empty[acc], acc_phase ^ 1)) { ok = false; break; }
+          if (!mbar_wait_cluster(&bars->acc_empty, acc_phase ^ 1)) { ok = false; break; }
         }
         tc_fence_after_sync();
-        const uint32_t h_addr = smem_u32(smemAR + ra.idx * ar_stage_bytes);
-        const uint32_t b_addr = smem_u32(smemB + rb.idx * b_stage_bytes);
+        const uint32_t h_tmem = tmem_base + kHCol0 + hb * 32;
+        const uint32_t b_addr = smem_u32(smemB + hb * b_stage_bytes);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-          umma_f16_pair(tmem_base + acc * 256, desc_kmajor_sw128(h_addr + ks * 32, 1024),
-                        desc_kmajor_sw128(b_addr + ks * 32, 1024), idesc_c, (cm > 0 || ks > 0) ? 1u : 0u);
+          umma_f16_pair_ts(tmem_base, h_tmem + ks * 8, desc_kmajor_sw128(b_addr + ks * 32, 1024), idesc_c,
+                           (cm > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit_pair(&bars->a_empty[ra.idx], 0x3);   // both CTAs' rings move on
-        umma_commit_pair(&bars->b_empty[rb.idx], 0x3);
-        ra.next();
-        rb.next();
+        umma_commit_pair(&bars->hb_empty[hb], 0x3);   // both CTAs: H buffer and B stage are free
         if (++cm == nk) {
           cm = 0;
-          umma_commit_pair(&bars->acc_full[acc], 0x3);
-          acc ^= 1u;
-          if (acc == 0) acc_phase ^= 1u;
+          umma_commit_pair(&bars->acc_full, 0x3);
+          acc_phase ^= 1u;
         }
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
@@ -219,19 +218,24 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------------ gate warps
     const uint32_t gw = warp - kGateWarp0;
     const uint32_t group = gw / kWarpsPerGroup;               // which chunks (j mod kGateGroups)
-    const uint32_t r0 = (gw % kWarpsPerGroup) * 16;           // this warp's 16 rows of the tile
+    const uint32_t r0 = (gw & 3) * 32 + ((gw >> 2) & 1) * 16; // this warp's 16 rows, inside its TMEM lane quarter
     Ring ra(p.sa);
     for (uint32_t i = 0; i < group; ++i) ra.next();
     bool ok = true;
     for (uint32_t j = group; j < total; j += kGateGroups, ra.next(), ra.next()) {
+      const uint32_t hb = j & (kHBufs - 1), hphase = (j / kHBufs) & 1;
       if (!mbar_wait(&bars->ar_full[ra.idx], ra.phase)) { ok = false; break; }
+      if (!mbar_wait(&bars->hb_empty[hb], hphase ^ 1)) { ok = false; break; }
+      tc_fence_after_sync();
       const uint32_t tile = smem_u32(smemAR + ra.idx * ar_stage_bytes);
-#if !(PRISM_DBG & 1)
-      rotate_gate_rows16<DT, GATE, E>(tile, tile + kATileBytes, r0, lane);
-#endif
-      fence_proxy_async_smem();
+      rotate_gate_rows16<DT, GATE, E>(tile, tile + kATileBytes, r0, lane, tmem_base + (r0 << 16) + kHCol0 + hb * 32);
+      tmem_st_wait();
+      tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars->h_full[ra.idx]), 0));
+      if (lane == 0) {
+        mbar_arrive(&bars->a_empty[ra.idx]);                                   // A and R tiles are free again
+        mbar_arrive_cluster(mapa_shared(smem_u32(&bars->hb_full[hb]), 0));     // H chunk is in TMEM
+      }
     }
     if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
   } else if (warp >= kEpiWarp0) {
@@ -241,14 +245,14 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t lane_base = uint32_t(q * 32) << 16;
     uint8_t* stage = smemEpi + (warp - kEpiWarp0) * kEpiStageBytes;
     const uint16_t* bias = reinterpret_cast<const uint16_t*>(p.bias);
-    uint32_t acc = 0, acc_phase = 0;
+    uint32_t acc_phase = 0;
     bool ok = true;
-    for (int t = cid; t < p.n_tiles && ok; t += n_clusters) {
+    for (int t = cid; t < p.n_tiles && ok; t += n_clusters, acc_phase ^= 1u) {
       int mp, nt;
       tile_coords(p, t, mp, nt);
       const int mt = mp * 2 + (int)rank;   // this CTA's 128-row block
-      if (!mbar_wait(&bars->acc_full[acc], acc_phase)) { ok = false; break; }
-      const uint32_t tacc = tmem_base + lane_base + acc * 256;
+      if (!mbar_wait(&bars->acc_full, acc_phase)) { ok = false; break; }
+      const uint32_t tacc = tmem_base + lane_base;
       tc_fence_after_sync();
       const long long grow = (long long)mt * 128 + row;
       const int n0 = nt * p.BN;
@@ -316,9 +320,7 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars->acc_empty[acc]), 0));
-      acc ^= 1u;
-      if (acc == 0) acc_phase ^= 1u;
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars->acc_empty), 0));
     }
     if (lane == 0) tma_store_wait_all<0>();   // outstanding stores read shared memory
     if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
@@ -354,22 +356,13 @@ int launch_fwd(const FwdArgs& a) {
   const int ar_bytes = fwd::kATileBytes + p.r_tile_bytes;
   const int b_bytes = a.BN * 64;   // per CTA: half of the B tile
   // the AR ring feeds rotation + gate, which run ahead of the dense product: give it the deeper pipeline
-  int sb = a.sb > 0 ? a.sb : 4;
-  int sa = a.sa > 0 ? a.sa : 6;
+  // the B ring has one stage per H buffer (they share barriers); the AR ring takes what is left
+  const int sb = fwd::kHBufs;
+  int sa = a.sa > 0 ? a.sa : fwd::kMaxStages;
   if (sa > fwd::kMaxStages) sa = fwd::kMaxStages;
-  if (sb > fwd::kMaxStages) sb = fwd::kMaxStages;
-  while (sa * ar_bytes + sb * b_bytes > budget && sa > 4) --sa;
-  while (sa * ar_bytes + sb * b_bytes > budget && sb > 2) --sb;
+  while (sa > 2 && sa * ar_bytes + sb * b_bytes > budget) --sa;
   if (sa * ar_bytes + sb * b_bytes > budget)
     return fail(PRISM_ERR_UNSUPPORTED, "forward tile does not fit shared memory (BN=%d E=%d)", a.BN, a.E);
-  if (a.sa <= 0 && a.sb <= 0) {  // spend what is left
-    while (sb < 4 && sa * ar_bytes + (sb + 1) * b_bytes <= budget) ++sb;
-    while (sa < fwd::kMaxStages && (sa + 1) * ar_bytes + sb * b_bytes <= budget) ++sa;
-    while (sb < fwd::kMaxStages && sa * ar_bytes + (sb + 1) * b_bytes <= budget) ++sb;
-  }
-  if (sa < sb) sa = sb;  // the producer assumes the AR ring is at least as deep as the B ring
-  if (sa * ar_bytes + sb * b_bytes > budget) sb = sa = (budget / (ar_bytes + b_bytes));
-  if (sa < 2) return fail(PRISM_ERR_UNSUPPORTED, "forward tile does not fit shared memory (BN=%d E=%d)", a.BN, a.E);
   p.sa = sa; p.sb = sb;
   const int smem_bytes = sa * ar_bytes + sb * b_bytes + fwd::kNumEpiWarps * fwd::kEpiStageBytes +
                          (int)sizeof(FwdBarriers) + 1024;
