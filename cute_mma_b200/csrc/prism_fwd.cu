@@ -64,8 +64,10 @@ struct FwdParams {
 struct FwdBarriers {
   uint64_t ar_full[fwd::kMaxStages];
   uint64_t a_empty[fwd::kMaxStages];
-  uint64_t hb_full[fwd::kHBufs];    // H chunk in TMEM (both CTAs' gate warps) and both B halves in shared memory
-  uint64_t hb_empty[fwd::kHBufs];   // the dense MMAs of the chunk are done: H buffer and B stage are free
+  uint64_t b_full[fwd::kHBufs];
+  uint64_t b_empty[fwd::kHBufs];
+  uint64_t h_full[fwd::kHBufs];
+  uint64_t h_empty[fwd::kHBufs];
   uint64_t acc_full;
   uint64_t acc_empty;
   uint32_t tmem_base;
@@ -110,9 +112,10 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(&bars->a_empty[i], kWarpsPerGroup);       // local: the gate warps have read the tiles
     }
     for (int i = 0; i < kHBufs; ++i) {
-      // leader's copy is used: gate warps of both CTAs + the two B producers (with their byte counts)
-      mbar_init(&bars->hb_full[i], 2 * kWarpsPerGroup + 2);
-      mbar_init(&bars->hb_empty[i], 1);                   // local, arrived by the multicast commit
+      mbar_init(&bars->b_full[i], 2);                     // leader's copy is used: both CTAs' B halves
+      mbar_init(&bars->b_empty[i], 1);                    // local, arrived by the multicast commit
+      mbar_init(&bars->h_full[i], 2 * kWarpsPerGroup);    // leader's copy is used: gate warps of both CTAs
+      mbar_init(&bars->h_empty[i], 1);                    // local, arrived by the multicast commit
     }
     mbar_init(&bars->acc_full, 1);                        // local, arrived by the multicast commit
     mbar_init(&bars->acc_empty, 2 * kNumEpiWarps);        // leader's copy is used
@@ -170,9 +173,9 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       for (uint32_t j = 0; j < total; ++j) {
         const uint32_t hb = j & (kHBufs - 1), hphase = (j / kHBufs) & 1;   // B stage = H buffer index
-        if (!mbar_wait(&bars->hb_empty[hb], hphase ^ 1)) { ok = false; break; }
+        if (!mbar_wait(&bars->b_empty[hb], hphase ^ 1)) { ok = false; break; }
         // completion is counted on the leader's barrier
-        const uint32_t bfull = mapa_shared(smem_u32(&bars->hb_full[hb]), 0);
+        const uint32_t bfull = mapa_shared(smem_u32(&bars->b_full[hb]), 0);
         mbar_arrive_expect_tx_cluster(bfull, b_stage_bytes);
         tma_load_2d_pair(smemB + hb * b_stage_bytes, &tmB, bfull, cb * 64, ntb * p.BN + (int)rank * (p.BN / 2));
         if (++cb == nk) {
@@ -190,10 +193,10 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int cm = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      // one wait and one commit per chunk: while this thread does anything else the tensor pipe drains
       for (uint32_t j = 0; j < total; ++j) {
         const uint32_t hb = j & (kHBufs - 1), hphase = (j / kHBufs) & 1;
-        if (!mbar_wait_cluster(&bars->hb_full[hb], hphase)) { ok = false; break; }
+        if (!mbar_wait_cluster(&bars->h_full[hb], hphase)) { ok = false; break; }
+        if (!mbar_wait_cluster(&bars->b_full[hb], hphase)) { ok = false; break; }
         if (cm == 0) {
           if (!mbar_wait_cluster(&bars->acc_empty, acc_phase ^ 1)) { ok = false; break; }
         }
@@ -205,7 +208,8 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           umma_f16_pair_ts(tmem_base, h_tmem + ks * 8, desc_kmajor_sw128(b_addr + ks * 32, 1024), idesc_c,
                            (cm > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit_pair(&bars->hb_empty[hb], 0x3);   // both CTAs: H buffer and B stage are free
+        umma_commit_pair(&bars->h_empty[hb], 0x3);   // both CTAs' gate warps may refill the H buffer
+        umma_commit_pair(&bars->b_empty[hb], 0x3);   // both CTAs' B stages are free
         if (++cm == nk) {
           cm = 0;
           umma_commit_pair(&bars->acc_full, 0x3);
@@ -225,7 +229,7 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (uint32_t j = group; j < total; j += kGateGroups, ra.next(), ra.next()) {
       const uint32_t hb = j & (kHBufs - 1), hphase = (j / kHBufs) & 1;
       if (!mbar_wait(&bars->ar_full[ra.idx], ra.phase)) { ok = false; break; }
-      if (!mbar_wait(&bars->hb_empty[hb], hphase ^ 1)) { ok = false; break; }
+      if (!mbar_wait(&bars->h_empty[hb], hphase ^ 1)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t tile = smem_u32(smemAR + ra.idx * ar_stage_bytes);
       rotate_gate_rows16<DT, GATE, E>(tile, tile + kATileBytes, r0, lane, tmem_base + (r0 << 16) + kHCol0 + hb * 32);
@@ -234,7 +238,7 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&bars->a_empty[ra.idx]);                                   // A and R tiles are free again
-        mbar_arrive_cluster(mapa_shared(smem_u32(&bars->hb_full[hb]), 0));     // H chunk is in TMEM
+        mbar_arrive_cluster(mapa_shared(smem_u32(&bars->h_full[hb]), 0));      // H chunk is in TMEM
       }
     }
     if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
