@@ -99,7 +99,7 @@ class ClockSampler(threading.Thread):
                 self.power.append(nv.nvmlDeviceGetPowerUsage(self.handle) / 1000.0)
             except Exception:
                 pass
-            self._stop_evt.wait(0.05)
+            self._stop_evt.wait(0.004)
 
     def stop(self):
         self._stop_evt.set()
@@ -301,12 +301,14 @@ def main():
     }
 
     # ---- end-to-end through the public API with host buffers (rank-local; N ranks do the same).
-    # The step's tokens are processed as micro-batches (gradient accumulation): the host->device
+    # Every step's tokens are processed as micro-batches (gradient accumulation).  The host->device
     # copy of micro-batch i+1, the kernels of micro-batch i and the device->host copy of micro-batch
-    # i-1 run on three streams, so PCIe traffic in both directions overlaps the compute.
+    # i-1 run on three streams, so PCIe traffic in both directions overlaps the compute; the stream
+    # of micro-batches runs on across step boundaries (the next step's inputs are already on their
+    # way while this step's gradients go back), and the host waits once, after the last step.
     if not args.no_e2e:
-        e_steps = max(2, min(args.steps, 5))
-        n_mb = 4 if M % 4 == 0 and M >= 4096 else 1
+        e_steps = max(2, min(args.steps, 8))
+        n_mb = 8 if M % 8 == 0 and M >= 8192 else (4 if M % 4 == 0 and M >= 4096 else 1)
         mb = M // n_mb
         A_h, dC_h = A.cpu().pin_memory(), dC.cpu().pin_memory()
         C_h = torch.empty(M, N, dtype=dt, pin_memory=True)
@@ -314,61 +316,78 @@ def main():
         dR_h = torch.empty(R.shape, dtype=dt, pin_memory=True)
         dB_h = torch.empty(B.shape, dtype=dt, pin_memory=True) if gate else None
         s_in, s_out, s_cmp = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
-        A_d = [torch.empty(mb, K, dtype=dt, device=dev) for _ in range(2)]
-        dC_d = [torch.empty(mb, N, dtype=dt, device=dev) for _ in range(2)]
-        dR_acc = torch.zeros(R.shape, dtype=torch.float32, device=dev)
-        dB_acc = torch.zeros(B.shape, dtype=torch.float32, device=dev) if gate else None
+        n_buf = 3
+        A_d = [torch.empty(mb, K, dtype=dt, device=dev) for _ in range(n_buf)]
+        dC_d = [torch.empty(mb, N, dtype=dt, device=dev) for _ in range(n_buf)]
+        # gradient accumulators of two steps in flight (one is copied out while the next one fills)
+        dR_acc = [torch.zeros(R.shape, dtype=torch.float32, device=dev) for _ in range(2)]
+        dB_acc = [torch.zeros(B.shape, dtype=torch.float32, device=dev) for _ in range(2)] if gate else None
+        grads_out = [None, None]   # events: the step's gradients have left the accumulator pair
 
-        def e2e_step():
-            in_ready = [torch.cuda.Event() for _ in range(n_mb)]
-            buf_free = [torch.cuda.Event() for _ in range(n_mb)]
-            keep = []
-            dR_acc.zero_()
-            if gate:
-                dB_acc.zero_()
-            for i in range(n_mb):
-                sl = slice(i * mb, (i + 1) * mb)
-                with torch.cuda.stream(s_in):
-                    if i >= 2:
-                        s_in.wait_event(buf_free[i - 2])      # the kernels that read this buffer are done
-                    A_d[i % 2].copy_(A_h[sl], non_blocking=True)
-                    dC_d[i % 2].copy_(dC_h[sl], non_blocking=True)
-                    in_ready[i].record(s_in)
-                s_cmp.wait_event(in_ready[i])
-                Ci, _ = cp.forward(A_d[i % 2], B, R, gs, rs, activation=act)
-                dAi, dRi, dBi, _ = cp.backward(dC_d[i % 2], A_d[i % 2], B, R, gs, rs, activation=act)
-                dR_acc.add_(dRi)
+        def e2e_steps(n_steps):
+            buf_free = [None] * n_buf
+            it = 0
+            for st in range(n_steps):
+                acc = st % 2
+                if grads_out[acc] is not None:
+                    s_cmp.wait_event(grads_out[acc])
+                dR_acc[acc].zero_()
                 if gate:
-                    dB_acc.add_(dBi)
-                buf_free[i].record(s_cmp)
+                    dB_acc[acc].zero_()
+                for i in range(n_mb):
+                    sl = slice(i * mb, (i + 1) * mb)
+                    bi = it % n_buf
+                    with torch.cuda.stream(s_in):
+                        if buf_free[bi] is not None:
+                            s_in.wait_event(buf_free[bi])      # the kernels that read this buffer are done
+                        A_d[bi].copy_(A_h[sl], non_blocking=True)
+                        dC_d[bi].copy_(dC_h[sl], non_blocking=True)
+                        ready = torch.cuda.Event()
+                        ready.record(s_in)
+                    s_cmp.wait_event(ready)
+                    Ci, _ = cp.forward(A_d[bi], B, R, gs, rs, activation=act)
+                    dAi, dRi, dBi, _ = cp.backward(dC_d[bi], A_d[bi], B, R, gs, rs, activation=act)
+                    dR_acc[acc].add_(dRi)
+                    if gate:
+                        dB_acc[acc].add_(dBi)
+                    buf_free[bi] = torch.cuda.Event()
+                    buf_free[bi].record(s_cmp)
+                    with torch.cuda.stream(s_out):
+                        s_out.wait_event(buf_free[bi])
+                        C_h[sl].copy_(Ci, non_blocking=True)
+                        dA_h[sl].copy_(dAi, non_blocking=True)
+                    Ci.record_stream(s_out)                    # keep the blocks until the copies have run
+                    dAi.record_stream(s_out)
+                    it += 1
+                dR_out = dR_acc[acc].to(dt)                    # gradients leave in the parameters' dtype
+                dB_out = dB_acc[acc].to(dt) if gate else None
+                done = torch.cuda.Event()
+                done.record(s_cmp)
                 with torch.cuda.stream(s_out):
-                    s_out.wait_event(buf_free[i])
-                    C_h[sl].copy_(Ci, non_blocking=True)
-                    dA_h[sl].copy_(dAi, non_blocking=True)
-                keep.append((Ci, dAi))                         # stay alive until the copies have run
-            dR_out = dR_acc.to(dt)                             # gradients leave in the parameters' dtype
-            dB_out = dB_acc.to(dt) if gate else None
-            done = torch.cuda.Event()
-            done.record(s_cmp)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(done)
-                dR_h.copy_(dR_out, non_blocking=True)
-                if gate:
-                    dB_h.copy_(dB_out, non_blocking=True)
+                    s_out.wait_event(done)
+                    dR_h.copy_(dR_out, non_blocking=True)
+                    dR_out.record_stream(s_out)
+                    if gate:
+                        dB_h.copy_(dB_out, non_blocking=True)
+                        dB_out.record_stream(s_out)
+                    grads_out[acc] = torch.cuda.Event()
+                    grads_out[acc].record(s_out)
             torch.cuda.synchronize()
 
-        e2e_step()
+        e2e_steps(2)
         t0 = time.perf_counter()
-        for _ in range(e_steps):
-            e2e_step()
+        e2e_steps(e_steps)
         e_ms = (time.perf_counter() - t0) / e_steps * 1e3
+        cp.check_device_status()
         d2h = C_h.numel() * 2 + dA_h.numel() * 2 + dR_h.numel() * 2 + (dB_h.numel() * 2 if gate else 0)
         line["e2e"] = {"value": world * step_flops / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                        "h2d_bytes_per_step": int((A_h.numel() + dC_h.numel()) * 2),
                        "d2h_bytes_per_step": int(d2h), "ms_per_step": e_ms, "steps": e_steps,
                        "micro_batches": n_mb,
                        "note": "cute_mma_b200.forward/backward per micro-batch with A, dC from pinned host memory; "
-                               "C, dA copied back per micro-batch, dR, dB (accumulated in fp32, cast to 16 bit) once per step"}
+                               "C, dA copied back per micro-batch, dR, dB (accumulated in fp32, cast to 16 bit) once per "
+                               "step; copies and kernels of neighbouring micro-batches and steps overlap on three "
+                               "streams, one host wait after the last step"}
         del A_h, dC_h, C_h, dA_h
 
     if not args.no_cpu_baseline:
