@@ -6,29 +6,45 @@
 
 namespace prism {
 
-__global__ void expand_r8_kernel(const uint16_t* __restrict__ R, uint16_t* __restrict__ Re, int G,
-                                 int K, long long ldr) {
-  // one thread per output element of R_eff [(G*16), K]
+// R_eff[(G*E), K] = factor * R with, for reconn_sz = 8 (E = 16), two neighbouring 8x8 blocks widened
+// to one block-diagonal 16x16 block.  One thread per output element.
+template <int DT>
+__global__ void prep_r_kernel(const uint16_t* __restrict__ R, uint16_t* __restrict__ Re, int G, int rs, int E,
+                              int K, long long ldr, float factor) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long total = (long long)G * 16 * K;
+  const long long total = (long long)G * E * K;
   if (idx >= total) return;
   const int k = (int)(idx % K);
   const int row = (int)(idx / K);
-  const int g = row >> 4, i = row & 15;
-  const bool upper_cols = (k & 15) >= 8;
+  const int g = row / E, i = row - g * E;
   uint16_t v = 0;
-  if (i < 8 && !upper_cols) v = R[(long long)(g * 8 + i) * ldr + k];
-  if (i >= 8 && upper_cols) v = R[(long long)(g * 8 + i - 8) * ldr + k];
+  if (rs == 8) {
+    const bool upper_cols = (k & 15) >= 8;
+    if (i < 8 && !upper_cols) v = R[(long long)(g * 8 + i) * ldr + k];
+    if (i >= 8 && upper_cols) v = R[(long long)(g * 8 + i - 8) * ldr + k];
+  } else {
+    v = R[(long long)(g * rs + i) * ldr + k];
+  }
+  if (factor != 1.0f) v = (uint16_t)(Elem<DT>::pack(Elem<DT>::unpack((uint32_t)v).x * factor, 0.f) & 0xffffu);
   Re[idx] = v;
 }
 
-int launch_expand_r8(const void* R, void* R_eff, int G, int K, long long ldr, cudaStream_t stream) {
-  const long long total = (long long)G * 16 * K;
+int launch_prep_r(const void* R, void* R_eff, int G, int rs, int E, int K, long long ldr, float factor, int dtype,
+                  cudaStream_t stream) {
+  const long long total = (long long)G * E * K;
   const int threads = 256;
   const long long blocks = (total + threads - 1) / threads;
-  expand_r8_kernel<<<(unsigned)blocks, threads, 0, stream>>>(
-      reinterpret_cast<const uint16_t*>(R), reinterpret_cast<uint16_t*>(R_eff), G, K, ldr);
-  return check_launch("expand_r8");
+  if (dtype == DT_BF16)
+    prep_r_kernel<DT_BF16><<<(unsigned)blocks, threads, 0, stream>>>(
+        reinterpret_cast<const uint16_t*>(R), reinterpret_cast<uint16_t*>(R_eff), G, rs, E, K, ldr, factor);
+  else
+    prep_r_kernel<DT_F16><<<(unsigned)blocks, threads, 0, stream>>>(
+        reinterpret_cast<const uint16_t*>(R), reinterpret_cast<uint16_t*>(R_eff), G, rs, E, K, ldr, factor);
+  return check_launch("prep_r");
+}
+
+int launch_expand_r8(const void* R, void* R_eff, int G, int K, long long ldr, int dtype, cudaStream_t stream) {
+  return launch_prep_r(R, R_eff, G, 8, 16, K, ldr, 1.0f, dtype, stream);
 }
 
 static int num_sms() {
@@ -100,7 +116,9 @@ extern "C" size_t prism_workspace_bytes(int kind, int M, int N, int K, int gs, i
   size_t bytes = PRISM_WORKSPACE_HEADER_BYTES;
   if (gs <= 0 || rs <= 0 || N <= 0 || K <= 0) return bytes;
   const size_t G = (size_t)(N / gs);
-  if (rs == 8) bytes += align256(G * 16 * (size_t)K * 2);  // R_eff
+  // copy of R the kernels read: widened for rs = 8 (all kinds), halved for the gated dA+dR kernel
+  if (rs == 8) bytes += align256(G * 16 * (size_t)K * 2);
+  else if (kind == PRISM_KIND_BWD_DADR) bytes += align256(G * (size_t)effective_block(rs) * K * 2);
   if (kind == PRISM_KIND_FWD) return bytes;
   if (kind == PRISM_KIND_BWD_DB) {
     const int bn = (cfg && cfg[0] > 0) ? cfg[0] : default_bn(gs);
@@ -164,7 +182,7 @@ extern "C" int prism_fwd(const void* A, const void* B, const void* R, const void
   a.R_eff = R; a.ldr = ldr;
   if (rs == 8) {
     void* re = reinterpret_cast<uint8_t*>(workspace) + PRISM_WORKSPACE_HEADER_BYTES;
-    if ((rc = launch_expand_r8(R, re, N / gs, K, ldr, s))) return rc;
+    if ((rc = launch_expand_r8(R, re, N / gs, K, ldr, dtype, s))) return rc;
     a.R_eff = re; a.ldr = K;
   }
   a.BN = (cfg && cfg[0] > 0) ? cfg[0] : default_bn(gs);
@@ -208,7 +226,7 @@ extern "C" int prism_bwd_db(const void* dC, const void* A, const void* R, void* 
   a.R_eff = R; a.ldr = ldr;
   uint8_t* wp = reinterpret_cast<uint8_t*>(workspace) + PRISM_WORKSPACE_HEADER_BYTES;
   if (rs == 8) {
-    if ((rc = launch_expand_r8(R, wp, N / gs, K, ldr, s))) return rc;
+    if ((rc = launch_expand_r8(R, wp, N / gs, K, ldr, dtype, s))) return rc;
     a.R_eff = wp; a.ldr = K;
     wp += align256((size_t)(N / gs) * 16 * K * 2);
   }
@@ -254,11 +272,13 @@ extern "C" int prism_bwd_dadr(const void* dC, const void* A, const void* B, cons
   a.lddc = lddc; a.lda = lda; a.ldb = ldb; a.ldda = ldda; a.lddr = lddr;
   a.R_eff = R; a.ldr = ldr;
   uint8_t* wp = reinterpret_cast<uint8_t*>(workspace) + PRISM_WORKSPACE_HEADER_BYTES;
-  if (rs == 8) {
-    if ((rc = launch_expand_r8(R, wp, N / gs, K, ldr, s))) return rc;
+  // The kernel reads a copy of R: widened to 16x16 blocks for rs = 8, and halved in the gated mode
+  // (its gate math works on S/2, see gate_bwd_pair).  The plain mode with rs >= 16 reads R itself.
+  if (rs == 8 || gate == GATE_SILU) {
+    if ((rc = launch_prep_r(R, wp, N / gs, rs, a.E, K, ldr, gate == GATE_SILU ? 0.5f : 1.0f, dtype, s))) return rc;
     a.R_eff = wp; a.ldr = K;
-    wp += align256((size_t)(N / gs) * 16 * K * 2);
   }
+  wp += align256((size_t)(N / gs) * a.E * K * 2);
   a.num_sms = num_sms();
   a.runs = (cfg && cfg[0] > 0) ? cfg[0] : dadr_default_runs(M, K, a.num_sms);
   a.partial = reinterpret_cast<float*>(wp);

@@ -88,25 +88,22 @@ __device__ __forceinline__ void dr_accumulate(float* addr, float x, float y, boo
   }
 }
 
-template <int DT> struct NegHalf;
-template <> struct NegHalf<DT_F16> { static constexpr uint32_t v = 0xB800B800u; };
-template <> struct NegHalf<DT_BF16> { static constexpr uint32_t v = 0xBF00BF00u; };
-
-// One pair of elements of the gated backward (sp = packed S): returns dS (packed) and adds
-// dh*silu(s) to acc0/acc1.
+// One pair of elements of the gated backward.  The R tiles of the gated mode hold R/2, so the
+// rotation delivers hs = S/2 directly.  With t = tanh(hs):
+//   silu(S)  = g = hs + hs t
+//   silu'(S) = (1 + x) / 2,  x = g + t (1 - g)
+// Returns 2 dS = dh a (1 + x) (the factor 2 is undone by the halved R in dS.R and by the scale of
+// the dR reduction) and p = dh silu(S), the gate term of dA, both packed 16-bit.
 template <int DT>
-__device__ __forceinline__ uint32_t gate_bwd_pair(uint32_t a2, uint32_t sp, float dh0, float dh1,
-                                                  float& acc0, float& acc1) {
-  const uint32_t hs = Pk<DT>::mul(sp, Pk<DT>::kHalf);
+__device__ __forceinline__ uint32_t gate_bwd_pair(uint32_t a2, uint32_t hs, float dh0, float dh1, uint32_t& p) {
   const uint32_t t = Pk<DT>::tanh(hs);
-  const uint32_t g = Pk<DT>::fma(hs, t, hs);                          // silu(s)
-  const uint32_t sg = Pk<DT>::fma(t, Pk<DT>::kHalf, Pk<DT>::kHalf);   // sigmoid(s)
-  const uint32_t oms = Pk<DT>::fma(t, NegHalf<DT>::v, Pk<DT>::kHalf); // 1 - sigmoid(s)
-  const uint32_t gp = Pk<DT>::fma(g, oms, sg);                        // silu'(s) = sg + silu*(1 - sg)
-  const float2 gf = Elem<DT>::unpack(g);
-  acc0 = fmaf(dh0, gf.x, acc0);
-  acc1 = fmaf(dh1, gf.y, acc1);
-  return Pk<DT>::mul(Pk<DT>::mul(Pk<DT>::cvt(dh0, dh1), a2), gp);
+  const uint32_t g = Pk<DT>::fma(hs, t, hs);
+  const uint32_t w = Pk<DT>::fma(g, Pk<DT>::kNegOne, Pk<DT>::kOne);
+  const uint32_t x = Pk<DT>::fma(t, w, g);
+  const uint32_t d = Pk<DT>::cvt(dh0, dh1);
+  p = Pk<DT>::mul(d, g);
+  const uint32_t q = Pk<DT>::mul(d, a2);
+  return Pk<DT>::fma(q, x, q);
 }
 
 template <int DT, int GATE, int E>
@@ -206,24 +203,36 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     // ------------------------------------------------------------------ dense issuer: dH = dC . B
     if (lane == 0 && rank == 0) {
       const uint32_t idesc_h = make_idesc(DT, 256, 128, 0, 1);   // M = 256 tokens; dC K-major, B_g MN-major
+      // descriptors of stage 0; a stage further on adds kStageBytes >> 4 to the low words
+      const uint64_t da0 = desc_kmajor_sw128(smem_u32(smemSt), 1024);
+      const uint64_t db0 = desc_mnmajor_sw128(smem_u32(smemSt) + 2 * kTile, kBTile, 1024);
+      const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
       bool ok = true;
       uint32_t gg = 0;
       Ring rst(p.ns);
       for (int mp = run; mp < n_mpairs && ok; mp += p.runs) {
         for (int g = 0; g < G && ok; ++g, ++gg) {
           const uint32_t hb = gg & (kDhBufs - 1);
+          const uint32_t d_tmem = tmem_base + hb * 128;
           if (!mbar_wait_cluster(&bars->dh_empty[hb], ((gg / kDhBufs) & 1) ^ 1)) { ok = false; break; }
           for (int s = 0; s < nstg; ++s, rst.next()) {
             const int st = rst.idx;
             if (!mbar_wait_cluster(&bars->st_full[st], rst.phase)) { ok = false; break; }
             tc_fence_after_sync();
-            const uint32_t dc_addr = smem_u32(smemSt + st * kStageBytes);
-            const uint32_t b_addr = dc_addr + 2 * kTile;
+            const uint32_t a_lo = (uint32_t)da0 + st * (kStageBytes >> 4);
+            const uint32_t b_lo = (uint32_t)db0 + st * (kStageBytes >> 4);
             const int ksteps = min(8, (p.gs - s * 128) / 16);
-            for (int ks = 0; ks < ksteps; ++ks) {
-              umma_f16_pair(tmem_base + hb * 128, desc_kmajor_sw128(dc_addr + (ks >> 2) * kTile + (ks & 3) * 32, 1024),
-                            desc_mnmajor_sw128(b_addr + ks * 2048, kBTile, 1024), idesc_h,
-                            (s > 0 || ks > 0) ? 1u : 0u);
+            if (ksteps == 8) {
+              // K16 step ks: dC tile ks/4 (+kTile), 32 bytes per step inside it; B_g rows 16 ks (+2048 bytes)
+              umma_f16_pair_lh(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc_h, s > 0 ? 1u : 0u);
+#pragma unroll
+              for (int ks = 1; ks < 8; ++ks)
+                umma_f16_pair_lh(d_tmem, a_lo + (((ks >> 2) * kTile + (ks & 3) * 32) >> 4), a_hi,
+                                 b_lo + ((ks * 2048) >> 4), b_hi, idesc_h, 1u);
+            } else {
+              for (int ks = 0; ks < ksteps; ++ks)
+                umma_f16_pair_lh(d_tmem, a_lo + (((ks >> 2) * kTile + (ks & 3) * 32) >> 4), a_hi,
+                                 b_lo + ((ks * 2048) >> 4), b_hi, idesc_h, (s > 0 || ks > 0) ? 1u : 0u);
             }
             umma_commit_pair(&bars->st_empty[st], 0x3);
           }
@@ -244,6 +253,9 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const uint32_t rn_row = l8 + (mat >> 1) * 8;               // R as B operand of S = A . R^T (rows = i)
     const uint32_t rt_row = l8 + (mat & 1) * 8;                // R as B operand of dS . R (rows = i, transposed load)
     const uint32_t tileA = smem_u32(smemA + ch * kTile);
+    // B-operand fragment of a 16x16 identity (the k = n diagonal of one 8-column half): adds the gate
+    // term p to the accumulators through the tensor pipe instead of unpack + FMA instructions
+    const uint32_t idf = ((lane >> 3) == (lane & 3)) ? (((lane >> 2) & 1) ? (Pk<DT>::kOneLo << 16) : Pk<DT>::kOneLo) : 0u;
     float dacc[8][4];   // dA accumulator fragments: 16 rows x 64 columns of this warp, whole tile
 #pragma unroll
     for (int i = 0; i < 8; ++i) { dacc[i][0] = dacc[i][1] = dacc[i][2] = dacc[i][3] = 0.f; }
@@ -264,7 +276,7 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         const uint32_t tdh = tmem_base + lane_base + hb * 128 + ch * 64;
 #pragma unroll
         for (int b = 0; b < ((PRISM_DBG & 1) ? 0 : NB); ++b) {
-          uint32_t af[KS][4], dsf[KS][4];
+          uint32_t af[KS][4], dsf[KS][4], pf[KS][4];
           if (GATE == GATE_SILU) {
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks)
@@ -274,7 +286,7 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           for (int np = 0; np < KS; ++np) {
             uint32_t dh[8];
             tmem_ld_16x256b_x2(tdh + b * E + np * 16, dh);
-            uint32_t sp[4] = {0u, 0u, 0u, 0u};   // packed S of this thread's four pairs
+            uint32_t sp[4] = {0u, 0u, 0u, 0u};   // packed S/2 of this thread's four pairs (the R tile holds R/2)
             if (GATE == GATE_SILU) {
               if (DT == DT_F16) {
                 uint32_t c0[2] = {0u, 0u}, c1[2] = {0u, 0u};   // fp16 accumulation: packed result
@@ -300,13 +312,11 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
               }
             }
             tmem_ld_wait();
-            float* d0 = dacc[(b * KS + np) * 2];
-            float* d1 = dacc[(b * KS + np) * 2 + 1];
             if (GATE == GATE_SILU) {
-              dsf[np][0] = gate_bwd_pair<DT>(af[np][0], sp[0], __uint_as_float(dh[0]), __uint_as_float(dh[1]), d0[0], d0[1]);
-              dsf[np][1] = gate_bwd_pair<DT>(af[np][1], sp[1], __uint_as_float(dh[2]), __uint_as_float(dh[3]), d0[2], d0[3]);
-              dsf[np][2] = gate_bwd_pair<DT>(af[np][2], sp[2], __uint_as_float(dh[4]), __uint_as_float(dh[5]), d1[0], d1[1]);
-              dsf[np][3] = gate_bwd_pair<DT>(af[np][3], sp[3], __uint_as_float(dh[6]), __uint_as_float(dh[7]), d1[2], d1[3]);
+              dsf[np][0] = gate_bwd_pair<DT>(af[np][0], sp[0], __uint_as_float(dh[0]), __uint_as_float(dh[1]), pf[np][0]);
+              dsf[np][1] = gate_bwd_pair<DT>(af[np][1], sp[1], __uint_as_float(dh[2]), __uint_as_float(dh[3]), pf[np][1]);
+              dsf[np][2] = gate_bwd_pair<DT>(af[np][2], sp[2], __uint_as_float(dh[4]), __uint_as_float(dh[5]), pf[np][2]);
+              dsf[np][3] = gate_bwd_pair<DT>(af[np][3], sp[3], __uint_as_float(dh[6]), __uint_as_float(dh[7]), pf[np][3]);
             } else {
               dsf[np][0] = Pk<DT>::cvt(__uint_as_float(dh[0]), __uint_as_float(dh[1]));
               dsf[np][1] = Pk<DT>::cvt(__uint_as_float(dh[2]), __uint_as_float(dh[3]));
@@ -315,9 +325,13 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             }
             stmatrix_x4(tileDS + sw128_offset(a_row, b * (E / 8) + np * 2 + (mat >> 1)), dsf[np]);
           }
-          // dA[:, block b] += dS[:, block b] . R_g[block b]   (contraction over the block's i)
+          // dA[:, block b] += p + dS[:, block b] . R_g[block b]   (contraction over the block's i)
 #pragma unroll
           for (int jp = 0; jp < KS; ++jp) {
+            if (GATE == GATE_SILU) {
+              mma_m16n8k16<DT>(dacc[(b * KS + jp) * 2], pf[jp], idf, 0u);
+              mma_m16n8k16<DT>(dacc[(b * KS + jp) * 2 + 1], pf[jp], 0u, idf);
+            }
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
               uint32_t rt[4];
@@ -481,7 +495,8 @@ int launch_bwd_dadr(const DadrArgs& a) {
   if (ns > dadr::kMaxStages) ns = dadr::kMaxStages;
   if (ns < 2) return fail(PRISM_ERR_UNSUPPORTED, "bwd_dadr does not fit shared memory (E=%d)", a.E);
   p.ns = ns;
-  const int smem_bytes = 6 * dadr::kTile + p.rb * 2 * p.r_tile_bytes + ns * dadr::kStageBytes +
+  const int smem_bytes = 6 * dadr::kTile +
+ p.rb * 2 * p.r_tile_bytes + ns * dadr::kStageBytes +
                          (int)sizeof(DadrBarriers) + 1024;
 
   CUtensorMap tmA, tmR, tmdC, tmB;
@@ -505,13 +520,15 @@ int launch_bwd_dadr(const DadrArgs& a) {
   kern<<<grid, dadr::kThreads, smem_bytes, a.stream>>>(tmA, tmR, tmdC, tmB, p);
   if ((rc = check_launch("prism_bwd_dadr"))) return rc;
 
+  // gated mode: the kernel formed 2 dS against the halved R tiles, so the dR partials are doubled
+  const float r_scale = (a.gate == GATE_SILU) ? 0.5f * a.scale : a.scale;
   const long long pairs = (long long)p.G * a.rs * a.K / 2;
   const int threads = 256;
   const long long blocks = (pairs + threads - 1) / threads;
   if (a.dtype == DT_BF16)
-    dr_reduce_kernel<DT_BF16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, reinterpret_cast<uint16_t*>(a.dR), p.G, a.rs, a.E, a.K, a.lddr, 2 * p.runs, a.scale);
+    dr_reduce_kernel<DT_BF16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, reinterpret_cast<uint16_t*>(a.dR), p.G, a.rs, a.E, a.K, a.lddr, 2 * p.runs, r_scale);
   else
-    dr_reduce_kernel<DT_F16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, reinterpret_cast<uint16_t*>(a.dR), p.G, a.rs, a.E, a.K, a.lddr, 2 * p.runs, a.scale);
+    dr_reduce_kernel<DT_F16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, reinterpret_cast<uint16_t*>(a.dR), p.G, a.rs, a.E, a.K, a.lddr, 2 * p.runs, r_scale);
   return check_launch("prism_bwd_dadr reduce");
 }
 

@@ -306,6 +306,24 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, u
       : "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same with each descriptor given as (low word, high word).  The start address (>> 4) sits in bits
+// [0,14) of the low word, so an issuer steps through a tile with one 32-bit add per operand; the
+// single issuing thread is latency-bound, every instruction saved per MMA shows in the MMA rate.
+__device__ __forceinline__ void umma_f16_pair_lh(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                 uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Same, with the A operand read from TMEM (lane = row, each 32-bit column = two K elements).
 __device__ __forceinline__ void umma_f16_pair_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
                                                  uint32_t accumulate) {
@@ -441,6 +459,7 @@ struct Pk;
 template <>
 struct Pk<DT_F16> {
   static constexpr uint32_t kHalf = 0x38003800u;  // (0.5, 0.5)
+  static constexpr uint32_t kOne = 0x3C003C00u, kNegOne = 0xBC00BC00u, kOneLo = 0x00003C00u;
   __device__ __forceinline__ static uint32_t cvt(float lo, float hi) {
     uint32_t d;
     asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
@@ -465,6 +484,7 @@ struct Pk<DT_F16> {
 template <>
 struct Pk<DT_BF16> {
   static constexpr uint32_t kHalf = 0x3F003F00u;
+  static constexpr uint32_t kOne = 0x3F803F80u, kNegOne = 0xBF80BF80u, kOneLo = 0x00003F80u;
   // fp32 pair -> bf16x2 with integer ops: add half an ulp to the bit patterns and keep the upper
   // halves (round to nearest, ties away from zero).  The cvt.rn.bf16x2.f32 instruction runs on the
   // 16-lane/clk special-function pipe (measured: as expensive as a tanh), these three ALU ops do not.

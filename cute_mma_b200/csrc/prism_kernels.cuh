@@ -26,7 +26,10 @@ int launch_fwd(const FwdArgs& a);
 
 // R [(G*8), K] -> R_eff [(G*16), K]: two neighbouring 8x8 blocks become one 16x16
 // block-diagonal block, so that every rotation is a 16-wide tensor-core product.
-int launch_expand_r8(const void* R, void* R_eff, int G, int K, long long ldr, cudaStream_t stream);
+int launch_expand_r8(const void* R, void* R_eff, int G, int K, long long ldr, int dtype, cudaStream_t stream);
+// R_eff [(G*E), K] = factor * R (widened as above when rs = 8)
+int launch_prep_r(const void* R, void* R_eff, int G, int rs, int E, int K, long long ldr, float factor, int dtype,
+                  cudaStream_t stream);
 
 struct DbArgs {
   const void* dC;     // [M, N]

@@ -59,5 +59,6 @@ def test_workspace_sizes(built_lib):
     assert L.prism_workspace_bytes(0, 1024, 1024, 256, 256, 8, 1, None) == hdr + 4 * 16 * 256 * 2
     cfg = (ctypes.c_int * 8)(256, 3, 0, 0, 0, 0, 0, 0)
     assert L.prism_workspace_bytes(2, 1024, 1024, 256, 256, 16, 1, cfg) == hdr + 3 * 1024 * 256 * 4
-    cfg = (ctypes.c_int * 8)(3, 0, 0, 0, 0, 0, 0, 0)   # 3 CTA pairs per feature column -> 6 partial buffers
-    assert L.prism_workspace_bytes(1, 1024, 1024, 256, 256, 16, 1, cfg) == hdr + 2 * 3 * 4 * 16 * 256 * 4
+    # dA+dR: the kernel's (halved) copy of R, then 6 partial buffers for 3 CTA pairs per feature column
+    cfg = (ctypes.c_int * 8)(3, 0, 0, 0, 0, 0, 0, 0)
+    assert L.prism_workspace_bytes(1, 1024, 1024, 256, 256, 16, 1, cfg) == hdr + 4 * 16 * 256 * 2 + 2 * 3 * 4 * 16 * 256 * 4
