@@ -43,10 +43,16 @@ constexpr int kNumGateWarps = 16;
 constexpr int kNumDrWarps = 4;     // warps 2, 3, 20, 21
 constexpr int kDhBufs = 4;         // TMEM ring of dH buffers, 128 columns each
 constexpr int kTile = 128 * 128;   // bytes of a [128 x 64] 16-bit tile
-constexpr int kBTile = 128 * 128;  // bytes of a [128 outputs x 64 features] 16-bit tile
-// one stage = 128 outputs of the group: two dC tiles [128 tokens x 64] and this CTA's half of the B_g features
-constexpr int kStageBytes = 2 * kTile + kBTile;
-constexpr int kMaxStages = 4;
+#ifndef PRISM_DADR_STAGE_OUT
+#define PRISM_DADR_STAGE_OUT 128
+#endif
+// one stage = kStageOut outputs of the group: kStageOut/64 dC tiles [128 tokens x 64] and this CTA's
+// half of the B_g features, a [kStageOut outputs x 64 features] tile
+constexpr int kStageOut = PRISM_DADR_STAGE_OUT;
+constexpr int kDcTiles = kStageOut / 64;
+constexpr int kBTile = kStageOut * 128;
+constexpr int kStageBytes = kDcTiles * kTile + kBTile;
+constexpr int kMaxStages = 6;
 constexpr int kMaxRBufs = 4;
 }  // namespace dadr
 
@@ -70,15 +76,6 @@ struct DadrBarriers {
   uint64_t ds_full[2], ds_empty[2];
   uint32_t tmem_base;
 };
-
-// TMEM -> registers in the mma.sync accumulator layout: 16 lanes x 16 columns; thread t gets
-// r[0..1] = (lane t/4, cols 2(t%4)+{0,1}), r[2..3] = (lane t/4+8, same cols), r[4..7] = cols + 8.
-__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)[8]) {
-  asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(taddr)
-               : "memory");
-}
 
 __device__ __forceinline__ void dr_accumulate(float* addr, float x, float y, bool first) {
   if (first) {
@@ -131,7 +128,7 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int run = blockIdx.y;                // the pair walks token-tile pairs run, run + runs, ...
   const int n_mpairs = (p.n_mtiles + 1) / 2;
   const int G = p.G;
-  const int nstg = (p.gs + 127) / 128;  // 128-output slices per group
+  const int nstg = (p.gs + kStageOut - 1) / kStageOut;  // stages per group
   const bool is_gate = warp >= kGateWarp0 && warp < kGateWarp0 + kNumGateWarps;
   const bool is_dr = warp == 2 || warp == 3 || warp >= kGateWarp0 + kNumGateWarps;
 
@@ -186,14 +183,14 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             const int st = rst.idx;
             if (!mbar_wait(&bars->st_empty[st], rst.phase ^ 1)) { ok = false; break; }
             uint8_t* dst = smemSt + st * kStageBytes;
-            const int n0 = g * p.gs + s * 128;
-            const bool two = p.gs - s * 128 > 64;   // the slice has more than 64 outputs
+            const int n0 = g * p.gs + s * kStageOut;
+            const bool two = kDcTiles == 2 && p.gs - s * kStageOut > 64;   // the slice has more than 64 outputs
             // completion is counted on the leader's barrier: its MMAs read both CTAs' tiles
             const uint32_t stfull = mapa_shared(smem_u32(&bars->st_full[st]), 0);
             mbar_arrive_expect_tx_cluster(stfull, (two ? 2 : 1) * kTile + kBTile);
             tma_load_2d_pair(dst, &tmdC, stfull, n0, m0);
             if (two) tma_load_2d_pair(dst + kTile, &tmdC, stfull, n0 + 64, m0);
-            tma_load_2d_pair(dst + 2 * kTile, &tmB, stfull, f0 + (int)rank * 64, n0);
+            tma_load_2d_pair(dst + kDcTiles * kTile, &tmB, stfull, f0 + (int)rank * 64, n0);
           }
         }
       }
@@ -205,7 +202,7 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const uint32_t idesc_h = make_idesc(DT, 256, 128, 0, 1);   // M = 256 tokens; dC K-major, B_g MN-major
       // descriptors of stage 0; a stage further on adds kStageBytes >> 4 to the low words
       const uint64_t da0 = desc_kmajor_sw128(smem_u32(smemSt), 1024);
-      const uint64_t db0 = desc_mnmajor_sw128(smem_u32(smemSt) + 2 * kTile, kBTile, 1024);
+      const uint64_t db0 = desc_mnmajor_sw128(smem_u32(smemSt) + kDcTiles * kTile, kBTile, 1024);
       const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
       bool ok = true;
       uint32_t gg = 0;
@@ -221,12 +218,13 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             tc_fence_after_sync();
             const uint32_t a_lo = (uint32_t)da0 + st * (kStageBytes >> 4);
             const uint32_t b_lo = (uint32_t)db0 + st * (kStageBytes >> 4);
-            const int ksteps = min(8, (p.gs - s * 128) / 16);
-            if (ksteps == 8) {
+            constexpr int kSteps = kStageOut / 16;
+            const int ksteps = min(kSteps, (p.gs - s * kStageOut) / 16);
+            if (ksteps == kSteps) {
               // K16 step ks: dC tile ks/4 (+kTile), 32 bytes per step inside it; B_g rows 16 ks (+2048 bytes)
               umma_f16_pair_lh(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc_h, s > 0 ? 1u : 0u);
 #pragma unroll
-              for (int ks = 1; ks < 8; ++ks)
+              for (int ks = 1; ks < kSteps; ++ks)
                 umma_f16_pair_lh(d_tmem, a_lo + (((ks >> 2) * kTile + (ks & 3) * 32) >> 4), a_hi,
                                  b_lo + ((ks * 2048) >> 4), b_hi, idesc_h, 1u);
             } else {
@@ -504,7 +502,7 @@ int launch_bwd_dadr(const DadrArgs& a) {
   if ((rc = make_tmap_2d(&tmA, a.dtype, a.A, a.M, a.K, a.lda, 128, 64, true))) return rc;
   if ((rc = make_tmap_2d(&tmR, a.dtype, a.R_eff, (uint64_t)p.G * a.E, a.K, a.ldr, a.E, 64, true))) return rc;
   if ((rc = make_tmap_2d(&tmdC, a.dtype, a.dC, a.M, a.N, a.lddc, 128, 64, true))) return rc;
-  if ((rc = make_tmap_2d(&tmB, a.dtype, a.B, a.N, a.K, a.ldb, 128, 64, true))) return rc;
+  if ((rc = make_tmap_2d(&tmB, a.dtype, a.B, a.N, a.K, a.ldb, dadr::kStageOut, 64, true))) return rc;
 
   using KernT = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, DadrParams);
   KernT kern = nullptr;

@@ -75,11 +75,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   asm volatile(
       "{\n\t"
       ".reg .pred P1;\n\t"
+#ifdef PRISM_TRYWAIT_HINT
+      "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2, %3;\n\t"
+#else
       "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+#endif
       "selp.b32 %0, 1, 0, P1;\n\t"
       "}\n"
       : "=r"(ok)
+#ifdef PRISM_TRYWAIT_HINT
+      : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)PRISM_TRYWAIT_HINT)
+#else
       : "r"(smem_u32(bar)), "r"(parity)
+#endif
       : "memory");
   return ok != 0;
 }
@@ -251,11 +259,19 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
   asm volatile(
       "{\n\t"
       ".reg .pred P1;\n\t"
+#ifdef PRISM_TRYWAIT_HINT
+      "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2, %3;\n\t"
+#else
       "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+#endif
       "selp.b32 %0, 1, 0, P1;\n\t"
       "}\n"
       : "=r"(ok)
+#ifdef PRISM_TRYWAIT_HINT
+      : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)PRISM_TRYWAIT_HINT)
+#else
       : "r"(smem_u32(bar)), "r"(parity)
+#endif
       : "memory");
   return ok != 0;
 }
@@ -335,6 +351,21 @@ __device__ __forceinline__ void umma_f16_pair_ts(uint32_t d_tmem, uint32_t a_tme
       "}\n"
       :
       : "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// A from TMEM, B descriptor as (low word, high word).
+__device__ __forceinline__ void umma_f16_pair_ts_lh(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                                    uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 db;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], db, %4, p;\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // Arrive (count 1) on the barrier at this shared-memory offset in every CTA of `cta_mask`
@@ -735,6 +766,51 @@ __device__ __forceinline__ void rotate_gate_rows16(uint32_t tile, uint32_t rtile
       }
     }
   }
+}
+
+// TMEM -> registers in the mma.sync accumulator layout: 16 lanes x 16 columns; thread t gets
+// r[0..1] = (lane t/4, cols 2(t%4)+{0,1}), r[2..3] = (lane t/4+8, same cols), r[4..7] = cols + 8.
+__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+
+// Gate step when the rotation runs on tcgen05: one warp turns its 16 rows x 64 columns of
+// S = A . blockdiag(R_g)^T (fp32 in TMEM at s_tmem, lane field = the warp's first row) into H
+// (16-bit) and writes H to TMEM at h_tmem as the A operand of the dense MMA (8 columns per 16 K
+// elements).  The TMEM load delivers the mma.sync accumulator layout and ldmatrix of the A tile the
+// matching A-fragment layout, so the gate is elementwise on registers.  h_tmem may alias the first
+// 32 of the S columns: every S value is in registers before the first H column is written.
+// Nothing here touches the legacy tensor path: mma.sync shares the tensor cores with tcgen05.mma
+// and is starved while a burst of tcgen05.mma runs (measured: 13x slower), which would serialise
+// the gate warps with the dense product.
+template <int DT, int GATE>
+__device__ __forceinline__ void gate_rows16_tmem(uint32_t s_tmem, uint32_t tile, uint32_t r0, int lane,
+                                                 uint32_t h_tmem) {
+  const uint32_t mat = lane >> 3, l8 = lane & 7;
+  const uint32_t a_row = r0 + l8 + (mat & 1) * 8;
+  uint32_t s[4][8], af[4][4], h[4][4];
+#pragma unroll
+  for (int pc = 0; pc < 4; ++pc) tmem_ld_16x256b_x2(s_tmem + pc * 16, s[pc]);
+  if (GATE == GATE_SILU) {
+#pragma unroll
+    for (int pc = 0; pc < 4; ++pc) ldmatrix_x4(tile + sw128_offset(a_row, pc * 2 + (mat >> 1)), af[pc]);
+  } else {
+#pragma unroll
+    for (int pc = 0; pc < 4; ++pc) af[pc][0] = af[pc][1] = af[pc][2] = af[pc][3] = 0u;
+  }
+  tmem_ld_wait();
+#pragma unroll
+  for (int pc = 0; pc < 4; ++pc) {
+    h[pc][0] = gate_pair<DT, GATE>(af[pc][0], __uint_as_float(s[pc][0]), __uint_as_float(s[pc][1]));
+    h[pc][1] = gate_pair<DT, GATE>(af[pc][1], __uint_as_float(s[pc][2]), __uint_as_float(s[pc][3]));
+    h[pc][2] = gate_pair<DT, GATE>(af[pc][2], __uint_as_float(s[pc][4]), __uint_as_float(s[pc][5]));
+    h[pc][3] = gate_pair<DT, GATE>(af[pc][3], __uint_as_float(s[pc][6]), __uint_as_float(s[pc][7]));
+  }
+#pragma unroll
+  for (int pc = 0; pc < 4; ++pc) tmem_st_frag16x16(h_tmem + pc * 8, h[pc]);
 }
 
 }  // namespace prism

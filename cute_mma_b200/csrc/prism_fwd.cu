@@ -8,38 +8,43 @@
 //
 // CTAs work in pairs (cluster of 2, tcgen05 cta_group::2) on (256-row, BN-column) output tiles: each CTA
 // owns 128 of the rows and loads half of the B tile, which halves the L2 traffic per flop.  Per CTA a
-// persistent loop over the pair's tiles; per 64-wide K chunk
-//   warps 0, 2  TMA producers: A tile [128 x 64] + R_g tile [E x 64] into the "AR" ring (warp 0), this
-//               CTA's half of the B_g tile [BN/2 x 64] into the "B" ring (warp 2); 128-byte swizzle,
-//               zero fill outside the tensors
-//   warps 4-19  gate warps, two groups of eight that take alternate chunks, 16 rows per warp: A and R fragments by ldmatrix, block rotation
-//               S = A_blk . R_blk^T by mma.sync (fp32), H = A*silu(S) (or H = S) on registers,
-//               H written to TMEM (tcgen05.st) as the A operand of the dense MMA: H never goes
-//               through shared memory, which is the scarce resource of this kernel
-//   warp 1      dense issuer (leader CTA only): C += H . B^T as 4 x tcgen05.mma M256 N=BN K=16 spanning
-//               both CTAs (A = H from TMEM, B = B_g from shared memory), fp32 accumulator in TMEM
+// persistent loop over the pair's tiles.  One ring of shared-memory stages, one stage per 64-wide K
+// chunk: the A tile [128 x 64], this CTA's half of the R_g tile [E/2 x 64] and of the B_g tile [BN/2 x 64].
+//   warps 0, 2  TMA producers (A + R, B); 128-byte swizzle, zero fill outside the tensors
+//   warp 1      MMA issuer (leader CTA only), per chunk
+//                 rotation  S = A_blk . R_blk^T per rotation block: tcgen05.mma M256 N=E K=16, fp32 into
+//                           one of four 64-column TMEM slots
+//                 dense     C += H . B^T: 4 x tcgen05.mma M256 N=BN K=16 with H read from TMEM, two chunks
+//                           behind the rotation
+//   warps 4-19  gate warps, two groups of eight that take alternate chunks, 16 rows per warp: S from
+//               TMEM (tcgen05.ld delivers the accumulator-fragment layout), A by ldmatrix (same layout),
+//               H = A*silu(S) (or H = S) on registers, H back to TMEM over the first half of the S slot
 //   warps 20-23 epilogue: tcgen05.ld C, + bias, cast, swizzled staging tile, TMA store.
-// Every role keeps its ring positions as counters; the single-thread roles do no division.
+// Both products run on tcgen05: mma.sync shares the tensor cores with tcgen05.mma and is starved
+// while tcgen05.mma bursts run, so a rotation on mma.sync serialises the gate warps with the dense
+// product.  The issuing thread runs alone on its instruction stream (a barrier test costs it ~65
+// clocks, a tcgen05.commit ~90): descriptors advance by 32-bit adds, and there is one wait and one
+// commit per product and chunk.
 #include "prism_host.cuh"
 #include "prism_kernels.cuh"
 
 #ifndef PRISM_DBG
-#define PRISM_DBG 0   // debugging aid: bit 0 skips the gate math, bit 1 the output stores, bit 2 the rotation MMAs
+#define PRISM_DBG 0   // debugging aid: bit 1 skips the output stores
 #endif
 
 namespace prism {
 
 namespace fwd {
 constexpr int kThreads = 768;
-constexpr int kWarpTma = 0, kWarpMma = 1, kWarpTmaB = 2;
+constexpr int kWarpTma = 0, kWarpMma = 1, kWarpTmaB = 2, kWarpRot = 3;
 constexpr int kGateWarp0 = 4;         // multiple of 4: (warp & 3) is the TMEM lane quarter a warp may touch
 constexpr int kGateGroups = 2;        // groups take alternate chunks ...
 constexpr int kWarpsPerGroup = 8;     // ... with 16 rows per warp
 constexpr int kNumGateWarps = kGateGroups * kWarpsPerGroup;
 constexpr int kEpiWarp0 = kGateWarp0 + kNumGateWarps;   // 20
-constexpr int kHBufs = 4;             // TMEM ring of H chunks (power of two), 32 columns each
-constexpr int kHCol0 = 256;           // accumulator: TMEM columns [0, 256); H ring: [256, 384)
 constexpr int kNumEpiWarps = 4;
+constexpr int kSlots = 4;             // TMEM slots of 64 columns: S (fp32), then H over its first 32 columns
+constexpr int kSlotCol0 = 256;        // accumulator: TMEM columns [0, 256); slots: [256, 512)
 constexpr int kMaxStages = 8;
 constexpr int kATileBytes = 128 * 128;   // [128 rows x 64 elems] 16-bit
 constexpr int kEpiStageBytes = 32 * 128; // per epilogue warp: [32 rows x 64 elems]
@@ -52,8 +57,9 @@ struct FwdParams {
   int n_mtiles, n_ntiles, ntiles_per_group, n_tiles;
   int PM;               // m-tiles per rasterisation panel
   int n_kchunks;
-  int sa, sb;           // stages of the AR ring / B ring
-  int r_tile_bytes;     // bytes reserved for the R tile of one AR stage (multiple of 1024)
+  int ns;               // stages of the shared-memory ring
+  int r_tile_bytes;     // bytes reserved for this CTA's half of the R tile (multiple of 1024)
+  int stage_bytes;
   int tma_store;        // 1: epilogue goes through TMA stores (BN multiple of 64)
   const void* bias;     // [N] or null
   void* C;
@@ -62,14 +68,12 @@ struct FwdParams {
 };
 
 struct FwdBarriers {
-  uint64_t ar_full[fwd::kMaxStages];
-  uint64_t a_empty[fwd::kMaxStages];
-  uint64_t b_full[fwd::kHBufs];
-  uint64_t b_empty[fwd::kHBufs];
-  uint64_t h_full[fwd::kHBufs];
-  uint64_t h_empty[fwd::kHBufs];
-  uint64_t acc_full;
-  uint64_t acc_empty;
+  uint64_t loads_full[fwd::kMaxStages];   // leader's copy is used: A, R, B of the stage landed in both CTAs
+  uint64_t done[fwd::kMaxStages];         // local, multicast commit: the dense product has read the stage
+  uint64_t s_full[fwd::kSlots];           // local, multicast commit: S of the chunk is in the slot
+  uint64_t h_full[fwd::kSlots];           // leader's copy is used: the gate warps of both CTAs wrote H
+  uint64_t acc_full;                      // local, multicast commit
+  uint64_t acc_empty;                     // leader's copy is used
   uint32_t tmem_base;
 };
 
@@ -89,14 +93,16 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
                  const FwdParams p) {
   using namespace fwd;
+  constexpr int KS = E / 16;   // K16 steps per rotation block
+  constexpr int NB = 64 / E;   // rotation blocks per chunk
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  const int ar_stage_bytes = kATileBytes + p.r_tile_bytes;
-  const int b_stage_bytes = p.BN * 64;   // this CTA's half of the B tile: BN/2 rows of 128 bytes
-  uint8_t* smemAR = smem;
-  uint8_t* smemB = smemAR + p.sa * ar_stage_bytes;
-  uint8_t* smemEpi = smemB + p.sb * b_stage_bytes;
+  // stage: [A tile | this CTA's half of the R tile | this CTA's half of the B tile]
+  const int b_off = kATileBytes + p.r_tile_bytes;
+  const int b_bytes = p.BN * 64;   // BN/2 rows of 128 bytes
+  uint8_t* smemSt = smem;
+  uint8_t* smemEpi = smemSt + p.ns * p.stage_bytes;
   FwdBarriers* bars = reinterpret_cast<FwdBarriers*>(smemEpi + kNumEpiWarps * kEpiStageBytes);
 
   const int warp = threadIdx.x >> 5;
@@ -108,17 +114,15 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kMaxStages; ++i) {
-      mbar_init(&bars->ar_full[i], 1);                    // local: this CTA's A and R tiles landed
-      mbar_init(&bars->a_empty[i], kWarpsPerGroup);       // local: the gate warps have read the tiles
+      mbar_init(&bars->loads_full[i], 4);   // two producers in each CTA, one arrive.expect_tx each
+      mbar_init(&bars->done[i], 1);
     }
-    for (int i = 0; i < kHBufs; ++i) {
-      mbar_init(&bars->b_full[i], 2);                     // leader's copy is used: both CTAs' B halves
-      mbar_init(&bars->b_empty[i], 1);                    // local, arrived by the multicast commit
-      mbar_init(&bars->h_full[i], 2 * kWarpsPerGroup);    // leader's copy is used: gate warps of both CTAs
-      mbar_init(&bars->h_empty[i], 1);                    // local, arrived by the multicast commit
+    for (int i = 0; i < kSlots; ++i) {
+      mbar_init(&bars->s_full[i], 1);
+      mbar_init(&bars->h_full[i], 2 * kWarpsPerGroup);
     }
-    mbar_init(&bars->acc_full, 1);                        // local, arrived by the multicast commit
-    mbar_init(&bars->acc_empty, 2 * kNumEpiWarps);        // leader's copy is used
+    mbar_init(&bars->acc_full, 1);
+    mbar_init(&bars->acc_empty, 2 * kNumEpiWarps);
     fence_mbar_init();
   }
   if (warp == kWarpMma) {
@@ -143,20 +147,21 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t total = (uint32_t)my_tiles * nk;   // chunks this CTA pair processes
 
   if (warp == kWarpTma) {
-    // ------------------------------------------------------------------ TMA producer: A and R tiles
+    // ------------------------------------------------------------------ TMA producer: A tile and half of the R tile
     if (lane == 0) {
-      Ring ra(p.sa);
+      Ring rs(p.ns);
       int ta = cid, ca = 0, mta, nta;
       tile_coords(p, ta, mta, nta);
       int ga = nta / p.ntiles_per_group;
       bool ok = true;
-      for (uint32_t j = 0; j < total; ++j) {
-        if (!mbar_wait(&bars->a_empty[ra.idx], ra.phase ^ 1)) { ok = false; break; }
-        uint8_t* dstA = smemAR + ra.idx * ar_stage_bytes;
-        mbar_arrive_expect_tx(&bars->ar_full[ra.idx], kATileBytes + p.E * 128);
-        tma_load_2d(dstA, &tmA, &bars->ar_full[ra.idx], ca * 64, mta * 256 + (int)rank * 128);
-        tma_load_2d(dstA + kATileBytes, &tmR, &bars->ar_full[ra.idx], ca * 64, ga * p.E);
-        ra.next();
+      for (uint32_t j = 0; j < total; ++j, rs.next()) {
+        if (!mbar_wait(&bars->done[rs.idx], rs.phase ^ 1)) { ok = false; break; }
+        uint8_t* dst = smemSt + rs.idx * p.stage_bytes;
+        // completion is counted on the leader's barrier: its MMAs read both CTAs' tiles
+        const uint32_t full = mapa_shared(smem_u32(&bars->loads_full[rs.idx]), 0);
+        mbar_arrive_expect_tx_cluster(full, kATileBytes + (E / 2) * 128);
+        tma_load_2d_pair(dst, &tmA, full, ca * 64, mta * 256 + (int)rank * 128);
+        tma_load_2d_pair(dst + kATileBytes, &tmR, full, ca * 64, ga * E + (int)rank * (E / 2));
         if (++ca == nk) {
           ca = 0;
           ta += n_clusters;
@@ -168,16 +173,16 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == kWarpTmaB) {
     // ------------------------------------------------------------------ TMA producer: this CTA's half of the B tiles
     if (lane == 0) {
+      Ring rs(p.ns);
       int tb = cid, cb = 0, mtb, ntb;
       tile_coords(p, tb, mtb, ntb);
       bool ok = true;
-      for (uint32_t j = 0; j < total; ++j) {
-        const uint32_t hb = j & (kHBufs - 1), hphase = (j / kHBufs) & 1;   // B stage = H buffer index
-        if (!mbar_wait(&bars->b_empty[hb], hphase ^ 1)) { ok = false; break; }
-        // completion is counted on the leader's barrier
-        const uint32_t bfull = mapa_shared(smem_u32(&bars->b_full[hb]), 0);
-        mbar_arrive_expect_tx_cluster(bfull, b_stage_bytes);
-        tma_load_2d_pair(smemB + hb * b_stage_bytes, &tmB, bfull, cb * 64, ntb * p.BN + (int)rank * (p.BN / 2));
+      for (uint32_t j = 0; j < total; ++j, rs.next()) {
+        if (!mbar_wait(&bars->done[rs.idx], rs.phase ^ 1)) { ok = false; break; }
+        const uint32_t full = mapa_shared(smem_u32(&bars->loads_full[rs.idx]), 0);
+        mbar_arrive_expect_tx_cluster(full, b_bytes);
+        tma_load_2d_pair(smemSt + rs.idx * p.stage_bytes + b_off, &tmB, full, cb * 64,
+                         ntb * p.BN + (int)rank * (p.BN / 2));
         if (++cb == nk) {
           cb = 0;
           tb += n_clusters;
@@ -186,30 +191,72 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
-  } else if (warp == kWarpMma) {
-    // ------------------------------------------------------------------ dense issuer
+  } else if (warp == kWarpRot) {
+    // ------------------------------------------------------------------ MMA issuer 1: rotation S = A . blockdiag(R_g)^T
+    // Two threads issue tcgen05.mma, one per product: while one of them tests barriers or commits, the
+    // MMAs of the other keep the tensor pipe busy.  Their MMAs are ordered by barriers only.
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc_c = make_idesc(DT, 256, p.BN, 0, 0);   // M = 256: 128 rows in each CTA
+      const uint32_t idesc_r = make_idesc(DT, 256, E, 0, 0);      // S block: M = 256 rows, N = E
+      // descriptors of stage 0; a stage further on adds stage_bytes >> 4 to the low words
+      const uint64_t da0 = desc_kmajor_sw128(smem_u32(smemSt), 1024);
+      const uint64_t dr0 = desc_kmajor_sw128(smem_u32(smemSt) + kATileBytes, 1024);
+      const uint32_t d_hi = (uint32_t)(da0 >> 32);
+      const uint32_t st_step = (uint32_t)p.stage_bytes >> 4;
+      const uint32_t slot0 = tmem_base + kSlotCol0;
+      Ring rl(p.ns), rf(p.ns);   // stage of chunk i / of chunk i - kSlots
+      bool ok = true;
+      for (uint32_t i = 0; i < total; ++i, rl.next()) {
+        const uint32_t slot = i & (kSlots - 1);
+        if (i >= (uint32_t)kSlots) {
+          // the slot still holds H of chunk i - 4 until that chunk's dense product has completed
+          // (the ring has at least kSlots stages, so this barrier cannot run a phase ahead)
+          if (!mbar_wait_cluster(&bars->done[rf.idx], rf.phase)) { ok = false; break; }
+          rf.next();
+        }
+        if (!mbar_wait_cluster(&bars->loads_full[rl.idx], rl.phase)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t a_lo = (uint32_t)da0 + rl.idx * st_step;
+        const uint32_t r_lo = (uint32_t)dr0 + rl.idx * st_step;
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+#pragma unroll
+          for (int ks = 0; ks < KS; ++ks) {
+            const int kk = b * KS + ks;   // K16 step inside the 64-wide chunk: +32 bytes on both operands
+            umma_f16_pair_lh(slot0 + slot * 64 + b * E, a_lo + kk * 2, d_hi, r_lo + kk * 2, d_hi, idesc_r,
+                             ks > 0 ? 1u : 0u);
+          }
+        }
+        umma_commit_pair(&bars->s_full[slot], 0x3);
+      }
+      if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
+    }
+  } else if (warp == kWarpMma) {
+    // ------------------------------------------------------------------ MMA issuer 2: dense product C += H . B^T
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc_c = make_idesc(DT, 256, p.BN, 0, 0);   // C tile:  M = 256 rows, N = BN
+      const uint64_t db0 = desc_kmajor_sw128(smem_u32(smemSt) + b_off, 1024);
+      const uint32_t d_hi = (uint32_t)(db0 >> 32);
+      const uint32_t st_step = (uint32_t)p.stage_bytes >> 4;
+      const uint32_t slot0 = tmem_base + kSlotCol0;
+      Ring rd(p.ns);
       int cm = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (uint32_t j = 0; j < total; ++j) {
-        const uint32_t hb = j & (kHBufs - 1), hphase = (j / kHBufs) & 1;
-        if (!mbar_wait_cluster(&bars->h_full[hb], hphase)) { ok = false; break; }
-        if (!mbar_wait_cluster(&bars->b_full[hb], hphase)) { ok = false; break; }
+      for (uint32_t jd = 0; jd < total; ++jd, rd.next()) {
+        const uint32_t slot = jd & (kSlots - 1);
+        // H complete implies that the stage's loads (B included) landed: the rotation waited for them
+        if (!mbar_wait_cluster(&bars->h_full[slot], (jd / kSlots) & 1)) { ok = false; break; }
         if (cm == 0) {
           if (!mbar_wait_cluster(&bars->acc_empty, acc_phase ^ 1)) { ok = false; break; }
         }
         tc_fence_after_sync();
-        const uint32_t h_tmem = tmem_base + kHCol0 + hb * 32;
-        const uint32_t b_addr = smem_u32(smemB + hb * b_stage_bytes);
+        const uint32_t h_tmem = slot0 + slot * 64;
+        const uint32_t b_lo = (uint32_t)db0 + rd.idx * st_step;
+        umma_f16_pair_ts_lh(tmem_base, h_tmem, b_lo, d_hi, idesc_c, cm > 0 ? 1u : 0u);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          umma_f16_pair_ts(tmem_base, h_tmem + ks * 8, desc_kmajor_sw128(b_addr + ks * 32, 1024), idesc_c,
-                           (cm > 0 || ks > 0) ? 1u : 0u);
-        }
-        umma_commit_pair(&bars->h_empty[hb], 0x3);   // both CTAs' gate warps may refill the H buffer
-        umma_commit_pair(&bars->b_empty[hb], 0x3);   // both CTAs' B stages are free
+        for (int ks = 1; ks < 4; ++ks)
+          umma_f16_pair_ts_lh(tmem_base, h_tmem + ks * 8, b_lo + ks * 2, d_hi, idesc_c, 1u);
+        umma_commit_pair(&bars->done[rd.idx], 0x3);   // both CTAs may refill the stage; the slot is free
         if (++cm == nk) {
           cm = 0;
           umma_commit_pair(&bars->acc_full, 0x3);
@@ -223,23 +270,19 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t gw = warp - kGateWarp0;
     const uint32_t group = gw / kWarpsPerGroup;               // which chunks (j mod kGateGroups)
     const uint32_t r0 = (gw & 3) * 32 + ((gw >> 2) & 1) * 16; // this warp's 16 rows, inside its TMEM lane quarter
-    Ring ra(p.sa);
-    for (uint32_t i = 0; i < group; ++i) ra.next();
+    Ring rs(p.ns);
+    for (uint32_t i = 0; i < group; ++i) rs.next();
     bool ok = true;
-    for (uint32_t j = group; j < total; j += kGateGroups, ra.next(), ra.next()) {
-      const uint32_t hb = j & (kHBufs - 1), hphase = (j / kHBufs) & 1;
-      if (!mbar_wait(&bars->ar_full[ra.idx], ra.phase)) { ok = false; break; }
-      if (!mbar_wait(&bars->h_empty[hb], hphase ^ 1)) { ok = false; break; }
+    for (uint32_t j = group; j < total; j += kGateGroups, rs.next(), rs.next()) {
+      const uint32_t slot = j & (kSlots - 1);
+      if (!mbar_wait(&bars->s_full[slot], (j / kSlots) & 1)) { ok = false; break; }
       tc_fence_after_sync();
-      const uint32_t tile = smem_u32(smemAR + ra.idx * ar_stage_bytes);
-      rotate_gate_rows16<DT, GATE, E>(tile, tile + kATileBytes, r0, lane, tmem_base + (r0 << 16) + kHCol0 + hb * 32);
+      const uint32_t s_tmem = tmem_base + (r0 << 16) + kSlotCol0 + slot * 64;
+      gate_rows16_tmem<DT, GATE>(s_tmem, smem_u32(smemSt + rs.idx * p.stage_bytes), r0, lane, s_tmem);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&bars->a_empty[ra.idx]);                                   // A and R tiles are free again
-        mbar_arrive_cluster(mapa_shared(smem_u32(&bars->h_full[hb]), 0));      // H chunk is in TMEM
-      }
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars->h_full[slot]), 0));   // H is in TMEM
     }
     if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
   } else if (warp >= kEpiWarp0) {
@@ -352,29 +395,25 @@ int launch_fwd(const FwdArgs& a) {
   p.PM = a.PM > 0 ? a.PM : 8;
   if (p.PM > p.n_mtiles) p.PM = p.n_mtiles;
   p.n_kchunks = (a.K + 63) / 64;
-  p.r_tile_bytes = ((a.E * 128) + 1023) / 1024 * 1024;
+  p.r_tile_bytes = ((a.E / 2 * 128) + 1023) / 1024 * 1024;   // this CTA's E/2 rows of the R tile
   p.tma_store = (a.BN % 64 == 0) ? 1 : 0;
   p.bias = a.bias; p.C = a.C; p.ldc = a.ldc; p.err = a.err;
 
   const int budget = 227 * 1024 - 1024 - (int)sizeof(FwdBarriers) - 256 - fwd::kNumEpiWarps * fwd::kEpiStageBytes;
-  const int ar_bytes = fwd::kATileBytes + p.r_tile_bytes;
-  const int b_bytes = a.BN * 64;   // per CTA: half of the B tile
-  // the AR ring feeds rotation + gate, which run ahead of the dense product: give it the deeper pipeline
-  // the B ring has one stage per H buffer (they share barriers); the AR ring takes what is left
-  const int sb = fwd::kHBufs;
-  int sa = a.sa > 0 ? a.sa : fwd::kMaxStages;
-  if (sa > fwd::kMaxStages) sa = fwd::kMaxStages;
-  while (sa > 2 && sa * ar_bytes + sb * b_bytes > budget) --sa;
-  if (sa * ar_bytes + sb * b_bytes > budget)
+  p.stage_bytes = fwd::kATileBytes + p.r_tile_bytes + a.BN * 64;   // A tile, halves of the R and B tiles
+  int ns = a.sa > 0 ? a.sa : fwd::kMaxStages;
+  if (ns > fwd::kMaxStages) ns = fwd::kMaxStages;
+  while (ns > fwd::kSlots && ns * p.stage_bytes > budget) --ns;
+  if (ns < fwd::kSlots || ns * p.stage_bytes > budget)   // a stage per TMEM slot at least (see the rotation issuer)
     return fail(PRISM_ERR_UNSUPPORTED, "forward tile does not fit shared memory (BN=%d E=%d)", a.BN, a.E);
-  p.sa = sa; p.sb = sb;
-  const int smem_bytes = sa * ar_bytes + sb * b_bytes + fwd::kNumEpiWarps * fwd::kEpiStageBytes +
+  p.ns = ns;
+  const int smem_bytes = ns * p.stage_bytes + fwd::kNumEpiWarps * fwd::kEpiStageBytes +
                          (int)sizeof(FwdBarriers) + 1024;
 
   CUtensorMap tmA, tmR, tmB, tmC;
   int rc;
   if ((rc = make_tmap_2d(&tmA, a.dtype, a.A, a.M, a.K, a.lda, 128, 64, true))) return rc;
-  if ((rc = make_tmap_2d(&tmR, a.dtype, a.R_eff, (uint64_t)(a.N / a.gs) * a.E, a.K, a.ldr, a.E, 64, true))) return rc;
+  if ((rc = make_tmap_2d(&tmR, a.dtype, a.R_eff, (uint64_t)(a.N / a.gs) * a.E, a.K, a.ldr, a.E / 2, 64, true))) return rc;
   if ((rc = make_tmap_2d(&tmB, a.dtype, a.B, a.N, a.K, a.ldb, a.BN / 2, 64, true))) return rc;
   if ((rc = make_tmap_2d(&tmC, a.dtype, a.C, a.M, a.N, a.ldc, 32, 64, true))) return rc;
 
