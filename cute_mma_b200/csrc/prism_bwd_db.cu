@@ -7,39 +7,46 @@
 //
 // CTAs work in pairs (cluster of 2, tcgen05 cta_group::2).  A pair owns one accumulator tile
 // D[f, n] (256 features x BN outputs of one group; each CTA holds its 128 features in its own TMEM
-// and loads half of the dC columns) and a contiguous range of 128-token blocks.  The contraction runs over tokens, so both
-// tensor-core operands are "MN-major": H tiles [128 tokens x 64 features] and dC tiles
-// [128 tokens x 64 outputs] are used exactly as TMA / the gate warps lay them out, no transposes.
-//   TMA warp   : R_g tiles once; per token block two A tiles and ceil(BN/64) dC tiles
-//   gate warps : two groups taking alternate token blocks, 16 token rows per warp; block rotation S = A_blk . R_blk^T by mma.sync on ldmatrix
-//                fragments, H = A*silu(S) on registers, stmatrix of H over the A tiles in place
-//   MMA issuer : D += H^T . dC as 8 x tcgen05.mma M128 N=BN K=16 per token block
-//   epilogue   : D -> dB (transposed store), or fp32 partials when the token range is split;
-//                a second kernel then adds the partials in a fixed order (deterministic).
+// and loads half of the dC columns) and a contiguous range of 128-token blocks.  The contraction of
+// the dense product runs over tokens, so both its operands are "MN-major": H tiles [128 tokens x 64
+// features] and dC tiles [128 tokens x 64 outputs] are used as the gate warps / TMA lay them out.
+//   warp 0      TMA: R_g tiles once; per token block two A tiles and ceil(BN/128) dC tiles
+//   warp 1      MMA issuer (leader): rotation S = A_blk . R_blk^T per rotation block as tcgen05.mma
+//               M256 N=2E K=16.  The two CTAs hold different features, hence different R blocks; an
+//               MMA spanning both takes its N rows half from each CTA, so it multiplies every row by
+//               both R blocks: a CTA's own product lands in columns [rank*E, rank*E+E) of the block's
+//               2E columns of S, the other half is ignored.
+//   warps 4-19  gate warps, 16 token rows x 64 features each: S from TMEM, A by ldmatrix, H = A*silu(S)
+//               on registers, stmatrix of H over the A tile in place
+//               Dense product D += H^T . dC as 8 x tcgen05.mma M256 N=BN K=16 per token block.
+//   warps 20-23 epilogue: D -> dB (transposed store), or fp32 partials when the token range is split;
+//               a second kernel then adds the partials in a fixed order (deterministic).
+// Both products run on tcgen05: mma.sync would share the tensor cores with tcgen05.mma and starve
+// behind it.
 #include "prism_host.cuh"
 #include "prism_kernels.cuh"
 
 namespace prism {
 
 namespace db {
-constexpr int kThreads = 704;     // warp 0 TMA, 1 dense issuer, 2-17 gate, 18-21 epilogue
+constexpr int kThreads = 768;
 constexpr int kWarpTma = 0, kWarpMma = 1;
-constexpr int kGateWarp0 = 2;
-constexpr int kGateGroups = 2;    // groups take alternate token blocks ...
-constexpr int kWarpsPerGroup = 8; // ... with 16 token rows per warp
-constexpr int kNumGateWarps = kGateGroups * kWarpsPerGroup;
-constexpr int kEpiWarp0 = kGateWarp0 + kNumGateWarps;   // (warp & 3) of warps 18..21 covers 2,3,0,1
+constexpr int kGateWarp0 = 4;      // multiple of 4: (warp & 3) is the TMEM lane quarter a warp may touch
+constexpr int kNumGateWarps = 16;  // 8 row groups x 2 feature tiles
+constexpr int kEpiWarp0 = kGateWarp0 + kNumGateWarps;   // 20
 constexpr int kMaxStages = 4;
-constexpr int kTile = 128 * 128;  // bytes of a [128 x 64] 16-bit tile
+constexpr int kTile = 128 * 128;   // bytes of a [128 x 64] 16-bit tile
+constexpr int kSCol0 = 256;        // accumulator: TMEM columns [0, 256); S: [256, 512)
 }  // namespace db
 
 struct DbParams {
   int M, N, K, gs, E, BN;
   int ntiles_per_group;
   int blocks_per_split, n_tokblocks;
-  int dc_tiles;       // ceil(BN / 64)
+  int dc_tiles;       // ceil(BN / 128): 64-column dC tiles per CTA
   int r_tile_bytes;   // bytes reserved per R tile (multiple of 1024)
-  int sa, sd;         // stages of the A ring / dC ring
+  int ns;             // stages: two A tiles + this CTA's dC tiles
+  int stage_bytes;
   int splits;
   float scale;
   void* dB;
@@ -49,12 +56,11 @@ struct DbParams {
 };
 
 struct DbBarriers {
-  uint64_t r_full;
-  uint64_t a_full[db::kMaxStages];
-  uint64_t h_full[db::kMaxStages];
-  uint64_t a_empty[db::kMaxStages];
-  uint64_t dc_full[db::kMaxStages];
-  uint64_t dc_empty[db::kMaxStages];
+  uint64_t r_full;                     // local: this CTA's R tiles landed (once)
+  uint64_t a_full[db::kMaxStages];     // leader's copy is used: both CTAs' A tiles landed
+  uint64_t hd_full[db::kMaxStages];    // leader's copy is used: gate warps of both CTAs wrote H, dC halves landed
+  uint64_t stage_free[db::kMaxStages]; // local, multicast commit: the dense product has read the stage
+  uint64_t s_full;                     // local, multicast commit: S of the token block is in TMEM
   uint64_t acc_full;
   uint32_t tmem_base;
 };
@@ -64,15 +70,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(db::kThreads, 1)
 prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmR,
                     const __grid_constant__ CUtensorMap tmdC, const DbParams p) {
   using namespace db;
+  constexpr int KS = E / 16;    // K16 steps per rotation block
+  constexpr int NBLK = 128 / E; // rotation blocks of this CTA's 128 features
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  const int a_stage_bytes = 2 * kTile;
-  const int dc_stage_bytes = p.dc_tiles * kTile;
-  uint8_t* smemR = smem;
-  uint8_t* smemA = smemR + 2 * p.r_tile_bytes;
-  uint8_t* smemD = smemA + p.sa * a_stage_bytes;
-  DbBarriers* bars = reinterpret_cast<DbBarriers*>(smemD + p.sd * dc_stage_bytes);
+  uint8_t* smemR = smem;                           // two R tiles [E x 64]
+  uint8_t* smemSt = smemR + 2 * p.r_tile_bytes;    // stages: [A tile f0.. | A tile f0+64.. | dC tiles]
+  DbBarriers* bars = reinterpret_cast<DbBarriers*>(smemSt + p.ns * p.stage_bytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -88,12 +93,11 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(&bars->r_full, 1);
     for (int i = 0; i < kMaxStages; ++i) {
-      mbar_init(&bars->a_full[i], 1);                  // local: this CTA's A tiles landed
-      mbar_init(&bars->h_full[i], 2 * kWarpsPerGroup); // leader's copy is used: gate warps of both CTAs
-      mbar_init(&bars->a_empty[i], 1);                 // local, arrived by the multicast commit
-      mbar_init(&bars->dc_full[i], 2);                 // leader's copy is used: both CTAs' dC halves
-      mbar_init(&bars->dc_empty[i], 1);
+      mbar_init(&bars->a_full[i], 2);                        // one arrive.expect_tx per CTA
+      mbar_init(&bars->hd_full[i], 2 * kNumGateWarps + 2);   // gate warps of both CTAs + one arrive.expect_tx per CTA
+      mbar_init(&bars->stage_free[i], 1);
     }
+    mbar_init(&bars->s_full, 1);
     mbar_init(&bars->acc_full, 1);
     fence_mbar_init();
   }
@@ -118,69 +122,104 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       bool ok = true;
-      mbar_arrive_expect_tx(&bars->r_full, 2 * p.E * 128);
-      tma_load_2d(smemR, &tmR, &bars->r_full, f0, g * p.E);
-      tma_load_2d(smemR + p.r_tile_bytes, &tmR, &bars->r_full, f0 + 64, g * p.E);
-      Ring ra(p.sa), rd(p.sd);
-      for (int j = 0; j < nb && ok; ++j, ra.next(), rd.next()) {
+      mbar_arrive_expect_tx(&bars->r_full, 2 * E * 128);
+      tma_load_2d(smemR, &tmR, &bars->r_full, f0, g * E);
+      tma_load_2d(smemR + p.r_tile_bytes, &tmR, &bars->r_full, f0 + 64, g * E);
+      // the rotation issuer (leader) reads the peer's R tiles too: it learns of them through the peer's
+      // first A tiles, which are issued after this wait
+      if (!mbar_wait(&bars->r_full, 0)) ok = false;
+      Ring rs(p.ns);
+      for (int j = 0; j < nb && ok; ++j, rs.next()) {
         const int tok0 = (tb0 + j) * 128;
-        const int sa = ra.idx, sd = rd.idx;
-        if (!mbar_wait(&bars->a_empty[sa], ra.phase ^ 1)) { ok = false; break; }
-        uint8_t* dstA = smemA + sa * a_stage_bytes;
-        mbar_arrive_expect_tx(&bars->a_full[sa], 2 * kTile);
-        tma_load_2d(dstA, &tmA, &bars->a_full[sa], f0, tok0);
-        tma_load_2d(dstA + kTile, &tmA, &bars->a_full[sa], f0 + 64, tok0);
-        if (!mbar_wait(&bars->dc_empty[sd], rd.phase ^ 1)) { ok = false; break; }
-        uint8_t* dstD = smemD + sd * dc_stage_bytes;
-        // this CTA's half of the dC columns; completion is counted on the leader's barrier
-        const uint32_t dcfull = mapa_shared(smem_u32(&bars->dc_full[sd]), 0);
-        mbar_arrive_expect_tx_cluster(dcfull, dc_stage_bytes);
-        for (int t = 0; t < p.dc_tiles; ++t)
-          tma_load_2d_pair(dstD + t * kTile, &tmdC, dcfull, n0 + (int)rank * (p.BN / 2) + 64 * t, tok0);
+        if (!mbar_wait(&bars->stage_free[rs.idx], rs.phase ^ 1)) { ok = false; break; }
+        uint8_t* dst = smemSt + rs.idx * p.stage_bytes;
+        // completion is counted on the leader's barriers: its MMAs read both CTAs' tiles
+        const uint32_t afull = mapa_shared(smem_u32(&bars->a_full[rs.idx]), 0);
+        mbar_arrive_expect_tx_cluster(afull, 2 * kTile);
+        tma_load_2d_pair(dst, &tmA, afull, f0, tok0);
+        tma_load_2d_pair(dst + kTile, &tmA, afull, f0 + 64, tok0);
+        const uint32_t hdfull = mapa_shared(smem_u32(&bars->hd_full[rs.idx]), 0);
+        mbar_arrive_expect_tx_cluster(hdfull, p.dc_tiles * kTile);
+        for (int t = 0; t < p.dc_tiles; ++t)   // this CTA's half of the dC columns
+          tma_load_2d_pair(dst + (2 + t) * kTile, &tmdC, hdfull, n0 + (int)rank * (p.BN / 2) + 64 * t, tok0);
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
   } else if (warp == kWarpMma) {
-    // ------------------------------------------------------------------ dense issuer
+    // ------------------------------------------------------------------ MMA issuer: rotation and dense product
+    // S is single-buffered (TMEM: 256 columns of accumulator, 256 of S), so the rotation of block
+    // j + 1 has to wait for the gate warps of block j - and has to be queued BEFORE the dense product
+    // of block j (tcgen05.mma executes in order): the gate warps then work on block j + 1 while the
+    // tensor pipe runs the dense product of block j.
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc_d = make_idesc(DT, 256, p.BN, 1, 1);   // M = 256: 128 features in each CTA
+      const uint32_t idesc_r = make_idesc(DT, 256, 2 * E, 0, 0);   // rows: both CTAs' tokens; N: E rows of R from each CTA
+      const uint32_t idesc_d = make_idesc(DT, 256, p.BN, 1, 1);    // M = 256: 128 features in each CTA
+      const uint64_t da0 = desc_kmajor_sw128(smem_u32(smemSt), 1024);
+      const uint64_t dr0 = desc_kmajor_sw128(smem_u32(smemR), 1024);
+      const uint64_t dh0 = desc_mnmajor_sw128(smem_u32(smemSt), kTile, 1024);
+      const uint64_t dd0 = desc_mnmajor_sw128(smem_u32(smemSt) + 2 * kTile, kTile, 1024);
+      const uint32_t k_hi = (uint32_t)(da0 >> 32), h_hi = (uint32_t)(dh0 >> 32), d_hi = (uint32_t)(dd0 >> 32);
+      const uint32_t st_step = (uint32_t)p.stage_bytes >> 4;
+      const uint32_t r_step = (uint32_t)p.r_tile_bytes >> 4;
+      const uint32_t s0 = tmem_base + kSCol0;
       bool ok = true;
-      Ring ra(p.sa), rd(p.sd);
-      for (int j = 0; j < nb && ok; ++j, ra.next(), rd.next()) {
-        if (!mbar_wait_cluster(&bars->h_full[ra.idx], ra.phase)) { ok = false; break; }
-        if (!mbar_wait_cluster(&bars->dc_full[rd.idx], rd.phase)) { ok = false; break; }
-        tc_fence_after_sync();
-        const uint32_t h_addr = smem_u32(smemA + ra.idx * a_stage_bytes);
-        const uint32_t d_addr = smem_u32(smemD + rd.idx * dc_stage_bytes);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          umma_f16_pair(tmem_base, desc_mnmajor_sw128(h_addr + ks * 2048, kTile, 1024),
-                        desc_mnmajor_sw128(d_addr + ks * 2048, kTile, 1024), idesc_d,
-                        (j > 0 || ks > 0) ? 1u : 0u);
+      Ring rr(p.ns), rd(p.ns);   // stage of the block being rotated / multiplied
+      for (int j = -1; j < nb && ok; ++j) {
+        if (j >= 0) {
+          // gate warps done with block j: H written, S free again; the dC halves landed
+          if (!mbar_wait_cluster(&bars->hd_full[rd.idx], rd.phase)) { ok = false; break; }
         }
-        umma_commit_pair(&bars->a_empty[ra.idx], 0x3);
-        umma_commit_pair(&bars->dc_empty[rd.idx], 0x3);
-        if (j == nb - 1) umma_commit_pair(&bars->acc_full, 0x3);
+        if (j + 1 < nb) {
+          if (!mbar_wait_cluster(&bars->a_full[rr.idx], rr.phase)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_lo = (uint32_t)da0 + rr.idx * st_step;
+#pragma unroll
+          for (int b = 0; b < NBLK; ++b) {
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+              // features b*E + ks*16 .. +16 of the CTA's 128: tile (64 features) and 32-byte step inside it
+              const int fo = b * E + ks * 16;
+              const uint32_t ta = (uint32_t)((fo >> 6) * (kTile >> 4) + ((fo & 63) >> 4) * 2);
+              const uint32_t tr = (uint32_t)(fo >> 6) * r_step + (uint32_t)(((fo & 63) >> 4) * 2);
+              umma_f16_pair_lh(s0 + b * 2 * E, a_lo + ta, k_hi, (uint32_t)dr0 + tr, k_hi, idesc_r, ks > 0 ? 1u : 0u);
+            }
+          }
+          umma_commit_pair(&bars->s_full, 0x3);
+          rr.next();
+        }
+        if (j >= 0) {
+          tc_fence_after_sync();
+          const uint32_t h_lo = (uint32_t)dh0 + rd.idx * st_step;
+          const uint32_t d_lo = (uint32_t)dd0 + rd.idx * st_step;
+          umma_f16_pair_lh(tmem_base, h_lo, h_hi, d_lo, d_hi, idesc_d, j > 0 ? 1u : 0u);
+#pragma unroll
+          for (int ks = 1; ks < 8; ++ks)   // 16 tokens = 2048 bytes further on in both tiles
+            umma_f16_pair_lh(tmem_base, h_lo + ks * 128, h_hi, d_lo + ks * 128, d_hi, idesc_d, 1u);
+          umma_commit_pair(&bars->stage_free[rd.idx], 0x3);
+          if (j == nb - 1) umma_commit_pair(&bars->acc_full, 0x3);
+          rd.next();
+        }
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
   } else if (warp >= kGateWarp0 && warp < kEpiWarp0) {
     // ------------------------------------------------------------------ gate warps
-    const int gw = warp - kGateWarp0;
-    const int group = gw / kWarpsPerGroup;            // which token blocks (j mod kGateGroups)
-    const uint32_t r0 = (gw % kWarpsPerGroup) * 16;   // this warp's 16 token rows of the block
-    bool ok = mbar_wait(&bars->r_full, 0);
-    const uint32_t r_addr = smem_u32(smemR);
-    Ring ra(p.sa);
-    for (int i = 0; i < group; ++i) ra.next();
-    for (int j = group; j < nb && ok; j += kGateGroups, ra.next(), ra.next()) {
-      if (!mbar_wait(&bars->a_full[ra.idx], ra.phase)) { ok = false; break; }
-      const uint32_t tile = smem_u32(smemA + ra.idx * a_stage_bytes);
-      rotate_gate_rows16<DT, GATE, E>(tile, r_addr, r0, lane);
-      rotate_gate_rows16<DT, GATE, E>(tile + kTile, r_addr + p.r_tile_bytes, r0, lane);
-      fence_proxy_async_smem();
+    const uint32_t gw = warp - kGateWarp0;
+    const uint32_t r0 = (gw & 3) * 32 + ((gw >> 2) & 1) * 16;   // 16 token rows inside the warp's TMEM lane quarter
+    const uint32_t ft = gw >> 3;                                // which 64-feature tile
+    // S of rotation block b sits in columns [2E b, 2E b + 2E); this CTA's product in the rank-th half
+    const uint32_t s_tmem = tmem_base + (r0 << 16) + kSCol0 + ft * (64 / E) * 2 * E + rank * E;
+    bool ok = true;
+    Ring rs(p.ns);
+    for (int j = 0; j < nb && ok; ++j, rs.next()) {
+      if (!mbar_wait(&bars->s_full, j & 1)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t tile = smem_u32(smemSt + rs.idx * p.stage_bytes + ft * kTile);
+      gate_rows16_tmem_smem<DT, GATE, E>(s_tmem, 2 * E, tile, r0, lane);
+      fence_proxy_async_smem();   // H was written by the generic proxy, the MMA reads it through the async proxy
+      tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars->h_full[ra.idx]), 0));
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&bars->hd_full[rs.idx]), 0));
     }
     if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
   } else if (warp >= kEpiWarp0) {
@@ -267,18 +306,13 @@ int launch_bwd_db(const DbArgs& a) {
     return fail(PRISM_ERR_WORKSPACE, "bwd_db: split accumulation needs a partial-sum workspace");
 
   const int budget = 227 * 1024 - 1024 - (int)sizeof(DbBarriers) - 256 - 2 * p.r_tile_bytes;
-  const int a_bytes = 2 * db::kTile, d_bytes = p.dc_tiles * db::kTile;
-  int sa = 2, sd = 2;
-  if (sa * a_bytes + sd * d_bytes > budget)
+  p.stage_bytes = (2 + p.dc_tiles) * db::kTile;
+  int ns = db::kMaxStages;
+  while (ns > 2 && ns * p.stage_bytes > budget) --ns;
+  if (ns * p.stage_bytes > budget)
     return fail(PRISM_ERR_UNSUPPORTED, "bwd_db tile does not fit shared memory (BN=%d E=%d)", a.BN, a.E);
-  bool grew = true;
-  while (grew) {
-    grew = false;
-    if (sd < db::kMaxStages && sa * a_bytes + (sd + 1) * d_bytes <= budget) { ++sd; grew = true; }
-    if (sa < db::kMaxStages && (sa + 1) * a_bytes + sd * d_bytes <= budget) { ++sa; grew = true; }
-  }
-  p.sa = sa; p.sd = sd;
-  const int smem_bytes = 2 * p.r_tile_bytes + sa * a_bytes + sd * d_bytes + (int)sizeof(DbBarriers) + 1024;
+  p.ns = ns;
+  const int smem_bytes = 2 * p.r_tile_bytes + ns * p.stage_bytes + (int)sizeof(DbBarriers) + 1024;
 
   CUtensorMap tmA, tmR, tmdC;
   int rc;

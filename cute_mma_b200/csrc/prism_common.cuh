@@ -813,4 +813,37 @@ __device__ __forceinline__ void gate_rows16_tmem(uint32_t s_tmem, uint32_t tile,
   for (int pc = 0; pc < 4; ++pc) tmem_st_frag16x16(h_tmem + pc * 8, h[pc]);
 }
 
+// The same gate step with H going to shared memory: the warp's 16 rows x 64 columns of the A tile
+// are overwritten in place with H (stmatrix), for kernels whose dense product needs H as a
+// shared-memory operand.  Piece pc (16 columns) of S sits at TMEM column s_col(pc) of s_tmem:
+// with S laid out in rotation blocks of `blk_stride` columns (>= E), the piece of block b, part np
+// starts at b * blk_stride + np * 16.
+template <int DT, int GATE, int E>
+__device__ __forceinline__ void gate_rows16_tmem_smem(uint32_t s_tmem, uint32_t blk_stride, uint32_t tile, uint32_t r0,
+                                                      int lane) {
+  constexpr int KS = E / 16;
+  const uint32_t mat = lane >> 3, l8 = lane & 7;
+  const uint32_t a_row = r0 + l8 + (mat & 1) * 8;
+  uint32_t s[4][8], af[4][4], h[4][4];
+#pragma unroll
+  for (int pc = 0; pc < 4; ++pc) tmem_ld_16x256b_x2(s_tmem + (pc / KS) * blk_stride + (pc % KS) * 16, s[pc]);
+  if (GATE == GATE_SILU) {
+#pragma unroll
+    for (int pc = 0; pc < 4; ++pc) ldmatrix_x4(tile + sw128_offset(a_row, pc * 2 + (mat >> 1)), af[pc]);
+  } else {
+#pragma unroll
+    for (int pc = 0; pc < 4; ++pc) af[pc][0] = af[pc][1] = af[pc][2] = af[pc][3] = 0u;
+  }
+  tmem_ld_wait();
+#pragma unroll
+  for (int pc = 0; pc < 4; ++pc) {
+    h[pc][0] = gate_pair<DT, GATE>(af[pc][0], __uint_as_float(s[pc][0]), __uint_as_float(s[pc][1]));
+    h[pc][1] = gate_pair<DT, GATE>(af[pc][1], __uint_as_float(s[pc][2]), __uint_as_float(s[pc][3]));
+    h[pc][2] = gate_pair<DT, GATE>(af[pc][2], __uint_as_float(s[pc][4]), __uint_as_float(s[pc][5]));
+    h[pc][3] = gate_pair<DT, GATE>(af[pc][3], __uint_as_float(s[pc][6]), __uint_as_float(s[pc][7]));
+  }
+#pragma unroll
+  for (int pc = 0; pc < 4; ++pc) stmatrix_x4(tile + sw128_offset(a_row, pc * 2 + (mat >> 1)), h[pc]);
+}
+
 }  // namespace prism
