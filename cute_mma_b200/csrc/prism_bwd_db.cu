@@ -61,6 +61,7 @@ struct DbBarriers {
   uint64_t hd_full[db::kMaxStages];    // leader's copy is used: gate warps of both CTAs wrote H, dC halves landed
   uint64_t stage_free[db::kMaxStages]; // local, multicast commit: the dense product has read the stage
   uint64_t s_full;                     // local, multicast commit: S of the token block is in TMEM
+  uint64_t s_free;                     // leader's copy is used: the gate warps of both CTAs hold S in registers
   uint64_t acc_full;
   uint32_t tmem_base;
 };
@@ -98,6 +99,7 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       mbar_init(&bars->stage_free[i], 1);
     }
     mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->s_free, 2 * kNumGateWarps);
     mbar_init(&bars->acc_full, 1);
     fence_mbar_init();
   }
@@ -147,10 +149,10 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ MMA issuer: rotation and dense product
-    // S is single-buffered (TMEM: 256 columns of accumulator, 256 of S), so the rotation of block
-    // j + 1 has to wait for the gate warps of block j - and has to be queued BEFORE the dense product
-    // of block j (tcgen05.mma executes in order): the gate warps then work on block j + 1 while the
-    // tensor pipe runs the dense product of block j.
+    // S is single-buffered (TMEM: 256 columns of accumulator, 256 of S).  The gate warps copy their S
+    // values to registers first thing and release the buffer, so the rotation of block j + 1 is
+    // issued while they still work on block j; it is queued BEFORE the dense product of block j
+    // (tcgen05.mma executes in order), which has to wait for them.
     if (lane == 0 && rank == 0) {
       const uint32_t idesc_r = make_idesc(DT, 256, 2 * E, 0, 0);   // rows: both CTAs' tokens; N: E rows of R from each CTA
       const uint32_t idesc_d = make_idesc(DT, 256, p.BN, 1, 1);    // M = 256: 128 features in each CTA
@@ -165,11 +167,10 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       bool ok = true;
       Ring rr(p.ns), rd(p.ns);   // stage of the block being rotated / multiplied
       for (int j = -1; j < nb && ok; ++j) {
-        if (j >= 0) {
-          // gate warps done with block j: H written, S free again; the dC halves landed
-          if (!mbar_wait_cluster(&bars->hd_full[rd.idx], rd.phase)) { ok = false; break; }
-        }
         if (j + 1 < nb) {
+          if (j >= 0) {   // the gate warps hold S of block j in registers
+            if (!mbar_wait_cluster(&bars->s_free, j & 1)) { ok = false; break; }
+          }
           if (!mbar_wait_cluster(&bars->a_full[rr.idx], rr.phase)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t a_lo = (uint32_t)da0 + rr.idx * st_step;
@@ -188,6 +189,8 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           rr.next();
         }
         if (j >= 0) {
+          // gate warps done with block j: H written; the dC halves landed
+          if (!mbar_wait_cluster(&bars->hd_full[rd.idx], rd.phase)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t h_lo = (uint32_t)dh0 + rd.idx * st_step;
           const uint32_t d_lo = (uint32_t)dd0 + rd.idx * st_step;
@@ -209,13 +212,14 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const uint32_t ft = gw >> 3;                                // which 64-feature tile
     // S of rotation block b sits in columns [2E b, 2E b + 2E); this CTA's product in the rank-th half
     const uint32_t s_tmem = tmem_base + (r0 << 16) + kSCol0 + ft * (64 / E) * 2 * E + rank * E;
+    const uint32_t s_free_addr = mapa_shared(smem_u32(&bars->s_free), 0);
     bool ok = true;
     Ring rs(p.ns);
     for (int j = 0; j < nb && ok; ++j, rs.next()) {
       if (!mbar_wait(&bars->s_full, j & 1)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t tile = smem_u32(smemSt + rs.idx * p.stage_bytes + ft * kTile);
-      gate_rows16_tmem_smem<DT, GATE, E>(s_tmem, 2 * E, tile, r0, lane);
+      gate_rows16_tmem_smem<DT, GATE, E>(s_tmem, 2 * E, tile, r0, lane, s_free_addr);
       fence_proxy_async_smem();   // H was written by the generic proxy, the MMA reads it through the async proxy
       tc_fence_before_sync();
       __syncwarp();

@@ -818,9 +818,11 @@ __device__ __forceinline__ void gate_rows16_tmem(uint32_t s_tmem, uint32_t tile,
 // shared-memory operand.  Piece pc (16 columns) of S sits at TMEM column s_col(pc) of s_tmem:
 // with S laid out in rotation blocks of `blk_stride` columns (>= E), the piece of block b, part np
 // starts at b * blk_stride + np * 16.
+// s_free (a shared::cluster barrier address, or 0) is arrived on as soon as this warp holds its S
+// values in registers: a single S buffer can then be refilled while the gate math still runs.
 template <int DT, int GATE, int E>
 __device__ __forceinline__ void gate_rows16_tmem_smem(uint32_t s_tmem, uint32_t blk_stride, uint32_t tile, uint32_t r0,
-                                                      int lane) {
+                                                      int lane, uint32_t s_free) {
   constexpr int KS = E / 16;
   const uint32_t mat = lane >> 3, l8 = lane & 7;
   const uint32_t a_row = r0 + l8 + (mat & 1) * 8;
@@ -835,6 +837,11 @@ __device__ __forceinline__ void gate_rows16_tmem_smem(uint32_t s_tmem, uint32_t 
     for (int pc = 0; pc < 4; ++pc) af[pc][0] = af[pc][1] = af[pc][2] = af[pc][3] = 0u;
   }
   tmem_ld_wait();
+  if (s_free != 0) {
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) mbar_arrive_cluster(s_free);
+  }
 #pragma unroll
   for (int pc = 0; pc < 4; ++pc) {
     h[pc][0] = gate_pair<DT, GATE>(af[pc][0], __uint_as_float(s[pc][0]), __uint_as_float(s[pc][1]));
