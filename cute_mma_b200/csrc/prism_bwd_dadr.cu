@@ -1,6 +1,6 @@
 // Prism backward, input and rotation gradients, for sm_100a:
-//   dH_g = dC_g . B_g                                   (dense, tcgen05, fp32 in TMEM)
-//   S_g  = A . blockdiag(R_g)^T                         (recomputed, mma.sync)
+//   dH_g = dC_g . B_g                                   (dense)
+//   S_g  = A . blockdiag(R_g)^T                         (recomputed)
 //   gated:  dS = dH * A * silu'(S),  dA += dH * silu(S) + blockdiag(dS) . R_g
 //   plain:  dS = dH,                 dA += blockdiag(dS) . R_g
 //   dR_g[block b] = dS_b^T . A_b
@@ -14,18 +14,22 @@
 //
 // CTAs work in pairs (cluster of 2, tcgen05 cta_group::2) on [256 tokens x 128 features]: each CTA
 // owns 128 of the tokens and loads half of the B_g features, which cuts the L2 traffic per flop.
-// One CTA works on its [128 tokens x 128 features] tile of dA and walks over all groups:
-//   warp 0       TMA producer: A tiles once per tile; per group the R_g tiles and, per 64 outputs,
-//                two dC tiles [128 x 64] and this CTA's B_g tile [128 x 64]
-//   warp 1       dense issuer (leader CTA): dH_g = dC_g . B_g as tcgen05.mma M256 N128 K16 (dC K-major, B_g
-//                MN-major) into a ring of four 128-column TMEM buffers
-//   warps 4-19   gate warps, 16 tokens x 64 features each: dH fragments straight from TMEM
-//                (tcgen05.ld.16x256b delivers the mma.sync accumulator layout), A and R fragments by
-//                ldmatrix, S by mma.sync; dS on registers -> stmatrix to shared memory for the dR
-//                warps and, as the A operand of a second mma.sync, dA += dS . R_g; dA lives in
-//                fp32 accumulator fragments for the whole tile
-//   warps 2,3,20,21  dR warps: ldmatrix.trans of the dS and A tiles, mma.sync over the 128 tokens,
-//                read-modify-write of this CTA's fp32 partial buffer.
+// One CTA works on its [128 tokens x 128 features] tile of dA and walks over all groups.  All three
+// products of the dA path run on tcgen05 (mma.sync shares the tensor cores with tcgen05.mma and is
+// starved while tcgen05.mma bursts run, which would put the gate warps behind the dense product):
+//   warp 0       TMA producer: A tiles once per tile; per group the R_g tiles and the dC / B_g stages
+//   warp 1       MMA issuer (leader CTA), per group
+//                  rotation  S_g = A . blockdiag(R_g)^T: M256 N=E K=16 per rotation block (gated mode)
+//                  dense     dH_g = dC_g . B_g: M256 N128 K16 (dC K-major, B_g MN-major), two TMEM buffers
+//                  dS . R    dA += blockdiag(dS_g) . R_g: M256 N=E K=16 per block (dS K-major from shared
+//                            memory, R_g MN-major), accumulated over the groups in TMEM
+//   warps 4-19   gate warps, 16 tokens x 64 features each: S and dH fragments straight from TMEM
+//                (tcgen05.ld.16x256b delivers the mma.sync accumulator layout), A fragments by ldmatrix
+//                (same layout), gate math on registers, dS -> stmatrix to shared memory; the gate
+//                term dH * silu(S) of dA stays in fp32 registers for the whole tile
+//   warps 2,3,20,21  dR warps: ldmatrix.trans of the dS and A tiles, mma.sync over the 128 tokens
+//                (off the critical path), fixed-order accumulation into this CTA's fp32 partial buffer.
+// TMEM: dH 2 x 128 columns, S 128, dA 128.
 #include "prism_host.cuh"
 #include "prism_kernels.cuh"
 
@@ -41,26 +45,26 @@ constexpr int kWarpTma = 0, kWarpMma = 1;
 constexpr int kGateWarp0 = 4;      // multiple of 4: (warp & 3) is the TMEM lane quarter
 constexpr int kNumGateWarps = 16;
 constexpr int kNumDrWarps = 4;     // warps 2, 3, 20, 21
-constexpr int kDhBufs = 4;         // TMEM ring of dH buffers, 128 columns each
+constexpr int kDhCol0 = 0, kSCol0 = 256, kDaCol0 = 384;   // TMEM columns: dH ring (2 x 128), S, dA
 constexpr int kTile = 128 * 128;   // bytes of a [128 x 64] 16-bit tile
-#ifndef PRISM_DADR_STAGE_OUT
-#define PRISM_DADR_STAGE_OUT 128
-#endif
-// one stage = kStageOut outputs of the group: kStageOut/64 dC tiles [128 tokens x 64] and this CTA's
-// half of the B_g features, a [kStageOut outputs x 64 features] tile
-constexpr int kStageOut = PRISM_DADR_STAGE_OUT;
-constexpr int kDcTiles = kStageOut / 64;
-constexpr int kBTile = kStageOut * 128;
-constexpr int kStageBytes = kDcTiles * kTile + kBTile;
 constexpr int kMaxStages = 6;
 constexpr int kMaxRBufs = 4;
+// one pipeline stage = kStageOut outputs of the group: kStageOut/64 dC tiles [128 tokens x 64] and
+// this CTA's half of the B_g features, a [kStageOut outputs x 64 features] tile
+template <int E> struct Stage {
+  static constexpr int kOut = (E == 64) ? 64 : 128;   // the R buffers of E = 64 leave less room
+  static constexpr int kDcTiles = kOut / 64;
+  static constexpr int kBTile = kOut * 128;
+  static constexpr int kBytes = kDcTiles * kTile + kBTile;
+};
 }  // namespace dadr
 
 struct DadrParams {
   int M, N, K, gs, E, G;
   int n_mtiles, runs;
   int ns, rb;          // stages of the dC/B ring, number of R buffers
-  int r_tile_bytes;    // bytes reserved per [E x 64] R tile (multiple of 1024)
+  int rr_tile_bytes;   // bytes reserved per rotation R tile [E/2 x 64] (multiple of 1024)
+  int rd_tile_bytes;   // bytes reserved per dS.R R tile [E x 64] (multiple of 1024)
   float scale;
   void* dA;
   long long ldda;
@@ -69,11 +73,20 @@ struct DadrParams {
 };
 
 struct DadrBarriers {
-  uint64_t a_full, a_empty;
-  uint64_t r_full[dadr::kMaxRBufs], r_empty[dadr::kMaxRBufs];
-  uint64_t st_full[dadr::kMaxStages], st_empty[dadr::kMaxStages];
-  uint64_t dh_full[dadr::kDhBufs], dh_empty[dadr::kDhBufs];
-  uint64_t ds_full[2], ds_empty[2];
+  uint64_t a_full;                         // local: this CTA's A tiles landed
+  uint64_t a_peer;                         // leader's copy is used: the peer's A tiles landed (forwarded by the peer)
+  uint64_t a_empty;                        // local: gate and dR warps are done with the A tiles
+  uint64_t r_full[dadr::kMaxRBufs];        // leader's copy is used: both CTAs' R tiles of the group landed
+  uint64_t r_empty[dadr::kMaxRBufs];       // local, multicast commit: dS.R of the group has read them
+  uint64_t st_full[dadr::kMaxStages];      // leader's copy is used
+  uint64_t st_empty[dadr::kMaxStages];     // local, multicast commit
+  uint64_t dh_full[2];                     // local, multicast commit: dH of the group is in its TMEM buffer
+  uint64_t s_full;                         // local, multicast commit: S of the group is in TMEM
+  uint64_t s_free;                         // leader's copy is used: the gate warps hold S in registers
+  uint64_t gate_done[2];                   // leader's copy is used: gate warps read dH, wrote dS (both CTAs)
+  uint64_t ds_full[2];                     // local: the gate warps wrote dS (for the dR warps)
+  uint64_t ds_empty[2];                    // local: dR warps + the commit after dS.R
+  uint64_t da_full;                        // local, multicast commit: dA of the tile is complete in TMEM
   uint32_t tmem_base;
 };
 
@@ -90,36 +103,43 @@ __device__ __forceinline__ void dr_accumulate(float* addr, float x, float y, boo
 //   silu(S)  = g = hs + hs t
 //   silu'(S) = (1 + x) / 2,  x = g + t (1 - g)
 // Returns 2 dS = dh a (1 + x) (the factor 2 is undone by the halved R in dS.R and by the scale of
-// the dR reduction) and p = dh silu(S), the gate term of dA, both packed 16-bit.
+// the dR reduction) and adds the gate term dh silu(S) of dA to acc0 / acc1.
 template <int DT>
-__device__ __forceinline__ uint32_t gate_bwd_pair(uint32_t a2, uint32_t hs, float dh0, float dh1, uint32_t& p) {
+__device__ __forceinline__ uint32_t gate_bwd_pair(uint32_t a2, uint32_t hs, float dh0, float dh1, float& acc0,
+                                                  float& acc1) {
   const uint32_t t = Pk<DT>::tanh(hs);
   const uint32_t g = Pk<DT>::fma(hs, t, hs);
   const uint32_t w = Pk<DT>::fma(g, Pk<DT>::kNegOne, Pk<DT>::kOne);
   const uint32_t x = Pk<DT>::fma(t, w, g);
-  const uint32_t d = Pk<DT>::cvt(dh0, dh1);
-  p = Pk<DT>::mul(d, g);
-  const uint32_t q = Pk<DT>::mul(d, a2);
+  const uint32_t q = Pk<DT>::mul(Pk<DT>::cvt(dh0, dh1), a2);
+  const float2 gf = Elem<DT>::unpack(g);
+  acc0 = fmaf(dh0, gf.x, acc0);
+  acc1 = fmaf(dh1, gf.y, acc1);
   return Pk<DT>::fma(q, x, q);
 }
 
 template <int DT, int GATE, int E>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(dadr::kThreads, 1)
-prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmR,
-                      const __grid_constant__ CUtensorMap tmdC, const __grid_constant__ CUtensorMap tmB,
-                      const DadrParams p) {
+prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmRr,
+                      const __grid_constant__ CUtensorMap tmRd, const __grid_constant__ CUtensorMap tmdC,
+                      const __grid_constant__ CUtensorMap tmB, const DadrParams p) {
   using namespace dadr;
+  using St = Stage<E>;
   constexpr int KS = E / 16;       // 16-wide steps per rotation block
   constexpr int NB = 64 / E;       // rotation blocks per 64-column tile
+  constexpr int NBLK = 128 / E;    // rotation blocks of the tile's 128 features
+  constexpr bool kGated = (GATE == GATE_SILU);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  const int r_buf_bytes = 2 * p.r_tile_bytes;
+  // R buffer of a group: two rotation tiles [E/2 x 64] (this CTA's half of the rows), then two dS.R
+  // tiles [E x 64] (shifted by E/2 columns in the peer, see the producer)
+  const int r_buf_bytes = 2 * p.rr_tile_bytes + 2 * p.rd_tile_bytes;
   uint8_t* smemA = smem;                        // 2 tiles [128 x 64]
   uint8_t* smemDS = smemA + 2 * kTile;          // 2 buffers x 2 tiles [128 x 64]
-  uint8_t* smemR = smemDS + 4 * kTile;          // rb buffers x 2 tiles [E x 64]
-  uint8_t* smemSt = smemR + p.rb * r_buf_bytes; // ns stages: dC tile + 2 B tiles
-  DadrBarriers* bars = reinterpret_cast<DadrBarriers*>(smemSt + p.ns * kStageBytes);
+  uint8_t* smemR = smemDS + 4 * kTile;          // rb buffers
+  uint8_t* smemSt = smemR + p.rb * r_buf_bytes; // ns stages: dC tiles + B tile
+  DadrBarriers* bars = reinterpret_cast<DadrBarriers*>(smemSt + p.ns * St::kBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -128,18 +148,27 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int run = blockIdx.y;                // the pair walks token-tile pairs run, run + runs, ...
   const int n_mpairs = (p.n_mtiles + 1) / 2;
   const int G = p.G;
-  const int nstg = (p.gs + kStageOut - 1) / kStageOut;  // stages per group
+  const int nstg = (p.gs + St::kOut - 1) / St::kOut;  // stages per group
   const bool is_gate = warp >= kGateWarp0 && warp < kGateWarp0 + kNumGateWarps;
   const bool is_dr = warp == 2 || warp == 3 || warp >= kGateWarp0 + kNumGateWarps;
+  const int n_units = (n_mpairs - run + p.runs - 1) / p.runs;   // token-tile pairs of this CTA pair
+  const int total = n_units * G;                                // groups it walks
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->a_full, 1);
+    mbar_init(&bars->a_peer, 1);
     mbar_init(&bars->a_empty, kNumGateWarps + kNumDrWarps);
-    for (int i = 0; i < kMaxRBufs; ++i) { mbar_init(&bars->r_full[i], 1); mbar_init(&bars->r_empty[i], kNumGateWarps); }
-    // st_full and dh_empty are used in the leader's copy only and count both CTAs
+    for (int i = 0; i < kMaxRBufs; ++i) { mbar_init(&bars->r_full[i], 2); mbar_init(&bars->r_empty[i], 1); }
     for (int i = 0; i < kMaxStages; ++i) { mbar_init(&bars->st_full[i], 2); mbar_init(&bars->st_empty[i], 1); }
-    for (int i = 0; i < kDhBufs; ++i) { mbar_init(&bars->dh_full[i], 1); mbar_init(&bars->dh_empty[i], 2 * kNumGateWarps); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&bars->ds_full[i], kNumGateWarps); mbar_init(&bars->ds_empty[i], kNumDrWarps); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->dh_full[i], 1);
+      mbar_init(&bars->gate_done[i], 2 * kNumGateWarps);
+      mbar_init(&bars->ds_full[i], kNumGateWarps);
+      mbar_init(&bars->ds_empty[i], kNumDrWarps + 1);
+    }
+    mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->s_free, 2 * kNumGateWarps);
+    mbar_init(&bars->da_full, 1);
     fence_mbar_init();
   }
   if (warp == kWarpMma) {
@@ -148,7 +177,8 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   }
   if (warp == kWarpTma && lane == 0) {
     prefetch_tmap(&tmA);
-    prefetch_tmap(&tmR);
+    prefetch_tmap(&tmRr);
+    prefetch_tmap(&tmRd);
     prefetch_tmap(&tmdC);
     prefetch_tmap(&tmB);
   }
@@ -162,6 +192,8 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
   if (warp == kWarpTma) {
     // ------------------------------------------------------------------ TMA producer
+    // The completion of the R and stage loads is counted on the leader's barriers: its MMAs read both
+    // CTAs' tiles.  The A tiles complete on the local barrier (gate and dR warps read them too).
     if (lane == 0) {
       bool ok = true;
       uint32_t tile_iter = 0;
@@ -173,70 +205,175 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         tma_load_2d(smemA, &tmA, &bars->a_full, f0, m0);
         tma_load_2d(smemA + kTile, &tmA, &bars->a_full, f0 + 64, m0);
         for (int g = 0; g < G && ok; ++g, rr.next()) {
-          const int rb = rr.idx;
-          if (!mbar_wait(&bars->r_empty[rb], rr.phase ^ 1)) { ok = false; break; }
-          uint8_t* dstR = smemR + rb * r_buf_bytes;
-          mbar_arrive_expect_tx(&bars->r_full[rb], 2 * E * 128);
-          tma_load_2d(dstR, &tmR, &bars->r_full[rb], f0, g * E);
-          tma_load_2d(dstR + p.r_tile_bytes, &tmR, &bars->r_full[rb], f0 + 64, g * E);
+          if (!mbar_wait(&bars->r_empty[rr.idx], rr.phase ^ 1)) { ok = false; break; }
+          uint8_t* dstR = smemR + rr.idx * r_buf_bytes;
+          const uint32_t rfull = mapa_shared(smem_u32(&bars->r_full[rr.idx]), 0);
+          mbar_arrive_expect_tx_cluster(rfull, (kGated ? 2 * (E / 2) * 128 : 0) + 2 * E * 128);
+          if (kGated) {
+            // rotation: an MMA spanning the pair takes the first E/2 rows of R_g from the leader, the rest from the peer
+            tma_load_2d_pair(dstR, &tmRr, rfull, f0, g * E + (int)rank * (E / 2));
+            tma_load_2d_pair(dstR + p.rr_tile_bytes, &tmRr, rfull, f0 + 64, g * E + (int)rank * (E / 2));
+          }
+          // dS . R: R_g is the MN-major operand there and the pair splits its N (the block's columns):
+          // the peer loads its tiles E/2 columns further right, so that its half of every block sits
+          // where the leader's half sits
+          uint8_t* dstD = dstR + 2 * p.rr_tile_bytes;
+          tma_load_2d_pair(dstD, &tmRd, rfull, f0 + (int)rank * (E / 2), g * E);
+          tma_load_2d_pair(dstD + p.rd_tile_bytes, &tmRd, rfull, f0 + 64 + (int)rank * (E / 2), g * E);
           for (int s = 0; s < nstg; ++s, rst.next()) {
             const int st = rst.idx;
             if (!mbar_wait(&bars->st_empty[st], rst.phase ^ 1)) { ok = false; break; }
-            uint8_t* dst = smemSt + st * kStageBytes;
-            const int n0 = g * p.gs + s * kStageOut;
-            const bool two = kDcTiles == 2 && p.gs - s * kStageOut > 64;   // the slice has more than 64 outputs
-            // completion is counted on the leader's barrier: its MMAs read both CTAs' tiles
+            uint8_t* dst = smemSt + st * St::kBytes;
+            const int n0 = g * p.gs + s * St::kOut;
+            const bool two = St::kDcTiles == 2 && p.gs - s * St::kOut > 64;   // the slice has more than 64 outputs
             const uint32_t stfull = mapa_shared(smem_u32(&bars->st_full[st]), 0);
-            mbar_arrive_expect_tx_cluster(stfull, (two ? 2 : 1) * kTile + kBTile);
+            mbar_arrive_expect_tx_cluster(stfull, (two ? 2 : 1) * kTile + St::kBTile);
             tma_load_2d_pair(dst, &tmdC, stfull, n0, m0);
             if (two) tma_load_2d_pair(dst + kTile, &tmdC, stfull, n0 + 64, m0);
-            tma_load_2d_pair(dst + kDcTiles * kTile, &tmB, stfull, f0 + (int)rank * 64, n0);
+            tma_load_2d_pair(dst + St::kDcTiles * kTile, &tmB, stfull, f0 + (int)rank * 64, n0);
           }
         }
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
   } else if (warp == kWarpMma) {
-    // ------------------------------------------------------------------ dense issuer: dH = dC . B
+    // ------------------------------------------------------------------ MMA issuer
+    // Iteration i issues, in this order (tcgen05.mma executes in order):
+    //   dS . R of group i - 1            (its gate warps are done: dS is in shared memory)
+    //   rotation of group i              only when group i opens a tile (it needs the new A tiles)
+    //   dense product of group i + 1     (the dH buffer of group i - 1 is free)
+    //   rotation of group i + 1          once the gate warps hold S of group i in registers; not
+    //                                    across a tile boundary
+    // so that while the gate warps work on group i the tensor pipe has everything group i + 1 needs.
     if (lane == 0 && rank == 0) {
-      const uint32_t idesc_h = make_idesc(DT, 256, 128, 0, 1);   // M = 256 tokens; dC K-major, B_g MN-major
-      // descriptors of stage 0; a stage further on adds kStageBytes >> 4 to the low words
-      const uint64_t da0 = desc_kmajor_sw128(smem_u32(smemSt), 1024);
-      const uint64_t db0 = desc_mnmajor_sw128(smem_u32(smemSt) + kDcTiles * kTile, kBTile, 1024);
-      const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
+      const uint32_t idesc_h = make_idesc(DT, 256, 128, 0, 1);   // dH: M = 256 tokens; dC K-major, B_g MN-major
+      const uint32_t idesc_s = make_idesc(DT, 256, E, 0, 0);     // S block: A K-major, R_g K-major
+      const uint32_t idesc_a = make_idesc(DT, 256, E, 0, 1);     // dA block: dS K-major, R_g MN-major
+      // descriptors of buffer 0 of each ring; later buffers add to the low words
+      const uint64_t dst0 = desc_kmajor_sw128(smem_u32(smemSt), 1024);
+      const uint64_t dsb0 = desc_mnmajor_sw128(smem_u32(smemSt) + St::kDcTiles * kTile, St::kBTile, 1024);
+      const uint64_t dA0 = desc_kmajor_sw128(smem_u32(smemA), 1024);
+      const uint64_t dS0 = desc_kmajor_sw128(smem_u32(smemDS), 1024);
+      const uint64_t dRr0 = desc_kmajor_sw128(smem_u32(smemR), 1024);
+      const uint64_t dRd0 = desc_mnmajor_sw128(smem_u32(smemR) + 2 * p.rr_tile_bytes, (uint32_t)p.rd_tile_bytes, 1024);
+      const uint32_t k_hi = (uint32_t)(dst0 >> 32), b_hi = (uint32_t)(dsb0 >> 32), rd_hi = (uint32_t)(dRd0 >> 32);
+      const uint32_t r_step = (uint32_t)r_buf_bytes >> 4;
+      const uint32_t rr_tile = (uint32_t)p.rr_tile_bytes >> 4, rd_tile = (uint32_t)p.rd_tile_bytes >> 4;
       bool ok = true;
-      uint32_t gg = 0;
       Ring rst(p.ns);
-      for (int mp = run; mp < n_mpairs && ok; mp += p.runs) {
-        for (int g = 0; g < G && ok; ++g, ++gg) {
-          const uint32_t hb = gg & (kDhBufs - 1);
-          const uint32_t d_tmem = tmem_base + hb * 128;
-          if (!mbar_wait_cluster(&bars->dh_empty[hb], ((gg / kDhBufs) & 1) ^ 1)) { ok = false; break; }
+      Ring r_rot(p.rb), r_dsr(p.rb);   // R buffer of the next group to rotate / to multiply with dS
+      int g_dsr = 0;                   // index inside its tile of the next group whose dS . R is due
+      uint32_t a_phase = 0;
+
+      auto rotate = [&](uint32_t rbuf) {
+        const uint32_t r_lo = (uint32_t)dRr0 + rbuf * r_step;
+#pragma unroll
+        for (int b = 0; b < NBLK; ++b) {
+#pragma unroll
+          for (int ks = 0; ks < KS; ++ks) {
+            const int fo = b * E + ks * 16;   // features fo .. fo+16 of the 128: tile and 32-byte step inside it
+            const uint32_t ta = (uint32_t)((fo >> 6) * (kTile >> 4) + ((fo & 63) >> 4) * 2);
+            const uint32_t tr = (uint32_t)(fo >> 6) * rr_tile + (uint32_t)(((fo & 63) >> 4) * 2);
+            umma_f16_pair_lh(tmem_base + kSCol0 + b * E, (uint32_t)dA0 + ta, k_hi, r_lo + tr, k_hi, idesc_s,
+                             ks > 0 ? 1u : 0u);
+          }
+        }
+      };
+
+      int gi = -1;   // index of group i inside its tile
+      for (int i = -1; i <= total && ok; ++i, gi = (gi + 1 == G) ? 0 : gi + 1) {
+        // ---- (1) dS . R of group i - 1: its gate warps (both CTAs) have written dS and read dH
+        if (i >= 1) {
+          const uint32_t gd = (uint32_t)(i - 1);
+          if (!mbar_wait_cluster(&bars->gate_done[gd & 1], (gd >> 1) & 1)) { ok = false; break; }
+          if (!kGated) {   // (the rotation has waited for these R tiles already)
+            if (!mbar_wait_cluster(&bars->r_full[r_dsr.idx], r_dsr.phase)) { ok = false; break; }
+          }
+          tc_fence_after_sync();
+          const uint32_t s_lo = (uint32_t)dS0 + (gd & 1) * ((2 * kTile) >> 4);
+          const uint32_t r_lo = (uint32_t)dRd0 + r_dsr.idx * r_step;
+#pragma unroll
+          for (int b = 0; b < NBLK; ++b) {
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+              // dS (K-major): features b*E + ks*16 ..; R_g (MN-major): rows ks*16 .. (2048 bytes per 16 rows),
+              // columns of block b
+              const int fo = b * E + ks * 16;
+              const uint32_t ta = (uint32_t)((fo >> 6) * (kTile >> 4) + ((fo & 63) >> 4) * 2);
+              const int co = b * E;
+              const uint32_t tr = (uint32_t)(co >> 6) * rd_tile + (uint32_t)(((co & 63) * 2) >> 4) + (uint32_t)(ks * 128);
+              umma_f16_pair_lh(tmem_base + kDaCol0 + b * E, s_lo + ta, k_hi, r_lo + tr, rd_hi, idesc_a,
+                               (g_dsr > 0 || ks > 0) ? 1u : 0u);
+            }
+          }
+          umma_commit_pair(&bars->ds_empty[gd & 1], 0x3);
+          umma_commit_pair(&bars->r_empty[r_dsr.idx], 0x3);
+          r_dsr.next();
+          if (++g_dsr == G) {
+            g_dsr = 0;
+            umma_commit_pair(&bars->da_full, 0x3);   // the tile's dA is complete
+          }
+        }
+        if (i >= total) break;
+        // ---- (2) rotation of group i when it opens a tile: the new A tiles must have landed in both CTAs
+        if (kGated && i >= 0 && gi == 0) {
+          if (!mbar_wait(&bars->a_full, a_phase)) { ok = false; break; }
+          if (!mbar_wait_cluster(&bars->a_peer, a_phase)) { ok = false; break; }
+          a_phase ^= 1u;
+          if (!mbar_wait_cluster(&bars->r_full[r_rot.idx], r_rot.phase)) { ok = false; break; }
+          tc_fence_after_sync();
+          rotate(r_rot.idx);
+          umma_commit_pair(&bars->s_full, 0x3);
+          r_rot.next();
+        }
+        // ---- (3) dense product of group i + 1 (the dH buffer of group i - 1 is free, see (1))
+        if (i + 1 < total) {
+          const uint32_t gn = (uint32_t)(i + 1);
+          const uint32_t d_tmem = tmem_base + kDhCol0 + (gn & 1) * 128;
           for (int s = 0; s < nstg; ++s, rst.next()) {
             const int st = rst.idx;
             if (!mbar_wait_cluster(&bars->st_full[st], rst.phase)) { ok = false; break; }
             tc_fence_after_sync();
-            const uint32_t a_lo = (uint32_t)da0 + st * (kStageBytes >> 4);
-            const uint32_t b_lo = (uint32_t)db0 + st * (kStageBytes >> 4);
-            constexpr int kSteps = kStageOut / 16;
-            const int ksteps = min(kSteps, (p.gs - s * kStageOut) / 16);
+            const uint32_t a_lo = (uint32_t)dst0 + st * (St::kBytes >> 4);
+            const uint32_t b_lo = (uint32_t)dsb0 + st * (St::kBytes >> 4);
+            constexpr int kSteps = St::kOut / 16;
+            const int ksteps = min(kSteps, (p.gs - s * St::kOut) / 16);
             if (ksteps == kSteps) {
               // K16 step ks: dC tile ks/4 (+kTile), 32 bytes per step inside it; B_g rows 16 ks (+2048 bytes)
-              umma_f16_pair_lh(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc_h, s > 0 ? 1u : 0u);
+              umma_f16_pair_lh(d_tmem, a_lo, k_hi, b_lo, b_hi, idesc_h, s > 0 ? 1u : 0u);
 #pragma unroll
               for (int ks = 1; ks < kSteps; ++ks)
-                umma_f16_pair_lh(d_tmem, a_lo + (((ks >> 2) * kTile + (ks & 3) * 32) >> 4), a_hi,
+                umma_f16_pair_lh(d_tmem, a_lo + (((ks >> 2) * kTile + (ks & 3) * 32) >> 4), k_hi,
                                  b_lo + ((ks * 2048) >> 4), b_hi, idesc_h, 1u);
             } else {
               for (int ks = 0; ks < ksteps; ++ks)
-                umma_f16_pair_lh(d_tmem, a_lo + (((ks >> 2) * kTile + (ks & 3) * 32) >> 4), a_hi,
+                umma_f16_pair_lh(d_tmem, a_lo + (((ks >> 2) * kTile + (ks & 3) * 32) >> 4), k_hi,
                                  b_lo + ((ks * 2048) >> 4), b_hi, idesc_h, (s > 0 || ks > 0) ? 1u : 0u);
             }
             umma_commit_pair(&bars->st_empty[st], 0x3);
           }
           if (!ok) break;
-          umma_commit_pair(&bars->dh_full[hb], 0x3);
+          umma_commit_pair(&bars->dh_full[gn & 1], 0x3);
         }
+        // ---- (4) rotation of group i + 1 inside the same tile, once the gate warps hold S of group i
+        if (kGated && i >= 0 && i + 1 < total && gi + 1 < G) {
+          if (!mbar_wait_cluster(&bars->s_free, (uint32_t)i & 1)) { ok = false; break; }
+          if (!mbar_wait_cluster(&bars->r_full[r_rot.idx], r_rot.phase)) { ok = false; break; }
+          tc_fence_after_sync();
+          rotate(r_rot.idx);
+          umma_commit_pair(&bars->s_full, 0x3);
+          r_rot.next();
+        }
+      }
+      if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
+    } else if (lane == 0 && rank == 1 && kGated) {
+      // the peer tells the leader's MMA issuer when its A tiles have landed
+      bool ok = true;
+      uint32_t ph = 0;
+      const uint32_t a_peer = mapa_shared(smem_u32(&bars->a_peer), 0);
+      for (int u = 0; u < n_units && ok; ++u, ph ^= 1u) {
+        if (!mbar_wait(&bars->a_full, ph)) { ok = false; break; }
+        mbar_arrive_cluster(a_peer);
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
@@ -247,123 +384,110 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const uint32_t r0 = q * 32 + half * 16;                    // first of this warp's 16 token rows
     const uint32_t lane_base = r0 << 16;                       // TMEM lane window [r0, r0+16)
     const uint32_t mat = lane >> 3, l8 = lane & 7;
-    const uint32_t a_row = r0 + l8 + (mat & 1) * 8;            // A-operand fragments (also dS stores)
-    const uint32_t rn_row = l8 + (mat >> 1) * 8;               // R as B operand of S = A . R^T (rows = i)
-    const uint32_t rt_row = l8 + (mat & 1) * 8;                // R as B operand of dS . R (rows = i, transposed load)
+    const uint32_t a_row = r0 + l8 + (mat & 1) * 8;            // A fragments, dS stores
     const uint32_t tileA = smem_u32(smemA + ch * kTile);
-    // B-operand fragment of a 16x16 identity (the k = n diagonal of one 8-column half): adds the gate
-    // term p to the accumulators through the tensor pipe instead of unpack + FMA instructions
-    const uint32_t idf = ((lane >> 3) == (lane & 3)) ? (((lane >> 2) & 1) ? (Pk<DT>::kOneLo << 16) : Pk<DT>::kOneLo) : 0u;
-    float dacc[8][4];   // dA accumulator fragments: 16 rows x 64 columns of this warp, whole tile
+    const uint32_t s_free_addr = mapa_shared(smem_u32(&bars->s_free), 0);
+    const uint32_t gate_done_addr = mapa_shared(smem_u32(&bars->gate_done[0]), 0);
+    float dacc[8][4];   // gate term of dA, 16 rows x 64 columns of this warp, whole tile
 #pragma unroll
     for (int i = 0; i < 8; ++i) { dacc[i][0] = dacc[i][1] = dacc[i][2] = dacc[i][3] = 0.f; }
     bool ok = true;
     uint32_t tile_iter = 0, gg = 0;
-    Ring rr(p.rb);
     for (int mp = run; mp < n_mpairs && ok; mp += p.runs, ++tile_iter) {
       const int mt = mp * 2 + (int)rank;
       if (!mbar_wait(&bars->a_full, tile_iter & 1)) { ok = false; break; }
-      for (int g = 0; g < G && ok; ++g, ++gg, rr.next()) {
-        const uint32_t hb = gg & (kDhBufs - 1), db = gg & 1;
-        if (!mbar_wait(&bars->r_full[rr.idx], rr.phase)) { ok = false; break; }
-        if (!mbar_wait(&bars->dh_full[hb], (gg / kDhBufs) & 1)) { ok = false; break; }
-        if (!mbar_wait(&bars->ds_empty[db], ((gg >> 1) & 1) ^ 1)) { ok = false; break; }
+      for (int g = 0; g < G && ok; ++g, ++gg) {
+        const uint32_t hb = gg & 1, ph = (gg >> 1) & 1;
+        if (kGated) {
+          if (!mbar_wait(&bars->s_full, gg & 1)) { ok = false; break; }
+        }
+        if (!mbar_wait(&bars->dh_full[hb], ph)) { ok = false; break; }
+        if (!mbar_wait(&bars->ds_empty[hb], ph ^ 1)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t tileDS = smem_u32(smemDS + db * 2 * kTile + ch * kTile);
-        const uint32_t rtile = smem_u32(smemR + rr.idx * r_buf_bytes + ch * p.r_tile_bytes);
-        const uint32_t tdh = tmem_base + lane_base + hb * 128 + ch * 64;
+        const uint32_t tileDS = smem_u32(smemDS + hb * 2 * kTile + ch * kTile);
+        const uint32_t tdh = tmem_base + lane_base + kDhCol0 + hb * 128 + ch * 64;
+        const uint32_t ts = tmem_base + lane_base + kSCol0 + ch * 64;
+        // two 16-column pieces per pass: all loads, then the gate math, then the stores
 #pragma unroll
-        for (int b = 0; b < ((PRISM_DBG & 1) ? 0 : NB); ++b) {
-          uint32_t af[KS][4], dsf[KS][4], pf[KS][4];
-          if (GATE == GATE_SILU) {
+        for (int pass = 0; pass < 2; ++pass) {
+          uint32_t sv[2][8], dh[2][8], af[2][4], dsf[2][4];
 #pragma unroll
-            for (int ks = 0; ks < KS; ++ks)
-              ldmatrix_x4(tileA + sw128_offset(a_row, b * (E / 8) + ks * 2 + (mat >> 1)), af[ks]);
+          for (int i = 0; i < 2; ++i) {
+            const int pc = pass * 2 + i;
+            if (kGated) {
+              tmem_ld_16x256b_x2(ts + pc * 16, sv[i]);
+              ldmatrix_x4(tileA + sw128_offset(a_row, pc * 2 + (mat >> 1)), af[i]);
+            }
+            tmem_ld_16x256b_x2(tdh + pc * 16, dh[i]);
+          }
+          tmem_ld_wait();
+          if (kGated && pass == 1) {
+            // this warp holds all its S values: the S buffer may be refilled for the next group
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(s_free_addr);
           }
 #pragma unroll
-          for (int np = 0; np < KS; ++np) {
-            uint32_t dh[8];
-            tmem_ld_16x256b_x2(tdh + b * E + np * 16, dh);
-            uint32_t sp[4] = {0u, 0u, 0u, 0u};   // packed S/2 of this thread's four pairs (the R tile holds R/2)
-            if (GATE == GATE_SILU) {
-              if (DT == DT_F16) {
-                uint32_t c0[2] = {0u, 0u}, c1[2] = {0u, 0u};   // fp16 accumulation: packed result
+          for (int i = 0; i < 2; ++i) {
+            const int pc = pass * 2 + i;
+            float* d0 = dacc[pc * 2];
+            float* d1 = dacc[pc * 2 + 1];
 #pragma unroll
-                for (int ks = 0; ks < KS; ++ks) {
-                  uint32_t rf[4];
-                  ldmatrix_x4(rtile + sw128_offset(np * 16 + rn_row, b * (E / 8) + ks * 2 + (mat & 1)), rf);
-                  mma_m16n8k16_f16acc(c0, af[ks], rf[0], rf[1]);
-                  mma_m16n8k16_f16acc(c1, af[ks], rf[2], rf[3]);
-                }
-                sp[0] = c0[0]; sp[1] = c0[1]; sp[2] = c1[0]; sp[3] = c1[1];
+            for (int e = 0; e < 4; ++e) {
+              // pair e of the fragment: (row, cols) as in the accumulator layout; e >> 1 selects columns + 8
+              const float x0 = __uint_as_float(dh[i][2 * e]), x1 = __uint_as_float(dh[i][2 * e + 1]);
+              if (kGated) {
+                const uint32_t hs = Pk<DT>::cvt(__uint_as_float(sv[i][2 * e]), __uint_as_float(sv[i][2 * e + 1]));
+                float* d = (e >> 1) ? d1 : d0;
+                dsf[i][e] = gate_bwd_pair<DT>(af[i][e], hs, x0, x1, d[(e & 1) * 2], d[(e & 1) * 2 + 1]);
               } else {
-                float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int ks = 0; ks < KS; ++ks) {
-                  uint32_t rf[4];
-                  ldmatrix_x4(rtile + sw128_offset(np * 16 + rn_row, b * (E / 8) + ks * 2 + (mat & 1)), rf);
-                  mma_m16n8k16<DT>(c0, af[ks], rf[0], rf[1]);
-                  mma_m16n8k16<DT>(c1, af[ks], rf[2], rf[3]);
-                }
-                sp[0] = Pk<DT>::cvt(c0[0], c0[1]); sp[1] = Pk<DT>::cvt(c0[2], c0[3]);
-                sp[2] = Pk<DT>::cvt(c1[0], c1[1]); sp[3] = Pk<DT>::cvt(c1[2], c1[3]);
+                dsf[i][e] = Pk<DT>::cvt(x0, x1);
               }
             }
-            tmem_ld_wait();
-            if (GATE == GATE_SILU) {
-              dsf[np][0] = gate_bwd_pair<DT>(af[np][0], sp[0], __uint_as_float(dh[0]), __uint_as_float(dh[1]), pf[np][0]);
-              dsf[np][1] = gate_bwd_pair<DT>(af[np][1], sp[1], __uint_as_float(dh[2]), __uint_as_float(dh[3]), pf[np][1]);
-              dsf[np][2] = gate_bwd_pair<DT>(af[np][2], sp[2], __uint_as_float(dh[4]), __uint_as_float(dh[5]), pf[np][2]);
-              dsf[np][3] = gate_bwd_pair<DT>(af[np][3], sp[3], __uint_as_float(dh[6]), __uint_as_float(dh[7]), pf[np][3]);
-            } else {
-              dsf[np][0] = Pk<DT>::cvt(__uint_as_float(dh[0]), __uint_as_float(dh[1]));
-              dsf[np][1] = Pk<DT>::cvt(__uint_as_float(dh[2]), __uint_as_float(dh[3]));
-              dsf[np][2] = Pk<DT>::cvt(__uint_as_float(dh[4]), __uint_as_float(dh[5]));
-              dsf[np][3] = Pk<DT>::cvt(__uint_as_float(dh[6]), __uint_as_float(dh[7]));
-            }
-            stmatrix_x4(tileDS + sw128_offset(a_row, b * (E / 8) + np * 2 + (mat >> 1)), dsf[np]);
           }
-          // dA[:, block b] += p + dS[:, block b] . R_g[block b]   (contraction over the block's i)
 #pragma unroll
-          for (int jp = 0; jp < KS; ++jp) {
-            if (GATE == GATE_SILU) {
-              mma_m16n8k16<DT>(dacc[(b * KS + jp) * 2], pf[jp], idf, 0u);
-              mma_m16n8k16<DT>(dacc[(b * KS + jp) * 2 + 1], pf[jp], 0u, idf);
-            }
-#pragma unroll
-            for (int ks = 0; ks < KS; ++ks) {
-              uint32_t rt[4];
-              ldmatrix_x4_trans(rtile + sw128_offset(ks * 16 + rt_row, b * (E / 8) + jp * 2 + (mat >> 1)), rt);
-              mma_m16n8k16<DT>(dacc[(b * KS + jp) * 2], dsf[ks], rt[0], rt[1]);
-              mma_m16n8k16<DT>(dacc[(b * KS + jp) * 2 + 1], dsf[ks], rt[2], rt[3]);
-            }
-          }
+          for (int i = 0; i < 2; ++i)
+            stmatrix_x4(tileDS + sw128_offset(a_row, (pass * 2 + i) * 2 + (mat >> 1)), dsf[i]);
         }
+        fence_proxy_async_smem();   // dS is read by the dS . R MMAs through the async proxy
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
-          mbar_arrive(&bars->ds_full[db]);
-          mbar_arrive_cluster(mapa_shared(smem_u32(&bars->dh_empty[hb]), 0));
-          mbar_arrive(&bars->r_empty[rr.idx]);
+          mbar_arrive(&bars->ds_full[hb]);                     // this CTA's dR warps
+          mbar_arrive_cluster(gate_done_addr + hb * 8);        // the MMA issuer: dS written, dH and S consumed
         }
       }
       if (!ok) break;
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->a_empty);   // this warp no longer reads the A tile
-      // tile epilogue: dA = scale * accumulators, written straight from the fragments
+      // tile epilogue: dA = scale * (dS . R sums from TMEM + gate term), written straight from the fragments
+      if (!mbar_wait(&bars->da_full, tile_iter & 1)) { ok = false; break; }
+      tc_fence_after_sync();
       const long long grow = (long long)mt * 128 + r0 + (lane >> 2);
       uint16_t* out = reinterpret_cast<uint16_t*>(p.dA);
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const int col = f0 + ch * 64 + nt * 8 + (lane & 3) * 2;
-        if (col < p.K) {
-          if (grow < p.M)
-            *reinterpret_cast<uint32_t*>(out + grow * p.ldda + col) = Elem<DT>::pack(dacc[nt][0] * p.scale, dacc[nt][1] * p.scale);
-          if (grow + 8 < p.M)
-            *reinterpret_cast<uint32_t*>(out + (grow + 8) * p.ldda + col) = Elem<DT>::pack(dacc[nt][2] * p.scale, dacc[nt][3] * p.scale);
+      for (int pc = 0; pc < 4; ++pc) {
+        uint32_t v[8];
+        tmem_ld_16x256b_x2(tmem_base + lane_base + kDaCol0 + ch * 64 + pc * 16, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {   // columns 0-7 / 8-15 of the piece
+          const int nt = pc * 2 + hh;
+          const int col = f0 + ch * 64 + nt * 8 + (lane & 3) * 2;
+          if (col < p.K) {
+            if (grow < p.M)
+              *reinterpret_cast<uint32_t*>(out + grow * p.ldda + col) =
+                  Elem<DT>::pack((dacc[nt][0] + __uint_as_float(v[hh * 4 + 0])) * p.scale,
+                                 (dacc[nt][1] + __uint_as_float(v[hh * 4 + 1])) * p.scale);
+            if (grow + 8 < p.M)
+              *reinterpret_cast<uint32_t*>(out + (grow + 8) * p.ldda + col) =
+                  Elem<DT>::pack((dacc[nt][2] + __uint_as_float(v[hh * 4 + 2])) * p.scale,
+                                 (dacc[nt][3] + __uint_as_float(v[hh * 4 + 3])) * p.scale);
+          }
+          dacc[nt][0] = dacc[nt][1] = dacc[nt][2] = dacc[nt][3] = 0.f;
         }
-        dacc[nt][0] = dacc[nt][1] = dacc[nt][2] = dacc[nt][3] = 0.f;
       }
+      tc_fence_before_sync();   // the TMEM reads are done before the next tile's first dS . R overwrites dA
     }
     if (!ok && lane == 0) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
   } else if (is_dr) {
@@ -478,33 +602,42 @@ int dadr_default_runs(int M, int K, int num_sms) {
   return best;
 }
 
+template <int E>
+static int dadr_plan(DadrParams& p, int& smem_bytes) {
+  using St = dadr::Stage<E>;
+  p.rr_tile_bytes = ((E / 2 * 128) + 1023) / 1024 * 1024;
+  p.rd_tile_bytes = ((E * 128) + 1023) / 1024 * 1024;
+  p.rb = (E <= 16) ? 4 : 2;
+  const int fixed = 6 * dadr::kTile + p.rb * 2 * (p.rr_tile_bytes + p.rd_tile_bytes) + (int)sizeof(DadrBarriers) + 1024;
+  int ns = (227 * 1024 - 256 - fixed) / St::kBytes;
+  if (ns > dadr::kMaxStages) ns = dadr::kMaxStages;
+  if (ns < 2) return fail(PRISM_ERR_UNSUPPORTED, "bwd_dadr does not fit shared memory (E=%d)", E);
+  p.ns = ns;
+  smem_bytes = fixed + ns * St::kBytes;
+  return PRISM_OK;
+}
+
 int launch_bwd_dadr(const DadrArgs& a) {
   DadrParams p;
   p.M = a.M; p.N = a.N; p.K = a.K; p.gs = a.gs; p.E = a.E; p.G = a.N / a.gs;
   p.n_mtiles = (a.M + 127) / 128;
   p.runs = a.runs < 1 ? 1 : a.runs;
   if (p.runs > (p.n_mtiles + 1) / 2) p.runs = (p.n_mtiles + 1) / 2;
-  p.r_tile_bytes = ((a.E * 128) + 1023) / 1024 * 1024;
   p.scale = a.scale;
   p.dA = a.dA; p.ldda = a.ldda; p.partial = a.partial; p.err = a.err;
-  p.rb = (a.E <= 16) ? 4 : (a.E == 32 ? 3 : 2);
-  const int fixed = 6 * dadr::kTile + p.rb * 2 * p.r_tile_bytes + (int)sizeof(DadrBarriers) + 1024 + 256;
-  int ns = (227 * 1024 - fixed) / dadr::kStageBytes;
-  if (ns > dadr::kMaxStages) ns = dadr::kMaxStages;
-  if (ns < 2) return fail(PRISM_ERR_UNSUPPORTED, "bwd_dadr does not fit shared memory (E=%d)", a.E);
-  p.ns = ns;
-  const int smem_bytes = 6 * dadr::kTile +
- p.rb * 2 * p.r_tile_bytes + ns * dadr::kStageBytes +
-                         (int)sizeof(DadrBarriers) + 1024;
+  int smem_bytes = 0;
+  int rc = (a.E == 16) ? dadr_plan<16>(p, smem_bytes) : (a.E == 32) ? dadr_plan<32>(p, smem_bytes) : dadr_plan<64>(p, smem_bytes);
+  if (rc) return rc;
+  const int stage_out = (a.E == 64) ? 64 : 128;
 
-  CUtensorMap tmA, tmR, tmdC, tmB;
-  int rc;
+  CUtensorMap tmA, tmRr, tmRd, tmdC, tmB;
   if ((rc = make_tmap_2d(&tmA, a.dtype, a.A, a.M, a.K, a.lda, 128, 64, true))) return rc;
-  if ((rc = make_tmap_2d(&tmR, a.dtype, a.R_eff, (uint64_t)p.G * a.E, a.K, a.ldr, a.E, 64, true))) return rc;
+  if ((rc = make_tmap_2d(&tmRr, a.dtype, a.R_eff, (uint64_t)p.G * a.E, a.K, a.ldr, a.E / 2, 64, true))) return rc;
+  if ((rc = make_tmap_2d(&tmRd, a.dtype, a.R_eff, (uint64_t)p.G * a.E, a.K, a.ldr, a.E, 64, true))) return rc;
   if ((rc = make_tmap_2d(&tmdC, a.dtype, a.dC, a.M, a.N, a.lddc, 128, 64, true))) return rc;
-  if ((rc = make_tmap_2d(&tmB, a.dtype, a.B, a.N, a.K, a.ldb, dadr::kStageOut, 64, true))) return rc;
+  if ((rc = make_tmap_2d(&tmB, a.dtype, a.B, a.N, a.K, a.ldb, stage_out, 64, true))) return rc;
 
-  using KernT = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, DadrParams);
+  using KernT = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, DadrParams);
   KernT kern = nullptr;
 #define PRISM_PICK(E_)                                                                               \
   kern = (a.dtype == DT_BF16)                                                                        \
@@ -515,7 +648,7 @@ int launch_bwd_dadr(const DadrArgs& a) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return fail(PRISM_ERR_CUDA, "bwd_dadr: cannot set %d B of shared memory: %s", smem_bytes, cudaGetErrorString(e));
   dim3 grid(2 * ((a.K + 127) / 128), p.runs, 1);   // x: the two CTAs of a pair
-  kern<<<grid, dadr::kThreads, smem_bytes, a.stream>>>(tmA, tmR, tmdC, tmB, p);
+  kern<<<grid, dadr::kThreads, smem_bytes, a.stream>>>(tmA, tmRr, tmRd, tmdC, tmB, p);
   if ((rc = check_launch("prism_bwd_dadr"))) return rc;
 
   // gated mode: the kernel formed 2 dS against the halved R tiles, so the dR partials are doubled
