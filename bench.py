@@ -106,6 +106,7 @@ class ClockSampler(threading.Thread):
         self.join(2.0)
         s = sorted(self.samples)
         return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
+                "sm_mhz_min": (s[0] if s else None), "sm_mhz_highest": (s[-1] if s else None),
                 "reasons": sorted(self.reasons), "samples": len(s),
                 "power_w_max": (max(self.power) if self.power else None)}
 

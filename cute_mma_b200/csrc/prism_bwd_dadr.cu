@@ -18,7 +18,7 @@
 // products of the dA path run on tcgen05 (mma.sync shares the tensor cores with tcgen05.mma and is
 // starved while tcgen05.mma bursts run, which would put the gate warps behind the dense product):
 //   warp 0       TMA producer: A tiles once per tile; per group the R_g tiles and the dC / B_g stages
-//   warp 1       MMA issuer (leader CTA), per group
+//   warps 1, 22, 23  MMA issuers (leader CTA), one product each, per group
 //                  rotation  S_g = A . blockdiag(R_g)^T: M256 N=E K=16 per rotation block (gated mode)
 //                  dense     dH_g = dC_g . B_g: M256 N128 K16 (dC K-major, B_g MN-major), two TMEM buffers
 //                  dS . R    dA += blockdiag(dS_g) . R_g: M256 N=E K=16 per block (dS K-major from shared
@@ -39,9 +39,12 @@
 
 namespace prism {
 
+#ifndef PRISM_DADR_SMALL_STAGES
+#define PRISM_DADR_SMALL_STAGES 0
+#endif
 namespace dadr {
-constexpr int kThreads = 704;
-constexpr int kWarpTma = 0, kWarpMma = 1;
+constexpr int kThreads = 768;
+constexpr int kWarpTma = 0, kWarpMma = 1, kWarpRot = 22, kWarpDsr = 23;
 constexpr int kGateWarp0 = 4;      // multiple of 4: (warp & 3) is the TMEM lane quarter
 constexpr int kNumGateWarps = 16;
 constexpr int kNumDrWarps = 4;     // warps 2, 3, 20, 21
@@ -52,7 +55,7 @@ constexpr int kMaxRBufs = 4;
 // one pipeline stage = kStageOut outputs of the group: kStageOut/64 dC tiles [128 tokens x 64] and
 // this CTA's half of the B_g features, a [kStageOut outputs x 64 features] tile
 template <int E> struct Stage {
-  static constexpr int kOut = (E == 64) ? 64 : 128;   // the R buffers of E = 64 leave less room
+  static constexpr int kOut = (E == 64 || PRISM_DADR_SMALL_STAGES) ? 64 : 128;   // the R buffers of E = 64 leave less room
   static constexpr int kDcTiles = kOut / 64;
   static constexpr int kBTile = kOut * 128;
   static constexpr int kBytes = kDcTiles * kTile + kBTile;
@@ -150,7 +153,7 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int G = p.G;
   const int nstg = (p.gs + St::kOut - 1) / St::kOut;  // stages per group
   const bool is_gate = warp >= kGateWarp0 && warp < kGateWarp0 + kNumGateWarps;
-  const bool is_dr = warp == 2 || warp == 3 || warp >= kGateWarp0 + kNumGateWarps;
+  const bool is_dr = warp == 2 || warp == 3 || warp == 20 || warp == 21;
   const int n_units = (n_mpairs - run + p.runs - 1) / p.runs;   // token-tile pairs of this CTA pair
   const int total = n_units * G;                                // groups it walks
 
@@ -238,35 +241,86 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     }
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ MMA issuer
-    // Iteration i issues, in this order (tcgen05.mma executes in order):
-    //   dS . R of group i - 1            (its gate warps are done: dS is in shared memory)
-    //   rotation of group i              only when group i opens a tile (it needs the new A tiles)
-    //   dense product of group i + 1     (the dH buffer of group i - 1 is free)
-    //   rotation of group i + 1          once the gate warps hold S of group i in registers; not
-    //                                    across a tile boundary
-    // so that while the gate warps work on group i the tensor pipe has everything group i + 1 needs.
+    // Three threads of the leader CTA issue tcgen05.mma, one per product (this one: the dense product).
+    // Issuing costs a thread 60-80 clocks per MMA whatever its size, a barrier test ~65 and a commit
+    // ~90, so one thread cannot feed the tensor pipe with the 32 MMAs of a group; the products are
+    // ordered among themselves by barriers only.
     if (lane == 0 && rank == 0) {
       const uint32_t idesc_h = make_idesc(DT, 256, 128, 0, 1);   // dH: M = 256 tokens; dC K-major, B_g MN-major
-      const uint32_t idesc_s = make_idesc(DT, 256, E, 0, 0);     // S block: A K-major, R_g K-major
-      const uint32_t idesc_a = make_idesc(DT, 256, E, 0, 1);     // dA block: dS K-major, R_g MN-major
-      // descriptors of buffer 0 of each ring; later buffers add to the low words
+      // descriptors of stage 0; a stage further on adds its size >> 4 to the low words
       const uint64_t dst0 = desc_kmajor_sw128(smem_u32(smemSt), 1024);
       const uint64_t dsb0 = desc_mnmajor_sw128(smem_u32(smemSt) + St::kDcTiles * kTile, St::kBTile, 1024);
-      const uint64_t dA0 = desc_kmajor_sw128(smem_u32(smemA), 1024);
-      const uint64_t dS0 = desc_kmajor_sw128(smem_u32(smemDS), 1024);
-      const uint64_t dRr0 = desc_kmajor_sw128(smem_u32(smemR), 1024);
-      const uint64_t dRd0 = desc_mnmajor_sw128(smem_u32(smemR) + 2 * p.rr_tile_bytes, (uint32_t)p.rd_tile_bytes, 1024);
-      const uint32_t k_hi = (uint32_t)(dst0 >> 32), b_hi = (uint32_t)(dsb0 >> 32), rd_hi = (uint32_t)(dRd0 >> 32);
-      const uint32_t r_step = (uint32_t)r_buf_bytes >> 4;
-      const uint32_t rr_tile = (uint32_t)p.rr_tile_bytes >> 4, rd_tile = (uint32_t)p.rd_tile_bytes >> 4;
+      const uint32_t k_hi = (uint32_t)(dst0 >> 32), b_hi = (uint32_t)(dsb0 >> 32);
       bool ok = true;
       Ring rst(p.ns);
-      Ring r_rot(p.rb), r_dsr(p.rb);   // R buffer of the next group to rotate / to multiply with dS
-      int g_dsr = 0;                   // index inside its tile of the next group whose dS . R is due
+      for (int n = 0; n < total && ok; ++n) {
+        if (n >= 2) {   // the gate warps have read dH of group n - 2 out of this buffer
+          const uint32_t gd = (uint32_t)(n - 2);
+          if (!mbar_wait_cluster(&bars->gate_done[gd & 1], (gd >> 1) & 1)) { ok = false; break; }
+        }
+        const uint32_t d_tmem = tmem_base + kDhCol0 + ((uint32_t)n & 1) * 128;
+        for (int s = 0; s < nstg; ++s, rst.next()) {
+          const int st = rst.idx;
+          if (!mbar_wait_cluster(&bars->st_full[st], rst.phase)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_lo = (uint32_t)dst0 + st * (St::kBytes >> 4);
+          const uint32_t b_lo = (uint32_t)dsb0 + st * (St::kBytes >> 4);
+          constexpr int kSteps = St::kOut / 16;
+          const int ksteps = min(kSteps, (p.gs - s * St::kOut) / 16);
+          if (ksteps == kSteps) {
+            // K16 step ks: dC tile ks/4 (+kTile), 32 bytes per step inside it; B_g rows 16 ks (+2048 bytes)
+            umma_f16_pair_lh(d_tmem, a_lo, k_hi, b_lo, b_hi, idesc_h, s > 0 ? 1u : 0u);
+#pragma unroll
+            for (int ks = 1; ks < kSteps; ++ks)
+              umma_f16_pair_lh(d_tmem, a_lo + (((ks >> 2) * kTile + (ks & 3) * 32) >> 4), k_hi,
+                               b_lo + ((ks * 2048) >> 4), b_hi, idesc_h, 1u);
+          } else {
+            for (int ks = 0; ks < ksteps; ++ks)
+              umma_f16_pair_lh(d_tmem, a_lo + (((ks >> 2) * kTile + (ks & 3) * 32) >> 4), k_hi,
+                               b_lo + ((ks * 2048) >> 4), b_hi, idesc_h, (s > 0 || ks > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(&bars->st_empty[st], 0x3);
+        }
+        if (!ok) break;
+        umma_commit_pair(&bars->dh_full[n & 1], 0x3);
+      }
+      if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
+    } else if (lane == 0 && rank == 1 && kGated) {
+      // the peer tells the leader's MMA issuer when its A tiles have landed
+      bool ok = true;
+      uint32_t ph = 0;
+      const uint32_t a_peer = mapa_shared(smem_u32(&bars->a_peer), 0);
+      for (int u = 0; u < n_units && ok; ++u, ph ^= 1u) {
+        if (!mbar_wait(&bars->a_full, ph)) { ok = false; break; }
+        mbar_arrive_cluster(a_peer);
+      }
+      if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
+    }
+  } else if (warp == kWarpRot) {
+    // ------------------------------------------------------------------ MMA issuer: rotation S_g = A . blockdiag(R_g)^T
+    if (lane == 0 && rank == 0 && kGated) {
+      const uint32_t idesc_s = make_idesc(DT, 256, E, 0, 0);     // S block: A K-major, R_g K-major
+      const uint64_t dA0 = desc_kmajor_sw128(smem_u32(smemA), 1024);
+      const uint64_t dRr0 = desc_kmajor_sw128(smem_u32(smemR), 1024);
+      const uint32_t k_hi = (uint32_t)(dA0 >> 32);
+      const uint32_t r_step = (uint32_t)r_buf_bytes >> 4;
+      const uint32_t rr_tile = (uint32_t)p.rr_tile_bytes >> 4;
+      bool ok = true;
+      Ring rr(p.rb);
       uint32_t a_phase = 0;
-
-      auto rotate = [&](uint32_t rbuf) {
-        const uint32_t r_lo = (uint32_t)dRr0 + rbuf * r_step;
+      int gi = 0;   // index of group n inside its tile
+      for (int n = 0; n < total && ok; ++n, rr.next(), gi = (gi + 1 == G) ? 0 : gi + 1) {
+        if (gi == 0) {   // a new tile: its A tiles must have landed in both CTAs
+          if (!mbar_wait(&bars->a_full, a_phase)) { ok = false; break; }
+          if (!mbar_wait_cluster(&bars->a_peer, a_phase)) { ok = false; break; }
+          a_phase ^= 1u;
+        }
+        if (n >= 1) {    // the gate warps hold S of group n - 1 in registers
+          if (!mbar_wait_cluster(&bars->s_free, (uint32_t)(n - 1) & 1)) { ok = false; break; }
+        }
+        if (!mbar_wait_cluster(&bars->r_full[rr.idx], rr.phase)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t r_lo = (uint32_t)dRr0 + rr.idx * r_step;
 #pragma unroll
         for (int b = 0; b < NBLK; ++b) {
 #pragma unroll
@@ -278,102 +332,51 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                              ks > 0 ? 1u : 0u);
           }
         }
-      };
-
-      int gi = -1;   // index of group i inside its tile
-      for (int i = -1; i <= total && ok; ++i, gi = (gi + 1 == G) ? 0 : gi + 1) {
-        // ---- (1) dS . R of group i - 1: its gate warps (both CTAs) have written dS and read dH
-        if (i >= 1) {
-          const uint32_t gd = (uint32_t)(i - 1);
-          if (!mbar_wait_cluster(&bars->gate_done[gd & 1], (gd >> 1) & 1)) { ok = false; break; }
-          if (!kGated) {   // (the rotation has waited for these R tiles already)
-            if (!mbar_wait_cluster(&bars->r_full[r_dsr.idx], r_dsr.phase)) { ok = false; break; }
-          }
-          tc_fence_after_sync();
-          const uint32_t s_lo = (uint32_t)dS0 + (gd & 1) * ((2 * kTile) >> 4);
-          const uint32_t r_lo = (uint32_t)dRd0 + r_dsr.idx * r_step;
-#pragma unroll
-          for (int b = 0; b < NBLK; ++b) {
-#pragma unroll
-            for (int ks = 0; ks < KS; ++ks) {
-              // dS (K-major): features b*E + ks*16 ..; R_g (MN-major): rows ks*16 .. (2048 bytes per 16 rows),
-              // columns of block b
-              const int fo = b * E + ks * 16;
-              const uint32_t ta = (uint32_t)((fo >> 6) * (kTile >> 4) + ((fo & 63) >> 4) * 2);
-              const int co = b * E;
-              const uint32_t tr = (uint32_t)(co >> 6) * rd_tile + (uint32_t)(((co & 63) * 2) >> 4) + (uint32_t)(ks * 128);
-              umma_f16_pair_lh(tmem_base + kDaCol0 + b * E, s_lo + ta, k_hi, r_lo + tr, rd_hi, idesc_a,
-                               (g_dsr > 0 || ks > 0) ? 1u : 0u);
-            }
-          }
-          umma_commit_pair(&bars->ds_empty[gd & 1], 0x3);
-          umma_commit_pair(&bars->r_empty[r_dsr.idx], 0x3);
-          r_dsr.next();
-          if (++g_dsr == G) {
-            g_dsr = 0;
-            umma_commit_pair(&bars->da_full, 0x3);   // the tile's dA is complete
-          }
-        }
-        if (i >= total) break;
-        // ---- (2) rotation of group i when it opens a tile: the new A tiles must have landed in both CTAs
-        if (kGated && i >= 0 && gi == 0) {
-          if (!mbar_wait(&bars->a_full, a_phase)) { ok = false; break; }
-          if (!mbar_wait_cluster(&bars->a_peer, a_phase)) { ok = false; break; }
-          a_phase ^= 1u;
-          if (!mbar_wait_cluster(&bars->r_full[r_rot.idx], r_rot.phase)) { ok = false; break; }
-          tc_fence_after_sync();
-          rotate(r_rot.idx);
-          umma_commit_pair(&bars->s_full, 0x3);
-          r_rot.next();
-        }
-        // ---- (3) dense product of group i + 1 (the dH buffer of group i - 1 is free, see (1))
-        if (i + 1 < total) {
-          const uint32_t gn = (uint32_t)(i + 1);
-          const uint32_t d_tmem = tmem_base + kDhCol0 + (gn & 1) * 128;
-          for (int s = 0; s < nstg; ++s, rst.next()) {
-            const int st = rst.idx;
-            if (!mbar_wait_cluster(&bars->st_full[st], rst.phase)) { ok = false; break; }
-            tc_fence_after_sync();
-            const uint32_t a_lo = (uint32_t)dst0 + st * (St::kBytes >> 4);
-            const uint32_t b_lo = (uint32_t)dsb0 + st * (St::kBytes >> 4);
-            constexpr int kSteps = St::kOut / 16;
-            const int ksteps = min(kSteps, (p.gs - s * St::kOut) / 16);
-            if (ksteps == kSteps) {
-              // K16 step ks: dC tile ks/4 (+kTile), 32 bytes per step inside it; B_g rows 16 ks (+2048 bytes)
-              umma_f16_pair_lh(d_tmem, a_lo, k_hi, b_lo, b_hi, idesc_h, s > 0 ? 1u : 0u);
-#pragma unroll
-              for (int ks = 1; ks < kSteps; ++ks)
-                umma_f16_pair_lh(d_tmem, a_lo + (((ks >> 2) * kTile + (ks & 3) * 32) >> 4), k_hi,
-                                 b_lo + ((ks * 2048) >> 4), b_hi, idesc_h, 1u);
-            } else {
-              for (int ks = 0; ks < ksteps; ++ks)
-                umma_f16_pair_lh(d_tmem, a_lo + (((ks >> 2) * kTile + (ks & 3) * 32) >> 4), k_hi,
-                                 b_lo + ((ks * 2048) >> 4), b_hi, idesc_h, (s > 0 || ks > 0) ? 1u : 0u);
-            }
-            umma_commit_pair(&bars->st_empty[st], 0x3);
-          }
-          if (!ok) break;
-          umma_commit_pair(&bars->dh_full[gn & 1], 0x3);
-        }
-        // ---- (4) rotation of group i + 1 inside the same tile, once the gate warps hold S of group i
-        if (kGated && i >= 0 && i + 1 < total && gi + 1 < G) {
-          if (!mbar_wait_cluster(&bars->s_free, (uint32_t)i & 1)) { ok = false; break; }
-          if (!mbar_wait_cluster(&bars->r_full[r_rot.idx], r_rot.phase)) { ok = false; break; }
-          tc_fence_after_sync();
-          rotate(r_rot.idx);
-          umma_commit_pair(&bars->s_full, 0x3);
-          r_rot.next();
-        }
+        umma_commit_pair(&bars->s_full, 0x3);
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
-    } else if (lane == 0 && rank == 1 && kGated) {
-      // the peer tells the leader's MMA issuer when its A tiles have landed
+    }
+  } else if (warp == kWarpDsr) {
+    // ------------------------------------------------------------------ MMA issuer: dA += blockdiag(dS_g) . R_g
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc_a = make_idesc(DT, 256, E, 0, 1);     // dA block: dS K-major, R_g MN-major
+      const uint64_t dS0 = desc_kmajor_sw128(smem_u32(smemDS), 1024);
+      const uint64_t dRd0 = desc_mnmajor_sw128(smem_u32(smemR) + 2 * p.rr_tile_bytes, (uint32_t)p.rd_tile_bytes, 1024);
+      const uint32_t k_hi = (uint32_t)(dS0 >> 32), rd_hi = (uint32_t)(dRd0 >> 32);
+      const uint32_t r_step = (uint32_t)r_buf_bytes >> 4;
+      const uint32_t rd_tile = (uint32_t)p.rd_tile_bytes >> 4;
       bool ok = true;
-      uint32_t ph = 0;
-      const uint32_t a_peer = mapa_shared(smem_u32(&bars->a_peer), 0);
-      for (int u = 0; u < n_units && ok; ++u, ph ^= 1u) {
-        if (!mbar_wait(&bars->a_full, ph)) { ok = false; break; }
-        mbar_arrive_cluster(a_peer);
+      Ring rr(p.rb);
+      int gi = 0;
+      for (int n = 0; n < total && ok; ++n, rr.next()) {
+        // the gate warps of both CTAs have written dS of group n
+        if (!mbar_wait_cluster(&bars->gate_done[n & 1], ((uint32_t)n >> 1) & 1)) { ok = false; break; }
+        if (!kGated) {   // (in the gated mode the rotation has waited for these R tiles already)
+          if (!mbar_wait_cluster(&bars->r_full[rr.idx], rr.phase)) { ok = false; break; }
+        }
+        tc_fence_after_sync();
+        const uint32_t s_lo = (uint32_t)dS0 + ((uint32_t)n & 1) * ((2 * kTile) >> 4);
+        const uint32_t r_lo = (uint32_t)dRd0 + rr.idx * r_step;
+#pragma unroll
+        for (int b = 0; b < NBLK; ++b) {
+#pragma unroll
+          for (int ks = 0; ks < KS; ++ks) {
+            // dS (K-major): features b*E + ks*16 ..; R_g (MN-major): rows ks*16 .. (2048 bytes per 16 rows),
+            // columns of block b
+            const int fo = b * E + ks * 16;
+            const uint32_t ta = (uint32_t)((fo >> 6) * (kTile >> 4) + ((fo & 63) >> 4) * 2);
+            const int co = b * E;
+            const uint32_t tr = (uint32_t)(co >> 6) * rd_tile + (uint32_t)(((co & 63) * 2) >> 4) + (uint32_t)(ks * 128);
+            umma_f16_pair_lh(tmem_base + kDaCol0 + b * E, s_lo + ta, k_hi, r_lo + tr, rd_hi, idesc_a,
+                             (gi > 0 || ks > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit_pair(&bars->ds_empty[n & 1], 0x3);
+        umma_commit_pair(&bars->r_empty[rr.idx], 0x3);
+        if (++gi == G) {
+          gi = 0;
+          umma_commit_pair(&bars->da_full, 0x3);   // the tile's dA is complete
+        }
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
@@ -513,20 +516,34 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           const uint32_t a_tile = smem_u32(smemA + chunk * kTile);
           const uint32_t ci = (b * E + is * 16) / 8;   // 16-byte chunk of the dS columns (i)
           const uint32_t cj = (b * E + js * 16) / 8;   // 16-byte chunk of the A columns (j)
+          // Four token steps at a time: all eight fragment loads first, then the MMAs on two independent
+          // accumulator pairs, so that a warp does not sit through one shared-memory and one tensor-pipe
+          // latency per step (the legacy tensor path only gets the gaps that tcgen05.mma leaves).
           float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
+          float e0[4] = {0.f, 0.f, 0.f, 0.f}, e1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            // A operand (i x tok) = dS^T: matrices (i-lo,tok-lo) (i-hi,tok-lo) (i-lo,tok-hi) (i-hi,tok-hi)
-            const uint32_t tok_a = ks * 16 + l8 + ((mat & 2) ? 8 : 0);
-            uint32_t af[4];
-            ldmatrix_x4_trans(ds_tile + sw128_offset(tok_a, ci + (mat & 1)), af);
-            // B operand (tok x j) = A: matrices (tok-lo,j-lo) (tok-hi,j-lo) (tok-lo,j-hi) (tok-hi,j-hi)
-            const uint32_t tok_b = ks * 16 + l8 + ((mat & 1) ? 8 : 0);
-            uint32_t bf[4];
-            ldmatrix_x4_trans(a_tile + sw128_offset(tok_b, cj + (mat >> 1)), bf);
-            mma_m16n8k16<DT>(d0, af, bf[0], bf[1]);
-            mma_m16n8k16<DT>(d1, af, bf[2], bf[3]);
+          for (int k4 = 0; k4 < 8; k4 += 4) {
+            uint32_t af[4][4], bf[4][4];
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              const int ks = k4 + kk;
+              // A operand (i x tok) = dS^T: matrices (i-lo,tok-lo) (i-hi,tok-lo) (i-lo,tok-hi) (i-hi,tok-hi)
+              const uint32_t tok_a = ks * 16 + l8 + ((mat & 2) ? 8 : 0);
+              ldmatrix_x4_trans(ds_tile + sw128_offset(tok_a, ci + (mat & 1)), af[kk]);
+              // B operand (tok x j) = A: matrices (tok-lo,j-lo) (tok-hi,j-lo) (tok-lo,j-hi) (tok-hi,j-hi)
+              const uint32_t tok_b = ks * 16 + l8 + ((mat & 1) ? 8 : 0);
+              ldmatrix_x4_trans(a_tile + sw128_offset(tok_b, cj + (mat >> 1)), bf[kk]);
+            }
+#pragma unroll
+            for (int kk = 0; kk < 4; kk += 2) {
+              mma_m16n8k16<DT>(d0, af[kk], bf[kk][0], bf[kk][1]);
+              mma_m16n8k16<DT>(d1, af[kk], bf[kk][2], bf[kk][3]);
+              mma_m16n8k16<DT>(e0, af[kk + 1], bf[kk + 1][0], bf[kk + 1][1]);
+              mma_m16n8k16<DT>(e1, af[kk + 1], bf[kk + 1][2], bf[kk + 1][3]);
+            }
           }
+#pragma unroll
+          for (int x = 0; x < 4; ++x) { d0[x] += e0[x]; d1[x] += e1[x]; }
           // Accumulate into this CTA's partial buffer.  Every address has exactly one writer thread,
           // which stores on its first token tile and afterwards issues fire-and-forget fp32 reductions
           // in token-tile order: same-address operations of one thread stay ordered, so the sum is
@@ -628,7 +645,7 @@ int launch_bwd_dadr(const DadrArgs& a) {
   int smem_bytes = 0;
   int rc = (a.E == 16) ? dadr_plan<16>(p, smem_bytes) : (a.E == 32) ? dadr_plan<32>(p, smem_bytes) : dadr_plan<64>(p, smem_bytes);
   if (rc) return rc;
-  const int stage_out = (a.E == 64) ? 64 : 128;
+  const int stage_out = (a.E == 64 || PRISM_DADR_SMALL_STAGES) ? 64 : 128;
 
   CUtensorMap tmA, tmRr, tmRd, tmdC, tmB;
   if ((rc = make_tmap_2d(&tmA, a.dtype, a.A, a.M, a.K, a.lda, 128, 64, true))) return rc;
