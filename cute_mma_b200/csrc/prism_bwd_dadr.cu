@@ -39,8 +39,8 @@
 
 namespace prism {
 
-#ifndef PRISM_DADR_SMALL_STAGES
-#define PRISM_DADR_SMALL_STAGES 0
+#ifndef PRISM_K2_CVT_HW
+#define PRISM_K2_CVT_HW 1
 #endif
 namespace dadr {
 constexpr int kThreads = 768;
@@ -52,10 +52,11 @@ constexpr int kDhCol0 = 0, kSCol0 = 256, kDaCol0 = 384;   // TMEM columns: dH ri
 constexpr int kTile = 128 * 128;   // bytes of a [128 x 64] 16-bit tile
 constexpr int kMaxStages = 6;
 constexpr int kMaxRBufs = 4;
-// one pipeline stage = kStageOut outputs of the group: kStageOut/64 dC tiles [128 tokens x 64] and
-// this CTA's half of the B_g features, a [kStageOut outputs x 64 features] tile
+// one pipeline stage = kOut outputs of the group: kOut/64 dC tiles [128 tokens x 64] and this CTA's
+// half of the B_g features, a [kOut outputs x 64 features] tile.  64-output stages (24 KB) are
+// released after four MMAs, which keeps the TMA queue fuller than 128-output stages do.
 template <int E> struct Stage {
-  static constexpr int kOut = (E == 64 || PRISM_DADR_SMALL_STAGES) ? 64 : 128;   // the R buffers of E = 64 leave less room
+  static constexpr int kOut = 64;
   static constexpr int kDcTiles = kOut / 64;
   static constexpr int kBTile = kOut * 128;
   static constexpr int kBytes = kDcTiles * kTile + kBTile;
@@ -440,7 +441,11 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
               // pair e of the fragment: (row, cols) as in the accumulator layout; e >> 1 selects columns + 8
               const float x0 = __uint_as_float(dh[i][2 * e]), x1 = __uint_as_float(dh[i][2 * e + 1]);
               if (kGated) {
+#if PRISM_K2_CVT_HW
+                const uint32_t hs = Pk<DT>::cvt_hw(__uint_as_float(sv[i][2 * e]), __uint_as_float(sv[i][2 * e + 1]));
+#else
                 const uint32_t hs = Pk<DT>::cvt(__uint_as_float(sv[i][2 * e]), __uint_as_float(sv[i][2 * e + 1]));
+#endif
                 float* d = (e >> 1) ? d1 : d0;
                 dsf[i][e] = gate_bwd_pair<DT>(af[i][e], hs, x0, x1, d[(e & 1) * 2], d[(e & 1) * 2 + 1]);
               } else {
@@ -645,7 +650,7 @@ int launch_bwd_dadr(const DadrArgs& a) {
   int smem_bytes = 0;
   int rc = (a.E == 16) ? dadr_plan<16>(p, smem_bytes) : (a.E == 32) ? dadr_plan<32>(p, smem_bytes) : dadr_plan<64>(p, smem_bytes);
   if (rc) return rc;
-  const int stage_out = (a.E == 64 || PRISM_DADR_SMALL_STAGES) ? 64 : 128;
+  const int stage_out = 64;
 
   CUtensorMap tmA, tmRr, tmRd, tmdC, tmB;
   if ((rc = make_tmap_2d(&tmA, a.dtype, a.A, a.M, a.K, a.lda, 128, 64, true))) return rc;

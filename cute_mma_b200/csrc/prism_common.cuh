@@ -496,6 +496,7 @@ struct Pk<DT_F16> {
     asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
     return d;
   }
+  __device__ __forceinline__ static uint32_t cvt_hw(float lo, float hi) { return cvt(lo, hi); }
   __device__ __forceinline__ static uint32_t mul(uint32_t a, uint32_t b) {
     uint32_t d;
     asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
@@ -519,6 +520,12 @@ struct Pk<DT_BF16> {
   // fp32 pair -> bf16x2 with integer ops: add half an ulp to the bit patterns and keep the upper
   // halves (round to nearest, ties away from zero).  The cvt.rn.bf16x2.f32 instruction runs on the
   // 16-lane/clk special-function pipe (measured: as expensive as a tanh), these three ALU ops do not.
+  // The single-instruction conversion (special-function pipe): for code whose ALU pipe is the busier one.
+  __device__ __forceinline__ static uint32_t cvt_hw(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+  }
   __device__ __forceinline__ static uint32_t cvt(float lo, float hi) {
     const uint32_t ulo = __float_as_uint(lo) + 0x8000u;
     const uint32_t uhi = __float_as_uint(hi) + 0x8000u;
