@@ -186,6 +186,7 @@ def main():
     ap.add_argument("--workload", default="cfg2_m16384", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-small-m", action="store_true")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
@@ -390,6 +391,36 @@ def main():
                                "step; copies and kernels of neighbouring micro-batches and steps overlap on three "
                                "streams, one host wait after the last step"}
         del A_h, dC_h, C_h, dA_h
+
+    # ---- small-M forward calls (decode-sized batches): HBM-bound, minimum traffic B + R + A + C.
+    # L2 (126 MB) would otherwise keep most of B (117 MB) between iterations: a 384 MB buffer is
+    # written before every timed call.
+    if not args.no_small_m and args.workload.startswith("cfg2"):
+        flush = torch.empty(384 * 1024 * 1024, dtype=torch.uint8, device=dev)
+        small = []
+        for m in (1, 16, 128):
+            A_s = torch.randn(m, K, device=dev, generator=gen).to(dt)
+            for _ in range(3):
+                cp.forward(A_s, B, R, gs, rs, activation=act)
+            ts = []
+            for _ in range(10):
+                flush.fill_(1)
+                t0e, t1e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0e.record()
+                cp.forward(A_s, B, R, gs, rs, activation=act)
+                t1e.record()
+                torch.cuda.synchronize()
+                ts.append(t0e.elapsed_time(t1e) * 1e3)
+            ts.sort()
+            nbytes = (B.numel() + R.numel() + m * K + m * N) * 2
+            med = ts[len(ts) // 2]
+            small.append({"M": m, "us_median": med, "us_min": ts[0], "bytes": nbytes,
+                          "gbs": nbytes / (med * 1e-6) / 1e9,
+                          "frac_of_measured_hbm": nbytes / (med * 1e-6) / 1e9 / peaks["hbm_gbs"]})
+        cp.check_device_status()
+        line["small_m_fwd"] = {"note": "forward only, cold L2 (384 MB written before each call), CUDA events, 10 calls",
+                               "hbm_peak_gbs": peaks["hbm_gbs"], "calls": small}
+        del flush
 
     if not args.no_cpu_baseline:
         line["cpu_baseline"], _ = cpu_baseline(w)

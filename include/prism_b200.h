@@ -51,7 +51,8 @@ extern "C" {
 /* size of the library's built-in scratch array used by prism_fwd_noalloc: 8 MiB + the status header */
 #define PRISM_NOALLOC_SCRATCH_BYTES (8 * 1024 * 1024 + 256)
 
-/* Forward.  bias: [N] in the same dtype, or NULL.  cfg (4 ints): {BN, PM, stagesAR, stagesB}. */
+/* Forward.  bias: [N] in the same dtype, or NULL.  cfg (4 ints, 0 = default): {BN, PM, stages, unused}:
+ * N tile (divides group_size, <= 256), row tiles per rasterisation panel, shared-memory stages. */
 int prism_fwd(const void* A, const void* B, const void* R, const void* bias, void* C,
               int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
               long long lda, long long ldb, long long ldr, long long ldc,
@@ -77,7 +78,8 @@ int prism_fwd_noalloc(const void* A, const void* B, const void* R, const void* b
 /* Input and rotation gradients: dA [M,K] and dR [(N/group_size)*reconn_sz, K], both scaled by
  * dc_scale.  cfg (1 int): {runs} -- the number of CTA pairs that share one 128-feature column of
  * dA; each CTA accumulates dR into its own fp32 buffer in the workspace in a fixed order and a
- * second kernel adds the buffers in a fixed order: dR is bit-identical from run to run. */
+ * second kernel adds the buffers in a fixed order: dR is bit-identical from run to run.  The
+ * workspace also holds the kernel's copy of R (widened for reconn_sz = 8, halved in the gated mode). */
 int prism_bwd_dadr(const void* dC, const void* A, const void* B, const void* R, void* dA, void* dR,
                    int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
                    float dc_scale, long long lddc, long long lda, long long ldb, long long ldr,
