@@ -11,8 +11,8 @@
 // the dense product runs over tokens, so both its operands are "MN-major": H tiles [128 tokens x 64
 // features] and dC tiles [128 tokens x 64 outputs] are used as the gate warps / TMA lay them out.
 //   warp 0      TMA: R_g tiles once; per token block two A tiles and ceil(BN/128) dC tiles
-//   warp 1      MMA issuer (leader): rotation S = A_blk . R_blk^T per rotation block as tcgen05.mma
-//               M256 N=2E K=16.  The two CTAs hold different features, hence different R blocks; an
+//   warps 1, 2  MMA issuers (leader), one per product.  Rotation S = A_blk . R_blk^T per rotation block
+//               as tcgen05.mma M256 N=2E K=16.  The two CTAs hold different features, hence different R blocks; an
 //               MMA spanning both takes its N rows half from each CTA, so it multiplies every row by
 //               both R blocks: a CTA's own product lands in columns [rank*E, rank*E+E) of the block's
 //               2E columns of S, the other half is ignored.
@@ -30,7 +30,7 @@ namespace prism {
 
 namespace db {
 constexpr int kThreads = 768;
-constexpr int kWarpTma = 0, kWarpMma = 1;
+constexpr int kWarpTma = 0, kWarpMma = 1, kWarpRot = 2;
 constexpr int kGateWarp0 = 4;      // multiple of 4: (warp & 3) is the TMEM lane quarter a warp may touch
 constexpr int kNumGateWarps = 16;  // 8 row groups x 2 feature tiles
 constexpr int kEpiWarp0 = kGateWarp0 + kNumGateWarps;   // 20
@@ -147,61 +147,66 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
-  } else if (warp == kWarpMma) {
-    // ------------------------------------------------------------------ MMA issuer: rotation and dense product
+  } else if (warp == kWarpRot) {
+    // ------------------------------------------------------------------ MMA issuer 1: rotation
     // S is single-buffered (TMEM: 256 columns of accumulator, 256 of S).  The gate warps copy their S
-    // values to registers first thing and release the buffer, so the rotation of block j + 1 is
-    // issued while they still work on block j; it is queued BEFORE the dense product of block j
-    // (tcgen05.mma executes in order), which has to wait for them.
+    // values to registers first thing and release the buffer, so the rotation of block j + 1 runs
+    // while they still work on block j.  Rotation and dense product have an issuing thread each:
+    // issuing costs a thread 60-80 clocks per MMA, a barrier test ~65, a commit ~90.
     if (lane == 0 && rank == 0) {
       const uint32_t idesc_r = make_idesc(DT, 256, 2 * E, 0, 0);   // rows: both CTAs' tokens; N: E rows of R from each CTA
-      const uint32_t idesc_d = make_idesc(DT, 256, p.BN, 1, 1);    // M = 256: 128 features in each CTA
       const uint64_t da0 = desc_kmajor_sw128(smem_u32(smemSt), 1024);
       const uint64_t dr0 = desc_kmajor_sw128(smem_u32(smemR), 1024);
-      const uint64_t dh0 = desc_mnmajor_sw128(smem_u32(smemSt), kTile, 1024);
-      const uint64_t dd0 = desc_mnmajor_sw128(smem_u32(smemSt) + 2 * kTile, kTile, 1024);
-      const uint32_t k_hi = (uint32_t)(da0 >> 32), h_hi = (uint32_t)(dh0 >> 32), d_hi = (uint32_t)(dd0 >> 32);
+      const uint32_t k_hi = (uint32_t)(da0 >> 32);
       const uint32_t st_step = (uint32_t)p.stage_bytes >> 4;
       const uint32_t r_step = (uint32_t)p.r_tile_bytes >> 4;
       const uint32_t s0 = tmem_base + kSCol0;
       bool ok = true;
-      Ring rr(p.ns), rd(p.ns);   // stage of the block being rotated / multiplied
-      for (int j = -1; j < nb && ok; ++j) {
-        if (j + 1 < nb) {
-          if (j >= 0) {   // the gate warps hold S of block j in registers
-            if (!mbar_wait_cluster(&bars->s_free, j & 1)) { ok = false; break; }
-          }
-          if (!mbar_wait_cluster(&bars->a_full[rr.idx], rr.phase)) { ok = false; break; }
-          tc_fence_after_sync();
-          const uint32_t a_lo = (uint32_t)da0 + rr.idx * st_step;
-#pragma unroll
-          for (int b = 0; b < NBLK; ++b) {
-#pragma unroll
-            for (int ks = 0; ks < KS; ++ks) {
-              // features b*E + ks*16 .. +16 of the CTA's 128: tile (64 features) and 32-byte step inside it
-              const int fo = b * E + ks * 16;
-              const uint32_t ta = (uint32_t)((fo >> 6) * (kTile >> 4) + ((fo & 63) >> 4) * 2);
-              const uint32_t tr = (uint32_t)(fo >> 6) * r_step + (uint32_t)(((fo & 63) >> 4) * 2);
-              umma_f16_pair_lh(s0 + b * 2 * E, a_lo + ta, k_hi, (uint32_t)dr0 + tr, k_hi, idesc_r, ks > 0 ? 1u : 0u);
-            }
-          }
-          umma_commit_pair(&bars->s_full, 0x3);
-          rr.next();
+      Ring rr(p.ns);
+      for (int j = 0; j < nb && ok; ++j, rr.next()) {
+        if (j > 0) {   // the gate warps hold S of block j - 1 in registers
+          if (!mbar_wait_cluster(&bars->s_free, (uint32_t)(j - 1) & 1)) { ok = false; break; }
         }
-        if (j >= 0) {
-          // gate warps done with block j: H written; the dC halves landed
-          if (!mbar_wait_cluster(&bars->hd_full[rd.idx], rd.phase)) { ok = false; break; }
-          tc_fence_after_sync();
-          const uint32_t h_lo = (uint32_t)dh0 + rd.idx * st_step;
-          const uint32_t d_lo = (uint32_t)dd0 + rd.idx * st_step;
-          umma_f16_pair_lh(tmem_base, h_lo, h_hi, d_lo, d_hi, idesc_d, j > 0 ? 1u : 0u);
+        if (!mbar_wait_cluster(&bars->a_full[rr.idx], rr.phase)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t a_lo = (uint32_t)da0 + rr.idx * st_step;
 #pragma unroll
-          for (int ks = 1; ks < 8; ++ks)   // 16 tokens = 2048 bytes further on in both tiles
-            umma_f16_pair_lh(tmem_base, h_lo + ks * 128, h_hi, d_lo + ks * 128, d_hi, idesc_d, 1u);
-          umma_commit_pair(&bars->stage_free[rd.idx], 0x3);
-          if (j == nb - 1) umma_commit_pair(&bars->acc_full, 0x3);
-          rd.next();
+        for (int b = 0; b < NBLK; ++b) {
+#pragma unroll
+          for (int ks = 0; ks < KS; ++ks) {
+            // features b*E + ks*16 .. +16 of the CTA's 128: tile (64 features) and 32-byte step inside it
+            const int fo = b * E + ks * 16;
+            const uint32_t ta = (uint32_t)((fo >> 6) * (kTile >> 4) + ((fo & 63) >> 4) * 2);
+            const uint32_t tr = (uint32_t)(fo >> 6) * r_step + (uint32_t)(((fo & 63) >> 4) * 2);
+            umma_f16_pair_lh(s0 + b * 2 * E, a_lo + ta, k_hi, (uint32_t)dr0 + tr, k_hi, idesc_r, ks > 0 ? 1u : 0u);
+          }
         }
+        umma_commit_pair(&bars->s_full, 0x3);
+      }
+      if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
+    }
+  } else if (warp == kWarpMma) {
+    // ------------------------------------------------------------------ MMA issuer 2: dense product
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc_d = make_idesc(DT, 256, p.BN, 1, 1);    // M = 256: 128 features in each CTA
+      const uint64_t dh0 = desc_mnmajor_sw128(smem_u32(smemSt), kTile, 1024);
+      const uint64_t dd0 = desc_mnmajor_sw128(smem_u32(smemSt) + 2 * kTile, kTile, 1024);
+      const uint32_t h_hi = (uint32_t)(dh0 >> 32), d_hi = (uint32_t)(dd0 >> 32);
+      const uint32_t st_step = (uint32_t)p.stage_bytes >> 4;
+      bool ok = true;
+      Ring rd(p.ns);
+      for (int j = 0; j < nb && ok; ++j, rd.next()) {
+        // gate warps done with block j: H written; the dC halves landed
+        if (!mbar_wait_cluster(&bars->hd_full[rd.idx], rd.phase)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t h_lo = (uint32_t)dh0 + rd.idx * st_step;
+        const uint32_t d_lo = (uint32_t)dd0 + rd.idx * st_step;
+        umma_f16_pair_lh(tmem_base, h_lo, h_hi, d_lo, d_hi, idesc_d, j > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 1; ks < 8; ++ks)   // 16 tokens = 2048 bytes further on in both tiles
+          umma_f16_pair_lh(tmem_base, h_lo + ks * 128, h_hi, d_lo + ks * 128, d_hi, idesc_d, 1u);
+        umma_commit_pair(&bars->stage_free[rd.idx], 0x3);
+        if (j == nb - 1) umma_commit_pair(&bars->acc_full, 0x3);
       }
       if (!ok) { atomicExch(p.err, PRISM_ERR_DEVICE_WAIT); }
     }
