@@ -41,7 +41,9 @@ WORKLOADS = {
 NOMINAL_TFLOPS = 2250.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture
 # summarised under profiles/ (null until captured for the workload)
-NCU_TRAFFIC_BYTES = {}
+# DRAM read + write bytes per launch from the committed ncu capture (profiles/launch_list_cfg2_m16384.md)
+NCU_TRAFFIC_BYTES = {("prism_bwd_dadr", "cfg2_m16384"): 7.68e9, ("prism_bwd_db", "cfg2_m16384"): 2.35e9,
+                     ("prism_fwd", "cfg2_m16384"): 1.32e9}
 
 
 def flops(w):
