@@ -130,10 +130,8 @@ extern "C" size_t prism_workspace_bytes(int kind, int M, int N, int K, int gs, i
   if (kind == PRISM_KIND_BWD_DADR) {
     const int E = effective_block(rs);
     if (E == 0) return bytes;
-    int runs = (cfg && cfg[0] > 0) ? cfg[0] : dadr_default_runs(M, K, num_sms());
-    const int n_mp = (M + 255) / 256;
-    if (runs > n_mp) runs = n_mp;
-    if (runs < 1) runs = 1;
+    int runs = 1, fpass = 1;
+    dadr_plan_grid(M, N, K, num_sms(), cfg, &runs, &fpass);
     bytes += align256((size_t)2 * runs * G * E * (size_t)K * 4);   // one buffer per CTA of every pair
     return bytes;
   }
@@ -280,7 +278,7 @@ extern "C" int prism_bwd_dadr(const void* dC, const void* A, const void* B, cons
   }
   wp += align256((size_t)(N / gs) * a.E * K * 2);
   a.num_sms = num_sms();
-  a.runs = (cfg && cfg[0] > 0) ? cfg[0] : dadr_default_runs(M, K, a.num_sms);
+  dadr_plan_grid(M, N, K, a.num_sms, cfg, &a.runs, &a.fpass);
   a.partial = reinterpret_cast<float*>(wp);
   a.err = reinterpret_cast<int*>(workspace);
   a.stream = s;

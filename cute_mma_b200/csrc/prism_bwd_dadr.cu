@@ -66,6 +66,7 @@ template <int E> struct Stage {
 struct DadrParams {
   int M, N, K, gs, E, G;
   int n_mtiles, runs;
+  int fpass, fcols;    // feature passes; 128-feature columns per pass (grid.x = 2 * fcols)
   int ns, rb;          // stages of the dC/B ring, number of R buffers
   int rr_tile_bytes;   // bytes reserved per rotation R tile [E/2 x 64] (multiple of 1024)
   int rd_tile_bytes;   // bytes reserved per dS.R R tile [E x 64] (multiple of 1024)
@@ -148,14 +149,19 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();   // 0 = leader (issues the MMAs), 1 = peer
-  const int f0 = (blockIdx.x >> 1) * 128;    // the pair's 128 features
-  const int run = blockIdx.y;                // the pair walks token-tile pairs run, run + runs, ...
+  // The pair owns the 128-feature columns fx, fx + fcols, ... (one per feature pass) and in each of
+  // them the token-tile pairs run, run + runs, ...  Only fcols columns of B are in use at a time:
+  // with all of B (N x K) in flight, L2 could not hold it next to the dC rows.
+  const int fx = blockIdx.x >> 1;
+  const int run = blockIdx.y;
   const int n_mpairs = (p.n_mtiles + 1) / 2;
+  const int n_ft = (p.K + 127) / 128;
+  const int my_passes = (n_ft - fx + p.fcols - 1) / p.fcols;   // feature columns of this pair
   const int G = p.G;
   const int nstg = (p.gs + St::kOut - 1) / St::kOut;  // stages per group
   const bool is_gate = warp >= kGateWarp0 && warp < kGateWarp0 + kNumGateWarps;
   const bool is_dr = warp == 2 || warp == 3 || warp == 20 || warp == 21;
-  const int n_units = (n_mpairs - run + p.runs - 1) / p.runs;   // token-tile pairs of this CTA pair
+  const int n_units = my_passes * ((n_mpairs - run + p.runs - 1) / p.runs);   // tiles of this CTA pair
   const int total = n_units * G;                                // groups it walks
 
   if (threadIdx.x == 0) {
@@ -202,7 +208,9 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       bool ok = true;
       uint32_t tile_iter = 0;
       Ring rr(p.rb), rst(p.ns);
+      for (int fp = 0; fp < my_passes && ok; ++fp)
       for (int mp = run; mp < n_mpairs && ok; mp += p.runs, ++tile_iter) {
+        const int f0 = (fp * p.fcols + fx) * 128;
         const int m0 = (mp * 2 + (int)rank) * 128;
         if (!mbar_wait(&bars->a_empty, (tile_iter & 1) ^ 1)) { ok = false; break; }
         mbar_arrive_expect_tx(&bars->a_full, 2 * kTile);
@@ -397,7 +405,9 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     for (int i = 0; i < 8; ++i) { dacc[i][0] = dacc[i][1] = dacc[i][2] = dacc[i][3] = 0.f; }
     bool ok = true;
     uint32_t tile_iter = 0, gg = 0;
+    for (int fp = 0; fp < my_passes && ok; ++fp)
     for (int mp = run; mp < n_mpairs && ok; mp += p.runs, ++tile_iter) {
+      const int f0 = (fp * p.fcols + fx) * 128;
       const int mt = mp * 2 + (int)rank;
       if (!mbar_wait(&bars->a_full, tile_iter & 1)) { ok = false; break; }
       for (int g = 0; g < G && ok; ++g, ++gg) {
@@ -508,7 +518,10 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     float* part = p.partial + (long long)(run * 2 + (int)rank) * GE * p.K;
     bool ok = true;
     uint32_t tile_iter = 0, gg = 0;
+    for (int fp = 0; fp < my_passes && ok; ++fp)
     for (int mp = run; mp < n_mpairs && ok; mp += p.runs, ++tile_iter) {
+      const int f0 = (fp * p.fcols + fx) * 128;
+      const bool first = (mp == run);   // first token tile of this feature column: store, do not add
       if (!mbar_wait(&bars->a_full, tile_iter & 1)) { ok = false; break; }
       for (int g = 0; g < G && ok; ++g, ++gg) {
         const int buf = gg & 1;
@@ -556,12 +569,12 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           const int rr0 = g * E + is * 16 + (lane >> 2);
           const int col = f0 + chunk * 64 + b * E + js * 16 + (lane & 3) * 2;
           if (col < p.K) {
-            dr_accumulate(part + (long long)rr0 * p.K + col, d0[0], d0[1], tile_iter == 0);
-            dr_accumulate(part + (long long)(rr0 + 8) * p.K + col, d0[2], d0[3], tile_iter == 0);
+            dr_accumulate(part + (long long)rr0 * p.K + col, d0[0], d0[1], first);
+            dr_accumulate(part + (long long)(rr0 + 8) * p.K + col, d0[2], d0[3], first);
           }
           if (col + 8 < p.K) {
-            dr_accumulate(part + (long long)rr0 * p.K + col + 8, d1[0], d1[1], tile_iter == 0);
-            dr_accumulate(part + (long long)(rr0 + 8) * p.K + col + 8, d1[2], d1[3], tile_iter == 0);
+            dr_accumulate(part + (long long)rr0 * p.K + col + 8, d1[0], d1[1], first);
+            dr_accumulate(part + (long long)(rr0 + 8) * p.K + col + 8, d1[2], d1[3], first);
           }
         }
         __syncwarp();
@@ -607,21 +620,35 @@ __global__ void dr_reduce_kernel(const float* __restrict__ partial, uint16_t* __
   *reinterpret_cast<uint32_t*>(dR + (long long)row * lddr + k) = Elem<DT>::pack(acc.x * scale, acc.y * scale);
 }
 
-// Number of CTA pairs that share one 128-feature column of dA (each pair walks every runs-th
-// 256-token tile).  Picks the count that minimises (waves of pairs over the SM pairs) x (tiles per
-// pair); ties go to the smaller count, which needs less workspace.
-int dadr_default_runs(int M, int K, int num_sms) {
+// Grid of the dA+dR kernel.  fpass: the 128-feature columns can be walked in several passes, so that
+// fewer B column slabs (N x 128 x 2 bytes each) are in use at a time; measured at N = 14336, K = 4096
+// it changes the DRAM traffic but not the time (the kernel is not DRAM-bound), so the default is one
+// pass, which also needs the fewest partial dR buffers.  runs: the number of CTA pairs that share
+// one feature column (each pair walks every runs-th 256-token tile); picks the count that minimises
+// (waves of pairs over the SM pairs) x (tiles per pair); ties go to the smaller count, which needs
+// less workspace.  cfg (or null): {runs, fpass}, 0 = default.
+void dadr_plan_grid(int M, int N, int K, int num_sms, const int* cfg, int* runs_out, int* fpass_out) {
   const int n_ft = (K + 127) / 128;
   const int n_mp = (M + 255) / 256;
-  const int slots = num_sms / 2 > 0 ? num_sms / 2 : 1;
-  int best = 1;
-  long long best_cost = -1;
-  for (int r = 1; r <= n_mp && r <= 32; ++r) {
-    const long long waves = ((long long)n_ft * r + slots - 1) / slots;
-    const long long cost = waves * ((n_mp + r - 1) / r);
-    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = r; }
+  int fpass = (cfg && cfg[1] > 0) ? cfg[1] : 1;
+  if (fpass > n_ft) fpass = n_ft;
+  if (fpass < 1) fpass = 1;
+  const int fcols = (n_ft + fpass - 1) / fpass;
+  int runs = (cfg && cfg[0] > 0) ? cfg[0] : 0;
+  if (runs <= 0) {
+    const int slots = num_sms / 2 > 0 ? num_sms / 2 : 1;
+    long long best_cost = -1;
+    runs = 1;
+    for (int r = 1; r <= n_mp && r <= 32; ++r) {
+      const long long waves = ((long long)fcols * r + slots - 1) / slots;
+      const long long cost = waves * ((n_mp + r - 1) / r);
+      if (best_cost < 0 || cost < best_cost) { best_cost = cost; runs = r; }
+    }
   }
-  return best;
+  if (runs > n_mp) runs = n_mp;
+  if (runs < 1) runs = 1;
+  *runs_out = runs;
+  *fpass_out = fpass;
 }
 
 template <int E>
@@ -645,6 +672,9 @@ int launch_bwd_dadr(const DadrArgs& a) {
   p.n_mtiles = (a.M + 127) / 128;
   p.runs = a.runs < 1 ? 1 : a.runs;
   if (p.runs > (p.n_mtiles + 1) / 2) p.runs = (p.n_mtiles + 1) / 2;
+  const int n_ft = (a.K + 127) / 128;
+  p.fpass = a.fpass < 1 ? 1 : (a.fpass > n_ft ? n_ft : a.fpass);
+  p.fcols = (n_ft + p.fpass - 1) / p.fpass;
   p.scale = a.scale;
   p.dA = a.dA; p.ldda = a.ldda; p.partial = a.partial; p.err = a.err;
   int smem_bytes = 0;
@@ -669,7 +699,7 @@ int launch_bwd_dadr(const DadrArgs& a) {
 #undef PRISM_PICK
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return fail(PRISM_ERR_CUDA, "bwd_dadr: cannot set %d B of shared memory: %s", smem_bytes, cudaGetErrorString(e));
-  dim3 grid(2 * ((a.K + 127) / 128), p.runs, 1);   // x: the two CTAs of a pair
+  dim3 grid(2 * p.fcols, p.runs, 1);   // x: the two CTAs of a pair
   kern<<<grid, dadr::kThreads, smem_bytes, a.stream>>>(tmA, tmRr, tmRd, tmdC, tmB, p);
   if ((rc = check_launch("prism_bwd_dadr"))) return rc;
 

@@ -161,44 +161,11 @@ __device__ __forceinline__ void tma_store_wait_all() {
 // ----------------------------------------------------------------------------
 // tcgen05: TMEM allocation, MMA, commit, loads
 // ----------------------------------------------------------------------------
-// Must be executed by one full warp; the TMEM base address lands in *dst_smem.
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                   smem_u32(dst_smem)),
-               "r"(ncols)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
-               : "memory");
-}
 __device__ __forceinline__ void tc_fence_before_sync() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
 __device__ __forceinline__ void tc_fence_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-// D[tmem] (+)= A[smem desc] * B[smem desc]; issued by ONE thread.
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                         uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-      "}\n"
-      :
-      : "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// mbarrier arrives (count 1) once every tcgen05.mma issued so far by this thread is done.
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   smem_u32(bar))
-               : "memory");
 }
 
 // TMEM -> registers: each thread of the warp reads its own lane (row), N consecutive
@@ -309,19 +276,6 @@ __device__ __forceinline__ void tmem_relinquish_pair() {
 __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
-// Issued by ONE thread of the leader CTA (rank 0); M of the instruction descriptor is 256.
-__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                              uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
-      "}\n"
-      :
-      : "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
 // Same with each descriptor given as (low word, high word).  The start address (>> 4) sits in bits
 // [0,14) of the low word, so an issuer steps through a tile with one 32-bit add per operand; the
 // single issuing thread is latency-bound, every instruction saved per MMA shows in the MMA rate.
@@ -338,19 +292,6 @@ __device__ __forceinline__ void umma_f16_pair_lh(uint32_t d_tmem, uint32_t a_lo,
       "}\n"
       :
       : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Same, with the A operand read from TMEM (lane = row, each 32-bit column = two K elements).
-__device__ __forceinline__ void umma_f16_pair_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
-                                                 uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t"
-      "}\n"
-      :
-      : "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // A from TMEM, B descriptor as (low word, high word).
@@ -520,16 +461,16 @@ struct Pk<DT_BF16> {
   // fp32 pair -> bf16x2 with integer ops: add half an ulp to the bit patterns and keep the upper
   // halves (round to nearest, ties away from zero).  The cvt.rn.bf16x2.f32 instruction runs on the
   // 16-lane/clk special-function pipe (measured: as expensive as a tanh), these three ALU ops do not.
+  __device__ __forceinline__ static uint32_t cvt(float lo, float hi) {
+    const uint32_t ulo = __float_as_uint(lo) + 0x8000u;
+    const uint32_t uhi = __float_as_uint(hi) + 0x8000u;
+    return __byte_perm(ulo, uhi, 0x7632);
+  }
   // The single-instruction conversion (special-function pipe): for code whose ALU pipe is the busier one.
   __device__ __forceinline__ static uint32_t cvt_hw(float lo, float hi) {
     uint32_t d;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
     return d;
-  }
-  __device__ __forceinline__ static uint32_t cvt(float lo, float hi) {
-    const uint32_t ulo = __float_as_uint(lo) + 0x8000u;
-    const uint32_t uhi = __float_as_uint(hi) + 0x8000u;
-    return __byte_perm(ulo, uhi, 0x7632);
   }
   __device__ __forceinline__ static uint32_t mul(uint32_t a, uint32_t b) {
     uint32_t d;
@@ -553,59 +494,6 @@ template <int DT>
 __device__ __forceinline__ uint32_t silu_pair(float s0, float s1) {
   const uint32_t hs = Pk<DT>::mul(Pk<DT>::cvt(s0, s1), Pk<DT>::kHalf);
   return Pk<DT>::fma(hs, Pk<DT>::tanh(hs), hs);
-}
-
-// ----------------------------------------------------------------------------
-// The gate producer step shared by the forward and dB kernels: 32 consecutive
-// columns of one row.  s[] holds S = (A . blockdiag(R_g)^T)[row, cols] in fp32
-// (read from TMEM); the matching 16-bit A values sit in the swizzled tile in
-// shared memory at 16-byte chunks chunk0..chunk0+3 of `row`; H = A * silu(S)
-// (or H = S in plain mode) is written over them in place.
-// ----------------------------------------------------------------------------
-template <int DT, int GATE>
-__device__ __forceinline__ void gate_h_32cols(uint8_t* tile, uint32_t row, uint32_t chunk0,
-                                              const uint32_t (&s)[32], const uint4 (&av)[4]) {
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    uint32_t aw[4] = {av[j].x, av[j].y, av[j].z, av[j].w};
-    uint32_t ow[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float s0 = __uint_as_float(s[j * 8 + e * 2]);
-      const float s1 = __uint_as_float(s[j * 8 + e * 2 + 1]);
-#if PRISM_GATE_PACKED
-      if (GATE == GATE_SILU) {
-        ow[e] = Pk<DT>::mul(aw[e], silu_pair<DT>(s0, s1));
-      } else {
-        ow[e] = Pk<DT>::cvt(s0, s1);
-      }
-#else
-      float h0, h1;
-      if (GATE == GATE_SILU) {
-        const float2 a2 = Elem<DT>::unpack(aw[e]);
-        h0 = a2.x * (s0 * sigmoid_fast(s0));
-        h1 = a2.y * (s1 * sigmoid_fast(s1));
-      } else {
-        h0 = s0;
-        h1 = s1;
-      }
-      ow[e] = Elem<DT>::pack(h0, h1);
-#endif
-    }
-    *reinterpret_cast<uint4*>(tile + sw128_offset(row, chunk0 + j)) =
-        make_uint4(ow[0], ow[1], ow[2], ow[3]);
-  }
-}
-template <int GATE>
-__device__ __forceinline__ void load_a_32cols(const uint8_t* tile, uint32_t row, uint32_t chunk0,
-                                              uint4 (&av)[4]) {
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    if (GATE == GATE_SILU)
-      av[j] = *reinterpret_cast<const uint4*>(tile + sw128_offset(row, chunk0 + j));
-    else
-      av[j] = make_uint4(0, 0, 0, 0);
-  }
 }
 
 // ----------------------------------------------------------------------------
@@ -648,22 +536,6 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[
   }
 }
 
-// fp16 operands with fp16 accumulation: the accumulator comes out as packed pairs, ready for the
-// packed gate math without an f32 -> f16 conversion (special-function pipe).  The reference's own
-// fp16 kernels accumulate the rotation in fp16 as well (cute_prism_dtype.hpp:55-66).
-__device__ __forceinline__ void mma_m16n8k16_f16acc(uint32_t (&d)[2], const uint32_t (&a)[4], uint32_t b0,
-                                                    uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f16.f16.f16.f16 {%0, %1}, {%2, %3, %4, %5}, {%6, %7}, {%0, %1};"
-      : "+r"(d[0]), "+r"(d[1])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// silu of a packed pair: with hs = s/2, silu(s) = hs + hs*tanh(hs)
-template <int DT>
-__device__ __forceinline__ uint32_t silu_packed(uint32_t sp) {
-  const uint32_t hs = Pk<DT>::mul(sp, Pk<DT>::kHalf);
-  return Pk<DT>::fma(hs, Pk<DT>::tanh(hs), hs);
-}
 
 // H for one pair of elements from fp32 S and packed 16-bit A: A*silu(S), or S in plain mode.
 template <int DT, int GATE>
@@ -678,101 +550,6 @@ __device__ __forceinline__ uint32_t gate_pair(uint32_t a2, float s0, float s1) {
   }
   return Elem<DT>::pack(s0, s1);
 #endif
-}
-
-// One warp turns its 16 rows of a [rows x 64] swizzled A tile into H in place.
-//   tile   : shared-memory address of the A tile (1024-byte aligned), r0 = first of the warp's 16 rows
-//   rtile  : shared-memory address of the R_g tile [E x 64] of the same 64 columns
-// Per rotation block: A fragments by ldmatrix, S by mma.sync against R fragments; an A fragment
-// and the S accumulators of the same 16 columns hold the same (row, column) elements in the same
-// lanes, so the gate is elementwise on registers and H goes back with stmatrix to where A came from.
-// h_tmem = 0: H goes back into the A tile (stmatrix); otherwise H is written to TMEM at h_tmem
-// (lane field = r0) as the A operand of the dense tcgen05.mma, 8 columns per 16 K elements.
-// The 64 columns are four 16-wide pieces; PP of them are processed together, phase by phase (all
-// loads, all MMAs, all gate math, all stores), so that a warp has PP independent dependency chains
-// in flight: with one chain per warp the gate warps are latency-bound.
-template <int DT, int GATE, int E, int PP = 4>
-__device__ __forceinline__ void rotate_gate_rows16(uint32_t tile, uint32_t rtile, uint32_t r0, int lane,
-                                                   uint32_t h_tmem = 0) {
-  constexpr int KS = E / 16;           // 16-wide k-steps (= 16-column output pieces) per rotation block
-  static_assert(PP == 2 || PP == 4, "pieces per pass");
-  static_assert(PP % KS == 0 || KS % PP == 0, "a pass must not straddle rotation blocks unevenly");
-  const uint32_t mat = lane >> 3, l8 = lane & 7;
-  const uint32_t a_row = r0 + l8 + (mat & 1) * 8;   // A operand: matrices (r-lo,k-lo) (r-hi,k-lo) (r-lo,k-hi) (r-hi,k-hi)
-  const uint32_t r_row = l8 + (mat >> 1) * 8;       // B operand: matrices (n-lo,k-lo) (n-lo,k-hi) (n-hi,k-lo) (n-hi,k-hi)
-#pragma unroll
-  for (int pass = 0; pass < 4 / PP; ++pass) {
-    // A fragments of every 16-wide piece that this pass reads: the pieces of the blocks it covers
-    constexpr int NA = (PP > KS) ? PP : KS;          // pieces of A needed (whole rotation blocks)
-    const int pa0 = (pass * PP / NA) * NA;           // first A piece (block aligned)
-    uint32_t af[NA][4];
-#pragma unroll
-    for (int i = 0; i < NA; ++i)
-      ldmatrix_x4(tile + sw128_offset(a_row, (pa0 + i) * 2 + (mat >> 1)), af[i]);
-    float c[PP][2][4];
-    uint32_t ch[PP][2][2];
-#pragma unroll
-    for (int i = 0; i < PP; ++i) {
-#pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        c[i][t][0] = c[i][t][1] = c[i][t][2] = c[i][t][3] = 0.f;
-        ch[i][t][0] = ch[i][t][1] = 0u;
-      }
-    }
-#pragma unroll
-    for (int ks = 0; ks < KS; ++ks) {
-      uint32_t rf[PP][4];
-#pragma unroll
-      for (int i = 0; i < PP; ++i) {
-        const int pc = pass * PP + i;                // output piece: block b, 16-column part np
-        const int b = pc / KS, np = pc % KS;
-        ldmatrix_x4(rtile + sw128_offset(np * 16 + r_row, b * (E / 8) + ks * 2 + (mat & 1)), rf[i]);
-      }
-#pragma unroll
-      for (int i = 0; i < PP; ++i) {
-        const int pc = pass * PP + i;
-        const int b = pc / KS;
-        const uint32_t (&a)[4] = af[b * KS + ks - pa0];
-        if (DT == DT_F16) {
-          mma_m16n8k16_f16acc(ch[i][0], a, rf[i][0], rf[i][1]);
-          mma_m16n8k16_f16acc(ch[i][1], a, rf[i][2], rf[i][3]);
-        } else {
-          mma_m16n8k16<DT>(c[i][0], a, rf[i][0], rf[i][1]);
-          mma_m16n8k16<DT>(c[i][1], a, rf[i][2], rf[i][3]);
-        }
-      }
-    }
-    uint32_t h[PP][4];
-#pragma unroll
-    for (int i = 0; i < PP; ++i) {
-      const int pc = pass * PP + i;
-      const uint32_t (&a)[4] = af[pc - pa0];         // the A values of this output piece's columns
-      if (DT == DT_F16) {
-        if (GATE == GATE_SILU) {
-          h[i][0] = Pk<DT>::mul(a[0], silu_packed<DT>(ch[i][0][0]));
-          h[i][1] = Pk<DT>::mul(a[1], silu_packed<DT>(ch[i][0][1]));
-          h[i][2] = Pk<DT>::mul(a[2], silu_packed<DT>(ch[i][1][0]));
-          h[i][3] = Pk<DT>::mul(a[3], silu_packed<DT>(ch[i][1][1]));
-        } else {
-          h[i][0] = ch[i][0][0]; h[i][1] = ch[i][0][1]; h[i][2] = ch[i][1][0]; h[i][3] = ch[i][1][1];
-        }
-      } else {
-        h[i][0] = gate_pair<DT, GATE>(a[0], c[i][0][0], c[i][0][1]);
-        h[i][1] = gate_pair<DT, GATE>(a[1], c[i][0][2], c[i][0][3]);
-        h[i][2] = gate_pair<DT, GATE>(a[2], c[i][1][0], c[i][1][1]);
-        h[i][3] = gate_pair<DT, GATE>(a[3], c[i][1][2], c[i][1][3]);
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < PP; ++i) {
-      const int pc = pass * PP + i;
-      if (h_tmem != 0) {
-        tmem_st_frag16x16(h_tmem + pc * 8, h[i]);
-      } else {
-        stmatrix_x4(tile + sw128_offset(a_row, pc * 2 + (mat >> 1)), h[i]);
-      }
-    }
-  }
 }
 
 // TMEM -> registers in the mma.sync accumulator layout: 16 lanes x 16 columns; thread t gets

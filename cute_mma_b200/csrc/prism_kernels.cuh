@@ -60,13 +60,15 @@ struct DadrArgs {
   int dtype, gate;
   float scale;
   long long lddc, lda, ldb, ldr, ldda, lddr;
-  int runs;           // CTAs per 128-feature column; each owns one fp32 partial dR buffer
+  int runs;           // CTA pairs per 128-feature column; each CTA owns one fp32 partial dR buffer
+  int fpass;          // feature passes (see dadr_plan_grid)
   float* partial;     // [runs][(N/gs)*E][K]
   int num_sms;
   int* err;
   cudaStream_t stream;
 };
 int launch_bwd_dadr(const DadrArgs& a);
-int dadr_default_runs(int M, int K, int num_sms);
+// grid of the dA+dR kernel: CTA pairs per feature column and feature passes; cfg = {runs, fpass} or null
+void dadr_plan_grid(int M, int N, int K, int num_sms, const int* cfg, int* runs_out, int* fpass_out);
 
 }  // namespace prism
