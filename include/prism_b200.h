@@ -76,10 +76,12 @@ int prism_fwd_noalloc(const void* A, const void* B, const void* R, const void* b
                       const int* cfg, int* device_status, void* stream);
 
 /* Input and rotation gradients: dA [M,K] and dR [(N/group_size)*reconn_sz, K], both scaled by
- * dc_scale.  cfg (2 ints, 0 = default): {runs, fpass} -- the number of CTA pairs that share one 128-feature column of
- * dA; each CTA accumulates dR into its own fp32 buffer in the workspace in a fixed order and a
- * second kernel adds the buffers in a fixed order: dR is bit-identical from run to run.  The
- * workspace also holds the kernel's copy of R (widened for reconn_sz = 8, halved in the gated mode). */
+ * dc_scale.  cfg (2 ints, 0 = default): {runs, fpass} -- runs: the number of CTA pairs that share
+ * one 128-feature column of dA (each walks every runs-th 256-token tile); fpass: the number of
+ * passes in which the feature columns are walked.  Each CTA accumulates dR into its own fp32 buffer
+ * in the workspace in a fixed order and a second kernel adds the buffers in a fixed order: dR is
+ * bit-identical from run to run.  The workspace also holds the kernel's copy of R (widened for
+ * reconn_sz = 8, halved in the gated mode). */
 int prism_bwd_dadr(const void* dC, const void* A, const void* B, const void* R, void* dA, void* dR,
                    int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
                    float dc_scale, long long lddc, long long lda, long long ldb, long long ldr,
