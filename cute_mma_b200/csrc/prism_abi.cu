@@ -130,9 +130,10 @@ extern "C" size_t prism_workspace_bytes(int kind, int M, int N, int K, int gs, i
   if (kind == PRISM_KIND_BWD_DADR) {
     const int E = effective_block(rs);
     if (E == 0) return bytes;
-    int runs = 1, fpass = 1;
-    dadr_plan_grid(M, N, K, num_sms(), cfg, &runs, &fpass);
-    bytes += align256((size_t)2 * runs * G * E * (size_t)K * 4);   // one buffer per CTA of every pair
+    DadrGrid gr;
+    dadr_plan_grid(M, K, num_sms(), cfg, &gr);
+    bytes += align256((size_t)2 * gr.runs * G * E * (size_t)K * 4);                 // one buffer per CTA of every main pair
+    bytes += align256((size_t)2 * gr.n_extra * gr.slots * G * E * (size_t)128 * 4); // slabs of the extra pairs' CTAs
     return bytes;
   }
   return bytes;
@@ -278,8 +279,10 @@ extern "C" int prism_bwd_dadr(const void* dC, const void* A, const void* B, cons
   }
   wp += align256((size_t)(N / gs) * a.E * K * 2);
   a.num_sms = num_sms();
-  dadr_plan_grid(M, N, K, a.num_sms, cfg, &a.runs, &a.fpass);
+  dadr_plan_grid(M, K, a.num_sms, cfg, &a.grid);
   a.partial = reinterpret_cast<float*>(wp);
+  wp += align256((size_t)2 * a.grid.runs * (N / gs) * a.E * (size_t)K * 4);
+  a.partial_x = reinterpret_cast<float*>(wp);
   a.err = reinterpret_cast<int*>(workspace);
   a.stream = s;
   return launch_bwd_dadr(a);

@@ -66,14 +66,18 @@ template <int E> struct Stage {
 struct DadrParams {
   int M, N, K, gs, E, G;
   int n_mtiles, runs;
-  int fpass, fcols;    // feature passes; 128-feature columns per pass (grid.x = 2 * fcols)
+  int n_ft;            // 128-feature columns of dA
+  int n_main;          // main CTA pairs: n_ft * runs, pair = run * n_ft + column
+  int n_extra, steal;  // extra CTA pairs; token tiles each main pair leaves to them (0: none)
+  int slots;           // dR partial slabs per extra CTA (one per main pair it helps)
   int ns, rb;          // stages of the dC/B ring, number of R buffers
   int rr_tile_bytes;   // bytes reserved per rotation R tile [E/2 x 64] (multiple of 1024)
   int rd_tile_bytes;   // bytes reserved per dS.R R tile [E x 64] (multiple of 1024)
   float scale;
   void* dA;
   long long ldda;
-  float* partial;      // [2*runs][G*E][K] fp32: one buffer per CTA of every pair
+  float* partial;      // [2*runs][G*E][K] fp32: one buffer per CTA of every main pair
+  float* partial_x;    // [2*n_extra][slots][G*E][128] fp32: slabs of the extra pairs' CTAs
   int* err;
 };
 
@@ -123,6 +127,53 @@ __device__ __forceinline__ uint32_t gate_bwd_pair(uint32_t a2, uint32_t hs, floa
   return Pk<DT>::fma(q, x, q);
 }
 
+// Work of a CTA pair: a list of tiles [256 tokens x 128 features].  A main pair (column fx, run)
+// walks the token-tile pairs run, run + runs, ... of its column and leaves the last `steal` of them
+// to the extra pairs, which exist when the main pairs do not fill the GPU: extra pair e helps the
+// main pairs [e n_main / n_extra, (e+1) n_main / n_extra), token tile by token tile.  Every CTA
+// adds its dR contributions to memory of its own (a [G*E x K] buffer per main CTA, a [G*E x 128]
+// slab per helped main pair in an extra CTA), first tile stored, later tiles added in order.
+struct DadrUnit {
+  int f0;         // first feature of the tile
+  int mp;         // token-tile pair
+  bool first;     // first tile that touches this dR slab: store, do not add
+  float* part;    // dR slab of this CTA for the tile's column (row 0, feature f0)
+  long long ld;   // its row pitch
+};
+__device__ __forceinline__ int dadr_tiles_of_run(const DadrParams& p, int run) {
+  return ((p.n_mtiles + 1) / 2 - run + p.runs - 1) / p.runs;
+}
+__device__ __forceinline__ int dadr_num_units(const DadrParams& p, int pidx) {
+  if (pidx < p.n_main) return dadr_tiles_of_run(p, pidx / p.n_ft) - p.steal;
+  const int e = pidx - p.n_main;
+  return ((e + 1) * p.n_main / p.n_extra - e * p.n_main / p.n_extra) * p.steal;
+}
+__device__ __forceinline__ DadrUnit dadr_unit(const DadrParams& p, int pidx, int rank, int k) {
+  DadrUnit u;
+  const long long GE = (long long)p.G * p.E;
+  if (pidx < p.n_main) {
+    const int fx = pidx % p.n_ft, run = pidx / p.n_ft;
+    u.f0 = fx * 128;
+    u.mp = run + k * p.runs;
+    u.first = (k == 0);
+    u.part = p.partial + (long long)(run * 2 + rank) * GE * p.K + u.f0;
+    u.ld = p.K;
+  } else {
+    const int e = pidx - p.n_main;
+    const int m_lo = e * p.n_main / p.n_extra;
+    const int cnt = (e + 1) * p.n_main / p.n_extra - m_lo;
+    const int j = k / cnt, mi = k - j * cnt;      // token tile by token tile over the helped pairs
+    const int m = m_lo + mi;
+    const int fx = m % p.n_ft, run = m / p.n_ft;
+    u.f0 = fx * 128;
+    u.mp = run + (dadr_tiles_of_run(p, run) - p.steal + j) * p.runs;
+    u.first = (j == 0);
+    u.part = p.partial_x + ((long long)(e * 2 + rank) * p.slots + mi) * GE * 128;
+    u.ld = 128;
+  }
+  return u;
+}
+
 template <int DT, int GATE, int E>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(dadr::kThreads, 1)
 prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmRr,
@@ -149,19 +200,12 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();   // 0 = leader (issues the MMAs), 1 = peer
-  // The pair owns the 128-feature columns fx, fx + fcols, ... (one per feature pass) and in each of
-  // them the token-tile pairs run, run + runs, ...  Only fcols columns of B are in use at a time:
-  // with all of B (N x K) in flight, L2 could not hold it next to the dC rows.
-  const int fx = blockIdx.x >> 1;
-  const int run = blockIdx.y;
-  const int n_mpairs = (p.n_mtiles + 1) / 2;
-  const int n_ft = (p.K + 127) / 128;
-  const int my_passes = (n_ft - fx + p.fcols - 1) / p.fcols;   // feature columns of this pair
+  const int pidx = blockIdx.x >> 1;          // CTA pair: main pairs first, then the extra pairs
   const int G = p.G;
   const int nstg = (p.gs + St::kOut - 1) / St::kOut;  // stages per group
   const bool is_gate = warp >= kGateWarp0 && warp < kGateWarp0 + kNumGateWarps;
   const bool is_dr = warp == 2 || warp == 3 || warp == 20 || warp == 21;
-  const int n_units = my_passes * ((n_mpairs - run + p.runs - 1) / p.runs);   // tiles of this CTA pair
+  const int n_units = dadr_num_units(p, pidx);                  // tiles of this CTA pair
   const int total = n_units * G;                                // groups it walks
 
   if (threadIdx.x == 0) {
@@ -208,10 +252,10 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       bool ok = true;
       uint32_t tile_iter = 0;
       Ring rr(p.rb), rst(p.ns);
-      for (int fp = 0; fp < my_passes && ok; ++fp)
-      for (int mp = run; mp < n_mpairs && ok; mp += p.runs, ++tile_iter) {
-        const int f0 = (fp * p.fcols + fx) * 128;
-        const int m0 = (mp * 2 + (int)rank) * 128;
+      for (int k = 0; k < n_units && ok; ++k, ++tile_iter) {
+        const DadrUnit u = dadr_unit(p, pidx, (int)rank, k);
+        const int f0 = u.f0;
+        const int m0 = (u.mp * 2 + (int)rank) * 128;
         if (!mbar_wait(&bars->a_empty, (tile_iter & 1) ^ 1)) { ok = false; break; }
         mbar_arrive_expect_tx(&bars->a_full, 2 * kTile);
         tma_load_2d(smemA, &tmA, &bars->a_full, f0, m0);
@@ -405,10 +449,10 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     for (int i = 0; i < 8; ++i) { dacc[i][0] = dacc[i][1] = dacc[i][2] = dacc[i][3] = 0.f; }
     bool ok = true;
     uint32_t tile_iter = 0, gg = 0;
-    for (int fp = 0; fp < my_passes && ok; ++fp)
-    for (int mp = run; mp < n_mpairs && ok; mp += p.runs, ++tile_iter) {
-      const int f0 = (fp * p.fcols + fx) * 128;
-      const int mt = mp * 2 + (int)rank;
+    for (int k = 0; k < n_units && ok; ++k, ++tile_iter) {
+      const DadrUnit u = dadr_unit(p, pidx, (int)rank, k);
+      const int f0 = u.f0;
+      const int mt = u.mp * 2 + (int)rank;
       if (!mbar_wait(&bars->a_full, tile_iter & 1)) { ok = false; break; }
       for (int g = 0; g < G && ok; ++g, ++gg) {
         const uint32_t hb = gg & 1, ph = (gg >> 1) & 1;
@@ -514,14 +558,12 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     constexpr int spb = KS * KS;                 // 16x16 sub-tiles per rotation block
     constexpr int n_sub = (128 / E) * spb;       // sub-tiles of this CTA's 128 features
     const int mat = lane >> 3, l8 = lane & 7;
-    const long long GE = (long long)G * E;
-    float* part = p.partial + (long long)(run * 2 + (int)rank) * GE * p.K;
     bool ok = true;
     uint32_t tile_iter = 0, gg = 0;
-    for (int fp = 0; fp < my_passes && ok; ++fp)
-    for (int mp = run; mp < n_mpairs && ok; mp += p.runs, ++tile_iter) {
-      const int f0 = (fp * p.fcols + fx) * 128;
-      const bool first = (mp == run);   // first token tile of this feature column: store, do not add
+    for (int k = 0; k < n_units && ok; ++k, ++tile_iter) {
+      const DadrUnit tu = dadr_unit(p, pidx, (int)rank, k);
+      const int f0 = tu.f0;
+      const bool first = tu.first;
       if (!mbar_wait(&bars->a_full, tile_iter & 1)) { ok = false; break; }
       for (int g = 0; g < G && ok; ++g, ++gg) {
         const int buf = gg & 1;
@@ -567,14 +609,15 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           // in token-tile order: same-address operations of one thread stay ordered, so the sum is
           // formed in a fixed order (bit-stable) without waiting for a read-modify-write round trip.
           const int rr0 = g * E + is * 16 + (lane >> 2);
-          const int col = f0 + chunk * 64 + b * E + js * 16 + (lane & 3) * 2;
+          const int lc = chunk * 64 + b * E + js * 16 + (lane & 3) * 2;   // column inside the tile's 128
+          const int col = f0 + lc;
           if (col < p.K) {
-            dr_accumulate(part + (long long)rr0 * p.K + col, d0[0], d0[1], first);
-            dr_accumulate(part + (long long)(rr0 + 8) * p.K + col, d0[2], d0[3], first);
+            dr_accumulate(tu.part + (long long)rr0 * tu.ld + lc, d0[0], d0[1], first);
+            dr_accumulate(tu.part + (long long)(rr0 + 8) * tu.ld + lc, d0[2], d0[3], first);
           }
           if (col + 8 < p.K) {
-            dr_accumulate(part + (long long)rr0 * p.K + col + 8, d1[0], d1[1], first);
-            dr_accumulate(part + (long long)(rr0 + 8) * p.K + col + 8, d1[2], d1[3], first);
+            dr_accumulate(tu.part + (long long)rr0 * tu.ld + lc + 8, d1[0], d1[1], first);
+            dr_accumulate(tu.part + (long long)(rr0 + 8) * tu.ld + lc + 8, d1[2], d1[3], first);
           }
         }
         __syncwarp();
@@ -595,12 +638,14 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   if (warp == kWarpMma) tmem_dealloc_pair(tmem_base, 512);
 }
 
-// dR[g*rs + i, k] = cast( scale * sum_run partial[run][g*E + i'][k] ), runs in increasing order.
-// For rs = 8 two neighbouring blocks share one 16-row group of the partial buffer:
-// the block in the upper 8 columns of each 16-column pair sits in rows 8..15.
+// dR[g*rs + i, k] = cast( scale * sum of the CTAs' partial sums ), in a fixed order: the main CTAs'
+// buffers in increasing order, then, for every run, the slabs of the extra pair that helped the
+// main pair (run, column of k).  For rs = 8 two neighbouring blocks share one 16-row group of the
+// partial buffers: the block in the upper 8 columns of each 16-column pair sits in rows 8..15.
 template <int DT>
-__global__ void dr_reduce_kernel(const float* __restrict__ partial, uint16_t* __restrict__ dR, int G,
-                                 int rs, int E, int K, long long lddr, int runs, float scale) {
+__global__ void dr_reduce_kernel(const float* __restrict__ partial, const float* __restrict__ partial_x,
+                                 uint16_t* __restrict__ dR, int G, int rs, int E, int K, long long lddr, int runs,
+                                 int n_ft, int n_main, int n_extra, int steal, int slots, float scale) {
   const long long pair = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long total = (long long)G * rs * K / 2;
   if (pair >= total) return;
@@ -611,44 +656,69 @@ __global__ void dr_reduce_kernel(const float* __restrict__ partial, uint16_t* __
   int ip = i;
   if (rs == 8) ip = i + (((k & 15) >= 8) ? 8 : 0);
   const long long GE = (long long)G * E;
+  const long long prow = (long long)g * E + ip;
   float2 acc = make_float2(0.f, 0.f);
-  for (int r = 0; r < runs; ++r) {
-    const float2 v = *reinterpret_cast<const float2*>(partial + ((long long)r * GE + (long long)g * E + ip) * K + k);
+  for (int r = 0; r < 2 * runs; ++r) {
+    const float2 v = *reinterpret_cast<const float2*>(partial + ((long long)r * GE + prow) * K + k);
     acc.x += v.x;
     acc.y += v.y;
+  }
+  if (steal > 0) {
+    const int fx = k >> 7, kk = k & 127;
+    for (int run = 0; run < runs; ++run) {
+      const int m = run * n_ft + fx;
+      const int e = ((m + 1) * n_extra - 1) / n_main;   // the extra pair that helps main pair m
+      const int mi = m - e * n_main / n_extra;
+      for (int rank = 0; rank < 2; ++rank) {
+        const float2 v = *reinterpret_cast<const float2*>(
+            partial_x + (((long long)(e * 2 + rank) * slots + mi) * GE + prow) * 128 + kk);
+        acc.x += v.x;
+        acc.y += v.y;
+      }
+    }
   }
   *reinterpret_cast<uint32_t*>(dR + (long long)row * lddr + k) = Elem<DT>::pack(acc.x * scale, acc.y * scale);
 }
 
-// Grid of the dA+dR kernel.  fpass: the 128-feature columns can be walked in several passes, so that
-// fewer B column slabs (N x 128 x 2 bytes each) are in use at a time; measured at N = 14336, K = 4096
-// it changes the DRAM traffic but not the time (the kernel is not DRAM-bound), so the default is one
-// pass, which also needs the fewest partial dR buffers.  runs: the number of CTA pairs that share
-// one feature column (each pair walks every runs-th 256-token tile); picks the count that minimises
-// (waves of pairs over the SM pairs) x (tiles per pair); ties go to the smaller count, which needs
-// less workspace.  cfg (or null): {runs, fpass}, 0 = default.
-void dadr_plan_grid(int M, int N, int K, int num_sms, const int* cfg, int* runs_out, int* fpass_out) {
+// Grid of the dA+dR kernel.  runs: the number of main CTA pairs that share one feature column (each
+// walks every runs-th 256-token tile); picks the count that minimises (waves of pairs over the SM
+// pairs) x (tiles per pair); ties go to the smaller count, which needs less workspace.  When the
+// main pairs leave SM pairs idle and have enough tiles each, the idle pairs become extra pairs and
+// every main pair leaves its last `steal` tiles to them (see DadrUnit).
+// cfg (or null): {runs, steal, n_extra}; 0 = default; steal < 0 = no extra pairs.
+void dadr_plan_grid(int M, int K, int num_sms, const int* cfg, DadrGrid* gr) {
   const int n_ft = (K + 127) / 128;
   const int n_mp = (M + 255) / 256;
-  int fpass = (cfg && cfg[1] > 0) ? cfg[1] : 1;
-  if (fpass > n_ft) fpass = n_ft;
-  if (fpass < 1) fpass = 1;
-  const int fcols = (n_ft + fpass - 1) / fpass;
+  const int slots_sm = num_sms / 2 > 0 ? num_sms / 2 : 1;
   int runs = (cfg && cfg[0] > 0) ? cfg[0] : 0;
   if (runs <= 0) {
-    const int slots = num_sms / 2 > 0 ? num_sms / 2 : 1;
     long long best_cost = -1;
     runs = 1;
     for (int r = 1; r <= n_mp && r <= 32; ++r) {
-      const long long waves = ((long long)fcols * r + slots - 1) / slots;
+      const long long waves = ((long long)n_ft * r + slots_sm - 1) / slots_sm;
       const long long cost = waves * ((n_mp + r - 1) / r);
       if (best_cost < 0 || cost < best_cost) { best_cost = cost; runs = r; }
     }
   }
   if (runs > n_mp) runs = n_mp;
   if (runs < 1) runs = 1;
-  *runs_out = runs;
-  *fpass_out = fpass;
+  gr->runs = runs;
+  gr->n_ft = n_ft;
+  gr->n_main = n_ft * runs;
+  gr->n_extra = 0; gr->steal = 0; gr->slots = 0;
+  const int t_min = n_mp / runs, t_max = (n_mp + runs - 1) / runs;   // tiles of the shortest / longest run
+  int steal = cfg ? cfg[1] : 0;
+  int n_extra = (cfg && cfg[2] > 0) ? cfg[2] : (slots_sm - gr->n_main);
+  if (steal < 0 || n_extra < 1) return;
+  if (n_extra > gr->n_main) n_extra = gr->n_main;
+  const int cnt_max = (gr->n_main + n_extra - 1) / n_extra;          // main pairs per extra pair
+  if (steal == 0) {
+    steal = (t_max * n_extra + (gr->n_main + n_extra) / 2) / (gr->n_main + n_extra);
+    while (steal > 0 && cnt_max * steal > t_max - steal) --steal;   // an extra pair must not become the longest
+  }
+  if (steal > t_min - 1) steal = t_min - 1;                           // every main pair keeps a tile
+  if (steal < 1) return;
+  gr->n_extra = n_extra; gr->steal = steal; gr->slots = cnt_max;
 }
 
 template <int E>
@@ -670,11 +740,10 @@ int launch_bwd_dadr(const DadrArgs& a) {
   DadrParams p;
   p.M = a.M; p.N = a.N; p.K = a.K; p.gs = a.gs; p.E = a.E; p.G = a.N / a.gs;
   p.n_mtiles = (a.M + 127) / 128;
-  p.runs = a.runs < 1 ? 1 : a.runs;
-  if (p.runs > (p.n_mtiles + 1) / 2) p.runs = (p.n_mtiles + 1) / 2;
-  const int n_ft = (a.K + 127) / 128;
-  p.fpass = a.fpass < 1 ? 1 : (a.fpass > n_ft ? n_ft : a.fpass);
-  p.fcols = (n_ft + p.fpass - 1) / p.fpass;
+  p.runs = a.grid.runs;
+  p.n_ft = a.grid.n_ft; p.n_main = a.grid.n_main;
+  p.n_extra = a.grid.n_extra; p.steal = a.grid.steal; p.slots = a.grid.slots;
+  p.partial_x = a.partial_x;
   p.scale = a.scale;
   p.dA = a.dA; p.ldda = a.ldda; p.partial = a.partial; p.err = a.err;
   int smem_bytes = 0;
@@ -699,7 +768,7 @@ int launch_bwd_dadr(const DadrArgs& a) {
 #undef PRISM_PICK
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return fail(PRISM_ERR_CUDA, "bwd_dadr: cannot set %d B of shared memory: %s", smem_bytes, cudaGetErrorString(e));
-  dim3 grid(2 * p.fcols, p.runs, 1);   // x: the two CTAs of a pair
+  dim3 grid(2 * (p.n_main + p.n_extra), 1, 1);   // the two CTAs of a pair are neighbours
   kern<<<grid, dadr::kThreads, smem_bytes, a.stream>>>(tmA, tmRr, tmRd, tmdC, tmB, p);
   if ((rc = check_launch("prism_bwd_dadr"))) return rc;
 
@@ -709,9 +778,9 @@ int launch_bwd_dadr(const DadrArgs& a) {
   const int threads = 256;
   const long long blocks = (pairs + threads - 1) / threads;
   if (a.dtype == DT_BF16)
-    dr_reduce_kernel<DT_BF16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, reinterpret_cast<uint16_t*>(a.dR), p.G, a.rs, a.E, a.K, a.lddr, 2 * p.runs, r_scale);
+    dr_reduce_kernel<DT_BF16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, a.partial_x, reinterpret_cast<uint16_t*>(a.dR), p.G, a.rs, a.E, a.K, a.lddr, p.runs, p.n_ft, p.n_main, p.n_extra, p.steal, p.slots, r_scale);
   else
-    dr_reduce_kernel<DT_F16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, reinterpret_cast<uint16_t*>(a.dR), p.G, a.rs, a.E, a.K, a.lddr, 2 * p.runs, r_scale);
+    dr_reduce_kernel<DT_F16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, a.partial_x, reinterpret_cast<uint16_t*>(a.dR), p.G, a.rs, a.E, a.K, a.lddr, p.runs, p.n_ft, p.n_main, p.n_extra, p.steal, p.slots, r_scale);
   return check_launch("prism_bwd_dadr reduce");
 }
 

@@ -49,6 +49,15 @@ struct DbArgs {
 int launch_bwd_db(const DbArgs& a);
 int db_default_splits(int M, int N, int K, int BN, int num_sms);
 
+// grid of the dA+dR kernel (see dadr_plan_grid in prism_bwd_dadr.cu); cfg = {runs, steal, n_extra} or null
+struct DadrGrid {
+  int runs;      // main CTA pairs per 128-feature column
+  int n_ft;      // 128-feature columns
+  int n_main;    // n_ft * runs
+  int n_extra;   // extra CTA pairs that take over the main pairs' last tiles (0: none)
+  int steal;     // tiles every main pair leaves to them
+  int slots;     // dR slabs per extra CTA
+};
 struct DadrArgs {
   const void* dC;     // [M, N]
   const void* A;      // [M, K]
@@ -60,15 +69,14 @@ struct DadrArgs {
   int dtype, gate;
   float scale;
   long long lddc, lda, ldb, ldr, ldda, lddr;
-  int runs;           // CTA pairs per 128-feature column; each CTA owns one fp32 partial dR buffer
-  int fpass;          // feature passes (see dadr_plan_grid)
-  float* partial;     // [runs][(N/gs)*E][K]
+  DadrGrid grid;      // CTA pairs and their tiles
+  float* partial;     // [2*runs][(N/gs)*E][K] fp32: dR buffers of the main pairs' CTAs
+  float* partial_x;   // [2*n_extra][slots][(N/gs)*E][128] fp32: dR slabs of the extra pairs' CTAs
   int num_sms;
   int* err;
   cudaStream_t stream;
 };
 int launch_bwd_dadr(const DadrArgs& a);
-// grid of the dA+dR kernel: CTA pairs per feature column and feature passes; cfg = {runs, fpass} or null
-void dadr_plan_grid(int M, int N, int K, int num_sms, const int* cfg, int* runs_out, int* fpass_out);
+void dadr_plan_grid(int M, int K, int num_sms, const int* cfg, DadrGrid* grid);
 
 }  // namespace prism

@@ -76,9 +76,10 @@ int prism_fwd_noalloc(const void* A, const void* B, const void* R, const void* b
                       const int* cfg, int* device_status, void* stream);
 
 /* Input and rotation gradients: dA [M,K] and dR [(N/group_size)*reconn_sz, K], both scaled by
- * dc_scale.  cfg (2 ints, 0 = default): {runs, fpass} -- runs: the number of CTA pairs that share
- * one 128-feature column of dA (each walks every runs-th 256-token tile); fpass: the number of
- * passes in which the feature columns are walked.  Each CTA accumulates dR into its own fp32 buffer
+ * dc_scale.  cfg (3 ints, 0 = default): {runs, steal, n_extra} -- runs: the number of main CTA
+ * pairs that share one 128-feature column of dA (each walks every runs-th 256-token tile); when
+ * the main pairs leave SMs idle, n_extra extra pairs take over the last `steal` tiles of every
+ * main pair (steal < 0: never).  Each CTA accumulates dR into fp32 memory of its own
  * in the workspace in a fixed order and a second kernel adds the buffers in a fixed order: dR is
  * bit-identical from run to run.  The workspace also holds the kernel's copy of R (widened for
  * reconn_sz = 8, halved in the gated mode). */

@@ -230,7 +230,8 @@ def test_tile_configurations_agree():
         C, _ = cp.forward(A, B, R, gs, rs, activation="silu_gate", tile_cfg=cfg)
         assert O.rel_err(C.float(), ref) < TOL, cfg
     rA, rR, rB = O.prism_backward(dC.float(), A.float(), B.float(), R.float(), gs, rs, "silu_gate")
-    for cfg in ([1], [2], [8], [2, 2], [1, 3], [3, 4]):   # {CTA pairs per feature column, feature passes}
+    # {main CTA pairs per feature column, token tiles left to extra pairs (-1: none), extra pairs}
+    for cfg in ([1, -1], [2, -1], [8, -1], [1, 1, 3], [1, 2, 1], [2, 1, 0], [1, 3, 4]):
         dA, dR = F._backward_dadr(dC, A, B, R, gs, rs, 1, tile_cfg=cfg)
         assert O.rel_err(dA.float(), rA) < TOL and O.rel_err(dR.float(), rR) < TOL, cfg
     for cfg in ([256, 1], [128, 2], [64, 8]):
