@@ -62,3 +62,10 @@ def test_workspace_sizes(built_lib):
     # dA+dR: the kernel's (halved) copy of R, then 6 partial buffers for 3 CTA pairs per feature column
     cfg = (ctypes.c_int * 8)(3, 0, 0, 0, 0, 0, 0, 0)
     assert L.prism_workspace_bytes(1, 1024, 1024, 256, 256, 16, 1, cfg) == hdr + 4 * 16 * 256 * 2 + 2 * 3 * 4 * 16 * 256 * 4
+    # benchmark shape (148 SMs assumed without a GPU): 32 feature columns x 2 runs = 64 main CTA pairs,
+    # 10 extra pairs that each help up to 7 main pairs -> 20 CTAs x 7 slabs of [G*E x 128] fp32
+    G, E, K = 56, 16, 4096
+    want = hdr + G * E * K * 2 + 2 * 2 * G * E * K * 4 + 2 * 10 * 7 * G * E * 128 * 4
+    assert L.prism_workspace_bytes(1, 16384, 14336, K, 256, 16, 1, None) == want
+    cfg = (ctypes.c_int * 8)(2, -1, 0, 0, 0, 0, 0, 0)   # no extra pairs
+    assert L.prism_workspace_bytes(1, 16384, 14336, K, 256, 16, 1, cfg) == hdr + G * E * K * 2 + 2 * 2 * G * E * K * 4
