@@ -123,8 +123,10 @@ extern "C" size_t prism_workspace_bytes(int kind, int M, int N, int K, int gs, i
   if (kind == PRISM_KIND_BWD_DB) {
     const int bn = (cfg && cfg[0] > 0) ? cfg[0] : default_bn(gs);
     if (bn <= 0) return bytes;
-    const int splits = (cfg && cfg[1] > 0) ? cfg[1] : db_default_splits(M, N, K, bn, num_sms());
-    if (splits > 1) bytes += align256((size_t)splits * N * K * 4);
+    DbPlan pl;
+    db_plan(M, N, K, bn, num_sms(), cfg, &pl);
+    if (pl.splits > 1) bytes += align256((size_t)pl.splits * N * K * 4);
+    else if (pl.tail_rows > 0) bytes += align256((size_t)pl.tail_splits * pl.tail_rows * bn * K * 4);
     return bytes;
   }
   if (kind == PRISM_KIND_BWD_DADR) {
@@ -233,8 +235,8 @@ extern "C" int prism_bwd_db(const void* dC, const void* A, const void* R, void* 
   if (a.BN % 16 != 0 || a.BN > 256 || gs % a.BN != 0)
     return fail(PRISM_ERR_BAD_ARG, "%s: tile BN=%d must be a multiple of 16, <= 256 and divide group_size=%d", fn, a.BN, gs);
   a.num_sms = num_sms();
-  a.splits = (cfg && cfg[1] > 0) ? cfg[1] : db_default_splits(M, N, K, a.BN, a.num_sms);
-  a.partial = a.splits > 1 ? reinterpret_cast<float*>(wp) : nullptr;
+  db_plan(M, N, K, a.BN, a.num_sms, cfg, &a.plan);
+  a.partial = (a.plan.splits > 1 || a.plan.tail_rows > 0) ? reinterpret_cast<float*>(wp) : nullptr;
   a.err = reinterpret_cast<int*>(workspace);
   a.stream = s;
   return launch_bwd_db(a);

@@ -51,7 +51,9 @@ struct DbParams {
   float scale;
   void* dB;
   long long lddb;
-  float* partial;     // [splits][N][K] when splits > 1
+  float* partial;     // [splits][part_rows][K] when splits > 1
+  int nt0;            // first n-tile of this launch (blockIdx.y counts from it)
+  int part_rows;      // output rows covered by the partial buffer, starting at row nt0 * BN
   int* err;
 };
 
@@ -84,7 +86,7 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();   // 0 = leader (issues the MMAs), 1 = peer
   const int f0 = blockIdx.x * 128;           // first of this CTA's 128 features (column of A / dB)
-  const int nt = blockIdx.y;
+  const int nt = blockIdx.y + p.nt0;
   const int n0 = nt * p.BN;                  // first output (row of dB)
   const int g = nt / p.ntiles_per_group;
   const int split = blockIdx.z;
@@ -244,7 +246,7 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tmem_ld_wait();
         if (f < p.K) {
           if (p.splits > 1) {
-            float* dst = p.partial + ((long long)split * p.N + n0 + c0) * p.K + f;
+            float* dst = p.partial + ((long long)split * p.part_rows + (n0 - p.nt0 * p.BN) + c0) * p.K + f;
 #pragma unroll
             for (int j = 0; j < 16; ++j) dst[(long long)j * p.K] = __uint_as_float(v[j]) * p.scale;
           } else {
@@ -288,7 +290,7 @@ __global__ void db_reduce_kernel(const float* __restrict__ partial, uint16_t* __
   *reinterpret_cast<uint32_t*>(dB + (long long)n * lddb + k) = Elem<DT>::pack(acc.x, acc.y);
 }
 
-int db_default_splits(int M, int N, int K, int BN, int num_sms) {
+static int db_default_splits(int M, int N, int K, int BN, int num_sms) {
   const int base = 2 * ((K + 255) / 256) * (N / BN);
   const int tokblocks = (M + 127) / 128;
   if (base >= 2 * num_sms) return 1;
@@ -298,20 +300,41 @@ int db_default_splits(int M, int N, int K, int BN, int num_sms) {
   return s < 1 ? 1 : s;
 }
 
+// Launch plan.  cfg = {BN, splits} or null: splits > 0 splits the token range of every tile, splits < 0
+// never splits.  Default: tiles that fill the GPU at least once are not split; when their count
+// leaves a last wave that is mostly empty, the last n-tile rows go to a second launch whose token
+// range is split so that it fills the GPU too (its partial sums cover those rows only).
+void db_plan(int M, int N, int K, int BN, int num_sms, const int* cfg, DbPlan* pl) {
+  pl->splits = 1; pl->tail_rows = 0; pl->tail_splits = 1;
+  const int user = cfg ? cfg[1] : 0;
+  if (user > 0) { pl->splits = user; return; }
+  if (user < 0 || BN <= 0) return;
+  pl->splits = db_default_splits(M, N, K, BN, num_sms);
+  if (pl->splits != 1) return;
+  const int x_pairs = (K + 255) / 256, rows = N / BN, slots = num_sms / 2 > 0 ? num_sms / 2 : 1;
+  const int tiles = x_pairs * rows, tokblocks = (M + 127) / 128;
+  if (tiles <= slots) return;
+  const int tail = tiles % slots;
+  if (tail == 0 || 2 * tail > slots) return;          // the last wave is full enough
+  const int yb = (tail + x_pairs - 1) / x_pairs;       // n-tile rows that hold the tail
+  int sb = slots / (yb * x_pairs);
+  if (sb > 16) sb = 16;
+  if (sb > tokblocks) sb = tokblocks;
+  if (sb < 2 || yb >= rows) return;
+  pl->tail_rows = yb;
+  pl->tail_splits = sb;
+}
+
 int launch_bwd_db(const DbArgs& a) {
   DbParams p;
   p.M = a.M; p.N = a.N; p.K = a.K; p.gs = a.gs; p.E = a.E; p.BN = a.BN;
   p.ntiles_per_group = a.gs / a.BN;
   p.n_tokblocks = (a.M + 127) / 128;
-  p.splits = a.splits;
-  p.blocks_per_split = (p.n_tokblocks + a.splits - 1) / a.splits;
-  // drop splits that would own no token block
-  p.splits = (p.n_tokblocks + p.blocks_per_split - 1) / p.blocks_per_split;
   p.dc_tiles = (a.BN / 2 + 63) / 64;   // per CTA: half of the tile's dC columns
   p.r_tile_bytes = ((a.E * 128) + 1023) / 1024 * 1024;
   p.scale = a.scale;
   p.dB = a.dB; p.lddb = a.lddb; p.partial = a.partial; p.err = a.err;
-  if (p.splits > 1 && a.partial == nullptr)
+  if ((a.plan.splits > 1 || a.plan.tail_rows > 0) && a.partial == nullptr)
     return fail(PRISM_ERR_WORKSPACE, "bwd_db: split accumulation needs a partial-sum workspace");
 
   const int budget = 227 * 1024 - 1024 - (int)sizeof(DbBarriers) - 256 - 2 * p.r_tile_bytes;
@@ -339,18 +362,34 @@ int launch_bwd_db(const DbArgs& a) {
 #undef PRISM_PICK
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return fail(PRISM_ERR_CUDA, "bwd_db: cannot set %d B of shared memory: %s", smem_bytes, cudaGetErrorString(e));
-  dim3 grid(2 * ((a.K + 255) / 256), a.N / a.BN, p.splits);   // x: CTA pairs of 2 x 128 features
-  kern<<<grid, db::kThreads, smem_bytes, a.stream>>>(tmA, tmR, tmdC, p);
-  if ((rc = check_launch("prism_bwd_db"))) return rc;
-  if (p.splits > 1) {
-    const long long pairs = (long long)a.N * a.K / 2;
-    const int threads = 256;
-    const long long blocks = (pairs + threads - 1) / threads;
-    if (a.dtype == DT_BF16)
-      db_reduce_kernel<DT_BF16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, reinterpret_cast<uint16_t*>(a.dB), a.N, a.K, a.lddb, p.splits);
-    else
-      db_reduce_kernel<DT_F16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, reinterpret_cast<uint16_t*>(a.dB), a.N, a.K, a.lddb, p.splits);
-    if ((rc = check_launch("prism_bwd_db reduce"))) return rc;
+  const int rows = a.N / a.BN;
+  // one launch over the n-tile rows [nt0, nt0 + nrows) with the token range of every tile split `splits` ways
+  auto launch = [&](int nt0, int nrows, int splits) -> int {
+    DbParams q = p;
+    q.nt0 = nt0;
+    q.part_rows = nrows * a.BN;
+    q.blocks_per_split = (p.n_tokblocks + splits - 1) / splits;
+    q.splits = (p.n_tokblocks + q.blocks_per_split - 1) / q.blocks_per_split;   // drop splits that would own no token block
+    dim3 grid(2 * ((a.K + 255) / 256), nrows, q.splits);   // x: CTA pairs of 2 x 128 features
+    kern<<<grid, db::kThreads, smem_bytes, a.stream>>>(tmA, tmR, tmdC, q);
+    int rcl;
+    if ((rcl = check_launch("prism_bwd_db"))) return rcl;
+    if (q.splits > 1) {
+      const long long pairs = (long long)q.part_rows * a.K / 2;
+      const int threads = 256;
+      const long long blocks = (pairs + threads - 1) / threads;
+      uint16_t* out = reinterpret_cast<uint16_t*>(a.dB) + (long long)nt0 * a.BN * a.lddb;
+      if (a.dtype == DT_BF16)
+        db_reduce_kernel<DT_BF16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, out, q.part_rows, a.K, a.lddb, q.splits);
+      else
+        db_reduce_kernel<DT_F16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, out, q.part_rows, a.K, a.lddb, q.splits);
+      if ((rcl = check_launch("prism_bwd_db reduce"))) return rcl;
+    }
+    return PRISM_OK;
+  };
+  if ((rc = launch(0, rows - a.plan.tail_rows, a.plan.splits))) return rc;
+  if (a.plan.tail_rows > 0) {
+    if ((rc = launch(rows - a.plan.tail_rows, a.plan.tail_rows, a.plan.tail_splits))) return rc;
   }
   return PRISM_OK;
 }

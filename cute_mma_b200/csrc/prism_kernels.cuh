@@ -31,6 +31,12 @@ int launch_expand_r8(const void* R, void* R_eff, int G, int K, long long ldr, in
 int launch_prep_r(const void* R, void* R_eff, int G, int rs, int E, int K, long long ldr, float factor, int dtype,
                   cudaStream_t stream);
 
+// launch plan of the dB kernel (see db_plan in prism_bwd_db.cu)
+struct DbPlan {
+  int splits;       // token-range splits of every tile of the main launch
+  int tail_rows;    // n-tile rows handled by a second launch (0: none) ...
+  int tail_splits;  // ... with this many token-range splits
+};
 struct DbArgs {
   const void* dC;     // [M, N]
   const void* A;      // [M, K]
@@ -40,14 +46,15 @@ struct DbArgs {
   int dtype, gate;
   float scale;        // dB = scale * dC^T H
   long long lddc, lda, ldr, lddb;
-  int BN, splits;
-  float* partial;     // [splits][N][K] fp32 scratch when splits > 1
+  int BN;
+  DbPlan plan;        // token-range splits of the main launch and of the tail rows
+  float* partial;     // fp32 scratch of the split launch: [splits][rows it covers][K]
   int num_sms;
   int* err;
   cudaStream_t stream;
 };
 int launch_bwd_db(const DbArgs& a);
-int db_default_splits(int M, int N, int K, int BN, int num_sms);
+void db_plan(int M, int N, int K, int BN, int num_sms, const int* cfg, DbPlan* plan);
 
 // grid of the dA+dR kernel (see dadr_plan_grid in prism_bwd_dadr.cu); cfg = {runs, steal, n_extra} or null
 struct DadrGrid {

@@ -90,8 +90,10 @@ int prism_bwd_dadr(const void* dC, const void* A, const void* B, const void* R, 
                    const int* cfg, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Weight gradient dB [N,K] = dc_scale * dC^T . H (H recomputed from A and R; B is not needed).
- * cfg (2 ints): {BN, splits} -- splits > 1 divides the token range over several CTAs whose fp32
- * partial sums (in the workspace) are added in a fixed order, so the result is deterministic. */
+ * cfg (2 ints, 0 = default): {BN, splits} -- splits > 1 divides the token range of every tile over
+ * several CTA pairs whose fp32 partial sums (in the workspace) are added in a fixed order, so the
+ * result is deterministic; splits < 0 never splits.  By default only the n-tile rows of a mostly
+ * empty last wave are split (in a second launch). */
 int prism_bwd_db(const void* dC, const void* A, const void* R, void* dB,
                  int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
                  float dc_scale, long long lddc, long long lda, long long ldr, long long lddb,

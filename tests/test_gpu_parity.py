@@ -238,3 +238,29 @@ def test_tile_configurations_agree():
         dB = F._backward_db(dC, A, R, gs, rs, 1, tile_cfg=cfg)
         assert O.rel_err(dB.float(), rB) < TOL, cfg
     cp.check_device_status()
+
+
+def test_db_last_wave_split_and_dadr_extra_pairs():
+    """Launch plans that only large problems pick by themselves, forced at a small size: the dB kernel
+    gives the n-tile rows of a mostly empty last wave to a second launch with a split token range
+    (80 tiles of 64 outputs on 74 SM pairs here), the dA+dR kernel lets extra CTA pairs take over the
+    main pairs' last tiles.  Results must match the oracle and repeat bit-exactly."""
+    M, K, N, gs, rs = 512, 512, 2560, 128, 16
+    A, B, R, dC = _inputs(M, K, N, gs, rs, torch.bfloat16, 23)
+    rA, rR, rB = O.prism_backward(dC.float(), A.float(), B.float(), R.float(), gs, rs, "silu_gate")
+    outs = []
+    for cfg in ([64, 0], [64, -1], [64, 0]):
+        dB = F._backward_db(dC, A, R, gs, rs, 1, tile_cfg=cfg)
+        assert O.rel_err(dB.float(), rB) < TOL, cfg
+        outs.append(dB)
+    assert torch.equal(outs[0], outs[2])
+    M2 = 2048
+    A, B, R, dC = _inputs(M2, K, N, gs, rs, torch.bfloat16, 29)
+    rA, rR, rB = O.prism_backward(dC.float(), A.float(), B.float(), R.float(), gs, rs, "silu_gate")
+    outs = []
+    for cfg in ([1, 3, 2], [2, 1, 3], [1, 3, 2]):
+        dA, dR = F._backward_dadr(dC, A, B, R, gs, rs, 1, tile_cfg=cfg)
+        assert O.rel_err(dA.float(), rA) < TOL and O.rel_err(dR.float(), rR) < TOL, cfg
+        outs.append((dA, dR))
+    assert torch.equal(outs[0][0], outs[2][0]) and torch.equal(outs[0][1], outs[2][1])
+    cp.check_device_status()
