@@ -16,7 +16,8 @@ import torch
 from . import _lib
 from ._tile_table import lookup as _tile_lookup
 
-KIND_FWD, KIND_BWD_DADR, KIND_BWD_DB = 0, 1, 2
+KIND_FWD, KIND_BWD_DADR, KIND_BWD_DB, KIND_DBIAS = 0, 1, 2, 3
+DTYPE_F32, DTYPE_SAME = 2, -1
 ACTIVATIONS = (None, "silu_gate")
 _DTYPES = {torch.float16: 0, torch.bfloat16: 1}
 
@@ -31,6 +32,9 @@ def validate_kernel_params(group_size: int, reconn_sz: int) -> None:
         raise ValueError(f"reconn_sz must be a multiple of 8, got {reconn_sz}")
     if group_size % 8 != 0:
         raise ValueError(f"group_size must be a multiple of 8, got {group_size}")
+    if group_size % 16 != 0:
+        # narrower than the reference (multiples of 8): the tcgen05 tiles are 16 wide
+        raise ValueError(f"group_size must be a multiple of 16 for the sm_100a kernels, got {group_size}")
 
 
 def validate_tensor_params(A, B, R, group_size, reconn_sz) -> None:
@@ -64,21 +68,61 @@ def validate_tensor_params(A, B, R, group_size, reconn_sz) -> None:
 
 
 # --------------------------------------------------------------------------- workspace
-class _Workspace(threading.local):
-    """One growing scratch buffer per (thread, device); its first 256 bytes are the status header."""
+class _WorkspacePool:
+    """Scratch buffers for the C ABI, one per (device, CUDA stream); the first 256 bytes are the
+    status header.
+
+    Calls issued on one stream run in order on the GPU, and every kernel rewrites what it later
+    reads from the workspace, so one buffer per stream is enough whatever host thread issues the
+    call (autograd runs the backward on its own threads but on the forward's stream).  Calls on
+    different streams may overlap on the GPU and therefore never share a buffer.  A buffer that has
+    to grow is replaced; the old one stays referenced until its status word has been read
+    (``check_device_status``), so a device-side error recorded in it is not lost, and the caching
+    allocator hands its memory out again in stream order only.
+    """
+
+    _MAX_RETIRED = 4
 
     def __init__(self):
-        self.bufs = {}
+        self._lock = threading.Lock()
+        self._bufs = {}      # (device, stream handle) -> uint8 tensor
+        self._retired = []   # [(device, tensor)] replaced by a larger buffer, status not read yet
 
     def get(self, device: torch.device, nbytes: int) -> torch.Tensor:
-        buf = self.bufs.get(device)
-        if buf is None or buf.numel() < nbytes:
-            buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-            self.bufs[device] = buf
+        stream = torch.cuda.current_stream(device)
+        key = (device, stream.cuda_stream)
+        with self._lock:
+            buf = self._bufs.get(key)
+            if buf is None or buf.numel() < nbytes:
+                if buf is not None:
+                    self._retired.append((device, buf))
+                buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+                self._bufs[key] = buf
+                overflow = self._retired[:-self._MAX_RETIRED] if len(self._retired) > self._MAX_RETIRED else []
+                if overflow:
+                    del self._retired[:len(overflow)]
+            else:
+                overflow = []
+        for dev, old in overflow:   # bound the memory held by retired buffers: read their status now
+            _read_status(dev, old)
         return buf
 
+    def buffers(self, device: torch.device):
+        """Every live or retired buffer of ``device`` (whatever thread or stream created it)."""
+        with self._lock:
+            live = [b for (d, _), b in self._bufs.items() if d == device]
+            retired = [b for d, b in self._retired if d == device]
+            self._retired = [(d, b) for d, b in self._retired if d != device]
+        return live + retired
 
-_workspace = _Workspace()
+
+_workspace = _WorkspacePool()
+
+
+def _read_status(device, buf) -> None:
+    with torch.cuda.device(device):
+        torch.cuda.synchronize(device)
+        _lib.check(_lib.lib().prism_status(ctypes.c_void_p(buf.data_ptr()), _stream_ptr(device)))
 
 
 def _cfg_array(cfg):
@@ -93,13 +137,19 @@ def _stream_ptr(device):
 
 
 def check_device_status(device=None) -> None:
-    """Synchronise and raise if a kernel recorded a device-side error (bounded wait ran out)."""
+    """Synchronise the device and raise if any kernel recorded a device-side error (a bounded wait
+    that ran out) in any workspace of the device, including those used by autograd threads."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    buf = _workspace.bufs.get(device)
-    if buf is None:
-        return
-    with torch.cuda.device(device):
-        _lib.check(_lib.lib().prism_status(ctypes.c_void_p(buf.data_ptr()), _stream_ptr(device)))
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    first = None
+    for buf in _workspace.buffers(device):
+        try:
+            _read_status(device, buf)
+        except _lib.PrismError as e:   # keep polling: every header is read and cleared
+            first = first or e
+    if first is not None:
+        raise first
 
 
 def _gate_code(activation):
@@ -154,11 +204,22 @@ def forward(A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=None, mo
     return C, []
 
 
-def _backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=None):
-    """dB = dc_scale * dC^T . H  through ``prism_bwd_db`` (H recomputed on chip)."""
+def _grad_dtype(out_dtype, in_dtype, name):
+    """(torch dtype, C-ABI code) of a parameter gradient: the inputs' 16-bit type or float32."""
+    if out_dtype is None or out_dtype == in_dtype:
+        return in_dtype, DTYPE_SAME
+    if out_dtype == torch.float32:
+        return torch.float32, DTYPE_F32
+    raise ValueError(f"{name} must be None, the input dtype or torch.float32, got {out_dtype}")
+
+
+def _backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=None, out_dtype=None):
+    """dB = dc_scale * dC^T . H  through ``prism_bwd_db`` (H recomputed on chip); with
+    ``out_dtype=torch.float32`` the kernel's fp32 sums are returned unrounded."""
     M, K = A.shape
     N = dC.shape[1]
-    dB = torch.empty(N, K, dtype=A.dtype, device=A.device)
+    out_dtype, out_code = _grad_dtype(out_dtype, A.dtype, "dB_dtype")
+    dB = torch.empty(N, K, dtype=out_dtype, device=A.device)
     L = _lib.lib()
     cfg = tile_cfg if tile_cfg is not None else _tile_lookup("bwd_db", A.dtype, gate, M, N, K, group_size, reconn_sz)
     cfg_arr = _cfg_array(cfg)
@@ -168,18 +229,20 @@ def _backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=N
         ws = _workspace.get(A.device, need)
         _lib.check(L.prism_bwd_db(
             ctypes.c_void_p(dC.data_ptr()), ctypes.c_void_p(A.data_ptr()), ctypes.c_void_p(R.data_ptr()),
-            ctypes.c_void_p(dB.data_ptr()), M, N, K, group_size, reconn_sz, dt, gate,
+            ctypes.c_void_p(dB.data_ptr()), M, N, K, group_size, reconn_sz, dt, gate, out_code,
             ctypes.c_float(dc_scale), dC.stride(0), A.stride(0), R.stride(0), dB.stride(0),
             cfg_arr, ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(A.device)))
     return dB
 
 
-def _backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=None):
-    """(dA, dR), both scaled by ``dc_scale``, through ``prism_bwd_dadr``."""
+def _backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=None, dR_dtype=None):
+    """(dA, dR), both scaled by ``dc_scale``, through ``prism_bwd_dadr``; with
+    ``dR_dtype=torch.float32`` the fp32 sums of the dR reduction are returned unrounded."""
     M, K = A.shape
     N = B.shape[0]
+    dR_dtype, dr_code = _grad_dtype(dR_dtype, A.dtype, "dR_dtype")
     dA = torch.empty(M, K, dtype=A.dtype, device=A.device)
-    dR = torch.empty_like(R)
+    dR = torch.empty(R.shape, dtype=dR_dtype, device=A.device)
     L = _lib.lib()
     cfg = tile_cfg if tile_cfg is not None else _tile_lookup("bwd_dadr", A.dtype, gate, M, N, K, group_size, reconn_sz)
     cfg_arr = _cfg_array(cfg)
@@ -190,7 +253,7 @@ def _backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_
         _lib.check(L.prism_bwd_dadr(
             ctypes.c_void_p(dC.data_ptr()), ctypes.c_void_p(A.data_ptr()), ctypes.c_void_p(B.data_ptr()),
             ctypes.c_void_p(R.data_ptr()), ctypes.c_void_p(dA.data_ptr()), ctypes.c_void_p(dR.data_ptr()),
-            M, N, K, group_size, reconn_sz, dt, gate, ctypes.c_float(dc_scale),
+            M, N, K, group_size, reconn_sz, dt, gate, dr_code, ctypes.c_float(dc_scale),
             dC.stride(0), A.stride(0), B.stride(0), R.stride(0), dA.stride(0), dR.stride(0),
             cfg_arr, ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(A.device)))
     return dA, dR
@@ -204,6 +267,8 @@ def backward(dC, A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=Non
              tile_cfg_dadr=None, tile_cfg_db=None):
     """Gradients ``(dA, dR, dB, d_internal_bias)``; ``dB`` is None in plain mode and
     ``d_internal_bias`` is always None (internal bias is not part of the accelerated path).
+    ``dR_dtype`` / ``dB_dtype`` = ``torch.float32`` return the kernels' fp32 sums unrounded
+    (reference: src/cute_prism/__init__.py:288-289, 368, 375).
 
     ``dc_scale`` (keyword-only) multiplies dC on the fly, i.e. scales every returned gradient.
     """
@@ -216,10 +281,24 @@ def backward(dC, A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=Non
     N = B.shape[0]
     if dC.shape != (M, N) or dC.dtype != A.dtype or dC.device != A.device or not dC.is_contiguous():
         raise ValueError(f"dC must be a contiguous ({M}, {N}) tensor of the same dtype and device as A")
-    dA, dR = _backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, dc_scale, tile_cfg_dadr)
-    dB = _backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale, tile_cfg_db) if gate else None
-    if dR_dtype is not None and dR_dtype != dR.dtype:
-        dR = dR.to(dR_dtype)
-    if dB is not None and dB_dtype is not None and dB_dtype != dB.dtype:
-        dB = dB.to(dB_dtype)
+    dA, dR = _backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, dc_scale, tile_cfg_dadr, dR_dtype)
+    dB = _backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale, tile_cfg_db, dB_dtype) if gate else None
     return dA, dR, dB, None
+
+
+def bias_grad(dC, out_dtype=None):
+    """dbias [N] = sum of dC [M, N] over the token rows through ``prism_dbias`` (fixed summation
+    order, bit-stable); ``out_dtype``: None (dC's dtype) or torch.float32."""
+    if not dC.is_cuda or dC.dtype not in _DTYPES or dC.dim() != 2 or not dC.is_contiguous():
+        raise ValueError("dC must be a contiguous 2-D float16 / bfloat16 CUDA tensor")
+    M, N = dC.shape
+    out_dtype, out_code = _grad_dtype(out_dtype, dC.dtype, "out_dtype")
+    out = torch.empty(N, dtype=out_dtype, device=dC.device)
+    L = _lib.lib()
+    dt = _DTYPES[dC.dtype]
+    with torch.cuda.device(dC.device):
+        need = L.prism_workspace_bytes(KIND_DBIAS, M, N, 0, 0, 0, dt, None)
+        ws = _workspace.get(dC.device, need)
+        _lib.check(L.prism_dbias(ctypes.c_void_p(dC.data_ptr()), ctypes.c_void_p(out.data_ptr()), M, N, dt, out_code,
+                                 dC.stride(0), ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(dC.device)))
+    return out

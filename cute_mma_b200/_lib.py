@@ -25,9 +25,12 @@ NVCC_FLAGS = [
 
 # every symbol include/prism_b200.h declares
 EXPORTS = [
-    "prism_fwd", "prism_fwd_noalloc", "prism_bwd_dadr", "prism_bwd_db", "prism_workspace_bytes", "prism_status",
+    "prism_fwd", "prism_fwd_noalloc", "prism_bwd_dadr", "prism_bwd_db", "prism_dbias", "prism_workspace_bytes",
+    "prism_status",
     "prism_last_error_string", "prism_abi_version", "prism_launch_count",
 ]
+
+ABI_VERSION = 2
 
 _lock = threading.Lock()
 _lib = None
@@ -85,12 +88,14 @@ def lib() -> ctypes.CDLL:
             L.prism_fwd_noalloc.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, i, ll, ll, ll, ll, ip, vp, vp]
             if hasattr(L, "prism_bwd_dadr"):
                 L.prism_bwd_dadr.restype = i
-                L.prism_bwd_dadr.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, ctypes.c_float,
+                L.prism_bwd_dadr.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, i, ctypes.c_float,
                                              ll, ll, ll, ll, ll, ll, ip, vp, sz, vp]
             if hasattr(L, "prism_bwd_db"):
                 L.prism_bwd_db.restype = i
-                L.prism_bwd_db.argtypes = [vp, vp, vp, vp, i, i, i, i, i, i, i, ctypes.c_float,
+                L.prism_bwd_db.argtypes = [vp, vp, vp, vp, i, i, i, i, i, i, i, i, ctypes.c_float,
                                            ll, ll, ll, ll, ip, vp, sz, vp]
+            L.prism_dbias.restype = i
+            L.prism_dbias.argtypes = [vp, vp, i, i, i, i, ll, vp, sz, vp]
             L.prism_workspace_bytes.restype = sz
             L.prism_workspace_bytes.argtypes = [i, i, i, i, i, i, i, ip]
             L.prism_status.restype = i
@@ -98,6 +103,9 @@ def lib() -> ctypes.CDLL:
             L.prism_last_error_string.restype = ctypes.c_char_p
             L.prism_last_error_string.argtypes = []
             L.prism_abi_version.restype = i
+            if L.prism_abi_version() != ABI_VERSION:
+                raise RuntimeError(f"{LIB_PATH} has ABI version {L.prism_abi_version()}, this package needs "
+                                   f"{ABI_VERSION}: rebuild it (cute_mma_b200._lib.build(force=True))")
             L.prism_launch_count.restype = ll
             _lib = L
         return _lib

@@ -10,7 +10,7 @@ Differences, all on the fast path:
 * the output bias is added in the forward kernel's epilogue instead of a separate op;
 * the backward rescale is passed to the backward kernels as ``dc_scale`` instead of an extra
   pass over dC (the bias gradient, taken after the rescale point, stays unscaled as in the
-  reference);
+  reference) and the bias gradient is a fixed-order column sum kernel of the library;
 * in plain mode a frozen ``weight`` gets no gradient tensor at all; a trainable ``weight``
   in plain mode gets exact zeros, which is the reference's contract
   (src/cute_prism/_module.py:92-104);
@@ -51,7 +51,7 @@ def _(A, B, R, bias, group_size, reconn_sz, activation, bwd_scale):
 @torch.library.custom_op("prism_b200::backward", mutates_args=())
 def _prism_backward_op(dC: torch.Tensor, A: torch.Tensor, B: torch.Tensor, R: torch.Tensor,
                        group_size: int, reconn_sz: int, activation: str, bwd_scale: float,
-                       need_dB: bool) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+                       need_dB: bool, need_dbias: bool) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     dC = dC.contiguous()
     A, B, R = A.contiguous(), B.contiguous(), R.contiguous()
     gate = 1 if activation else 0
@@ -62,12 +62,15 @@ def _prism_backward_op(dC: torch.Tensor, A: torch.Tensor, B: torch.Tensor, R: to
         dB = F._backward_db(dC, A, R, group_size, reconn_sz, gate, bwd_scale)
     else:
         dB = torch.zeros_like(B)  # frozen-B contract of the reference's plain mode
-    return dA, dR, dB
+    # the bias is added after the rescale point: its gradient is the plain column sum of dC
+    dbias = F.bias_grad(dC) if need_dbias else dC.new_empty(0)
+    return dA, dR, dB, dbias
 
 
 @_prism_backward_op.register_fake
-def _(dC, A, B, R, group_size, reconn_sz, activation, bwd_scale, need_dB):
-    return A.new_empty(A.shape), R.new_empty(R.shape), (B.new_empty(B.shape) if need_dB else B.new_empty(0))
+def _(dC, A, B, R, group_size, reconn_sz, activation, bwd_scale, need_dB, need_dbias):
+    return (A.new_empty(A.shape), R.new_empty(R.shape), (B.new_empty(B.shape) if need_dB else B.new_empty(0)),
+            (dC.new_empty(dC.shape[1]) if need_dbias else dC.new_empty(0)))
 
 
 def _setup_context(ctx, inputs, output):
@@ -81,10 +84,10 @@ def _setup_context(ctx, inputs, output):
 def _backward(ctx, dC):
     A, B, R = ctx.saved_tensors
     need_dB = bool(ctx.needs_input_grad[1])
-    dA, dR, dB = _prism_backward_op(dC, A, B, R, ctx.group_size, ctx.reconn_sz, ctx.activation,
-                                    ctx.bwd_scale, need_dB)
-    dbias = dC.sum(dim=0) if (ctx.has_bias and ctx.needs_input_grad[3]) else None
-    return dA, (dB if need_dB else None), dR, dbias, None, None, None, None
+    need_dbias = bool(ctx.has_bias and ctx.needs_input_grad[3])
+    dA, dR, dB, dbias = _prism_backward_op(dC, A, B, R, ctx.group_size, ctx.reconn_sz, ctx.activation,
+                                           ctx.bwd_scale, need_dB, need_dbias)
+    return dA, (dB if need_dB else None), dR, (dbias if need_dbias else None), None, None, None, None
 
 
 _prism_forward_op.register_autograd(_backward, setup_context=_setup_context)
@@ -192,6 +195,14 @@ class PrismLinear(nn.Module):
                 Sp = Sp @ S
         return Rb.permute(0, 2, 1, 3).reshape(n_groups * r, self.in_features).to(out_dtype)
 
+    def reconn_diag_sq_sum(self) -> torch.Tensor:
+        """Sum over all rotation blocks of the squared diagonal entries of R (a scalar tensor):
+        0 for skew-symmetric blocks, about ``n_groups * n_blocks * reconn_sz`` for orthogonal
+        blocks close to the identity (reference: src/cute_prism/_module.py:579-597)."""
+        r = self.reconn_sz
+        R = self._build_R().reshape(self.out_features // self.group_size, r, self.in_features // r, r)
+        return torch.diagonal(R, dim1=1, dim2=3).pow(2).sum()
+
     def load_pretrained_weight(self, weight: torch.Tensor, bias: torch.Tensor | None = None) -> None:
         if weight.shape != self.weight.shape:
             raise ValueError(f"Weight shape mismatch: expected {self.weight.shape}, got {weight.shape}")
@@ -230,3 +241,20 @@ class PrismLinear(nn.Module):
         else:
             parts.append(f"cayley_order={self.cayley_order}")
         return ", ".join(parts)
+
+
+def mup_fix_prism_shapes(model: nn.Module) -> None:
+    """For models set up with the ``mup`` package: give the ``reconn`` parameter of every
+    ``PrismLinear`` a width multiplier of 1, because a rotation block's fan-in is ``reconn_sz``
+    whatever the model width (reference: src/cute_prism/_module.py:806-870).  Call it after
+    ``mup.set_base_shapes`` and before the optimizer is built; needs ``mup`` installed."""
+    from mup.infshape import InfDim, InfShape
+
+    for module in model.modules():
+        if not isinstance(module, PrismLinear):
+            continue
+        p = module.reconn
+        if hasattr(p, "infshape"):
+            dims = list(p.infshape)
+            dims[-1] = InfDim(dims[-1].dim, dims[-1].dim)
+            p.infshape = InfShape(dims)

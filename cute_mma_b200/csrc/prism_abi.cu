@@ -47,6 +47,61 @@ int launch_expand_r8(const void* R, void* R_eff, int G, int K, long long ldr, in
   return launch_prep_r(R, R_eff, G, 8, 16, K, ldr, 1.0f, dtype, stream);
 }
 
+// dbias[n] = sum over token rows of dC[m, n], in a fixed order: a block owns 256 columns and a
+// contiguous range of rows; its 8 warps take rows w, w + 8, ... (16-byte loads, 8 columns per lane)
+// and are added in warp order, then the row ranges are added in range order by the second kernel.
+template <int DT>
+__global__ void dbias_partial_kernel(const uint16_t* __restrict__ dC, float* __restrict__ partial, int M, int N,
+                                     long long lddc, int rows_per_split) {
+  __shared__ float red[8][256];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col0 = blockIdx.x * 256 + lane * 8;
+  const int r_lo = blockIdx.y * rows_per_split;
+  const int r_hi = min(M, r_lo + rows_per_split);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (col0 < N) {
+    for (int r = r_lo + warp; r < r_hi; r += 8) {
+      const uint4 v = *reinterpret_cast<const uint4*>(dC + (long long)r * lddc + col0);
+      const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = Elem<DT>::unpack(w4[e]);
+        acc[2 * e] += f.x;
+        acc[2 * e + 1] += f.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) red[warp][lane * 8 + e] = acc[e];
+  __syncthreads();
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < N) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w][threadIdx.x];
+    partial[(long long)blockIdx.y * N + c] = t;
+  }
+}
+
+template <int DT, bool F32OUT>
+__global__ void dbias_final_kernel(const float* __restrict__ partial, void* __restrict__ out, int N, int splits) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= N) return;
+  float t = 0.f;
+  for (int s = 0; s < splits; ++s) t += partial[(long long)s * N + c];
+  if (F32OUT) reinterpret_cast<float*>(out)[c] = t;
+  else reinterpret_cast<uint16_t*>(out)[c] = (uint16_t)(Elem<DT>::pack(t, 0.f) & 0xffffu);
+}
+
+static int num_sms();
+static int dbias_splits(int M, int N, int sms) {
+  const int strips = (N + 255) / 256;
+  int s = (4 * sms + strips - 1) / strips;
+  if (s > 64) s = 64;
+  if (s > (M + 63) / 64) s = (M + 63) / 64;   // at least 64 rows per block
+  return s < 1 ? 1 : s;
+}
+
 static int num_sms() {
   static int cached[64] = {0};
   int dev = 0;
@@ -92,6 +147,13 @@ static int check_common(const char* fn, int M, int N, int K, int gs, int rs, int
   return PRISM_OK;
 }
 
+// dtype of a gradient output: the inputs' 16-bit type or fp32; returns 1 for fp32, 0 for 16 bit, -1 if invalid
+static int grad_is_f32(int grad_dtype, int dtype) {
+  if (grad_dtype == PRISM_DTYPE_F32) return 1;
+  if (grad_dtype == PRISM_DTYPE_SAME || grad_dtype == dtype) return 0;
+  return -1;
+}
+
 static int check_ptr(const char* fn, const char* name, const void* p, long long ld, int min_ld) {
   if (p == nullptr) return fail(PRISM_ERR_BAD_ARG, "%s: %s is null", fn, name);
   if (reinterpret_cast<uintptr_t>(p) % 16 != 0) return fail(PRISM_ERR_BAD_ARG, "%s: %s must be 16-byte aligned", fn, name);
@@ -104,9 +166,9 @@ static int check_ptr(const char* fn, const char* name, const void* p, long long 
 
 using namespace prism;
 
-extern "C" int prism_abi_version(void) { return 1; }
+extern "C" int prism_abi_version(void) { return 2; }
 
-extern "C" long long prism_launch_count(void) { return launch_counter(); }
+extern "C" long long prism_launch_count(void) { return launch_counter().load(std::memory_order_relaxed); }
 
 extern "C" const char* prism_last_error_string(void) { return last_error_buf(); }
 
@@ -114,6 +176,10 @@ extern "C" size_t prism_workspace_bytes(int kind, int M, int N, int K, int gs, i
                                         const int* cfg) {
   (void)dtype; (void)cfg; (void)M;
   size_t bytes = PRISM_WORKSPACE_HEADER_BYTES;
+  if (kind == PRISM_KIND_DBIAS) {
+    if (N <= 0 || M <= 0) return bytes;
+    return bytes + align256((size_t)dbias_splits(M, N, num_sms()) * N * 4);
+  }
   if (gs <= 0 || rs <= 0 || N <= 0 || K <= 0) return bytes;
   const size_t G = (size_t)(N / gs);
   // copy of R the kernels read: widened for rs = 8 (all kinds), halved for the gated dA+dR kernel
@@ -199,17 +265,20 @@ extern "C" int prism_fwd(const void* A, const void* B, const void* R, const void
 }
 
 extern "C" int prism_bwd_db(const void* dC, const void* A, const void* R, void* dB,
-                            int M, int N, int K, int gs, int rs, int dtype, int gate, float dc_scale,
+                            int M, int N, int K, int gs, int rs, int dtype, int gate, int db_dtype, float dc_scale,
                             long long lddc, long long lda, long long ldr, long long lddb,
                             const int* cfg, void* workspace, size_t workspace_bytes, void* stream) {
   const char* fn = "prism_bwd_db";
   int rc;
   if ((rc = check_common(fn, M, N, K, gs, rs, dtype, gate))) return rc;
+  const int db_f32 = grad_is_f32(db_dtype, dtype);
+  if (db_f32 < 0) return fail(PRISM_ERR_BAD_ARG, "%s: db_dtype must be the input dtype, PRISM_DTYPE_SAME or PRISM_DTYPE_F32", fn);
   if (K % 8 != 0) return fail(PRISM_ERR_BAD_ARG, "%s: K must be a multiple of 8", fn);
   if ((rc = check_ptr(fn, "dB", dB, lddb, K))) return rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (M == 0) {  // no tokens: the gradient is zero
-    cudaError_t e = cudaMemset2DAsync(dB, lddb * 2, 0, (size_t)K * 2, N, s);
+    const size_t es = db_f32 ? 4 : 2;
+    cudaError_t e = cudaMemset2DAsync(dB, lddb * es, 0, (size_t)K * es, N, s);
     return e == cudaSuccess ? PRISM_OK : fail(PRISM_ERR_CUDA, "%s: %s", fn, cudaGetErrorString(e));
   }
   if ((rc = check_ptr(fn, "dC", dC, lddc, N))) return rc;
@@ -222,7 +291,7 @@ extern "C" int prism_bwd_db(const void* dC, const void* A, const void* R, void* 
   DbArgs a;
   a.dC = dC; a.A = A; a.dB = dB;
   a.M = M; a.N = N; a.K = K; a.gs = gs; a.E = effective_block(rs);
-  a.dtype = dtype; a.gate = gate; a.scale = dc_scale;
+  a.dtype = dtype; a.gate = gate; a.scale = dc_scale; a.out_f32 = db_f32;
   a.lddc = lddc; a.lda = lda; a.lddb = lddb;
   a.R_eff = R; a.ldr = ldr;
   uint8_t* wp = reinterpret_cast<uint8_t*>(workspace) + PRISM_WORKSPACE_HEADER_BYTES;
@@ -244,17 +313,20 @@ extern "C" int prism_bwd_db(const void* dC, const void* A, const void* R, void* 
 
 extern "C" int prism_bwd_dadr(const void* dC, const void* A, const void* B, const void* R, void* dA,
                               void* dR, int M, int N, int K, int gs, int rs, int dtype, int gate,
-                              float dc_scale, long long lddc, long long lda, long long ldb,
+                              int dr_dtype, float dc_scale, long long lddc, long long lda, long long ldb,
                               long long ldr, long long ldda, long long lddr, const int* cfg,
                               void* workspace, size_t workspace_bytes, void* stream) {
   const char* fn = "prism_bwd_dadr";
   int rc;
   if ((rc = check_common(fn, M, N, K, gs, rs, dtype, gate))) return rc;
+  const int dr_f32 = grad_is_f32(dr_dtype, dtype);
+  if (dr_f32 < 0) return fail(PRISM_ERR_BAD_ARG, "%s: dr_dtype must be the input dtype, PRISM_DTYPE_SAME or PRISM_DTYPE_F32", fn);
   if (K % 8 != 0) return fail(PRISM_ERR_BAD_ARG, "%s: K must be a multiple of 8", fn);
   if ((rc = check_ptr(fn, "dR", dR, lddr, K))) return rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (M == 0) {  // no tokens: dA is empty and dR is zero
-    cudaError_t e = cudaMemset2DAsync(dR, lddr * 2, 0, (size_t)K * 2, (size_t)(N / gs) * rs, s);
+    const size_t es = dr_f32 ? 4 : 2;
+    cudaError_t e = cudaMemset2DAsync(dR, lddr * es, 0, (size_t)K * es, (size_t)(N / gs) * rs, s);
     return e == cudaSuccess ? PRISM_OK : fail(PRISM_ERR_CUDA, "%s: %s", fn, cudaGetErrorString(e));
   }
   if ((rc = check_ptr(fn, "dC", dC, lddc, N))) return rc;
@@ -269,7 +341,7 @@ extern "C" int prism_bwd_dadr(const void* dC, const void* A, const void* B, cons
   DadrArgs a;
   a.dC = dC; a.A = A; a.B = B; a.dA = dA; a.dR = dR;
   a.M = M; a.N = N; a.K = K; a.gs = gs; a.rs = rs; a.E = effective_block(rs);
-  a.dtype = dtype; a.gate = gate; a.scale = dc_scale;
+  a.dtype = dtype; a.gate = gate; a.scale = dc_scale; a.dr_f32 = dr_f32;
   a.lddc = lddc; a.lda = lda; a.ldb = ldb; a.ldda = ldda; a.lddr = lddr;
   a.R_eff = R; a.ldr = ldr;
   uint8_t* wp = reinterpret_cast<uint8_t*>(workspace) + PRISM_WORKSPACE_HEADER_BYTES;
@@ -288,4 +360,43 @@ extern "C" int prism_bwd_dadr(const void* dC, const void* A, const void* B, cons
   a.err = reinterpret_cast<int*>(workspace);
   a.stream = s;
   return launch_bwd_dadr(a);
+}
+
+extern "C" int prism_dbias(const void* dC, void* dbias, int M, int N, int dtype, int dbias_dtype, long long lddc,
+                           void* workspace, size_t workspace_bytes, void* stream) {
+  const char* fn = "prism_dbias";
+  int rc;
+  if (M < 0 || N <= 0) return fail(PRISM_ERR_BAD_ARG, "%s: bad shape M=%d N=%d", fn, M, N);
+  if (N % 8 != 0) return fail(PRISM_ERR_BAD_ARG, "%s: N must be a multiple of 8", fn);
+  if (dtype != DT_F16 && dtype != DT_BF16) return fail(PRISM_ERR_BAD_ARG, "%s: dtype must be 0 (fp16) or 1 (bf16)", fn);
+  const int out_f32 = grad_is_f32(dbias_dtype, dtype);
+  if (out_f32 < 0) return fail(PRISM_ERR_BAD_ARG, "%s: dbias_dtype must be the input dtype, PRISM_DTYPE_SAME or PRISM_DTYPE_F32", fn);
+  if (dbias == nullptr) return fail(PRISM_ERR_BAD_ARG, "%s: dbias is null", fn);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (M == 0) {
+    cudaError_t e = cudaMemsetAsync(dbias, 0, (size_t)N * (out_f32 ? 4 : 2), s);
+    return e == cudaSuccess ? PRISM_OK : fail(PRISM_ERR_CUDA, "%s: %s", fn, cudaGetErrorString(e));
+  }
+  if ((rc = check_ptr(fn, "dC", dC, lddc, N))) return rc;
+  const size_t need = prism_workspace_bytes(PRISM_KIND_DBIAS, M, N, 0, 0, 0, dtype, nullptr);
+  if (workspace == nullptr || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+    return fail(PRISM_ERR_WORKSPACE, "%s: workspace must be 256-byte aligned and >= %zu bytes (got %zu)", fn, need, workspace_bytes);
+  float* partial = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + PRISM_WORKSPACE_HEADER_BYTES);
+  const int splits = dbias_splits(M, N, num_sms());
+  const int rows_per_split = (M + splits - 1) / splits;
+  const int used = (M + rows_per_split - 1) / rows_per_split;
+  dim3 grid((N + 255) / 256, used);
+  const uint16_t* src = reinterpret_cast<const uint16_t*>(dC);
+  if (dtype == DT_BF16) dbias_partial_kernel<DT_BF16><<<grid, 256, 0, s>>>(src, partial, M, N, lddc, rows_per_split);
+  else dbias_partial_kernel<DT_F16><<<grid, 256, 0, s>>>(src, partial, M, N, lddc, rows_per_split);
+  if ((rc = check_launch("prism_dbias"))) return rc;
+  const int blocks = (N + 255) / 256;
+  if (dtype == DT_BF16) {
+    if (out_f32) dbias_final_kernel<DT_BF16, true><<<blocks, 256, 0, s>>>(partial, dbias, N, used);
+    else dbias_final_kernel<DT_BF16, false><<<blocks, 256, 0, s>>>(partial, dbias, N, used);
+  } else {
+    if (out_f32) dbias_final_kernel<DT_F16, true><<<blocks, 256, 0, s>>>(partial, dbias, N, used);
+    else dbias_final_kernel<DT_F16, false><<<blocks, 256, 0, s>>>(partial, dbias, N, used);
+  }
+  return check_launch("prism_dbias reduce");
 }

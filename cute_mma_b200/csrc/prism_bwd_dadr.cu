@@ -33,10 +33,6 @@
 #include "prism_host.cuh"
 #include "prism_kernels.cuh"
 
-#ifndef PRISM_DBG
-#define PRISM_DBG 0   // debugging aid: bit 0 skips the gate warps' work, bit 1 the dR warps' work
-#endif
-
 namespace prism {
 
 #ifndef PRISM_K2_CVT_HW
@@ -125,6 +121,24 @@ __device__ __forceinline__ uint32_t gate_bwd_pair(uint32_t a2, uint32_t hs, floa
   acc0 = fmaf(dh0, gf.x, acc0);
   acc1 = fmaf(dh1, gf.y, acc1);
   return Pk<DT>::fma(q, x, q);
+}
+
+// The same in fp32 (hs0, hs1 = S/2 as delivered by the rotation): one rounding, when 2 dS is
+// converted to 16 bits for the dS . R and dR products.
+template <int DT>
+__device__ __forceinline__ uint32_t gate_bwd_pair_f32(uint32_t a2, float hs0, float hs1, float dh0, float dh1, float& acc0,
+                                                      float& acc1) {
+  const float2 hs = make_float2(hs0, hs1), dh = make_float2(dh0, dh1), one = make_float2(1.f, 1.f);
+  const float2 t = make_float2(tanh_approx(hs0), tanh_approx(hs1));
+  const float2 g = fma2(hs, t, hs);
+  const float2 w = fma2(g, make_float2(-1.f, -1.f), one);
+  const float2 x = fma2(t, w, g);
+  const float2 q = mul2(dh, Elem<DT>::unpack(a2));
+  const float2 acc = fma2(dh, g, make_float2(acc0, acc1));
+  acc0 = acc.x;
+  acc1 = acc.y;
+  const float2 ds = fma2(q, x, q);
+  return Pk<DT>::cvt_hw(ds.x, ds.y);
 }
 
 // Work of a CTA pair: a list of tiles [256 tokens x 128 features].  A main pair (column fx, run)
@@ -495,13 +509,18 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
               // pair e of the fragment: (row, cols) as in the accumulator layout; e >> 1 selects columns + 8
               const float x0 = __uint_as_float(dh[i][2 * e]), x1 = __uint_as_float(dh[i][2 * e + 1]);
               if (kGated) {
-#if PRISM_K2_CVT_HW
-                const uint32_t hs = Pk<DT>::cvt_hw(__uint_as_float(sv[i][2 * e]), __uint_as_float(sv[i][2 * e + 1]));
-#else
-                const uint32_t hs = Pk<DT>::cvt(__uint_as_float(sv[i][2 * e]), __uint_as_float(sv[i][2 * e + 1]));
-#endif
                 float* d = (e >> 1) ? d1 : d0;
-                dsf[i][e] = gate_bwd_pair<DT>(af[i][e], hs, x0, x1, d[(e & 1) * 2], d[(e & 1) * 2 + 1]);
+                const float h0 = __uint_as_float(sv[i][2 * e]), h1 = __uint_as_float(sv[i][2 * e + 1]);
+                if (gate_in_f32<DT>()) {
+                  dsf[i][e] = gate_bwd_pair_f32<DT>(af[i][e], h0, h1, x0, x1, d[(e & 1) * 2], d[(e & 1) * 2 + 1]);
+                } else {
+#if PRISM_K2_CVT_HW
+                  const uint32_t hs = Pk<DT>::cvt_hw(h0, h1);
+#else
+                  const uint32_t hs = Pk<DT>::cvt(h0, h1);
+#endif
+                  dsf[i][e] = gate_bwd_pair<DT>(af[i][e], hs, x0, x1, d[(e & 1) * 2], d[(e & 1) * 2 + 1]);
+                }
               } else {
                 dsf[i][e] = Pk<DT>::cvt(x0, x1);
               }
@@ -568,7 +587,7 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       for (int g = 0; g < G && ok; ++g, ++gg) {
         const int buf = gg & 1;
         if (!mbar_wait(&bars->ds_full[buf], (gg >> 1) & 1)) { ok = false; break; }
-        for (int u = w; u < ((PRISM_DBG & 2) ? 0 : n_sub); u += kNumDrWarps) {
+        for (int u = w; u < n_sub; u += kNumDrWarps) {
           const int block = u / spb, rem = u - block * spb;
           const int is = rem / KS, js = rem - is * KS;
           const int chunk = block / NB, b = block - chunk * NB;
@@ -642,9 +661,9 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 // buffers in increasing order, then, for every run, the slabs of the extra pair that helped the
 // main pair (run, column of k).  For rs = 8 two neighbouring blocks share one 16-row group of the
 // partial buffers: the block in the upper 8 columns of each 16-column pair sits in rows 8..15.
-template <int DT>
+template <int DT, bool F32OUT>
 __global__ void dr_reduce_kernel(const float* __restrict__ partial, const float* __restrict__ partial_x,
-                                 uint16_t* __restrict__ dR, int G, int rs, int E, int K, long long lddr, int runs,
+                                 void* __restrict__ dR_out, int G, int rs, int E, int K, long long lddr, int runs,
                                  int n_ft, int n_main, int n_extra, int steal, int slots, float scale) {
   const long long pair = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long total = (long long)G * rs * K / 2;
@@ -677,7 +696,10 @@ __global__ void dr_reduce_kernel(const float* __restrict__ partial, const float*
       }
     }
   }
-  *reinterpret_cast<uint32_t*>(dR + (long long)row * lddr + k) = Elem<DT>::pack(acc.x * scale, acc.y * scale);
+  if (F32OUT)   // the fp32 sums leave as they are (mixed-precision optimisers)
+    *reinterpret_cast<float2*>(reinterpret_cast<float*>(dR_out) + (long long)row * lddr + k) = make_float2(acc.x * scale, acc.y * scale);
+  else
+    *reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(dR_out) + (long long)row * lddr + k) = Elem<DT>::pack(acc.x * scale, acc.y * scale);
 }
 
 // Grid of the dA+dR kernel.  runs: the number of main CTA pairs that share one feature column (each
@@ -787,10 +809,12 @@ int launch_bwd_dadr(const DadrArgs& a) {
   const long long pairs = (long long)p.G * a.rs * a.K / 2;
   const int threads = 256;
   const long long blocks = (pairs + threads - 1) / threads;
-  if (a.dtype == DT_BF16)
-    dr_reduce_kernel<DT_BF16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, a.partial_x, reinterpret_cast<uint16_t*>(a.dR), p.G, a.rs, a.E, a.K, a.lddr, p.runs, p.n_ft, p.n_main, p.n_extra, p.steal, p.slots, r_scale);
-  else
-    dr_reduce_kernel<DT_F16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, a.partial_x, reinterpret_cast<uint16_t*>(a.dR), p.G, a.rs, a.E, a.K, a.lddr, p.runs, p.n_ft, p.n_main, p.n_extra, p.steal, p.slots, r_scale);
+#define PRISM_DR_REDUCE(DT_, F32_)                                                                          \
+  dr_reduce_kernel<DT_, F32_><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, a.partial_x, a.dR, p.G, a.rs, a.E, \
+      a.K, a.lddr, p.runs, p.n_ft, p.n_main, p.n_extra, p.steal, p.slots, r_scale)
+  if (a.dtype == DT_BF16) { if (a.dr_f32) PRISM_DR_REDUCE(DT_BF16, true); else PRISM_DR_REDUCE(DT_BF16, false); }
+  else { if (a.dr_f32) PRISM_DR_REDUCE(DT_F16, true); else PRISM_DR_REDUCE(DT_F16, false); }
+#undef PRISM_DR_REDUCE
   return check_launch("prism_bwd_dadr reduce");
 }
 

@@ -48,6 +48,7 @@ struct DbParams {
   int ns;             // stages: two A tiles + this CTA's dC tiles
   int stage_bytes;
   int splits;
+  int out_f32;        // 1: dB is fp32
   float scale;
   void* dB;
   long long lddb;
@@ -249,6 +250,10 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             float* dst = p.partial + ((long long)split * p.part_rows + (n0 - p.nt0 * p.BN) + c0) * p.K + f;
 #pragma unroll
             for (int j = 0; j < 16; ++j) dst[(long long)j * p.K] = __uint_as_float(v[j]) * p.scale;
+          } else if (p.out_f32) {
+            float* dst = reinterpret_cast<float*>(p.dB) + (long long)(n0 + c0) * p.lddb + f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) dst[(long long)j * p.lddb] = __uint_as_float(v[j]) * p.scale;
           } else {
             uint16_t* dst = reinterpret_cast<uint16_t*>(p.dB) + (long long)(n0 + c0) * p.lddb + f;
 #pragma unroll
@@ -273,8 +278,8 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 }
 
 // dB[n, k] = cast( sum_s partial[s][n][k] ), s in increasing order.
-template <int DT>
-__global__ void db_reduce_kernel(const float* __restrict__ partial, uint16_t* __restrict__ dB, int N,
+template <int DT, bool F32OUT>
+__global__ void db_reduce_kernel(const float* __restrict__ partial, void* __restrict__ dB_out, int N,
                                  int K, long long lddb, int splits) {
   const long long pair = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // two elements per thread
   const long long total = (long long)N * K / 2;
@@ -287,7 +292,10 @@ __global__ void db_reduce_kernel(const float* __restrict__ partial, uint16_t* __
     acc.x += v.x;
     acc.y += v.y;
   }
-  *reinterpret_cast<uint32_t*>(dB + (long long)n * lddb + k) = Elem<DT>::pack(acc.x, acc.y);
+  if (F32OUT)
+    *reinterpret_cast<float2*>(reinterpret_cast<float*>(dB_out) + (long long)n * lddb + k) = acc;
+  else
+    *reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(dB_out) + (long long)n * lddb + k) = Elem<DT>::pack(acc.x, acc.y);
 }
 
 static int db_default_splits(int M, int N, int K, int BN, int num_sms) {
@@ -332,7 +340,7 @@ int launch_bwd_db(const DbArgs& a) {
   p.n_tokblocks = (a.M + 127) / 128;
   p.dc_tiles = (a.BN / 2 + 63) / 64;   // per CTA: half of the tile's dC columns
   p.r_tile_bytes = ((a.E * 128) + 1023) / 1024 * 1024;
-  p.scale = a.scale;
+  p.scale = a.scale; p.out_f32 = a.out_f32;
   p.dB = a.dB; p.lddb = a.lddb; p.partial = a.partial; p.err = a.err;
   if ((a.plan.splits > 1 || a.plan.tail_rows > 0) && a.partial == nullptr)
     return fail(PRISM_ERR_WORKSPACE, "bwd_db: split accumulation needs a partial-sum workspace");
@@ -378,11 +386,12 @@ int launch_bwd_db(const DbArgs& a) {
       const long long pairs = (long long)q.part_rows * a.K / 2;
       const int threads = 256;
       const long long blocks = (pairs + threads - 1) / threads;
-      uint16_t* out = reinterpret_cast<uint16_t*>(a.dB) + (long long)nt0 * a.BN * a.lddb;
-      if (a.dtype == DT_BF16)
-        db_reduce_kernel<DT_BF16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, out, q.part_rows, a.K, a.lddb, q.splits);
-      else
-        db_reduce_kernel<DT_F16><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, out, q.part_rows, a.K, a.lddb, q.splits);
+      void* out = reinterpret_cast<uint8_t*>(a.dB) + (long long)nt0 * a.BN * a.lddb * (a.out_f32 ? 4 : 2);
+#define PRISM_DB_REDUCE(DT_, F32_) \
+  db_reduce_kernel<DT_, F32_><<<(unsigned)blocks, threads, 0, a.stream>>>(a.partial, out, q.part_rows, a.K, a.lddb, q.splits)
+      if (a.dtype == DT_BF16) { if (a.out_f32) PRISM_DB_REDUCE(DT_BF16, true); else PRISM_DB_REDUCE(DT_BF16, false); }
+      else { if (a.out_f32) PRISM_DB_REDUCE(DT_F16, true); else PRISM_DB_REDUCE(DT_F16, false); }
+#undef PRISM_DB_REDUCE
       if ((rcl = check_launch("prism_bwd_db reduce"))) return rcl;
     }
     return PRISM_OK;

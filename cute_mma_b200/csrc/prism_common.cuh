@@ -433,9 +433,53 @@ __device__ __forceinline__ float sigmoid_fast(float x) {
 #ifndef PRISM_DB_CVT_HW
 #define PRISM_DB_CVT_HW 1   // dB gate warps: S converted by the one-instruction cvt (their ALU pipe is the busier one)
 #endif
-#ifndef PRISM_GATE_PACKED
-#define PRISM_GATE_PACKED 1   // 1: gate math on f16x2 / bf16x2 pairs, 0: fp32 per element
+// Precision of the gate arithmetic, per data type.  1: fp32 per element (tanh.approx.f32, packed
+// fp32 FMAs), one rounding when H / dS is converted to 16 bits: the result sits at the error floor
+// that 16-bit tensor-core operands allow, like the reference's bf16 kernels, which evaluate the gate
+// in fp32 (cute_prism_coop_pc.cu:323-330).  0: arithmetic on f16x2 / bf16x2 pairs, four roundings
+// per element: half the instructions, twice the error.  Measured on bf16 at K = 4096: mean
+// relative error of C 0.0097 (fp32 gate) against 0.0197 (packed), forward 10 % slower.
+// fp16 keeps the packed form by default: its roundings are 8 times finer, and the reference's fp16
+// kernels use tanh.approx.f16x2 too (cute_prism_util.hpp:55-77).
+#ifndef PRISM_GATE_F32_BF16
+#define PRISM_GATE_F32_BF16 1
 #endif
+#ifndef PRISM_GATE_F32_F16
+#define PRISM_GATE_F32_F16 0
+#endif
+template <int DT>
+__device__ __forceinline__ constexpr bool gate_in_f32() {
+  return DT == DT_BF16 ? (PRISM_GATE_F32_BF16 != 0) : (PRISM_GATE_F32_F16 != 0);
+}
+
+// Two fp32 operations per instruction (sm_100 packed fp32 arithmetic).
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t"
+      ".reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rb, {%4, %5};\n\t"
+      "mov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t"
+      "}\n"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t"
+      ".reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t"
+      "}\n"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
 
 template <int DT>
 struct Pk;
@@ -471,11 +515,14 @@ struct Pk<DT_BF16> {
   static constexpr uint32_t kOne = 0x3F803F80u, kNegOne = 0xBF80BF80u, kOneLo = 0x00003F80u;
   // fp32 pair -> bf16x2 with integer ops: add half an ulp to the bit patterns and keep the upper
   // halves (round to nearest, ties away from zero).  The cvt.rn.bf16x2.f32 instruction runs on the
-  // 16-lane/clk special-function pipe (measured: as expensive as a tanh), these three ALU ops do not.
+  // 16-lane/clk special-function pipe (measured: as expensive as a tanh), these ALU ops do not.
+  // A NaN keeps its upper half with the quiet bit set (the plain add would carry out of a NaN whose
+  // upper mantissa bits are all ones and turn it into a zero); infinities pass through unchanged.
+  __device__ __forceinline__ static uint32_t round_bits(uint32_t u) {
+    return ((u << 1) > 0xFF000000u) ? (u | 0x00400000u) : (u + 0x8000u);
+  }
   __device__ __forceinline__ static uint32_t cvt(float lo, float hi) {
-    const uint32_t ulo = __float_as_uint(lo) + 0x8000u;
-    const uint32_t uhi = __float_as_uint(hi) + 0x8000u;
-    return __byte_perm(ulo, uhi, 0x7632);
+    return __byte_perm(round_bits(__float_as_uint(lo)), round_bits(__float_as_uint(hi)), 0x7632);
   }
   // The single-instruction conversion (special-function pipe): for code whose ALU pipe is the busier one.
   __device__ __forceinline__ static uint32_t cvt_hw(float lo, float hi) {
@@ -510,10 +557,10 @@ __device__ __forceinline__ uint32_t silu_pair(float s0, float s1) {
 
 // ----------------------------------------------------------------------------
 // Warp-level matrix fragments (ldmatrix / stmatrix / mma.sync m16n8k16).
-// The block rotation S = A_blk . R_blk^T runs here, on the legacy warp MMA path: measured on
-// B200 it sustains ~1000 FMA/clk/SM next to a saturated tcgen05 pipe and slows that pipe by
-// less than 10 %, whereas a 16-wide tcgen05.mma occupies the pipe for the ~46 clocks that
-// fetching its 128x16 A operand from shared memory takes, whatever its N.
+// ldmatrix / stmatrix move 16-bit tiles between shared memory and the register layout that
+// tcgen05.ld.16x256b delivers for fp32 TMEM data, so the gate math is elementwise on registers.
+// mma.sync itself is only used for the small dR products of the dA+dR kernel: it shares the tensor
+// cores with tcgen05.mma and only gets the gaps that tcgen05.mma leaves.
 // ----------------------------------------------------------------------------
 __device__ __forceinline__ void ldmatrix_x4(uint32_t saddr, uint32_t (&r)[4]) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -550,18 +597,19 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[
 
 
 // H for one pair of elements from fp32 S and packed 16-bit A: A*silu(S), or S in plain mode.
+// silu(s) = hs + hs tanh(hs) with hs = s/2: one special-function operation per element, no division.
 template <int DT, int GATE, bool HW = false>
 __device__ __forceinline__ uint32_t gate_pair(uint32_t a2, float s0, float s1) {
-#if PRISM_GATE_PACKED
-  if (GATE == GATE_SILU) return Pk<DT>::mul(a2, silu_pair<DT, HW>(s0, s1));
-  return Pk<DT>::cvt(s0, s1);
-#else
   if (GATE == GATE_SILU) {
-    const float2 a = Elem<DT>::unpack(a2);
-    return Elem<DT>::pack(a.x * (s0 * sigmoid_fast(s0)), a.y * (s1 * sigmoid_fast(s1)));
+    if (gate_in_f32<DT>()) {
+      const float2 hs = mul2(make_float2(s0, s1), make_float2(0.5f, 0.5f));
+      const float2 t = make_float2(tanh_approx(hs.x), tanh_approx(hs.y));
+      const float2 h = mul2(Elem<DT>::unpack(a2), fma2(hs, t, hs));
+      return Pk<DT>::cvt_hw(h.x, h.y);
+    }
+    return Pk<DT>::mul(a2, silu_pair<DT, HW>(s0, s1));
   }
-  return Elem<DT>::pack(s0, s1);
-#endif
+  return Pk<DT>::cvt(s0, s1);
 }
 
 // TMEM -> registers in the mma.sync accumulator layout: 16 lanes x 16 columns; thread t gets

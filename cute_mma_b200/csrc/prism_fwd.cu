@@ -28,10 +28,6 @@
 #include "prism_host.cuh"
 #include "prism_kernels.cuh"
 
-#ifndef PRISM_DBG
-#define PRISM_DBG 0   // debugging aid: bit 1 skips the output stores
-#endif
-
 namespace prism {
 
 namespace fwd {
@@ -333,7 +329,7 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0 && !(PRISM_DBG & 2) && mt * 128 + q * 32 < p.M) {
+          if (lane == 0 && mt * 128 + q * 32 < p.M) {
             tma_store_2d(&tmC, stage, n0 + c0, mt * 128 + q * 32);
             tma_store_commit();
           }
@@ -344,7 +340,7 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint32_t v[16];
           tmem_ld_x16(tacc + c0, v);
           tmem_ld_wait();
-          if (grow < p.M && !(PRISM_DBG & 2)) {
+          if (grow < p.M) {
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
               uint32_t ow[4];

@@ -4,6 +4,7 @@
 
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <atomic>
 #include <stdarg.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -71,14 +72,15 @@ inline int make_tmap_2d(CUtensorMap* out, int dt, const void* base, uint64_t row
   return PRISM_OK;
 }
 
-// Number of kernels this library has launched in this process (for benchmarks and tests).
-inline long long& launch_counter() {
-  static long long n = 0;
+// Number of kernels this library has launched in this process (for benchmarks and tests);
+// any host thread may launch, so the counter is atomic.
+inline std::atomic<long long>& launch_counter() {
+  static std::atomic<long long> n{0};
   return n;
 }
 
 inline int check_launch(const char* what) {
-  ++launch_counter();
+  launch_counter().fetch_add(1, std::memory_order_relaxed);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess)
     return fail(PRISM_ERR_CUDA, "%s: launch failed: %s", what, cudaGetErrorString(e));

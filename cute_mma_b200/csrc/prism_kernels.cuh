@@ -41,9 +41,10 @@ struct DbArgs {
   const void* dC;     // [M, N]
   const void* A;      // [M, K]
   const void* R_eff;  // [(N/gs)*E, K]
-  void* dB;           // [N, K]
+  void* dB;           // [N, K], 16-bit like the inputs or fp32 (out_f32)
   int M, N, K, gs, E;
   int dtype, gate;
+  int out_f32;        // 1: dB is written as fp32
   float scale;        // dB = scale * dC^T H
   long long lddc, lda, ldr, lddb;
   int BN;
@@ -71,9 +72,10 @@ struct DadrArgs {
   const void* B;      // [N, K]
   const void* R_eff;  // [(N/gs)*E, K]
   void* dA;           // [M, K]
-  void* dR;           // [(N/gs)*rs, K]
+  void* dR;           // [(N/gs)*rs, K], 16-bit like the inputs or fp32 (dr_f32)
   int M, N, K, gs, rs, E;
   int dtype, gate;
+  int dr_f32;         // 1: dR is written as fp32
   float scale;
   long long lddc, lda, ldb, ldr, ldda, lddr;
   DadrGrid grid;      // CTA pairs and their tiles

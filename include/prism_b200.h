@@ -13,6 +13,9 @@
  *   - all matrices are row-major 16-bit (dtype 0 = fp16, 1 = bf16), device pointers,
  *     16-byte aligned, leading dimensions in elements and multiples of 8;
  *     A [M,K], B [N,K], R [(N/group_size)*reconn_sz, K], C/dC [M,N];
+ *   - group_size must be a multiple of 16 (the reference accepts multiples of 8,
+ *     src/cute_prism/_validate.py:26-30; the tensor-core tiles here are 16 wide) and reconn_sz one
+ *     of 8, 16, 32, 64;
  *   - gate 0 = plain "ar" mode (C_g = (A.blockdiag(R_g)^T) B_g^T), 1 = silu_gate
  *     (C_g = (A * silu(A.blockdiag(R_g)^T)) B_g^T);
  *   - the library never allocates or frees device memory: outputs and the workspace
@@ -46,6 +49,13 @@ extern "C" {
 #define PRISM_KIND_FWD 0
 #define PRISM_KIND_BWD_DADR 1
 #define PRISM_KIND_BWD_DB 2
+#define PRISM_KIND_DBIAS 3
+
+/* element types: the 16-bit input types, and fp32 for gradient outputs that should leave unrounded */
+#define PRISM_DTYPE_F16 0
+#define PRISM_DTYPE_BF16 1
+#define PRISM_DTYPE_F32 2
+#define PRISM_DTYPE_SAME (-1)   /* a gradient output in the inputs' 16-bit type */
 
 #define PRISM_WORKSPACE_HEADER_BYTES 256
 /* size of the library's built-in scratch array used by prism_fwd_noalloc: 8 MiB + the status header */
@@ -76,7 +86,9 @@ int prism_fwd_noalloc(const void* A, const void* B, const void* R, const void* b
                       const int* cfg, int* device_status, void* stream);
 
 /* Input and rotation gradients: dA [M,K] and dR [(N/group_size)*reconn_sz, K], both scaled by
- * dc_scale.  cfg (3 ints, 0 = default): {runs, steal, n_extra} -- runs: the number of main CTA
+ * dc_scale.  dr_dtype: PRISM_DTYPE_SAME (dR in the inputs' type) or PRISM_DTYPE_F32 (the fp32 sums of
+ * the second-level reduction leave unrounded, lddr in fp32 elements; the reference offers the same
+ * through dR_dtype, src/cute_prism/__init__.py:288-289,368).  cfg (3 ints, 0 = default): {runs, steal, n_extra} -- runs: the number of main CTA
  * pairs that share one 128-feature column of dA (each walks every runs-th 256-token tile); when
  * the main pairs leave SMs idle, n_extra extra pairs take over the last `steal` tiles of every
  * main pair (steal < 0: never).  Each CTA accumulates dR into fp32 memory of its own
@@ -85,19 +97,29 @@ int prism_fwd_noalloc(const void* A, const void* B, const void* R, const void* b
  * reconn_sz = 8, halved in the gated mode). */
 int prism_bwd_dadr(const void* dC, const void* A, const void* B, const void* R, void* dA, void* dR,
                    int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
-                   float dc_scale, long long lddc, long long lda, long long ldb, long long ldr,
+                   int dr_dtype, float dc_scale, long long lddc, long long lda, long long ldb, long long ldr,
                    long long ldda, long long lddr,
                    const int* cfg, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Weight gradient dB [N,K] = dc_scale * dC^T . H (H recomputed from A and R; B is not needed).
+ * db_dtype: PRISM_DTYPE_SAME or PRISM_DTYPE_F32 (dB written as fp32, lddb in fp32 elements;
+ * reference: dB_dtype, src/cute_prism/__init__.py:288-289,375).
  * cfg (2 ints, 0 = default): {BN, splits} -- splits > 1 divides the token range of every tile over
  * several CTA pairs whose fp32 partial sums (in the workspace) are added in a fixed order, so the
  * result is deterministic; splits < 0 never splits.  By default only the n-tile rows of a mostly
  * empty last wave are split (in a second launch). */
 int prism_bwd_db(const void* dC, const void* A, const void* R, void* dB,
                  int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
-                 float dc_scale, long long lddc, long long lda, long long ldr, long long lddb,
+                 int db_dtype, float dc_scale, long long lddc, long long lda, long long ldr, long long lddb,
                  const int* cfg, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Output-bias gradient dbias [N] = sum over the M token rows of dC [M,N] (not scaled: the bias is
+ * added after the point where the reference's constant backward rescale applies).  The reference adds
+ * the bias as a separate torch op (src/cute_prism/_module.py:736-737), whose autograd is this column
+ * sum.  Two launches, partial sums over row ranges added in a fixed order: bit-stable.
+ * dbias_dtype: PRISM_DTYPE_SAME or PRISM_DTYPE_F32.  Workspace: prism_workspace_bytes(PRISM_KIND_DBIAS, M, N, ...). */
+int prism_dbias(const void* dC, void* dbias, int M, int N, int dtype, int dbias_dtype, long long lddc,
+                void* workspace, size_t workspace_bytes, void* stream);
 
 /* Bytes of workspace the given call needs (kind = PRISM_KIND_*), header included. */
 size_t prism_workspace_bytes(int kind, int M, int N, int K, int group_size, int reconn_sz,

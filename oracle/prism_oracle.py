@@ -131,9 +131,23 @@ def make_inputs(M, K, N, group_size, reconn_sz, seed=0, a_std=1.0, b_std=1.0, dc
 
 def rel_err(val, ref):
     """The reference tests' metric: max|val-ref| / (max|ref| + 1e-6)  (tests/test_correctness.py:24-31)."""
-    val = val.double()
-    ref = ref.double()
-    return ((val - ref).abs().max() / (ref.abs().max() + 1e-6)).item()
+    wide = torch.float64 if torch.float64 in (val.dtype, ref.dtype) else torch.float32
+    val = val.to(wide)
+    ref = ref.to(wide)
+    return ((val - ref).abs().max().double() / (ref.abs().max().double() + 1e-6)).item()
+
+
+def mean_rel_err(val, ref, floor=1e-4):
+    """The reference tests' second metric: mean of |val-ref| / |ref| over the elements with
+    |ref| > floor  (tests/test_backward.py:96-108, tests/test_correctness.py:90-100)."""
+    val = val.float()
+    ref = ref.float()
+    mask = ref.abs() > floor
+    n = int(mask.sum().item())
+    if n == 0:
+        return 0.0
+    rel = torch.where(mask, (val - ref).abs() / ref.abs().clamp_min(floor), torch.zeros_like(ref))
+    return (rel.double().sum() / n).item()
 
 
 def flops(M, K, N, group_size, reconn_sz):

@@ -24,7 +24,7 @@ def test_header_and_loader_agree():
 def test_library_exports_every_declared_symbol(built_lib):
     for name in _declared_symbols():
         assert hasattr(built_lib, name), name
-    assert built_lib.prism_abi_version() == 1
+    assert built_lib.prism_abi_version() == _lib.ABI_VERSION == 2
 
 
 def _call_fwd(L, M, N, K, gs, rs, dtype=1, gate=0, ptr=0x1000, ws=0x1000, ws_bytes=1 << 20):
@@ -50,6 +50,15 @@ def test_bad_arguments_are_rejected_without_a_gpu(built_lib, args, code):
     assert len(built_lib.prism_last_error_string()) > 0
 
 
+def test_gradient_dtype_codes_are_checked(built_lib):
+    p = ctypes.c_void_p(0x1000)
+    rc = built_lib.prism_bwd_db(p, p, p, p, 16, 64, 64, 32, 8, 1, 1, 0, ctypes.c_float(1.0), 64, 64, 64, 64, None,
+                                p, 1 << 20, None)
+    assert rc == 1 and b"db_dtype" in built_lib.prism_last_error_string()   # fp16 gradient of bf16 inputs
+    rc = built_lib.prism_dbias(p, p, 16, 60, 1, -1, 64, p, 1 << 20, None)
+    assert rc == 1                                                          # N not a multiple of 8
+
+
 def test_workspace_sizes(built_lib):
     L = built_lib
     hdr = 256
@@ -67,5 +76,8 @@ def test_workspace_sizes(built_lib):
     G, E, K = 56, 16, 4096
     want = hdr + G * E * K * 2 + 2 * 2 * G * E * K * 4 + 2 * 10 * 7 * G * E * 128 * 4
     assert L.prism_workspace_bytes(1, 16384, 14336, K, 256, 16, 1, None) == want
+    # bias gradient: one fp32 row of N partial sums per row range (64 ranges at most)
+    assert L.prism_workspace_bytes(3, 8192, 2304, 0, 0, 0, 1, None) == hdr + 64 * 2304 * 4
+    assert L.prism_workspace_bytes(3, 100, 256, 0, 0, 0, 1, None) == hdr + 2 * 256 * 4
     cfg = (ctypes.c_int * 8)(2, -1, 0, 0, 0, 0, 0, 0)   # no extra pairs
     assert L.prism_workspace_bytes(1, 16384, 14336, K, 256, 16, 1, cfg) == hdr + G * E * K * 2 + 2 * 2 * G * E * K * 4

@@ -1,0 +1,193 @@
+"""GPU tests of the boundary features around the three kernels: non-finite propagation, fp32
+gradient outputs, the bias-gradient kernel, the ``cute_prism`` import name and its custom ops, the
+per-stream workspaces, and the bounded-wait error path."""
+import ctypes
+import os
+import subprocess
+import threading
+
+import pytest
+import torch
+
+import cute_mma_b200 as cp
+from cute_mma_b200 import _functional as F
+from cute_mma_b200 import _lib
+from oracle import prism_oracle as O
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+DEV = "cuda"
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _inputs(M, K, N, gs, rs, dt, seed=0):
+    ts = O.make_inputs(M, K, N, gs, rs, seed=seed, b_std=K ** -0.5)
+    return [t.to(dt).to(DEV).contiguous() for t in ts]
+
+
+@pytest.mark.parametrize("act", [None, "silu_gate"])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_nan_and_inf_rows_propagate(dt, act):
+    """A NaN row and an Inf row in A (forward) and in dC (backward) come back non-finite exactly
+    where the oracle's are, and finite everywhere else: a diverged step must not look healthy."""
+    M, K, N, gs, rs = 256, 256, 512, 256, 16
+    A, B, R, dC = _inputs(M, K, N, gs, rs, dt, 31)
+    A[5, :] = float("nan")
+    A[77, 3] = float("inf")
+    # NaN bit patterns whose upper mantissa bits are all ones (a plain add-and-truncate rounding
+    # would turn these into zeros)
+    A.view(torch.int16)[130, 9] = 0x7FFF
+    C, _ = cp.forward(A, B, R, gs, rs, activation=act)
+    rC = O.prism_forward(A.float(), B.float(), R.float(), gs, rs, act)
+    bad_rows = ~torch.isfinite(rC).all(dim=1)
+    assert bad_rows[5] and bad_rows[77] and bad_rows[130]
+    assert (~torch.isfinite(C)).any(dim=1)[bad_rows].all(), "a non-finite input row came back finite"
+    assert torch.isfinite(C[~bad_rows]).all()
+    assert O.rel_err(C[~bad_rows].float(), rC[~bad_rows]) < TOL
+    # backward with clean A and poisoned dC rows
+    A, B, R, dC = _inputs(M, K, N, gs, rs, dt, 32)
+    dC[9, :] = float("nan")
+    dC[200, 17] = float("inf")
+    dA, dR, dB, _ = cp.backward(dC, A, B, R, gs, rs, activation=act)
+    assert not torch.isfinite(dA[9]).any() and not torch.isfinite(dA[200]).all()
+    ok_rows = torch.ones(M, dtype=torch.bool, device=DEV)
+    ok_rows[9] = ok_rows[200] = False
+    assert torch.isfinite(dA[ok_rows]).all()
+    assert not torch.isfinite(dR).all(), "dR sums over the poisoned rows"
+    if act is not None:
+        assert not torch.isfinite(dB).all()
+    cp.check_device_status()
+
+
+def test_fp32_gradient_outputs_are_the_unrounded_sums():
+    M, K, N, gs, rs = 1024, 512, 1024, 256, 8
+    A, B, R, dC = _inputs(M, K, N, gs, rs, torch.bfloat16, 41)
+    dA, dR, dB, _ = cp.backward(dC, A, B, R, gs, rs, activation="silu_gate")
+    dA2, dR32, dB32, _ = cp.backward(dC, A, B, R, gs, rs, activation="silu_gate",
+                                     dR_dtype=torch.float32, dB_dtype=torch.float32)
+    assert dR32.dtype == torch.float32 and dB32.dtype == torch.float32 and torch.equal(dA, dA2)
+    # rounding the fp32 outputs gives the 16-bit outputs bit for bit
+    assert torch.equal(dR32.to(torch.bfloat16), dR) and torch.equal(dB32.to(torch.bfloat16), dB)
+    rA, rR, rB = O.prism_backward(dC.float(), A.float(), B.float(), R.float(), gs, rs, "silu_gate")
+    e16, e32 = O.rel_err(dR.float(), rR), O.rel_err(dR32, rR)
+    assert e32 <= e16 + 1e-6 and e32 < TOL and O.rel_err(dB32, rB) < TOL
+    # split dB accumulation (second-level reduce) and the plain mode take the same path
+    dB32s = F._backward_db(dC, A, R, gs, rs, 1, tile_cfg=[128, 4], out_dtype=torch.float32)
+    assert O.rel_err(dB32s, rB) < TOL
+    _, dRp, _, _ = cp.backward(dC, A, B, R, gs, rs, dR_dtype=torch.float32)
+    assert dRp.dtype == torch.float32
+    with pytest.raises(ValueError):
+        cp.backward(dC, A, B, R, gs, rs, dR_dtype=torch.float64)
+    cp.check_device_status()
+
+
+@pytest.mark.parametrize("shape", [(1, 256), (300, 264), (4096, 2304), (8192, 14336)])
+def test_bias_grad_kernel(shape):
+    M, N = shape
+    g = torch.Generator(device=DEV).manual_seed(M + N)
+    dC = torch.randn(M, N, device=DEV, generator=g).to(torch.bfloat16)
+    ref = dC.double().sum(0)
+    out32 = cp.bias_grad(dC, torch.float32)
+    out16 = cp.bias_grad(dC)
+    assert out32.dtype == torch.float32 and out16.dtype == torch.bfloat16
+    assert (out32.double() - ref).abs().max() <= 1e-5 * max(1.0, ref.abs().max().item()) * max(1, M) ** 0.5
+    assert torch.equal(out32.to(torch.bfloat16), out16)
+    assert torch.equal(cp.bias_grad(dC, torch.float32), out32)   # fixed summation order
+    cp.check_device_status()
+
+
+def test_cute_prism_import_name_and_ops():
+    """A script written against the reference runs unedited: same package name, same op names."""
+    import cute_prism
+    M, K, N, gs, rs = 512, 256, 512, 256, 8
+    A, B, R, dC = _inputs(M, K, N, gs, rs, torch.float16, 43)
+    C, seeds = cute_prism.forward(A, B, R, group_size=gs, reconn_sz=rs, backend="cute", activation="silu_gate")
+    assert seeds == []
+    C2 = torch.ops.cute_prism.forward(A, B, R, gs, rs, "cute", "silu_gate", False, False)
+    assert torch.equal(C, C2)
+    dA, dR, dB = torch.ops.cute_prism.backward(dC, A, B, R, gs, rs, "cublas", "", False, False)
+    assert dB.abs().max() == 0          # plain mode: frozen-B contract
+    rA, rR, _ = O.prism_backward(dC.float(), A.float(), B.float(), R.float(), gs, rs, None)
+    assert O.rel_err(dA.float(), rA) < TOL and O.rel_err(dR.float(), rR) < TOL
+    # autograd through the reference-named op
+    Ar, Br, Rr = [t.clone().requires_grad_(True) for t in (A, B, R)]
+    torch.ops.cute_prism.forward(Ar, Br, Rr, gs, rs, "cute", "silu_gate", False, False).backward(dC)
+    gA, gR, gB, _ = cp.backward(dC, A, B, R, gs, rs, activation="silu_gate")
+    assert torch.equal(Ar.grad, gA) and torch.equal(Rr.grad, gR) and torch.equal(Br.grad, gB)
+    layer = cute_prism.PrismLinear(K, N, group_size=gs, reconn_sz=rs, backend="cute", autotuning=True)
+    assert float(layer.reconn_diag_sq_sum()) == pytest.approx((N // gs) * K, rel=1e-5)   # R = identity blocks
+    with pytest.raises(ValueError):
+        cute_prism.PrismLinear(64, 72, group_size=24, reconn_sz=8)   # 16-wide tensor-core tiles
+    cp.check_device_status()
+
+
+def test_workspaces_are_per_stream_and_all_are_polled():
+    """Calls on two streams use different scratch buffers (they may overlap on the GPU); a backward
+    run by an autograd thread uses the forward's stream, and check_device_status reads every header."""
+    M, K, N, gs, rs = 512, 256, 512, 256, 8
+    A, B, R, dC = _inputs(M, K, N, gs, rs, torch.float16, 47)
+    ref, _ = cp.forward(A, B, R, gs, rs, activation="silu_gate")
+    rA, rR, rB, _ = cp.backward(dC, A, B, R, gs, rs, activation="silu_gate")
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream() for _ in range(2)]
+    outs = [None, None]
+    for rep in range(10):
+        for i, s in enumerate(streams):
+            with torch.cuda.stream(s):
+                outs[i] = cp.backward(dC, A, B, R, gs, rs, activation="silu_gate")
+    torch.cuda.synchronize()
+    for o in outs:
+        assert torch.equal(o[0], rA) and torch.equal(o[1], rR) and torch.equal(o[2], rB)
+    keys = [k for k in F._workspace._bufs if k[0] == A.device]
+    assert len({k[1] for k in keys}) >= 3          # default stream + the two side streams
+    # a backward issued from another host thread on the same stream shares that stream's buffer
+    n_before = len(F._workspace._bufs)
+    t = threading.Thread(target=lambda: cp.backward(dC, A, B, R, gs, rs, activation="silu_gate"))
+    t.start(); t.join()
+    assert len(F._workspace._bufs) == n_before
+    # a sticky error word in ANY buffer of the device is reported and cleared
+    side = F._workspace._bufs[(A.device, streams[1].cuda_stream)]
+    side[:4].copy_(torch.tensor([5, 0, 0, 0], dtype=torch.uint8))
+    with pytest.raises(_lib.PrismError) as ei:
+        cp.check_device_status()
+    assert ei.value.code == 5
+    cp.check_device_status()
+    C, _ = cp.forward(A, B, R, gs, rs, activation="silu_gate")
+    assert torch.equal(C, ref)
+
+
+def _build_wait_probe():
+    src = os.path.join(HERE, "csrc", "wait_probe.cu")
+    out = os.path.join(HERE, "csrc", "libwait_probe.so")
+    if not os.path.exists(out) or os.path.getmtime(out) < os.path.getmtime(src):
+        subprocess.run([os.environ.get("NVCC", "nvcc"), "-gencode", "arch=compute_100a,code=sm_100a", "-O2",
+                        "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-o", out, src], check=True)
+    return ctypes.CDLL(out)
+
+
+def test_bounded_wait_runs_out_and_is_reported():
+    """The device-side failure path, without any fault: a wait on a barrier that nothing arrives on
+    gives up after its (shortened) limit, the kernel records PRISM_ERR_DEVICE_WAIT in the workspace
+    header and returns; prism_status reports code 5 and clears it; the same workspace then serves
+    a normal forward."""
+    probe = _build_wait_probe()
+    probe.wait_probe_launch.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+    L = _lib.lib()
+    M, K, N, gs, rs = 256, 256, 256, 256, 16
+    A, B, R, _ = _inputs(M, K, N, gs, rs, torch.bfloat16, 53)
+    need = L.prism_workspace_bytes(0, M, N, K, gs, rs, 1, None)
+    ws = torch.zeros(need, dtype=torch.uint8, device=DEV)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert L.prism_status(ctypes.c_void_p(ws.data_ptr()), stream) == 0
+    assert probe.wait_probe_launch(ctypes.c_void_p(ws.data_ptr()), stream) == 0
+    rc = L.prism_status(ctypes.c_void_p(ws.data_ptr()), stream)
+    assert rc == 5, L.prism_last_error_string()
+    assert b"wait ran out" in L.prism_last_error_string()
+    assert L.prism_status(ctypes.c_void_p(ws.data_ptr()), stream) == 0     # cleared
+    assert int(ws[:4].view(torch.int32).item()) == 0
+    C = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    _lib.check(L.prism_fwd(p(A), p(B), p(R), None, p(C), M, N, K, gs, rs, 1, 1, K, K, K, N, None,
+                           p(ws), ws.numel(), stream))
+    assert L.prism_status(p(ws), stream) == 0
+    assert O.rel_err(C.float(), O.prism_forward(A.float(), B.float(), R.float(), gs, rs, "silu_gate")) < TOL
