@@ -18,7 +18,8 @@ from ._tile_table import lookup as _tile_lookup
 
 KIND_FWD, KIND_BWD_DADR, KIND_BWD_DB, KIND_DBIAS = 0, 1, 2, 3
 DTYPE_F32, DTYPE_SAME = 2, -1
-ACTIVATIONS = (None, "silu_gate")
+ACTIVATIONS = (None, "silu_gate", "sigmoid_gate")
+_GATE_CODES = {None: 0, "silu_gate": 1, "sigmoid_gate": 2}   # the C ABI's gate argument
 _DTYPES = {torch.float16: 0, torch.bfloat16: 1}
 
 
@@ -154,10 +155,8 @@ def check_device_status(device=None) -> None:
 
 def _gate_code(activation):
     if activation not in ACTIVATIONS:
-        if activation == "sigmoid_gate":
-            raise ValueError("activation='sigmoid_gate' is not supported by the sm_100a kernels")
         raise ValueError(f"Unknown activation {activation!r}, must be one of {ACTIVATIONS}")
-    return 1 if activation == "silu_gate" else 0
+    return _GATE_CODES[activation]
 
 
 def _reject_unsupported(**kw):
@@ -170,14 +169,24 @@ def forward(A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=None, mo
             comp_params=None, activation=None, autotuning: bool = False, autotuning_search_space=None,
             force_rebenchmark: bool = False, internal_bias=None, dropout_p: float = 0.0,
             training: bool = False, shuffle_masks=None, *, bias=None, tile_cfg=None):
-    """C = per-group (A . blockdiag(R_g)^T) @ B_g^T, or the silu-gated form; returns ``(C, [])``.
+    """C = per-group (A . blockdiag(R_g)^T) @ B_g^T, or a gated form (``activation="silu_gate"``:
+    ``(A * silu(A . blockdiag(R_g)^T)) @ B_g^T``; ``"sigmoid_gate"``: ``(A * 2 sigmoid(...)) @ B_g^T``);
+    returns ``(C, [])``.
 
     ``bias`` (keyword-only, [N], same dtype) is added in the kernel epilogue.
     """
-    if mode != "ar":
-        raise ValueError("The sm_100a kernels only support mode='ar'")
+    if mode not in ("ar", "rw"):
+        raise ValueError(f"Unknown mode {mode!r}, must be 'ar' or 'rw'")
     gate = _gate_code(activation)
     validate_kernel_params(group_size, reconn_sz)
+    if mode == "rw":
+        # inference with the rotation folded into the weight: C = A @ (B . blockdiag(R))^T
+        if gate:
+            raise ValueError("mode='rw' has no gated form (the gate needs A . blockdiag(R)^T itself)")
+        _reject_unsupported(internal_bias=internal_bias, shuffle_masks=shuffle_masks)
+        validate_tensor_params(A, B, R, group_size, reconn_sz)
+        C = torch.matmul(A, fold_weight(B, R, group_size, reconn_sz).t())
+        return (C if bias is None else C + bias), []
     _reject_unsupported(internal_bias=internal_bias, shuffle_masks=shuffle_masks,
                         dropout_p=(dropout_p if training else 0.0))
     validate_tensor_params(A, B, R, group_size, reconn_sz)
@@ -211,6 +220,20 @@ def _grad_dtype(out_dtype, in_dtype, name):
     if out_dtype == torch.float32:
         return torch.float32, DTYPE_F32
     raise ValueError(f"{name} must be None, the input dtype or torch.float32, got {out_dtype}")
+
+
+def fold_weight(B, R, group_size: int, reconn_sz: int):
+    """``Bp = B . blockdiag(R)`` per group through ``prism_fold_weight``: the weight of the "rw"
+    mode, for which ``A @ Bp^T`` equals the plain-mode forward (reference:
+    src/cute_prism/_pytorch_backend.py:115-124).  Fold once, then serve with an ordinary GEMM."""
+    validate_kernel_params(group_size, reconn_sz)
+    N, K = B.shape
+    Bp = torch.empty_like(B)
+    with torch.cuda.device(B.device):
+        _lib.check(_lib.lib().prism_fold_weight(
+            ctypes.c_void_p(B.data_ptr()), ctypes.c_void_p(R.data_ptr()), ctypes.c_void_p(Bp.data_ptr()),
+            N, K, group_size, reconn_sz, _DTYPES[B.dtype], B.stride(0), R.stride(0), Bp.stride(0), _stream_ptr(B.device)))
+    return Bp
 
 
 def _backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=None, out_dtype=None):

@@ -16,8 +16,8 @@ Differences, all on the fast path:
   (src/cute_prism/_module.py:92-104);
 * the exact Cayley transform is solved in fp32 for fp16/bf16 parameters (``torch.linalg.solve``
   has no 16-bit kernels) and cast back;
-* input shuffle, internal bias, dropout and ``sigmoid_gate`` are not part of the accelerated
-  path and raise ``ValueError`` at construction.
+* input shuffle, internal bias and dropout are not part of the accelerated path and raise
+  ``ValueError`` at construction.
 """
 from __future__ import annotations
 
@@ -29,7 +29,9 @@ import torch.nn as nn
 
 from . import _functional as F
 
-_GATED_SILU_BWD_GAIN = 1.437  # same constant as the reference (src/cute_prism/_module.py:16)
+_GATED_SILU_BWD_GAIN = 1.437     # same constants as the reference (src/cute_prism/_module.py:14-15)
+_GATED_SIGMOID_BWD_GAIN = 1.15
+_GATED = ("silu_gate", "sigmoid_gate")
 
 
 # ---------------------------------------------------------------------------
@@ -54,7 +56,7 @@ def _prism_backward_op(dC: torch.Tensor, A: torch.Tensor, B: torch.Tensor, R: to
                        need_dB: bool, need_dbias: bool) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     dC = dC.contiguous()
     A, B, R = A.contiguous(), B.contiguous(), R.contiguous()
-    gate = 1 if activation else 0
+    gate = F._gate_code(activation or None)
     dA, dR = F._backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, bwd_scale)
     if not need_dB:
         dB = B.new_empty(0)
@@ -107,8 +109,8 @@ class PrismLinear(nn.Module):
 
     ``C = (A . blockdiag(R_g)^T) @ B_g^T`` per output group (``activation=None``: B frozen, R is
     the Cayley transform of the skew-symmetric part of ``reconn``), or
-    ``C = (A * silu(A . blockdiag(R_g)^T)) @ B_g^T`` (``activation="silu_gate"``: B and R trained,
-    R = ``reconn``).  Parameter names and shapes match the reference, so its checkpoints load:
+    ``C = (A * silu(A . blockdiag(R_g)^T)) @ B_g^T`` (``activation="silu_gate"``; ``"sigmoid_gate"`` uses
+    ``2 sigmoid`` in place of ``silu``: B and R trained, R = ``reconn``).  Parameter names and shapes match the reference, so its checkpoints load:
     ``weight (N, K)``, ``reconn (N/group_size*reconn_sz, K)``, ``bias (N)``, optional ``ar_scale``.
     """
 
@@ -120,10 +122,8 @@ class PrismLinear(nn.Module):
                  bwd_db_params=None, internal_bias: bool = False, dropout: float = 0.0,
                  r_init_scale=1.0, ar_scale_init: float | None = None):
         super().__init__()
-        if activation not in (None, "silu_gate"):
-            if activation == "sigmoid_gate":
-                raise ValueError("activation='sigmoid_gate' is not supported by the sm_100a kernels")
-            raise ValueError(f"Unknown activation {activation!r}, must be one of (None, 'silu_gate')")
+        if activation not in (None,) + _GATED:
+            raise ValueError(f"Unknown activation {activation!r}, must be one of (None, 'silu_gate', 'sigmoid_gate')")
         if input_shuffle or internal_bias or dropout > 0.0:
             raise ValueError("input_shuffle, internal_bias and dropout are not supported by the sm_100a kernels")
         if out_features % group_size != 0:
@@ -140,7 +140,7 @@ class PrismLinear(nn.Module):
         # accepted for signature compatibility; there is one backend and no autotuner
         self.backend, self.autotuning, self.force_rebenchmark = backend, autotuning, force_rebenchmark
 
-        gated = activation == "silu_gate"
+        gated = activation in _GATED
         n_groups = out_features // group_size
         self.weight = nn.Parameter(torch.empty(out_features, in_features), requires_grad=gated)
         self.reconn = nn.Parameter(torch.empty(n_groups * reconn_sz, in_features))
@@ -152,14 +152,14 @@ class PrismLinear(nn.Module):
             self.bias = nn.Parameter(torch.empty(out_features))
         else:
             self.register_parameter("bias", None)
-        self._bwd_scale = 1.0 / _GATED_SILU_BWD_GAIN if gated else 1.0
+        self._bwd_scale = {"silu_gate": 1.0 / _GATED_SILU_BWD_GAIN, "sigmoid_gate": 1.0 / _GATED_SIGMOID_BWD_GAIN}.get(activation, 1.0)
         self.reset_parameters()
 
     def reset_parameters(self) -> None:
         """Same initialisation as the reference (src/cute_prism/_module.py:474-532)."""
         K, r = self.in_features, self.reconn_sz
         nn.init.normal_(self.weight, std=1.0 / math.sqrt(K))
-        if self.activation == "silu_gate":
+        if self.activation in _GATED:
             n_groups = self.out_features // self.group_size
             sigma = 4.0 / math.sqrt(2 * (r - 1)) * self.r_init_scale
             Mb = torch.randn(n_groups, K // r, r, r, device=self.reconn.device, dtype=self.reconn.dtype) * sigma
@@ -174,7 +174,7 @@ class PrismLinear(nn.Module):
 
     def _build_R(self) -> torch.Tensor:
         """R from the stored parameter (reference: src/cute_prism/_module.py:534-577)."""
-        if self.activation == "silu_gate":
+        if self.activation in _GATED:
             return self.reconn if self.ar_scale is None else self.ar_scale * self.reconn
         n_groups = self.out_features // self.group_size
         r = self.reconn_sz

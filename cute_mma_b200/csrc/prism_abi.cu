@@ -93,6 +93,44 @@ __global__ void dbias_final_kernel(const float* __restrict__ partial, void* __re
   else reinterpret_cast<uint16_t*>(out)[c] = (uint16_t)(Elem<DT>::pack(t, 0.f) & 0xffffu);
 }
 
+// Weight folding of the "rw" mode: Bp[n, b*rs + j] = sum_i B[n, b*rs + i] * R[g*rs + i, b*rs + j] with
+// g = n / gs, so that C = A . Bp^T equals the plain-mode layer (A . blockdiag(R_g)^T) . B_g^T.  One thread
+// per (row n, rotation block b): rs contiguous inputs, rs contiguous outputs, fp32 accumulation.
+template <int DT, int RS>
+__global__ void fold_weight_kernel(const uint16_t* __restrict__ B, const uint16_t* __restrict__ R, uint16_t* __restrict__ Bp,
+                                   int N, int K, int gs, long long ldb, long long ldr, long long ldbp) {
+  const int nb = K / RS;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)N * nb) return;
+  const int n = (int)(idx / nb), b = (int)(idx - (long long)n * nb);
+  const int g = n / gs;
+  float x[RS], acc[RS];
+  const uint32_t* bp = reinterpret_cast<const uint32_t*>(B + (long long)n * ldb + b * RS);
+#pragma unroll
+  for (int i = 0; i < RS / 2; ++i) {
+    const float2 v = Elem<DT>::unpack(bp[i]);
+    x[2 * i] = v.x;
+    x[2 * i + 1] = v.y;
+  }
+#pragma unroll
+  for (int j = 0; j < RS; ++j) acc[j] = 0.f;
+  for (int i = 0; i < RS; ++i) {
+    const uint32_t* rp = reinterpret_cast<const uint32_t*>(R + (long long)(g * RS + i) * ldr + b * RS);
+    float xi = x[0];
+#pragma unroll
+    for (int t = 1; t < RS; ++t) xi = (t == i) ? x[t] : xi;
+#pragma unroll
+    for (int j = 0; j < RS / 2; ++j) {
+      const float2 r2 = Elem<DT>::unpack(rp[j]);
+      acc[2 * j] = fmaf(xi, r2.x, acc[2 * j]);
+      acc[2 * j + 1] = fmaf(xi, r2.y, acc[2 * j + 1]);
+    }
+  }
+  uint32_t* op = reinterpret_cast<uint32_t*>(Bp + (long long)n * ldbp + b * RS);
+#pragma unroll
+  for (int j = 0; j < RS / 2; ++j) op[j] = Elem<DT>::pack(acc[2 * j], acc[2 * j + 1]);
+}
+
 static int num_sms();
 static int dbias_splits(int M, int N, int sms) {
   const int strips = (N + 255) / 256;
@@ -139,7 +177,8 @@ static int check_common(const char* fn, int M, int N, int K, int gs, int rs, int
   if (N % gs != 0) return fail(PRISM_ERR_BAD_ARG, "%s: N (%d) must be divisible by group_size (%d)", fn, N, gs);
   if (K % rs != 0) return fail(PRISM_ERR_BAD_ARG, "%s: K (%d) must be divisible by reconn_sz (%d)", fn, K, rs);
   if (dtype != DT_F16 && dtype != DT_BF16) return fail(PRISM_ERR_BAD_ARG, "%s: dtype must be 0 (fp16) or 1 (bf16)", fn);
-  if (gate != GATE_NONE && gate != GATE_SILU) return fail(PRISM_ERR_BAD_ARG, "%s: gate must be 0 (none) or 1 (silu)", fn);
+  if (gate != GATE_NONE && gate != GATE_SILU && gate != GATE_SIGMOID)
+    return fail(PRISM_ERR_BAD_ARG, "%s: gate must be 0 (none), 1 (silu) or 2 (sigmoid)", fn);
   if (effective_block(rs) == 0)
     return fail(PRISM_ERR_UNSUPPORTED, "%s: reconn_sz %d is not supported (supported: 8, 16, 32, 64)", fn, rs);
   if (default_bn(gs) == 0)
@@ -185,7 +224,14 @@ extern "C" size_t prism_workspace_bytes(int kind, int M, int N, int K, int gs, i
   // copy of R the kernels read: widened for rs = 8 (all kinds), halved for the gated dA+dR kernel
   if (rs == 8) bytes += align256(G * 16 * (size_t)K * 2);
   else if (kind == PRISM_KIND_BWD_DADR) bytes += align256(G * (size_t)effective_block(rs) * K * 2);
-  if (kind == PRISM_KIND_FWD) return bytes;
+  if (kind == PRISM_KIND_FWD) {
+    // few tokens: the streaming forward keeps its arrival counters and fp32 partial sums here
+    // (cfg[3] = 1 asks for the general kernel, which needs none)
+    const int path = cfg ? cfg[3] : 0;
+    if (path != 1 && fwd_small_supported(M, N, K, gs, effective_block(rs)) && (path == 2 || fwd_small_preferred(M)))
+      bytes += fwd_small_scratch_bytes(M, N, K, gs, num_sms());
+    return bytes;
+  }
   if (kind == PRISM_KIND_BWD_DB) {
     const int bn = (cfg && cfg[0] > 0) ? cfg[0] : default_bn(gs);
     if (bn <= 0) return bytes;
@@ -247,20 +293,27 @@ extern "C" int prism_fwd(const void* A, const void* B, const void* R, const void
   a.dtype = dtype; a.gate = gate;
   a.lda = lda; a.ldb = ldb; a.ldc = ldc;
   a.R_eff = R; a.ldr = ldr;
+  uint8_t* wp = reinterpret_cast<uint8_t*>(workspace) + PRISM_WORKSPACE_HEADER_BYTES;
   if (rs == 8) {
-    void* re = reinterpret_cast<uint8_t*>(workspace) + PRISM_WORKSPACE_HEADER_BYTES;
-    if ((rc = launch_expand_r8(R, re, N / gs, K, ldr, dtype, s))) return rc;
-    a.R_eff = re; a.ldr = K;
+    if ((rc = launch_expand_r8(R, wp, N / gs, K, ldr, dtype, s))) return rc;
+    a.R_eff = wp; a.ldr = K;
+    wp += align256((size_t)(N / gs) * 16 * K * 2);
   }
-  a.BN = (cfg && cfg[0] > 0) ? cfg[0] : default_bn(gs);
-  a.PM = (cfg && cfg[1] > 0) ? cfg[1] : 16;
-  a.sa = (cfg && cfg[2] > 0) ? cfg[2] : 0;
-  a.sb = (cfg && cfg[3] > 0) ? cfg[3] : 0;
-  if (a.BN % 16 != 0 || a.BN > 256 || gs % a.BN != 0)
-    return fail(PRISM_ERR_BAD_ARG, "%s: tile BN=%d must be a multiple of 16, <= 256 and divide group_size=%d", fn, a.BN, gs);
   a.num_sms = num_sms();
   a.err = reinterpret_cast<int*>(workspace);
   a.stream = s;
+  // few tokens (M <= 128): the streaming kernel, unless cfg[3] = 1 asks for the general one
+  const int path = cfg ? cfg[3] : 0;
+  if (path == 2 && !fwd_small_supported(M, N, K, gs, a.E))
+    return fail(PRISM_ERR_UNSUPPORTED, "%s: the few-token kernel needs M <= 128 and group_size a multiple of 128 (M=%d, group_size=%d)", fn, M, gs);
+  if (path != 1 && fwd_small_supported(M, N, K, gs, a.E) && (path == 2 || fwd_small_preferred(M)))
+    return launch_fwd_small(a, wp);
+  a.BN = (cfg && cfg[0] > 0) ? cfg[0] : default_bn(gs);
+  a.PM = (cfg && cfg[1] > 0) ? cfg[1] : 16;
+  a.sa = (cfg && cfg[2] > 0) ? cfg[2] : 0;
+  a.sb = 0;
+  if (a.BN % 16 != 0 || a.BN > 256 || gs % a.BN != 0)
+    return fail(PRISM_ERR_BAD_ARG, "%s: tile BN=%d must be a multiple of 16, <= 256 and divide group_size=%d", fn, a.BN, gs);
   return launch_fwd(a);
 }
 
@@ -347,8 +400,8 @@ extern "C" int prism_bwd_dadr(const void* dC, const void* A, const void* B, cons
   uint8_t* wp = reinterpret_cast<uint8_t*>(workspace) + PRISM_WORKSPACE_HEADER_BYTES;
   // The kernel reads a copy of R: widened to 16x16 blocks for rs = 8, and halved in the gated mode
   // (its gate math works on S/2, see gate_bwd_pair).  The plain mode with rs >= 16 reads R itself.
-  if (rs == 8 || gate == GATE_SILU) {
-    if ((rc = launch_prep_r(R, wp, N / gs, rs, a.E, K, ldr, gate == GATE_SILU ? 0.5f : 1.0f, dtype, s))) return rc;
+  if (rs == 8 || gate != GATE_NONE) {
+    if ((rc = launch_prep_r(R, wp, N / gs, rs, a.E, K, ldr, gate != GATE_NONE ? 0.5f : 1.0f, dtype, s))) return rc;
     a.R_eff = wp; a.ldr = K;
   }
   wp += align256((size_t)(N / gs) * a.E * K * 2);
@@ -399,4 +452,27 @@ extern "C" int prism_dbias(const void* dC, void* dbias, int M, int N, int dtype,
     else dbias_final_kernel<DT_F16, false><<<blocks, 256, 0, s>>>(partial, dbias, N, used);
   }
   return check_launch("prism_dbias reduce");
+}
+
+extern "C" int prism_fold_weight(const void* B, const void* R, void* Bp, int N, int K, int gs, int rs, int dtype,
+                                 long long ldb, long long ldr, long long ldbp, void* stream) {
+  const char* fn = "prism_fold_weight";
+  int rc;
+  if ((rc = check_common(fn, 0, N, K, gs, rs, dtype, GATE_NONE))) return rc;
+  if ((rc = check_ptr(fn, "B", B, ldb, K))) return rc;
+  if ((rc = check_ptr(fn, "R", R, ldr, K))) return rc;
+  if ((rc = check_ptr(fn, "Bp", Bp, ldbp, K))) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const long long total = (long long)N * (K / rs);
+  const int threads = 128;
+  const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+  const uint16_t* b = reinterpret_cast<const uint16_t*>(B);
+  const uint16_t* r = reinterpret_cast<const uint16_t*>(R);
+  uint16_t* o = reinterpret_cast<uint16_t*>(Bp);
+#define PRISM_FOLD(DT_, RS_) fold_weight_kernel<DT_, RS_><<<blocks, threads, 0, s>>>(b, r, o, N, K, gs, ldb, ldr, ldbp)
+#define PRISM_FOLD_DT(RS_) do { if (dtype == DT_BF16) PRISM_FOLD(DT_BF16, RS_); else PRISM_FOLD(DT_F16, RS_); } while (0)
+  if (rs == 8) PRISM_FOLD_DT(8); else if (rs == 16) PRISM_FOLD_DT(16); else if (rs == 32) PRISM_FOLD_DT(32); else PRISM_FOLD_DT(64);
+#undef PRISM_FOLD_DT
+#undef PRISM_FOLD
+  return check_launch("prism_fold_weight");
 }

@@ -109,10 +109,19 @@ __device__ __forceinline__ void dr_accumulate(float* addr, float x, float y, boo
 //   silu'(S) = (1 + x) / 2,  x = g + t (1 - g)
 // Returns 2 dS = dh a (1 + x) (the factor 2 is undone by the halved R in dS.R and by the scale of
 // the dR reduction) and adds the gate term dh silu(S) of dA to acc0 / acc1.
-template <int DT>
+// sigmoid gate (gate value 2 sigmoid(S) = 1 + t, derivative (1 - t^2) / 2): 2 dS = dh a (1 - t^2).
+template <int DT, int GATE>
 __device__ __forceinline__ uint32_t gate_bwd_pair(uint32_t a2, uint32_t hs, float dh0, float dh1, float& acc0,
                                                   float& acc1) {
   const uint32_t t = Pk<DT>::tanh(hs);
+  if (GATE == GATE_SIGMOID) {
+    const uint32_t g1 = Pk<DT>::fma(t, Pk<DT>::kOne, Pk<DT>::kOne);
+    const uint32_t q1 = Pk<DT>::mul(Pk<DT>::cvt(dh0, dh1), a2);
+    const float2 gf1 = Elem<DT>::unpack(g1);
+    acc0 = fmaf(dh0, gf1.x, acc0);
+    acc1 = fmaf(dh1, gf1.y, acc1);
+    return Pk<DT>::fma(Pk<DT>::mul(q1, t), Pk<DT>::mul(t, Pk<DT>::kNegOne), q1);
+  }
   const uint32_t g = Pk<DT>::fma(hs, t, hs);
   const uint32_t w = Pk<DT>::fma(g, Pk<DT>::kNegOne, Pk<DT>::kOne);
   const uint32_t x = Pk<DT>::fma(t, w, g);
@@ -125,11 +134,20 @@ __device__ __forceinline__ uint32_t gate_bwd_pair(uint32_t a2, uint32_t hs, floa
 
 // The same in fp32 (hs0, hs1 = S/2 as delivered by the rotation): one rounding, when 2 dS is
 // converted to 16 bits for the dS . R and dR products.
-template <int DT>
+template <int DT, int GATE>
 __device__ __forceinline__ uint32_t gate_bwd_pair_f32(uint32_t a2, float hs0, float hs1, float dh0, float dh1, float& acc0,
                                                       float& acc1) {
   const float2 hs = make_float2(hs0, hs1), dh = make_float2(dh0, dh1), one = make_float2(1.f, 1.f);
   const float2 t = make_float2(tanh_approx(hs0), tanh_approx(hs1));
+  if (GATE == GATE_SIGMOID) {
+    const float2 q1 = mul2(dh, Elem<DT>::unpack(a2));
+    const float2 acc1s = fma2(dh, make_float2(1.f + t.x, 1.f + t.y), make_float2(acc0, acc1));
+    acc0 = acc1s.x;
+    acc1 = acc1s.y;
+    const float2 qt = mul2(q1, t);
+    const float2 ds1 = fma2(qt, make_float2(-t.x, -t.y), q1);
+    return Pk<DT>::cvt_hw(ds1.x, ds1.y);
+  }
   const float2 g = fma2(hs, t, hs);
   const float2 w = fma2(g, make_float2(-1.f, -1.f), one);
   const float2 x = fma2(t, w, g);
@@ -198,7 +216,7 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   constexpr int KS = E / 16;       // 16-wide steps per rotation block
   constexpr int NB = 64 / E;       // rotation blocks per 64-column tile
   constexpr int NBLK = 128 / E;    // rotation blocks of the tile's 128 features
-  constexpr bool kGated = (GATE == GATE_SILU);
+  constexpr bool kGated = (GATE != GATE_NONE);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -512,14 +530,14 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 float* d = (e >> 1) ? d1 : d0;
                 const float h0 = __uint_as_float(sv[i][2 * e]), h1 = __uint_as_float(sv[i][2 * e + 1]);
                 if (gate_in_f32<DT>()) {
-                  dsf[i][e] = gate_bwd_pair_f32<DT>(af[i][e], h0, h1, x0, x1, d[(e & 1) * 2], d[(e & 1) * 2 + 1]);
+                  dsf[i][e] = gate_bwd_pair_f32<DT, GATE>(af[i][e], h0, h1, x0, x1, d[(e & 1) * 2], d[(e & 1) * 2 + 1]);
                 } else {
 #if PRISM_K2_CVT_HW
                   const uint32_t hs = Pk<DT>::cvt_hw(h0, h1);
 #else
                   const uint32_t hs = Pk<DT>::cvt(h0, h1);
 #endif
-                  dsf[i][e] = gate_bwd_pair<DT>(af[i][e], hs, x0, x1, d[(e & 1) * 2], d[(e & 1) * 2 + 1]);
+                  dsf[i][e] = gate_bwd_pair<DT, GATE>(af[i][e], hs, x0, x1, d[(e & 1) * 2], d[(e & 1) * 2 + 1]);
                 }
               } else {
                 dsf[i][e] = Pk<DT>::cvt(x0, x1);
@@ -792,20 +810,20 @@ int launch_bwd_dadr(const DadrArgs& a) {
 
   using KernT = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, DadrParams);
   KernT kern = nullptr;
-#define PRISM_PICK(E_)                                                                               \
-  kern = (a.dtype == DT_BF16)                                                                        \
-             ? (a.gate == GATE_SILU ? (KernT)prism_bwd_dadr_kernel<DT_BF16, GATE_SILU, E_> : (KernT)prism_bwd_dadr_kernel<DT_BF16, GATE_NONE, E_>) \
-             : (a.gate == GATE_SILU ? (KernT)prism_bwd_dadr_kernel<DT_F16, GATE_SILU, E_> : (KernT)prism_bwd_dadr_kernel<DT_F16, GATE_NONE, E_>)
+#define PRISM_PICK_G(DT_, E_)                                                                    \
+  (a.gate == GATE_SILU ? (KernT)prism_bwd_dadr_kernel<DT_, GATE_SILU, E_>                                       \
+                       : a.gate == GATE_SIGMOID ? (KernT)prism_bwd_dadr_kernel<DT_, GATE_SIGMOID, E_> : (KernT)prism_bwd_dadr_kernel<DT_, GATE_NONE, E_>)
+#define PRISM_PICK(E_) kern = (a.dtype == DT_BF16) ? PRISM_PICK_G(DT_BF16, E_) : PRISM_PICK_G(DT_F16, E_)
   if (a.E == 16) { PRISM_PICK(16); } else if (a.E == 32) { PRISM_PICK(32); } else { PRISM_PICK(64); }
+#undef PRISM_PICK_G
 #undef PRISM_PICK
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-  if (e != cudaSuccess) return fail(PRISM_ERR_CUDA, "bwd_dadr: cannot set %d B of shared memory: %s", smem_bytes, cudaGetErrorString(e));
+  if ((rc = set_max_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes, "bwd_dadr"))) return rc;
   dim3 grid(2 * (p.n_main + p.n_extra), 1, 1);   // the two CTAs of a pair are neighbours
   kern<<<grid, dadr::kThreads, smem_bytes, a.stream>>>(tmA, tmRr, tmRd, tmdC, tmB, p);
   if ((rc = check_launch("prism_bwd_dadr"))) return rc;
 
   // gated mode: the kernel formed 2 dS against the halved R tiles, so the dR partials are doubled
-  const float r_scale = (a.gate == GATE_SILU) ? 0.5f * a.scale : a.scale;
+  const float r_scale = (a.gate != GATE_NONE) ? 0.5f * a.scale : a.scale;
   const long long pairs = (long long)p.G * a.rs * a.K / 2;
   const int threads = 256;
   const long long blocks = (pairs + threads - 1) / threads;

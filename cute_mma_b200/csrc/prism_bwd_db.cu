@@ -362,14 +362,14 @@ int launch_bwd_db(const DbArgs& a) {
 
   using KernT = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, DbParams);
   KernT kern = nullptr;
-#define PRISM_PICK(E_)                                                                               \
-  kern = (a.dtype == DT_BF16)                                                                        \
-             ? (a.gate == GATE_SILU ? (KernT)prism_bwd_db_kernel<DT_BF16, GATE_SILU, E_> : (KernT)prism_bwd_db_kernel<DT_BF16, GATE_NONE, E_>) \
-             : (a.gate == GATE_SILU ? (KernT)prism_bwd_db_kernel<DT_F16, GATE_SILU, E_> : (KernT)prism_bwd_db_kernel<DT_F16, GATE_NONE, E_>)
+#define PRISM_PICK_G(DT_, E_)                                                                    \
+  (a.gate == GATE_SILU ? (KernT)prism_bwd_db_kernel<DT_, GATE_SILU, E_>                                       \
+                       : a.gate == GATE_SIGMOID ? (KernT)prism_bwd_db_kernel<DT_, GATE_SIGMOID, E_> : (KernT)prism_bwd_db_kernel<DT_, GATE_NONE, E_>)
+#define PRISM_PICK(E_) kern = (a.dtype == DT_BF16) ? PRISM_PICK_G(DT_BF16, E_) : PRISM_PICK_G(DT_F16, E_)
   if (a.E == 16) { PRISM_PICK(16); } else if (a.E == 32) { PRISM_PICK(32); } else { PRISM_PICK(64); }
+#undef PRISM_PICK_G
 #undef PRISM_PICK
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-  if (e != cudaSuccess) return fail(PRISM_ERR_CUDA, "bwd_db: cannot set %d B of shared memory: %s", smem_bytes, cudaGetErrorString(e));
+  if ((rc = set_max_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes, "bwd_db"))) return rc;
   const int rows = a.N / a.BN;
   // one launch over the n-tile rows [nt0, nt0 + nrows) with the token range of every tile split `splits` ways
   auto launch = [&](int nt0, int nrows, int splits) -> int {

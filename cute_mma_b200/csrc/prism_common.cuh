@@ -29,7 +29,7 @@ namespace prism {
 
 // status codes (PRISM_OK, PRISM_ERR_*) come from the public header
 enum : int { DT_F16 = 0, DT_BF16 = 1 };
-enum : int { GATE_NONE = 0, GATE_SILU = 1 };
+enum : int { GATE_NONE = 0, GATE_SILU = 1, GATE_SIGMOID = 2 };   // plain, A*silu(S), A*2*sigmoid(S)
 
 // ----------------------------------------------------------------------------
 // small helpers
@@ -144,6 +144,23 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         "r"(c1)
       : "memory");
 }
+// The same with an L2 eviction-priority hint (a policy made by l2_policy_*): read-once streams
+// are loaded evict-first so that they do not push reused data out of L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4}], [%2], %5;"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1),
+        "l"(policy)
+      : "memory");
+}
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* smem_src, int c0,
                                              int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
@@ -200,6 +217,41 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ----------------------------------------------------------------------------
+// Single-CTA tcgen05 (cta_group::1): M = 128 rows of the A operand, accumulator in this CTA's TMEM.
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc_cta(uint32_t* dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_cta() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_cta(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_cta_lh(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive (count 1) on this CTA's barrier once all MMAs issued so far by this thread are complete.
+__device__ __forceinline__ void umma_commit_cta(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
 }
 
 // ----------------------------------------------------------------------------
@@ -596,20 +648,22 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[
 }
 
 
-// H for one pair of elements from fp32 S and packed 16-bit A: A*silu(S), or S in plain mode.
-// silu(s) = hs + hs tanh(hs) with hs = s/2: one special-function operation per element, no division.
+// H for one pair of elements from fp32 S and packed 16-bit A: A*silu(S), A*2*sigmoid(S), or S in
+// plain mode.  With hs = s/2 and t = tanh(hs): silu(s) = hs + hs t and 2 sigmoid(s) = 1 + t: one
+// special-function operation per element, no division.
 template <int DT, int GATE, bool HW = false>
 __device__ __forceinline__ uint32_t gate_pair(uint32_t a2, float s0, float s1) {
-  if (GATE == GATE_SILU) {
-    if (gate_in_f32<DT>()) {
-      const float2 hs = mul2(make_float2(s0, s1), make_float2(0.5f, 0.5f));
-      const float2 t = make_float2(tanh_approx(hs.x), tanh_approx(hs.y));
-      const float2 h = mul2(Elem<DT>::unpack(a2), fma2(hs, t, hs));
-      return Pk<DT>::cvt_hw(h.x, h.y);
-    }
-    return Pk<DT>::mul(a2, silu_pair<DT, HW>(s0, s1));
+  if (GATE == GATE_NONE) return Pk<DT>::cvt(s0, s1);
+  if (gate_in_f32<DT>()) {
+    const float2 hs = mul2(make_float2(s0, s1), make_float2(0.5f, 0.5f));
+    const float2 t = make_float2(tanh_approx(hs.x), tanh_approx(hs.y));
+    const float2 a = Elem<DT>::unpack(a2);
+    const float2 h = (GATE == GATE_SILU) ? mul2(a, fma2(hs, t, hs)) : fma2(a, t, a);
+    return Pk<DT>::cvt_hw(h.x, h.y);
   }
-  return Pk<DT>::cvt(s0, s1);
+  if (GATE == GATE_SILU) return Pk<DT>::mul(a2, silu_pair<DT, HW>(s0, s1));
+  const uint32_t hs = Pk<DT>::mul(HW ? Pk<DT>::cvt_hw(s0, s1) : Pk<DT>::cvt(s0, s1), Pk<DT>::kHalf);
+  return Pk<DT>::fma(a2, Pk<DT>::tanh(hs), a2);
 }
 
 // TMEM -> registers in the mma.sync accumulator layout: 16 lanes x 16 columns; thread t gets
@@ -638,7 +692,7 @@ __device__ __forceinline__ void gate_rows16_tmem(uint32_t s_tmem, uint32_t tile,
   uint32_t s[4][8], af[4][4], h[4][4];
 #pragma unroll
   for (int pc = 0; pc < 4; ++pc) tmem_ld_16x256b_x2(s_tmem + pc * 16, s[pc]);
-  if (GATE == GATE_SILU) {
+  if (GATE != GATE_NONE) {
 #pragma unroll
     for (int pc = 0; pc < 4; ++pc) ldmatrix_x4(tile + sw128_offset(a_row, pc * 2 + (mat >> 1)), af[pc]);
   } else {
@@ -648,10 +702,10 @@ __device__ __forceinline__ void gate_rows16_tmem(uint32_t s_tmem, uint32_t tile,
   tmem_ld_wait();
 #pragma unroll
   for (int pc = 0; pc < 4; ++pc) {
-    h[pc][0] = gate_pair<DT, GATE, (PRISM_FWD_CVT_HW != 0) && GATE == GATE_SILU>(af[pc][0], __uint_as_float(s[pc][0]), __uint_as_float(s[pc][1]));
-    h[pc][1] = gate_pair<DT, GATE, (PRISM_FWD_CVT_HW != 0) && GATE == GATE_SILU>(af[pc][1], __uint_as_float(s[pc][2]), __uint_as_float(s[pc][3]));
-    h[pc][2] = gate_pair<DT, GATE, (PRISM_FWD_CVT_HW != 0) && GATE == GATE_SILU>(af[pc][2], __uint_as_float(s[pc][4]), __uint_as_float(s[pc][5]));
-    h[pc][3] = gate_pair<DT, GATE, (PRISM_FWD_CVT_HW != 0) && GATE == GATE_SILU>(af[pc][3], __uint_as_float(s[pc][6]), __uint_as_float(s[pc][7]));
+    h[pc][0] = gate_pair<DT, GATE, (PRISM_FWD_CVT_HW != 0) && GATE != GATE_NONE>(af[pc][0], __uint_as_float(s[pc][0]), __uint_as_float(s[pc][1]));
+    h[pc][1] = gate_pair<DT, GATE, (PRISM_FWD_CVT_HW != 0) && GATE != GATE_NONE>(af[pc][1], __uint_as_float(s[pc][2]), __uint_as_float(s[pc][3]));
+    h[pc][2] = gate_pair<DT, GATE, (PRISM_FWD_CVT_HW != 0) && GATE != GATE_NONE>(af[pc][2], __uint_as_float(s[pc][4]), __uint_as_float(s[pc][5]));
+    h[pc][3] = gate_pair<DT, GATE, (PRISM_FWD_CVT_HW != 0) && GATE != GATE_NONE>(af[pc][3], __uint_as_float(s[pc][6]), __uint_as_float(s[pc][7]));
   }
 #pragma unroll
   for (int pc = 0; pc < 4; ++pc) tmem_st_frag16x16(h_tmem + pc * 8, h[pc]);
@@ -673,7 +727,7 @@ __device__ __forceinline__ void gate_rows16_tmem_smem(uint32_t s_tmem, uint32_t 
   uint32_t s[4][8], af[4][4], h[4][4];
 #pragma unroll
   for (int pc = 0; pc < 4; ++pc) tmem_ld_16x256b_x2(s_tmem + (pc / KS) * blk_stride + (pc % KS) * 16, s[pc]);
-  if (GATE == GATE_SILU) {
+  if (GATE != GATE_NONE) {
 #pragma unroll
     for (int pc = 0; pc < 4; ++pc) ldmatrix_x4(tile + sw128_offset(a_row, pc * 2 + (mat >> 1)), af[pc]);
   } else {
@@ -688,10 +742,10 @@ __device__ __forceinline__ void gate_rows16_tmem_smem(uint32_t s_tmem, uint32_t 
   }
 #pragma unroll
   for (int pc = 0; pc < 4; ++pc) {
-    h[pc][0] = gate_pair<DT, GATE, (PRISM_DB_CVT_HW != 0) && GATE == GATE_SILU>(af[pc][0], __uint_as_float(s[pc][0]), __uint_as_float(s[pc][1]));
-    h[pc][1] = gate_pair<DT, GATE, (PRISM_DB_CVT_HW != 0) && GATE == GATE_SILU>(af[pc][1], __uint_as_float(s[pc][2]), __uint_as_float(s[pc][3]));
-    h[pc][2] = gate_pair<DT, GATE, (PRISM_DB_CVT_HW != 0) && GATE == GATE_SILU>(af[pc][2], __uint_as_float(s[pc][4]), __uint_as_float(s[pc][5]));
-    h[pc][3] = gate_pair<DT, GATE, (PRISM_DB_CVT_HW != 0) && GATE == GATE_SILU>(af[pc][3], __uint_as_float(s[pc][6]), __uint_as_float(s[pc][7]));
+    h[pc][0] = gate_pair<DT, GATE, (PRISM_DB_CVT_HW != 0) && GATE != GATE_NONE>(af[pc][0], __uint_as_float(s[pc][0]), __uint_as_float(s[pc][1]));
+    h[pc][1] = gate_pair<DT, GATE, (PRISM_DB_CVT_HW != 0) && GATE != GATE_NONE>(af[pc][1], __uint_as_float(s[pc][2]), __uint_as_float(s[pc][3]));
+    h[pc][2] = gate_pair<DT, GATE, (PRISM_DB_CVT_HW != 0) && GATE != GATE_NONE>(af[pc][2], __uint_as_float(s[pc][4]), __uint_as_float(s[pc][5]));
+    h[pc][3] = gate_pair<DT, GATE, (PRISM_DB_CVT_HW != 0) && GATE != GATE_NONE>(af[pc][3], __uint_as_float(s[pc][6]), __uint_as_float(s[pc][7]));
   }
 #pragma unroll
   for (int pc = 0; pc < 4; ++pc) stmatrix_x4(tile + sw128_offset(a_row, pc * 2 + (mat >> 1)), h[pc]);

@@ -67,6 +67,11 @@ extern "C" int prism_fwd_noalloc(const void* A, const void* B, const void* R, co
                                  int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
                                  long long lda, long long ldb, long long ldr, long long ldc,
                                  const int* cfg, int* device_status, void* stream) {
+  // the general kernel is the one whose scratch need is small and fixed (status word, 16-wide copy of R):
+  // the few-token streaming kernel, which prism_fwd would pick for M <= 128, keeps partial sums whose
+  // size grows with the shape, so this entry point never takes it
+  int cfg_general[4] = {cfg ? cfg[0] : 0, cfg ? cfg[1] : 0, cfg ? cfg[2] : 0, 1};
+  cfg = cfg_general;
   // refuse what does not fit before touching the device
   const size_t need = prism_workspace_bytes(PRISM_KIND_FWD, M, N, K, group_size, reconn_sz, dtype, cfg);
   if (need > (size_t)PRISM_NOALLOC_SCRATCH_BYTES)

@@ -24,6 +24,14 @@ struct FwdArgs {
 };
 int launch_fwd(const FwdArgs& a);
 
+// Few-token forward (M <= 128, group_size a multiple of 128): B tiles as the M dimension of the MMA,
+// every SM streams an equal share of B once (prism_fwd_small.cu).  `scratch`: fwd_small_scratch_bytes
+// bytes after the workspace's status header and rotation copy.
+bool fwd_small_supported(int M, int N, int K, int gs, int E);
+bool fwd_small_preferred(int M);   // token counts for which it is the default choice
+size_t fwd_small_scratch_bytes(int M, int N, int K, int gs, int num_sms);
+int launch_fwd_small(const FwdArgs& a, void* scratch);
+
 // R [(G*8), K] -> R_eff [(G*16), K]: two neighbouring 8x8 blocks become one 16x16
 // block-diagonal block, so that every rotation is a 16-wide tensor-core product.
 int launch_expand_r8(const void* R, void* R_eff, int G, int K, long long ldr, int dtype, cudaStream_t stream);

@@ -21,8 +21,8 @@ from cute_mma_b200 import (PrismLinear, backward, forward, mup_fix_prism_shapes,
                            validate_kernel_params, validate_tensor_params)
 
 BACKENDS = ("cute", "cublas", "pytorch")   # accepted, all served by the one sm_100a backend
-MODES = ("ar",)
-ACTIVATIONS = (None, "silu_gate")
+MODES = ("ar", "rw")
+ACTIVATIONS = (None, "silu_gate", "sigmoid_gate")
 
 
 class CompilationError(RuntimeError):

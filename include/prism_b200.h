@@ -17,7 +17,9 @@
  *     src/cute_prism/_validate.py:26-30; the tensor-core tiles here are 16 wide) and reconn_sz one
  *     of 8, 16, 32, 64;
  *   - gate 0 = plain "ar" mode (C_g = (A.blockdiag(R_g)^T) B_g^T), 1 = silu_gate
- *     (C_g = (A * silu(A.blockdiag(R_g)^T)) B_g^T);
+ *     (C_g = (A * silu(A.blockdiag(R_g)^T)) B_g^T), 2 = sigmoid_gate
+ *     (C_g = (A * 2 sigmoid(A.blockdiag(R_g)^T)) B_g^T; the reference has it in its cuBLAS
+ *     and PyTorch backends only, src/cute_prism/_pytorch_backend.py:157-163);
  *   - the library never allocates or frees device memory: outputs and the workspace
  *     belong to the caller.  The workspace must be 256-byte aligned, at least
  *     prism_workspace_bytes(...) long, and its first 256 bytes (the status header)
@@ -61,8 +63,12 @@ extern "C" {
 /* size of the library's built-in scratch array used by prism_fwd_noalloc: 8 MiB + the status header */
 #define PRISM_NOALLOC_SCRATCH_BYTES (8 * 1024 * 1024 + 256)
 
-/* Forward.  bias: [N] in the same dtype, or NULL.  cfg (4 ints, 0 = default): {BN, PM, stages, unused}:
- * N tile (divides group_size, <= 256), row tiles per rasterisation panel, shared-memory stages. */
+/* Forward.  bias: [N] in the same dtype, or NULL.  cfg (4 ints, 0 = default): {BN, PM, stages, path}:
+ * N tile (divides group_size, <= 256), row tiles per rasterisation panel, shared-memory stages, and the
+ * kernel: 0 = by shape, 1 = the general tiled kernel, 2 = the few-token streaming kernel (M <= 128 and
+ * group_size a multiple of 128; picked by default up to 48 tokens).  The streaming kernel cuts B into
+ * equal shares for all SMs, keeps fp32 partial sums of the shares in the workspace and adds them in a
+ * fixed order, so its result is bit-stable; ask prism_workspace_bytes with the same cfg. */
 int prism_fwd(const void* A, const void* B, const void* R, const void* bias, void* C,
               int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
               long long lda, long long ldb, long long ldr, long long ldc,
@@ -120,6 +126,13 @@ int prism_bwd_db(const void* dC, const void* A, const void* R, void* dB,
  * dbias_dtype: PRISM_DTYPE_SAME or PRISM_DTYPE_F32.  Workspace: prism_workspace_bytes(PRISM_KIND_DBIAS, M, N, ...). */
 int prism_dbias(const void* dC, void* dbias, int M, int N, int dtype, int dbias_dtype, long long lddc,
                 void* workspace, size_t workspace_bytes, void* stream);
+
+/* Weight folding of the reference's "rw" mode (inference with the rotation folded into the weight,
+ * src/cute_prism/_pytorch_backend.py:115-124): Bp [N,K] with
+ * Bp[n, b*rs + j] = sum_i B[n, b*rs + i] * R[(n/group_size)*rs + i, b*rs + j], so that A . Bp^T equals the
+ * plain-mode forward.  No workspace.  The dense product that follows is an ordinary GEMM. */
+int prism_fold_weight(const void* B, const void* R, void* Bp, int N, int K, int group_size, int reconn_sz,
+                      int dtype, long long ldb, long long ldr, long long ldbp, void* stream);
 
 /* Bytes of workspace the given call needs (kind = PRISM_KIND_*), header included. */
 size_t prism_workspace_bytes(int kind, int M, int N, int K, int group_size, int reconn_sz,

@@ -6,18 +6,20 @@ package.  It restates, in plain torch tensor algebra, what the reference compute
 ``src/cute_prism/_pytorch_backend.py``:
 
 * forward  (``pytorch_forward``,  lines 78-176):  per output group g
-  ``S_g = A . blockdiag(R_g)^T``;  plain mode ``H_g = S_g``; gated mode
-  ``H_g = A * silu(S_g)``;  ``C[:, g] = H_g @ B_g^T``.
+  ``S_g = A . blockdiag(R_g)^T``;  plain mode ``H_g = S_g``; gated modes
+  ``H_g = A * silu(S_g)`` (silu_gate) or ``H_g = A * 2 sigmoid(S_g)`` (sigmoid_gate, lines 157-163);
+  ``C[:, g] = H_g @ B_g^T``.
 * backward (``pytorch_backward``, lines 179-321):  ``dH_g = dC_g @ B_g``;
-  gated: ``dS = dH * A * silu'(S)``, ``dA += dH * silu(S) + blockdiag(dS) . R_g``,
-  ``dB_g = dC_g^T @ H_g``;  plain: ``dS = dH``, ``dA += blockdiag(dS) . R_g``, no dB;
+  gated: ``dS = dH * A * gate'(S)``, ``dA += dH * gate(S) + blockdiag(dS) . R_g``,
+  ``dB_g = dC_g^T @ H_g`` (gate = silu, or 2 sigmoid with derivative 2 sigmoid (1 - sigmoid), lines 250-262);
+  plain: ``dS = dH``, ``dA += blockdiag(dS) . R_g``, no dB;
   both: ``dR_g[block b] = dS_b^T @ A_b``.
 
 Parity pin: ``tests/golden/make_golden.py`` imports the reference package itself,
 runs its pytorch backend on seeded inputs and stores inputs + outputs under
 ``tests/golden/``; ``tests/test_oracle.py`` checks this file against those vectors
 (and against torch autograd in float64).  Only the features on the accelerated path
-are restated: modes ``ar`` / ``silu_gate``; no dropout, shuffle, internal bias or rw mode.
+are restated: mode ``ar`` with ``silu_gate`` / ``sigmoid_gate``; no dropout, shuffle, internal bias or rw mode.
 """
 from __future__ import annotations
 
@@ -47,10 +49,21 @@ def rotate_t(dS: torch.Tensor, Rg_blocks: torch.Tensor) -> torch.Tensor:
     return torch.einsum("mbi,bij->mbj", dS.reshape(M, nb, rs), Rg_blocks).reshape(M, K)
 
 
+GATES = (None, "silu_gate", "sigmoid_gate")
+
+
+def _gate(S, activation):
+    """(gate(S), gate'(S)) of a gated mode."""
+    sig = torch.sigmoid(S)
+    if activation == "silu_gate":
+        return S * sig, sig * (1.0 + S * (1.0 - sig))
+    return 2.0 * sig, 2.0 * sig * (1.0 - sig)
+
+
 def prism_forward(A, B, R, group_size, reconn_sz, activation=None, bias=None):
-    """C (M, N) in the dtype of A.  Follows ``pytorch_forward`` (ar mode, optional silu_gate)."""
-    if activation not in (None, "silu_gate"):
-        raise ValueError(f"oracle restates None and 'silu_gate' only, got {activation!r}")
+    """C (M, N) in the dtype of A.  Follows ``pytorch_forward`` (ar mode, optional gate)."""
+    if activation not in GATES:
+        raise ValueError(f"oracle restates {GATES} only, got {activation!r}")
     M, K = A.shape
     N = B.shape[0]
     G = N // group_size
@@ -58,7 +71,7 @@ def prism_forward(A, B, R, group_size, reconn_sz, activation=None, bias=None):
     C = torch.empty(M, N, dtype=A.dtype, device=A.device)
     for g in range(G):
         S = rotate(A, Rb[g])
-        H = A * (S * torch.sigmoid(S)) if activation == "silu_gate" else S
+        H = A * _gate(S, activation)[0] if activation is not None else S
         C[:, g * group_size:(g + 1) * group_size] = H @ B[g * group_size:(g + 1) * group_size].T
     if bias is not None:
         C = C + bias
@@ -67,14 +80,14 @@ def prism_forward(A, B, R, group_size, reconn_sz, activation=None, bias=None):
 
 def prism_backward(dC, A, B, R, group_size, reconn_sz, activation=None):
     """(dA, dR, dB-or-None).  Follows ``pytorch_backward``."""
-    if activation not in (None, "silu_gate"):
-        raise ValueError(f"oracle restates None and 'silu_gate' only, got {activation!r}")
+    if activation not in GATES:
+        raise ValueError(f"oracle restates {GATES} only, got {activation!r}")
     M, K = A.shape
     N = B.shape[0]
     G = N // group_size
     rs = reconn_sz
     nb = K // rs
-    gated = activation == "silu_gate"
+    gated = activation is not None
     Rb = _blocks(R, G, rs)
     dA = torch.zeros_like(A)
     dR = torch.empty_like(R)
@@ -86,9 +99,7 @@ def prism_backward(dC, A, B, R, group_size, reconn_sz, activation=None):
         dH = dC_g @ B[sl]
         if gated:
             S = rotate(A, Rb[g])
-            sig = torch.sigmoid(S)
-            gate = S * sig
-            gate_d = sig * (1.0 + S * (1.0 - sig))
+            gate, gate_d = _gate(S, activation)
             dB[sl] = dC_g.T @ (A * gate)
             dS = dH * A * gate_d
             dA += dH * gate

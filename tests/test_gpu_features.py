@@ -191,3 +191,58 @@ def test_bounded_wait_runs_out_and_is_reported():
                            p(ws), ws.numel(), stream))
     assert L.prism_status(p(ws), stream) == 0
     assert O.rel_err(C.float(), O.prism_forward(A.float(), B.float(), R.float(), gs, rs, "silu_gate")) < TOL
+
+
+@pytest.mark.parametrize("shape", [
+    (1, 256, 256, 256, 16), (7, 200, 384, 128, 8), (16, 512, 512, 256, 16), (17, 320, 256, 128, 32),
+    (100, 576, 512, 256, 64), (128, 1024, 1024, 256, 16), (64, 256, 1024, 512, 16), (128, 4096, 1792, 256, 16),
+], ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("act", [None, "silu_gate"])
+def test_few_token_streaming_forward(shape, act):
+    """The streaming kernel that serves M <= 128 (B tiles as the M dimension of the MMA, K shared by
+    several CTAs, partial sums added in a fixed order): against the oracle, against the general
+    kernel, with a bias, and bit-identical over repeats."""
+    M, K, N, gs, rs = shape
+    dt = torch.bfloat16 if (M + rs) % 3 else torch.float16
+    A, B, R, _ = _inputs(M, K, N, gs, rs, dt, seed=M + K)
+    bias = (torch.randn(N, device=DEV) * 0.5).to(dt)
+    ref = O.prism_forward(A.float(), B.float(), R.float(), gs, rs, act, bias=bias.float())
+    C, _ = cp.forward(A, B, R, gs, rs, activation=act, bias=bias, tile_cfg=[0, 0, 0, 2])   # streaming kernel, forced
+    Cg, _ = cp.forward(A, B, R, gs, rs, activation=act, bias=bias, tile_cfg=[0, 0, 0, 1])  # general kernel
+    Cd, _ = cp.forward(A, B, R, gs, rs, activation=act, bias=bias)                         # default choice
+    cp.check_device_status()
+    assert torch.isfinite(C).all()
+    assert O.rel_err(C.float(), ref) < TOL and O.rel_err(Cg.float(), ref) < TOL
+    assert torch.equal(Cd, C if M <= 48 else Cg), "up to 48 tokens the streaming kernel is the default"
+    for _ in range(5):
+        C2, _ = cp.forward(A, B, R, gs, rs, activation=act, bias=bias)
+        assert torch.equal(C2, C)
+    cp.check_device_status()
+
+
+def test_few_token_kernel_is_refused_where_it_does_not_apply():
+    A, B, R, _ = _inputs(200, 256, 256, 256, 16, torch.bfloat16)
+    with pytest.raises(_lib.PrismError):
+        cp.forward(A, B, R, 256, 16, tile_cfg=[0, 0, 0, 2])           # more than 128 tokens
+    A, B, R, _ = _inputs(16, 256, 192, 64, 16, torch.bfloat16)
+    C, _ = cp.forward(A, B, R, 64, 16)                                # group size 64: general kernel
+    assert O.rel_err(C.float(), O.prism_forward(A.float(), B.float(), R.float(), 64, 16, None)) < TOL
+
+
+@pytest.mark.parametrize("shape", [(64, 256, 512, 256, 8), (200, 512, 768, 128, 16), (33, 256, 256, 64, 32), (128, 128, 128, 32, 64)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_rw_mode_weight_folding(shape):
+    """mode='rw' (the reference's inference form): the folded weight gives the plain-mode forward."""
+    M, K, N, gs, rs = shape
+    dt = torch.bfloat16 if rs != 8 else torch.float16
+    A, B, R, _ = _inputs(M, K, N, gs, rs, dt, seed=61)
+    Bp = cp.fold_weight(B, R, gs, rs)
+    G, nb = N // gs, K // rs
+    Rb = R.float().reshape(G, rs, nb, rs).permute(0, 2, 1, 3)                       # (G, nb, i, j)
+    ref_Bp = torch.einsum("gnbi,gbij->gnbj", B.float().reshape(G, gs, nb, rs), Rb).reshape(N, K)
+    assert O.rel_err(Bp.float(), ref_Bp) < 1e-2
+    C_rw, seeds = cp.forward(A, B, R, gs, rs, mode="rw")
+    C_ar, _ = cp.forward(A, B, R, gs, rs, mode="ar")
+    ref = O.prism_forward(A.float(), B.float(), R.float(), gs, rs, None)
+    assert seeds == [] and O.rel_err(C_rw.float(), ref) < TOL and O.rel_err(C_ar.float(), ref) < TOL
+    cp.check_device_status()

@@ -28,10 +28,12 @@ def test_forward_rejects_cpu_and_bad_options():
         cp.forward(A.half(), B.half(), R.half(), 32, 8)
     with pytest.raises(ValueError, match="activation"):
         cp.forward(A, B, R, 32, 8, activation="relu")
-    with pytest.raises(ValueError, match="sigmoid_gate"):
-        cp.forward(A, B, R, 32, 8, activation="sigmoid_gate")
+    with pytest.raises(ValueError, match="CUDA"):
+        cp.forward(A, B, R, 32, 8, activation="sigmoid_gate")   # a known activation: fails on the device check
     with pytest.raises(ValueError, match="mode"):
-        cp.forward(A, B, R, 32, 8, mode="rw")
+        cp.forward(A, B, R, 32, 8, mode="wr")
+    with pytest.raises(ValueError, match="gated"):
+        cp.forward(A, B, R, 32, 8, mode="rw", activation="silu_gate")
     with pytest.raises(ValueError, match="internal_bias"):
         cp.forward(A, B, R, 32, 8, activation="silu_gate", internal_bias=torch.zeros(2, 64))
     with pytest.raises(ValueError):
@@ -73,7 +75,9 @@ def test_prism_linear_construction_and_state():
     m2 = cp.PrismLinear(64, 128, group_size=32, reconn_sz=8)
     m2.load_state_dict(m.state_dict())
     assert torch.equal(m2.weight, m.weight)
-    for bad in (dict(activation="sigmoid_gate"), dict(input_shuffle=True), dict(dropout=0.1),
+    sg = cp.PrismLinear(64, 128, group_size=32, reconn_sz=16, activation="sigmoid_gate")
+    assert sg.weight.requires_grad and abs(sg._bwd_scale - 1 / 1.15) < 1e-12
+    for bad in (dict(input_shuffle=True), dict(dropout=0.1),
                 dict(internal_bias=True), dict(activation="tanh")):
         with pytest.raises(ValueError):
             cp.PrismLinear(64, 128, 32, 16, **bad)

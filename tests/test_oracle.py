@@ -24,7 +24,7 @@ def test_oracle_matches_reference_small(path):
     M, K, N, gs, rs = [int(v) for v in z["meta"]]
     A, B, R, dC = _t(z["A"]), _t(z["B"]), _t(z["R"]), _t(z["dC"])
     tol = 1e-12 if A.dtype == torch.float64 else 2e-5
-    for act, tag in ((None, "plain"), ("silu_gate", "gated")):
+    for act, tag in ((None, "plain"), ("silu_gate", "gated"), ("sigmoid_gate", "sgate")):
         C = O.prism_forward(A, B, R, gs, rs, act)
         dA, dR, dB = O.prism_backward(dC, A, B, R, gs, rs, act)
         assert O.rel_err(C, _t(z[f"C_{tag}"])) < tol
@@ -45,7 +45,7 @@ def test_oracle_matches_reference_config0(seed):
     chk = np.array([A.double().sum().item(), B.double().sum().item(), R.double().sum().item(),
                     dC.double().sum().item()])
     np.testing.assert_allclose(chk, z["input_checksum"], rtol=1e-9, atol=1e-9)
-    for act, tag in ((None, "plain"), ("silu_gate", "gated")):
+    for act, tag in ((None, "plain"), ("silu_gate", "gated"), ("sigmoid_gate", "sgate")):
         C = O.prism_forward(A, B, R, gs, rs, act)
         dA, dR, dB = O.prism_backward(dC, A, B, R, gs, rs, act)
         assert O.rel_err(C[::16, ::16], _t(z[f"C_{tag}"])) < 2e-5
@@ -55,7 +55,7 @@ def test_oracle_matches_reference_config0(seed):
             assert O.rel_err(dB[::16, ::4], _t(z[f"dB_{tag}"])) < 2e-5
 
 
-@pytest.mark.parametrize("act", [None, "silu_gate"])
+@pytest.mark.parametrize("act", [None, "silu_gate", "sigmoid_gate"])
 @pytest.mark.parametrize("rs", [8, 16])
 def test_oracle_backward_matches_autograd_fp64(act, rs):
     M, K, N, gs = 32, 128, 128, 32
