@@ -236,6 +236,37 @@ def fold_weight(B, R, group_size: int, reconn_sz: int):
     return Bp
 
 
+_CAYLEY_DTYPES = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+
+
+def cayley_supported(M, reconn_sz: int) -> bool:
+    return M.is_cuda and M.dtype in _CAYLEY_DTYPES and reconn_sz in (8, 16) and M.dim() == 2
+
+
+def cayley(M, reconn_sz: int):
+    """R blocks of the plain mode from the stored parameter ``M`` ([G*rs, K]): per block
+    ``S = M - M^T``, ``R = (I - S)^-1 (I + S)`` through ``prism_cayley`` (fp32 inside)."""
+    M = M.contiguous()
+    R = torch.empty_like(M)
+    with torch.cuda.device(M.device):
+        _lib.check(_lib.lib().prism_cayley(ctypes.c_void_p(M.data_ptr()), ctypes.c_void_p(R.data_ptr()),
+                                           M.shape[0] // reconn_sz, M.shape[1], reconn_sz, _CAYLEY_DTYPES[M.dtype],
+                                           M.stride(0), R.stride(0), _stream_ptr(M.device)))
+    return R
+
+
+def cayley_backward(M, dR, reconn_sz: int):
+    """Gradient of ``cayley`` with respect to ``M`` through ``prism_cayley_bwd``."""
+    M, dR = M.contiguous(), dR.contiguous().to(M.dtype)
+    dM = torch.empty_like(M)
+    with torch.cuda.device(M.device):
+        _lib.check(_lib.lib().prism_cayley_bwd(ctypes.c_void_p(M.data_ptr()), ctypes.c_void_p(dR.data_ptr()),
+                                               ctypes.c_void_p(dM.data_ptr()), M.shape[0] // reconn_sz, M.shape[1], reconn_sz,
+                                               _CAYLEY_DTYPES[M.dtype], M.stride(0), dR.stride(0), dM.stride(0),
+                                               _stream_ptr(M.device)))
+    return dM
+
+
 def _backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=None, out_dtype=None):
     """dB = dc_scale * dC^T . H  through ``prism_bwd_db`` (H recomputed on chip); with
     ``out_dtype=torch.float32`` the kernel's fp32 sums are returned unrounded."""

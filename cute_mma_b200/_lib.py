@@ -15,7 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.environ.get("PRISM_B200_LIB", os.path.join(_HERE, "libprism_b200.so"))
 SOURCES = ["prism_abi.cu", "prism_fwd.cu", "prism_fwd_small.cu", "prism_bwd_db.cu", "prism_bwd_dadr.cu",
-           "prism_fwd_noalloc.cu"]
+           "prism_fwd_noalloc.cu", "prism_cayley.cu"]
 HEADERS = ["prism_common.cuh", "prism_host.cuh", "prism_kernels.cuh"]
 PUBLIC_HEADER = os.path.join(os.path.dirname(_HERE), "include", "prism_b200.h")
 
@@ -26,7 +26,7 @@ NVCC_FLAGS = [
 
 # every symbol include/prism_b200.h declares
 EXPORTS = [
-    "prism_fwd", "prism_fwd_noalloc", "prism_bwd_dadr", "prism_bwd_db", "prism_dbias", "prism_fold_weight", "prism_workspace_bytes",
+    "prism_fwd", "prism_fwd_noalloc", "prism_bwd_dadr", "prism_bwd_db", "prism_dbias", "prism_fold_weight", "prism_cayley", "prism_cayley_bwd", "prism_workspace_bytes",
     "prism_status",
     "prism_last_error_string", "prism_abi_version", "prism_launch_count",
 ]
@@ -99,6 +99,10 @@ def lib() -> ctypes.CDLL:
             L.prism_dbias.argtypes = [vp, vp, i, i, i, i, ll, vp, sz, vp]
             L.prism_fold_weight.restype = i
             L.prism_fold_weight.argtypes = [vp, vp, vp, i, i, i, i, i, ll, ll, ll, vp]
+            L.prism_cayley.restype = i
+            L.prism_cayley.argtypes = [vp, vp, i, i, i, i, ll, ll, vp]
+            L.prism_cayley_bwd.restype = i
+            L.prism_cayley_bwd.argtypes = [vp, vp, vp, i, i, i, i, ll, ll, ll, vp]
             L.prism_workspace_bytes.restype = sz
             L.prism_workspace_bytes.argtypes = [i, i, i, i, i, i, i, ip]
             L.prism_status.restype = i

@@ -14,8 +14,9 @@ Differences, all on the fast path:
 * in plain mode a frozen ``weight`` gets no gradient tensor at all; a trainable ``weight``
   in plain mode gets exact zeros, which is the reference's contract
   (src/cute_prism/_module.py:92-104);
-* the exact Cayley transform is solved in fp32 for fp16/bf16 parameters (``torch.linalg.solve``
-  has no 16-bit kernels) and cast back;
+* the exact Cayley transform of CUDA parameters with ``reconn_sz`` 8 or 16 is one launch of the
+  library's batched kernel (fp32 inside, its own backward); elsewhere it is solved by
+  ``torch.linalg.solve`` in fp32 for fp16/bf16 parameters (which has no 16-bit kernels) and cast back;
 * input shuffle, internal bias and dropout are not part of the accelerated path and raise
   ``ValueError`` at construction.
 """
@@ -73,6 +74,39 @@ def _prism_backward_op(dC: torch.Tensor, A: torch.Tensor, B: torch.Tensor, R: to
 def _(dC, A, B, R, group_size, reconn_sz, activation, bwd_scale, need_dB, need_dbias):
     return (A.new_empty(A.shape), R.new_empty(R.shape), (B.new_empty(B.shape) if need_dB else B.new_empty(0)),
             (dC.new_empty(dC.shape[1]) if need_dbias else dC.new_empty(0)))
+
+
+@torch.library.custom_op("prism_b200::cayley", mutates_args=())
+def _cayley_op(M: torch.Tensor, reconn_sz: int) -> torch.Tensor:
+    return F.cayley(M, reconn_sz)
+
+
+@_cayley_op.register_fake
+def _(M, reconn_sz):
+    return M.new_empty(M.shape)
+
+
+@torch.library.custom_op("prism_b200::cayley_backward", mutates_args=())
+def _cayley_bwd_op(M: torch.Tensor, dR: torch.Tensor, reconn_sz: int) -> torch.Tensor:
+    return F.cayley_backward(M, dR, reconn_sz)
+
+
+@_cayley_bwd_op.register_fake
+def _(M, dR, reconn_sz):
+    return M.new_empty(M.shape)
+
+
+def _cayley_setup(ctx, inputs, output):
+    ctx.save_for_backward(inputs[0])
+    ctx.reconn_sz = inputs[1]
+
+
+def _cayley_backward(ctx, dR):
+    (M,) = ctx.saved_tensors
+    return _cayley_bwd_op(M, dR, ctx.reconn_sz), None
+
+
+_cayley_op.register_autograd(_cayley_backward, setup_context=_cayley_setup)
 
 
 def _setup_context(ctx, inputs, output):
@@ -180,6 +214,10 @@ class PrismLinear(nn.Module):
         r = self.reconn_sz
         nb = self.in_features // r
         out_dtype = self.reconn.dtype
+        if self.cayley_order == float("inf") and F.cayley_supported(self.reconn, r):
+            # the library's batched Cayley kernel: one launch, fp32 inside, any parameter dtype,
+            # differentiable, capturable in a CUDA graph
+            return _cayley_op(self.reconn, r)
         Mb = self.reconn.reshape(n_groups, r, nb, r).permute(0, 2, 1, 3)
         if out_dtype in (torch.float16, torch.bfloat16):
             Mb = Mb.float()

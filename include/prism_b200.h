@@ -134,6 +134,17 @@ int prism_dbias(const void* dC, void* dbias, int M, int N, int dtype, int dbias_
 int prism_fold_weight(const void* B, const void* R, void* Bp, int N, int K, int group_size, int reconn_sz,
                       int dtype, long long ldb, long long ldr, long long ldbp, void* stream);
 
+/* Rotation blocks of the plain (fine-tuning) mode from the stored parameter: for every reconn_sz x
+ * reconn_sz block, S = M - M^T and R = (I - S)^-1 (I + S), computed in fp32 by one thread per block
+ * (reconn_sz 8 or 16).  Replaces the torch.linalg.solve chain of the reference's
+ * PrismLinear._build_R (src/cute_prism/_module.py:534-577), works for fp16 / bf16 / fp32 parameters
+ * (dtype 0 / 1 / 2) and can be captured in a CUDA graph.  M, R: [n_groups*reconn_sz, K].
+ * prism_cayley_bwd: dM from dR (dL/dS = P^T dR (R + I)^T with P = (I - S)^-1, dM = dL/dS - (dL/dS)^T). */
+int prism_cayley(const void* M, void* R, int n_groups, int K, int reconn_sz, int dtype, long long ldm,
+                 long long ldr, void* stream);
+int prism_cayley_bwd(const void* M, const void* dR, void* dM, int n_groups, int K, int reconn_sz, int dtype,
+                     long long ldm, long long lddr, long long lddm, void* stream);
+
 /* Bytes of workspace the given call needs (kind = PRISM_KIND_*), header included. */
 size_t prism_workspace_bytes(int kind, int M, int N, int K, int group_size, int reconn_sz,
                              int dtype, const int* cfg);

@@ -215,7 +215,7 @@ def test_few_token_streaming_forward(shape, act):
     assert O.rel_err(C.float(), ref) < TOL and O.rel_err(Cg.float(), ref) < TOL
     assert torch.equal(Cd, C if M <= 48 else Cg), "up to 48 tokens the streaming kernel is the default"
     for _ in range(5):
-        C2, _ = cp.forward(A, B, R, gs, rs, activation=act, bias=bias)
+        C2, _ = cp.forward(A, B, R, gs, rs, activation=act, bias=bias, tile_cfg=[0, 0, 0, 2])
         assert torch.equal(C2, C)
     cp.check_device_status()
 
@@ -245,4 +245,68 @@ def test_rw_mode_weight_folding(shape):
     C_ar, _ = cp.forward(A, B, R, gs, rs, mode="ar")
     ref = O.prism_forward(A.float(), B.float(), R.float(), gs, rs, None)
     assert seeds == [] and O.rel_err(C_rw.float(), ref) < TOL and O.rel_err(C_ar.float(), ref) < TOL
+    cp.check_device_status()
+
+
+@pytest.mark.parametrize("rs", [8, 16])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_cayley_kernel_matches_linalg_solve(rs, dt):
+    """The batched Cayley kernel against the reference's construction (torch.linalg.solve per block,
+    src/cute_prism/_module.py:534-577), values and gradient; R is orthogonal."""
+    G, K = 5, 12 * rs
+    nb = K // rs
+    torch.manual_seed(rs)
+    M = (torch.randn(G * rs, K, device=DEV) * 0.3).to(dt).requires_grad_(True)
+    R = torch.ops.prism_b200.cayley(M, rs)
+    Mb = M.detach().float().reshape(G, rs, nb, rs).permute(0, 2, 1, 3).requires_grad_(True)
+    S = Mb - Mb.transpose(-1, -2)
+    eye = torch.eye(rs, device=DEV).expand_as(S)
+    Rb = torch.linalg.solve(eye - S, eye + S)
+    R_ref = Rb.permute(0, 2, 1, 3).reshape(G * rs, K)
+    tol = 1e-4 if dt == torch.float32 else 1e-2
+    assert O.rel_err(R.float(), R_ref) < tol
+    Rk = R.detach().float().reshape(G, rs, nb, rs).permute(0, 2, 1, 3)
+    if dt == torch.float32:
+        assert (Rk @ Rk.transpose(-1, -2) - torch.eye(rs, device=DEV)).abs().max() < 1e-4
+    W = torch.randn_like(R_ref)
+    (R.float() * W).sum().backward()
+    (R_ref * W).sum().backward()
+    dM_ref = Mb.grad.permute(0, 2, 1, 3).reshape(G * rs, K)
+    assert O.rel_err(M.grad.float(), dM_ref) < (1e-4 if dt == torch.float32 else 2e-2)
+
+
+def test_library_calls_can_be_captured_in_a_cuda_graph():
+    """Forward, backward, bias gradient and the Cayley construction replayed from a CUDA graph give
+    the eager results (every call is stream-ordered, no host synchronisation, no allocation)."""
+    M, K, N, gs, rs = 512, 256, 512, 256, 8
+    layer = cp.PrismLinear(K, N, group_size=gs, reconn_sz=rs).to(DEV).to(torch.bfloat16)
+    with torch.no_grad():
+        layer.reconn.normal_(std=0.1)
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    dy = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+
+    def fb():
+        layer.zero_grad(set_to_none=False)
+        if x.grad is not None:
+            x.grad.zero_()
+        y = layer(x)
+        y.backward(dy)
+        return y
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            y_eager = fb().detach().clone()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    gx, gr, gb = x.grad.clone(), layer.reconn.grad.clone(), layer.bias.grad.clone()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        y_static = fb()
+    x.grad.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(y_static, y_eager) and torch.equal(x.grad, gx)
+    assert torch.equal(layer.reconn.grad, gr) and torch.equal(layer.bias.grad, gb)
     cp.check_device_status()
