@@ -463,6 +463,41 @@ def run_e2e(args, w, dev, world, A, B, R, dC, step_flops):
                     "the last step; copy_bound_ms = the slower direction's bytes at this box's plain pinned-copy rate"}
 
 
+def run_small_m_sweep(w, dev, B, R, peaks):
+    """Streaming kernel (path 2) against the general tiled kernel (path 1) over token counts: the
+    measurement behind the default switch-over and the shipped tile-table entries."""
+    import cute_mma_b200 as cp
+    dt = B.dtype
+    N, K = B.shape
+    gs, rs, act = w["gs"], w["rs"], w["act"]
+    flush = torch.empty(384 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    flush_words = flush.view(torch.int32)
+    gen = torch.Generator(device=dev).manual_seed(99)
+    rows = []
+    for m in (1, 8, 16, 32, 48, 64, 96, 128):
+        A_s = torch.randn(m, K, device=dev, generator=gen).to(dt)
+        row = {"M": m}
+        for path, name in ((2, "streaming_us"), (1, "general_us")):
+            cfg = [0, 0, 0, path]
+            for _ in range(3):
+                cp.forward(A_s, B, R, gs, rs, activation=act, tile_cfg=cfg)
+            ts = []
+            for _ in range(8):
+                flush.fill_(1)
+                flush_words.sum()
+                t0e, t1e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0e.record()
+                cp.forward(A_s, B, R, gs, rs, activation=act, tile_cfg=cfg)
+                t1e.record()
+                torch.cuda.synchronize()
+                ts.append(t0e.elapsed_time(t1e) * 1e3)
+            ts.sort()
+            row[name] = {"min": ts[0], "median": ts[len(ts) // 2]}
+        rows.append(row)
+    cp.check_device_status()
+    return rows
+
+
 def run_small_m(w, dev, B, R, peaks):
     """Decode-sized forward calls: HBM-bound, minimum traffic B + R + A + C.  L2 (126 MB) would
     otherwise keep most of B (117 MB) between iterations: before every timed call a 384 MB buffer is
@@ -741,6 +776,8 @@ def main():
     ap.add_argument("--no-small-m", action="store_true")
     ap.add_argument("--no-sustained", action="store_true")
     ap.add_argument("--no-train-cfg3", action="store_true")
+    ap.add_argument("--small-m-sweep", action="store_true",
+                    help="only time the few-token forward, streaming against general kernel, and print the table")
     ap.add_argument("--no-cuda-graph", action="store_true", help="cfg4: issue the step eagerly")
     ap.add_argument("--cfg4-sequences", type=int, default=64, help="cfg4: global batch in sequences (64 = the configuration)")
     args = ap.parse_args()
@@ -780,6 +817,11 @@ def main():
 
     wname = args.workload
     w = WORKLOADS[wname]
+    if args.small_m_sweep:
+        _, B, R, _ = make_inputs(dict(w, M=16), dev, rank)
+        print(json.dumps({"small_m_sweep": run_small_m_sweep(w, dev, B, R, measured_peaks()[0]),
+                          "config": workload_config(wname, w, 1)}), flush=True)
+        return
     A, B, R, dC = make_inputs(w, dev, rank)
     fl = flops(w)
     step_flops = sum(fl.values())
