@@ -16,7 +16,7 @@ import torch
 from . import _lib
 from ._tile_table import lookup as _tile_lookup
 
-KIND_FWD, KIND_BWD_DADR, KIND_BWD_DB, KIND_DBIAS = 0, 1, 2, 3
+KIND_FWD, KIND_BWD_DADR, KIND_BWD_DB, KIND_DBIAS, KIND_BWD_DADR_IB = 0, 1, 2, 3, 4
 DTYPE_F32, DTYPE_SAME = 2, -1
 ACTIVATIONS = (None, "silu_gate", "sigmoid_gate")
 _GATE_CODES = {None: 0, "silu_gate": 1, "sigmoid_gate": 2}   # the C ABI's gate argument
@@ -159,6 +159,23 @@ def _gate_code(activation):
     return _GATE_CODES[activation]
 
 
+def _check_internal_bias(internal_bias, A, N, K, group_size, gate):
+    """Same contract as the reference (src/cute_prism/__init__.py:166-170): a (N/group_size, K) tensor of
+    A's dtype and device, gated modes only."""
+    if internal_bias is None:
+        return None
+    if not gate:
+        raise ValueError("internal_bias requires a gated activation; pass activation='silu_gate'")
+    if (internal_bias.shape != (N // group_size, K) or internal_bias.dtype != A.dtype
+            or internal_bias.device != A.device):
+        raise ValueError(f"internal_bias must be a ({N // group_size}, {K}) tensor of the same dtype and device as A")
+    return internal_bias.contiguous()
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
 def _reject_unsupported(**kw):
     for name, val in kw.items():
         if isinstance(val, torch.Tensor) or (val is not None and val is not False and val != 0.0):
@@ -187,11 +204,11 @@ def forward(A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=None, mo
         validate_tensor_params(A, B, R, group_size, reconn_sz)
         C = torch.matmul(A, fold_weight(B, R, group_size, reconn_sz).t())
         return (C if bias is None else C + bias), []
-    _reject_unsupported(internal_bias=internal_bias, shuffle_masks=shuffle_masks,
-                        dropout_p=(dropout_p if training else 0.0))
+    _reject_unsupported(shuffle_masks=shuffle_masks, dropout_p=(dropout_p if training else 0.0))
     validate_tensor_params(A, B, R, group_size, reconn_sz)
     M, K = A.shape
     N = B.shape[0]
+    internal_bias = _check_internal_bias(internal_bias, A, N, K, group_size, gate)
     if bias is not None:
         if bias.dtype != A.dtype or bias.shape != (N,) or not bias.is_contiguous() or bias.device != A.device:
             raise ValueError("bias must be a contiguous (N,) tensor of the same dtype and device as A")
@@ -207,7 +224,7 @@ def forward(A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=None, mo
         ws = _workspace.get(A.device, need)
         _lib.check(L.prism_fwd(
             ctypes.c_void_p(A.data_ptr()), ctypes.c_void_p(B.data_ptr()), ctypes.c_void_p(R.data_ptr()),
-            ctypes.c_void_p(bias.data_ptr()) if bias is not None else None, ctypes.c_void_p(C.data_ptr()),
+            _ptr(bias), _ptr(internal_bias), ctypes.c_void_p(C.data_ptr()),
             M, N, K, group_size, reconn_sz, dt, gate, A.stride(0), B.stride(0), R.stride(0), C.stride(0),
             cfg_arr, ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(A.device)))
     return C, []
@@ -267,7 +284,8 @@ def cayley_backward(M, dR, reconn_sz: int):
     return dM
 
 
-def _backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=None, out_dtype=None):
+def _backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=None, out_dtype=None,
+                 internal_bias=None):
     """dB = dc_scale * dC^T . H  through ``prism_bwd_db`` (H recomputed on chip); with
     ``out_dtype=torch.float32`` the kernel's fp32 sums are returned unrounded."""
     M, K = A.shape
@@ -283,33 +301,40 @@ def _backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=N
         ws = _workspace.get(A.device, need)
         _lib.check(L.prism_bwd_db(
             ctypes.c_void_p(dC.data_ptr()), ctypes.c_void_p(A.data_ptr()), ctypes.c_void_p(R.data_ptr()),
-            ctypes.c_void_p(dB.data_ptr()), M, N, K, group_size, reconn_sz, dt, gate, out_code,
+            _ptr(internal_bias), ctypes.c_void_p(dB.data_ptr()), M, N, K, group_size, reconn_sz, dt, gate, out_code,
             ctypes.c_float(dc_scale), dC.stride(0), A.stride(0), R.stride(0), dB.stride(0),
             cfg_arr, ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(A.device)))
     return dB
 
 
-def _backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=None, dR_dtype=None):
+def _backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=None, dR_dtype=None,
+                   internal_bias=None):
     """(dA, dR), both scaled by ``dc_scale``, through ``prism_bwd_dadr``; with
-    ``dR_dtype=torch.float32`` the fp32 sums of the dR reduction are returned unrounded."""
+    ``dR_dtype=torch.float32`` the fp32 sums of the dR reduction are returned unrounded.  With an
+    ``internal_bias`` the result is ``(dA, dR, d_internal_bias)``."""
     M, K = A.shape
     N = B.shape[0]
     dR_dtype, dr_code = _grad_dtype(dR_dtype, A.dtype, "dR_dtype")
     dA = torch.empty(M, K, dtype=A.dtype, device=A.device)
     dR = torch.empty(R.shape, dtype=dR_dtype, device=A.device)
+    d_ib = torch.empty_like(internal_bias) if internal_bias is not None else None
     L = _lib.lib()
     cfg = tile_cfg if tile_cfg is not None else _tile_lookup("bwd_dadr", A.dtype, gate, M, N, K, group_size, reconn_sz)
     cfg_arr = _cfg_array(cfg)
     dt = _DTYPES[A.dtype]
     with torch.cuda.device(A.device):
-        need = L.prism_workspace_bytes(KIND_BWD_DADR, M, N, K, group_size, reconn_sz, dt, cfg_arr)
+        kind = KIND_BWD_DADR_IB if internal_bias is not None else KIND_BWD_DADR
+        need = L.prism_workspace_bytes(kind, M, N, K, group_size, reconn_sz, dt, cfg_arr)
         ws = _workspace.get(A.device, need)
         _lib.check(L.prism_bwd_dadr(
             ctypes.c_void_p(dC.data_ptr()), ctypes.c_void_p(A.data_ptr()), ctypes.c_void_p(B.data_ptr()),
-            ctypes.c_void_p(R.data_ptr()), ctypes.c_void_p(dA.data_ptr()), ctypes.c_void_p(dR.data_ptr()),
+            ctypes.c_void_p(R.data_ptr()), _ptr(internal_bias), ctypes.c_void_p(dA.data_ptr()),
+            ctypes.c_void_p(dR.data_ptr()), _ptr(d_ib),
             M, N, K, group_size, reconn_sz, dt, gate, dr_code, ctypes.c_float(dc_scale),
             dC.stride(0), A.stride(0), B.stride(0), R.stride(0), dA.stride(0), dR.stride(0),
             cfg_arr, ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(A.device)))
+    if internal_bias is not None:
+        return dA, dR, d_ib
     return dA, dR
 
 
@@ -320,7 +345,7 @@ def backward(dC, A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=Non
              dropout_seeds=None, dropout_p: float = 0.0, shuffle_masks=None, *, dc_scale: float = 1.0,
              tile_cfg_dadr=None, tile_cfg_db=None):
     """Gradients ``(dA, dR, dB, d_internal_bias)``; ``dB`` is None in plain mode and
-    ``d_internal_bias`` is always None (internal bias is not part of the accelerated path).
+    ``d_internal_bias`` is None when no ``internal_bias`` is given.
     ``dR_dtype`` / ``dB_dtype`` = ``torch.float32`` return the kernels' fp32 sums unrounded
     (reference: src/cute_prism/__init__.py:288-289, 368, 375).
 
@@ -328,16 +353,17 @@ def backward(dC, A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=Non
     """
     gate = _gate_code(activation)
     validate_kernel_params(group_size, reconn_sz)
-    _reject_unsupported(internal_bias=internal_bias, shuffle_masks=shuffle_masks,
-                        dropout_seeds=dropout_seeds if dropout_p > 0.0 else None)
+    _reject_unsupported(shuffle_masks=shuffle_masks, dropout_seeds=dropout_seeds if dropout_p > 0.0 else None)
     validate_tensor_params(A, B, R, group_size, reconn_sz)
     M, K = A.shape
     N = B.shape[0]
     if dC.shape != (M, N) or dC.dtype != A.dtype or dC.device != A.device or not dC.is_contiguous():
         raise ValueError(f"dC must be a contiguous ({M}, {N}) tensor of the same dtype and device as A")
-    dA, dR = _backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, dc_scale, tile_cfg_dadr, dR_dtype)
-    dB = _backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale, tile_cfg_db, dB_dtype) if gate else None
-    return dA, dR, dB, None
+    internal_bias = _check_internal_bias(internal_bias, A, N, K, group_size, gate)
+    out = _backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, dc_scale, tile_cfg_dadr, dR_dtype, internal_bias)
+    dB = (_backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale, tile_cfg_db, dB_dtype, internal_bias)
+          if gate else None)
+    return out[0], out[1], dB, (out[2] if internal_bias is not None else None)
 
 
 def bias_grad(dC, out_dtype=None):

@@ -31,7 +31,7 @@ EXPORTS = [
     "prism_last_error_string", "prism_abi_version", "prism_launch_count",
 ]
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 _lock = threading.Lock()
 _lib = None
@@ -50,16 +50,40 @@ def needs_build() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile the library for sm_100a with nvcc (cross-compiles without a GPU)."""
+    """Compile the library for sm_100a with nvcc (cross-compiles without a GPU): one object per source
+    file, compiled side by side, then one link."""
     if not force and not needs_build():
         return LIB_PATH
+    import concurrent.futures
+    import tempfile
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB_PATH] + _existing_sources()
-    res = subprocess.run(cmd, cwd=_CSRC, capture_output=True, text=True)
+    flags = [f for f in NVCC_FLAGS if f != "-shared"] + (["-Xptxas", "-v"] if verbose else [])
+    objdir = tempfile.mkdtemp(prefix="prism_b200_build_")
+    sources = _existing_sources()
+
+    def compile_one(src):
+        obj = os.path.join(objdir, os.path.basename(src) + ".o")
+        cmd = [nvcc] + flags + ["-c", "-o", obj, src]
+        res = subprocess.run(cmd, cwd=_CSRC, capture_output=True, text=True)
+        return obj, cmd, res
+
+    log = []
+    with concurrent.futures.ThreadPoolExecutor(max_workers=max(1, min(len(sources), os.cpu_count() or 1))) as pool:
+        results = list(pool.map(compile_one, sources))
+    for obj, cmd, res in results:
+        if res.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
+        log.append(res.stderr)
+    link = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-Xcompiler", "-fPIC", "-o", LIB_PATH] + \
+           [obj for obj, _, _ in results]
+    res = subprocess.run(link, cwd=_CSRC, capture_output=True, text=True)
     if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
+        raise RuntimeError("nvcc link failed:\n" + " ".join(link) + "\n" + res.stdout + res.stderr)
+    for obj, _, _ in results:
+        os.remove(obj)
+    os.rmdir(objdir)
     if verbose:
-        print(res.stderr)
+        print("\n".join(log))
     return LIB_PATH
 
 
@@ -84,16 +108,16 @@ def lib() -> ctypes.CDLL:
             vp, ll, i, sz = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int, ctypes.c_size_t
             ip = ctypes.POINTER(ctypes.c_int)
             L.prism_fwd.restype = i
-            L.prism_fwd.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, i, ll, ll, ll, ll, ip, vp, sz, vp]
+            L.prism_fwd.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, ll, ll, ll, ll, ip, vp, sz, vp]
             L.prism_fwd_noalloc.restype = i
             L.prism_fwd_noalloc.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, i, ll, ll, ll, ll, ip, vp, vp]
             if hasattr(L, "prism_bwd_dadr"):
                 L.prism_bwd_dadr.restype = i
-                L.prism_bwd_dadr.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, i, ctypes.c_float,
+                L.prism_bwd_dadr.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, i, ctypes.c_float,
                                              ll, ll, ll, ll, ll, ll, ip, vp, sz, vp]
             if hasattr(L, "prism_bwd_db"):
                 L.prism_bwd_db.restype = i
-                L.prism_bwd_db.argtypes = [vp, vp, vp, vp, i, i, i, i, i, i, i, i, ctypes.c_float,
+                L.prism_bwd_db.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, i, i, ctypes.c_float,
                                            ll, ll, ll, ll, ip, vp, sz, vp]
             L.prism_dbias.restype = i
             L.prism_dbias.argtypes = [vp, vp, i, i, i, i, ll, vp, sz, vp]

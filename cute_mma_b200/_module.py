@@ -17,8 +17,9 @@ Differences, all on the fast path:
 * the exact Cayley transform of CUDA parameters with ``reconn_sz`` 8 or 16 is one launch of the
   library's batched kernel (fp32 inside, its own backward); elsewhere it is solved by
   ``torch.linalg.solve`` in fp32 for fp16/bf16 parameters (which has no 16-bit kernels) and cast back;
-* input shuffle, internal bias and dropout are not part of the accelerated path and raise
-  ``ValueError`` at construction.
+* the internal bias (``internal_bias=True``, gated modes) is added inside the kernels and its gradient
+  comes out of the dA+dR kernel; input shuffle and dropout are not part of the accelerated path and
+  raise ``ValueError`` at construction.
 """
 from __future__ import annotations
 
@@ -40,40 +41,46 @@ _GATED = ("silu_gate", "sigmoid_gate")
 # ---------------------------------------------------------------------------
 @torch.library.custom_op("prism_b200::forward", mutates_args=())
 def _prism_forward_op(A: torch.Tensor, B: torch.Tensor, R: torch.Tensor, bias: torch.Tensor | None,
-                      group_size: int, reconn_sz: int, activation: str, bwd_scale: float) -> torch.Tensor:
+                      group_size: int, reconn_sz: int, activation: str, bwd_scale: float,
+                      internal_bias: torch.Tensor | None = None) -> torch.Tensor:
     C, _ = F.forward(A.contiguous(), B.contiguous(), R.contiguous(), group_size, reconn_sz,
-                     activation=activation or None, bias=bias)
+                     activation=activation or None, bias=bias, internal_bias=internal_bias)
     return C
 
 
 @_prism_forward_op.register_fake
-def _(A, B, R, bias, group_size, reconn_sz, activation, bwd_scale):
+def _(A, B, R, bias, group_size, reconn_sz, activation, bwd_scale, internal_bias=None):
     return A.new_empty(A.shape[0], B.shape[0])
 
 
 @torch.library.custom_op("prism_b200::backward", mutates_args=())
 def _prism_backward_op(dC: torch.Tensor, A: torch.Tensor, B: torch.Tensor, R: torch.Tensor,
                        group_size: int, reconn_sz: int, activation: str, bwd_scale: float,
-                       need_dB: bool, need_dbias: bool) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+                       need_dB: bool, need_dbias: bool, internal_bias: torch.Tensor | None = None
+                       ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     dC = dC.contiguous()
     A, B, R = A.contiguous(), B.contiguous(), R.contiguous()
     gate = F._gate_code(activation or None)
-    dA, dR = F._backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, bwd_scale)
+    ib = internal_bias.contiguous() if internal_bias is not None else None
+    out = F._backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, bwd_scale, internal_bias=ib)
+    dA, dR = out[0], out[1]
+    d_ib = out[2] if ib is not None else dC.new_empty(0)
     if not need_dB:
         dB = B.new_empty(0)
     elif gate:
-        dB = F._backward_db(dC, A, R, group_size, reconn_sz, gate, bwd_scale)
+        dB = F._backward_db(dC, A, R, group_size, reconn_sz, gate, bwd_scale, internal_bias=ib)
     else:
         dB = torch.zeros_like(B)  # frozen-B contract of the reference's plain mode
     # the bias is added after the rescale point: its gradient is the plain column sum of dC
     dbias = F.bias_grad(dC) if need_dbias else dC.new_empty(0)
-    return dA, dR, dB, dbias
+    return dA, dR, dB, dbias, d_ib
 
 
 @_prism_backward_op.register_fake
-def _(dC, A, B, R, group_size, reconn_sz, activation, bwd_scale, need_dB, need_dbias):
+def _(dC, A, B, R, group_size, reconn_sz, activation, bwd_scale, need_dB, need_dbias, internal_bias=None):
     return (A.new_empty(A.shape), R.new_empty(R.shape), (B.new_empty(B.shape) if need_dB else B.new_empty(0)),
-            (dC.new_empty(dC.shape[1]) if need_dbias else dC.new_empty(0)))
+            (dC.new_empty(dC.shape[1]) if need_dbias else dC.new_empty(0)),
+            (internal_bias.new_empty(internal_bias.shape) if internal_bias is not None else dC.new_empty(0)))
 
 
 @torch.library.custom_op("prism_b200::cayley", mutates_args=())
@@ -110,29 +117,33 @@ _cayley_op.register_autograd(_cayley_backward, setup_context=_cayley_setup)
 
 
 def _setup_context(ctx, inputs, output):
-    A, B, R, bias, group_size, reconn_sz, activation, bwd_scale = inputs
-    ctx.save_for_backward(A, B, R)
+    A, B, R, bias, group_size, reconn_sz, activation, bwd_scale, internal_bias = inputs
+    ctx.save_for_backward(A, B, R, *(() if internal_bias is None else (internal_bias,)))
+    ctx.has_ib = internal_bias is not None
     ctx.has_bias = bias is not None
     ctx.group_size, ctx.reconn_sz = group_size, reconn_sz
     ctx.activation, ctx.bwd_scale = activation, bwd_scale
 
 
 def _backward(ctx, dC):
-    A, B, R = ctx.saved_tensors
+    A, B, R = ctx.saved_tensors[:3]
+    ib = ctx.saved_tensors[3] if ctx.has_ib else None
     need_dB = bool(ctx.needs_input_grad[1])
     need_dbias = bool(ctx.has_bias and ctx.needs_input_grad[3])
-    dA, dR, dB, dbias = _prism_backward_op(dC, A, B, R, ctx.group_size, ctx.reconn_sz, ctx.activation,
-                                           ctx.bwd_scale, need_dB, need_dbias)
-    return dA, (dB if need_dB else None), dR, (dbias if need_dbias else None), None, None, None, None
+    dA, dR, dB, dbias, d_ib = _prism_backward_op(dC, A, B, R, ctx.group_size, ctx.reconn_sz, ctx.activation,
+                                                 ctx.bwd_scale, need_dB, need_dbias, ib)
+    return (dA, (dB if need_dB else None), dR, (dbias if need_dbias else None), None, None, None, None,
+            (d_ib if ctx.has_ib else None))
 
 
 _prism_forward_op.register_autograd(_backward, setup_context=_setup_context)
 
 
-def prism_linear(A, B, R, bias=None, group_size=256, reconn_sz=8, activation=None, bwd_scale=1.0):
-    """Differentiable functional form: C = prism(A, B, R) + bias; gradients of A/B/R are
-    multiplied by ``bwd_scale`` (the bias gradient is not)."""
-    return _prism_forward_op(A, B, R, bias, group_size, reconn_sz, activation or "", float(bwd_scale))
+def prism_linear(A, B, R, bias=None, group_size=256, reconn_sz=8, activation=None, bwd_scale=1.0,
+                 internal_bias=None):
+    """Differentiable functional form: C = prism(A, B, R) + bias; gradients of A/B/R (and of the
+    internal bias) are multiplied by ``bwd_scale`` (the output-bias gradient is not)."""
+    return _prism_forward_op(A, B, R, bias, group_size, reconn_sz, activation or "", float(bwd_scale), internal_bias)
 
 
 # ---------------------------------------------------------------------------
@@ -158,8 +169,8 @@ class PrismLinear(nn.Module):
         super().__init__()
         if activation not in (None,) + _GATED:
             raise ValueError(f"Unknown activation {activation!r}, must be one of (None, 'silu_gate', 'sigmoid_gate')")
-        if input_shuffle or internal_bias or dropout > 0.0:
-            raise ValueError("input_shuffle, internal_bias and dropout are not supported by the sm_100a kernels")
+        if input_shuffle or dropout > 0.0:
+            raise ValueError("input_shuffle and dropout are not supported by the sm_100a kernels")
         if out_features % group_size != 0:
             raise ValueError(f"out_features ({out_features}) must be divisible by group_size ({group_size})")
         if in_features % reconn_sz != 0:
@@ -186,6 +197,11 @@ class PrismLinear(nn.Module):
             self.bias = nn.Parameter(torch.empty(out_features))
         else:
             self.register_parameter("bias", None)
+        # bias added to A . blockdiag(R_g)^T before the gate (gated modes only), one row per group
+        if internal_bias and gated:
+            self._internal_bias = nn.Parameter(torch.empty(n_groups, in_features))
+        else:
+            self.register_parameter("_internal_bias", None)
         self._bwd_scale = {"silu_gate": 1.0 / _GATED_SILU_BWD_GAIN, "sigmoid_gate": 1.0 / _GATED_SIGMOID_BWD_GAIN}.get(activation, 1.0)
         self.reset_parameters()
 
@@ -195,7 +211,7 @@ class PrismLinear(nn.Module):
         nn.init.normal_(self.weight, std=1.0 / math.sqrt(K))
         if self.activation in _GATED:
             n_groups = self.out_features // self.group_size
-            sigma = 4.0 / math.sqrt(2 * (r - 1)) * self.r_init_scale
+            sigma = 4.0 / math.sqrt(2 * (r - (2 if self._internal_bias is not None else 1))) * self.r_init_scale
             Mb = torch.randn(n_groups, K // r, r, r, device=self.reconn.device, dtype=self.reconn.dtype) * sigma
             S = Mb - Mb.transpose(-1, -2)
             with torch.no_grad():
@@ -205,6 +221,8 @@ class PrismLinear(nn.Module):
         if self.bias is not None:
             bound = 1 / math.sqrt(K) if K > 0 else 0
             nn.init.uniform_(self.bias, -bound, bound)
+        if self._internal_bias is not None:
+            nn.init.normal_(self._internal_bias, std=1.0 / math.sqrt(r - 1))
 
     def _build_R(self) -> torch.Tensor:
         """R from the stored parameter (reference: src/cute_prism/_module.py:534-577)."""
@@ -267,13 +285,15 @@ class PrismLinear(nn.Module):
     def forward(self, input: torch.Tensor) -> torch.Tensor:
         A = input.reshape(-1, self.in_features)
         C = _prism_forward_op(A, self.weight, self._build_R(), self.bias, self.group_size, self.reconn_sz,
-                              self.activation or "", float(self._bwd_scale))
+                              self.activation or "", float(self._bwd_scale), self._internal_bias)
         return C.reshape(input.shape[:-1] + (self.out_features,))
 
     def extra_repr(self) -> str:
         parts = [f"in_features={self.in_features}", f"out_features={self.out_features}",
                  f"group_size={self.group_size}", f"reconn_sz={self.reconn_sz}",
                  f"bias={self.bias is not None}"]
+        if self._internal_bias is not None:
+            parts.append("internal_bias=True")
         if self.activation is not None:
             parts.append(f"activation={self.activation!r}")
         else:

@@ -193,6 +193,14 @@ static int grad_is_f32(int grad_dtype, int dtype) {
   return -1;
 }
 
+// internal bias [N/gs, K], 16-bit, contiguous rows of K: gated modes only
+static int check_ib(const char* fn, const void* ib, int gate) {
+  if (ib == nullptr) return PRISM_OK;
+  if (gate == GATE_NONE) return fail(PRISM_ERR_BAD_ARG, "%s: internal_bias requires a gated mode", fn);
+  if (reinterpret_cast<uintptr_t>(ib) % 4 != 0) return fail(PRISM_ERR_BAD_ARG, "%s: internal_bias must be 4-byte aligned", fn);
+  return PRISM_OK;
+}
+
 static int check_ptr(const char* fn, const char* name, const void* p, long long ld, int min_ld) {
   if (p == nullptr) return fail(PRISM_ERR_BAD_ARG, "%s: %s is null", fn, name);
   if (reinterpret_cast<uintptr_t>(p) % 16 != 0) return fail(PRISM_ERR_BAD_ARG, "%s: %s must be 16-byte aligned", fn, name);
@@ -205,7 +213,7 @@ static int check_ptr(const char* fn, const char* name, const void* p, long long 
 
 using namespace prism;
 
-extern "C" int prism_abi_version(void) { return 2; }
+extern "C" int prism_abi_version(void) { return 3; }
 
 extern "C" long long prism_launch_count(void) { return launch_counter().load(std::memory_order_relaxed); }
 
@@ -223,7 +231,7 @@ extern "C" size_t prism_workspace_bytes(int kind, int M, int N, int K, int gs, i
   const size_t G = (size_t)(N / gs);
   // copy of R the kernels read: widened for rs = 8 (all kinds), halved for the gated dA+dR kernel
   if (rs == 8) bytes += align256(G * 16 * (size_t)K * 2);
-  else if (kind == PRISM_KIND_BWD_DADR) bytes += align256(G * (size_t)effective_block(rs) * K * 2);
+  else if (kind == PRISM_KIND_BWD_DADR || kind == PRISM_KIND_BWD_DADR_IB) bytes += align256(G * (size_t)effective_block(rs) * K * 2);
   if (kind == PRISM_KIND_FWD) {
     // few tokens: the streaming forward keeps its arrival counters and fp32 partial sums here
     // (cfg[3] = 1 asks for the general kernel, which needs none)
@@ -241,13 +249,17 @@ extern "C" size_t prism_workspace_bytes(int kind, int M, int N, int K, int gs, i
     else if (pl.tail_rows > 0) bytes += align256((size_t)pl.tail_splits * pl.tail_rows * bn * K * 4);
     return bytes;
   }
-  if (kind == PRISM_KIND_BWD_DADR) {
+  if (kind == PRISM_KIND_BWD_DADR || kind == PRISM_KIND_BWD_DADR_IB) {
     const int E = effective_block(rs);
     if (E == 0) return bytes;
     DadrGrid gr;
     dadr_plan_grid(M, K, num_sms(), cfg, &gr);
     bytes += align256((size_t)2 * gr.runs * G * E * (size_t)K * 4);                 // one buffer per CTA of every main pair
     bytes += align256((size_t)2 * gr.n_extra * gr.slots * G * E * (size_t)128 * 4); // slabs of the extra pairs' CTAs
+    if (kind == PRISM_KIND_BWD_DADR_IB) {   // the same for the column sums of dS (gradient of the internal bias)
+      bytes += align256((size_t)2 * gr.runs * G * (size_t)K * 4);
+      bytes += align256((size_t)2 * gr.n_extra * gr.slots * G * (size_t)128 * 4);
+    }
     return bytes;
   }
   return bytes;
@@ -267,7 +279,7 @@ extern "C" int prism_status(void* workspace, void* stream) {
   return PRISM_OK;
 }
 
-extern "C" int prism_fwd(const void* A, const void* B, const void* R, const void* bias, void* C,
+extern "C" int prism_fwd(const void* A, const void* B, const void* R, const void* bias, const void* internal_bias, void* C,
                          int M, int N, int K, int gs, int rs, int dtype, int gate,
                          long long lda, long long ldb, long long ldr, long long ldc,
                          const int* cfg, void* workspace, size_t workspace_bytes, void* stream) {
@@ -282,13 +294,14 @@ extern "C" int prism_fwd(const void* A, const void* B, const void* R, const void
   if ((rc = check_ptr(fn, "C", C, ldc, N))) return rc;
   if (bias != nullptr && reinterpret_cast<uintptr_t>(bias) % 4 != 0)
     return fail(PRISM_ERR_BAD_ARG, "%s: bias must be 4-byte aligned", fn);
+  if ((rc = check_ib(fn, internal_bias, gate))) return rc;
   const size_t need = prism_workspace_bytes(PRISM_KIND_FWD, M, N, K, gs, rs, dtype, cfg);
   if (workspace == nullptr || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
     return fail(PRISM_ERR_WORKSPACE, "%s: workspace must be 256-byte aligned and >= %zu bytes (got %zu)", fn, need, workspace_bytes);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 
   FwdArgs a;
-  a.A = A; a.B = B; a.bias = bias; a.C = C;
+  a.A = A; a.B = B; a.bias = bias; a.ib = internal_bias; a.C = C;
   a.M = M; a.N = N; a.K = K; a.gs = gs; a.E = effective_block(rs);
   a.dtype = dtype; a.gate = gate;
   a.lda = lda; a.ldb = ldb; a.ldc = ldc;
@@ -317,7 +330,7 @@ extern "C" int prism_fwd(const void* A, const void* B, const void* R, const void
   return launch_fwd(a);
 }
 
-extern "C" int prism_bwd_db(const void* dC, const void* A, const void* R, void* dB,
+extern "C" int prism_bwd_db(const void* dC, const void* A, const void* R, const void* internal_bias, void* dB,
                             int M, int N, int K, int gs, int rs, int dtype, int gate, int db_dtype, float dc_scale,
                             long long lddc, long long lda, long long ldr, long long lddb,
                             const int* cfg, void* workspace, size_t workspace_bytes, void* stream) {
@@ -328,6 +341,7 @@ extern "C" int prism_bwd_db(const void* dC, const void* A, const void* R, void* 
   if (db_f32 < 0) return fail(PRISM_ERR_BAD_ARG, "%s: db_dtype must be the input dtype, PRISM_DTYPE_SAME or PRISM_DTYPE_F32", fn);
   if (K % 8 != 0) return fail(PRISM_ERR_BAD_ARG, "%s: K must be a multiple of 8", fn);
   if ((rc = check_ptr(fn, "dB", dB, lddb, K))) return rc;
+  if ((rc = check_ib(fn, internal_bias, gate))) return rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (M == 0) {  // no tokens: the gradient is zero
     const size_t es = db_f32 ? 4 : 2;
@@ -342,7 +356,7 @@ extern "C" int prism_bwd_db(const void* dC, const void* A, const void* R, void* 
     return fail(PRISM_ERR_WORKSPACE, "%s: workspace must be 256-byte aligned and >= %zu bytes (got %zu)", fn, need, workspace_bytes);
 
   DbArgs a;
-  a.dC = dC; a.A = A; a.dB = dB;
+  a.dC = dC; a.A = A; a.dB = dB; a.ib = internal_bias;
   a.M = M; a.N = N; a.K = K; a.gs = gs; a.E = effective_block(rs);
   a.dtype = dtype; a.gate = gate; a.scale = dc_scale; a.out_f32 = db_f32;
   a.lddc = lddc; a.lda = lda; a.lddb = lddb;
@@ -364,8 +378,8 @@ extern "C" int prism_bwd_db(const void* dC, const void* A, const void* R, void* 
   return launch_bwd_db(a);
 }
 
-extern "C" int prism_bwd_dadr(const void* dC, const void* A, const void* B, const void* R, void* dA,
-                              void* dR, int M, int N, int K, int gs, int rs, int dtype, int gate,
+extern "C" int prism_bwd_dadr(const void* dC, const void* A, const void* B, const void* R, const void* internal_bias,
+                              void* dA, void* dR, void* d_internal_bias, int M, int N, int K, int gs, int rs, int dtype, int gate,
                               int dr_dtype, float dc_scale, long long lddc, long long lda, long long ldb,
                               long long ldr, long long ldda, long long lddr, const int* cfg,
                               void* workspace, size_t workspace_bytes, void* stream) {
@@ -376,9 +390,13 @@ extern "C" int prism_bwd_dadr(const void* dC, const void* A, const void* B, cons
   if (dr_f32 < 0) return fail(PRISM_ERR_BAD_ARG, "%s: dr_dtype must be the input dtype, PRISM_DTYPE_SAME or PRISM_DTYPE_F32", fn);
   if (K % 8 != 0) return fail(PRISM_ERR_BAD_ARG, "%s: K must be a multiple of 8", fn);
   if ((rc = check_ptr(fn, "dR", dR, lddr, K))) return rc;
+  if ((rc = check_ib(fn, internal_bias, gate))) return rc;
+  const bool with_ib = internal_bias != nullptr;
+  if (with_ib && d_internal_bias == nullptr) return fail(PRISM_ERR_BAD_ARG, "%s: d_internal_bias is null", fn);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (M == 0) {  // no tokens: dA is empty and dR is zero
     const size_t es = dr_f32 ? 4 : 2;
+    if (with_ib) (void)cudaMemsetAsync(d_internal_bias, 0, (size_t)(N / gs) * K * 2, s);
     cudaError_t e = cudaMemset2DAsync(dR, lddr * es, 0, (size_t)K * es, (size_t)(N / gs) * rs, s);
     return e == cudaSuccess ? PRISM_OK : fail(PRISM_ERR_CUDA, "%s: %s", fn, cudaGetErrorString(e));
   }
@@ -387,12 +405,12 @@ extern "C" int prism_bwd_dadr(const void* dC, const void* A, const void* B, cons
   if ((rc = check_ptr(fn, "B", B, ldb, K))) return rc;
   if ((rc = check_ptr(fn, "R", R, ldr, K))) return rc;
   if ((rc = check_ptr(fn, "dA", dA, ldda, K))) return rc;
-  const size_t need = prism_workspace_bytes(PRISM_KIND_BWD_DADR, M, N, K, gs, rs, dtype, cfg);
+  const size_t need = prism_workspace_bytes(with_ib ? PRISM_KIND_BWD_DADR_IB : PRISM_KIND_BWD_DADR, M, N, K, gs, rs, dtype, cfg);
   if (workspace == nullptr || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
     return fail(PRISM_ERR_WORKSPACE, "%s: workspace must be 256-byte aligned and >= %zu bytes (got %zu)", fn, need, workspace_bytes);
 
   DadrArgs a;
-  a.dC = dC; a.A = A; a.B = B; a.dA = dA; a.dR = dR;
+  a.dC = dC; a.A = A; a.B = B; a.dA = dA; a.dR = dR; a.ib = internal_bias; a.d_ib = d_internal_bias;
   a.M = M; a.N = N; a.K = K; a.gs = gs; a.rs = rs; a.E = effective_block(rs);
   a.dtype = dtype; a.gate = gate; a.scale = dc_scale; a.dr_f32 = dr_f32;
   a.lddc = lddc; a.lda = lda; a.ldb = ldb; a.ldda = ldda; a.lddr = lddr;
@@ -410,6 +428,10 @@ extern "C" int prism_bwd_dadr(const void* dC, const void* A, const void* B, cons
   a.partial = reinterpret_cast<float*>(wp);
   wp += align256((size_t)2 * a.grid.runs * (N / gs) * a.E * (size_t)K * 4);
   a.partial_x = reinterpret_cast<float*>(wp);
+  wp += align256((size_t)2 * a.grid.n_extra * a.grid.slots * (N / gs) * a.E * (size_t)128 * 4);
+  a.partial_ib = reinterpret_cast<float*>(wp);
+  wp += align256((size_t)2 * a.grid.runs * (N / gs) * (size_t)K * 4);
+  a.partial_ib_x = reinterpret_cast<float*>(wp);
   a.err = reinterpret_cast<int*>(workspace);
   a.stream = s;
   return launch_bwd_dadr(a);

@@ -74,6 +74,9 @@ struct DadrParams {
   long long ldda;
   float* partial;      // [2*runs][G*E][K] fp32: one buffer per CTA of every main pair
   float* partial_x;    // [2*n_extra][slots][G*E][128] fp32: slabs of the extra pairs' CTAs
+  const void* ib;      // internal bias [G, K] (gated modes, IB kernels) or null
+  float* partial_ib;   // [2*runs][G][K] fp32: column sums of dS of the main CTAs
+  float* partial_ib_x; // [2*n_extra][slots][G][128] fp32: ... of the extra pairs' CTAs
   int* err;
 };
 
@@ -92,6 +95,7 @@ struct DadrBarriers {
   uint64_t ds_full[2];                     // local: the gate warps wrote dS (for the dR warps)
   uint64_t ds_empty[2];                    // local: dR warps + the commit after dS.R
   uint64_t da_full;                        // local, multicast commit: dA of the tile is complete in TMEM
+  uint64_t ib_full[2];                     // local (IB): every gate warp wrote its column sums of dS
   uint32_t tmem_base;
 };
 
@@ -171,6 +175,7 @@ struct DadrUnit {
   bool first;     // first tile that touches this dR slab: store, do not add
   float* part;    // dR slab of this CTA for the tile's column (row 0, feature f0)
   long long ld;   // its row pitch
+  float* part_ib; // d(internal bias) slab of this CTA for the tile's column (group 0, feature f0), same pitch
 };
 __device__ __forceinline__ int dadr_tiles_of_run(const DadrParams& p, int run) {
   return ((p.n_mtiles + 1) / 2 - run + p.runs - 1) / p.runs;
@@ -190,6 +195,7 @@ __device__ __forceinline__ DadrUnit dadr_unit(const DadrParams& p, int pidx, int
     u.first = (k == 0);
     u.part = p.partial + (long long)(run * 2 + rank) * GE * p.K + u.f0;
     u.ld = p.K;
+    u.part_ib = p.partial_ib + (long long)(run * 2 + rank) * p.G * p.K + u.f0;
   } else {
     const int e = pidx - p.n_main;
     const int m_lo = e * p.n_main / p.n_extra;
@@ -202,11 +208,16 @@ __device__ __forceinline__ DadrUnit dadr_unit(const DadrParams& p, int pidx, int
     u.first = (j == 0);
     u.part = p.partial_x + ((long long)(e * 2 + rank) * p.slots + mi) * GE * 128;
     u.ld = 128;
+    u.part_ib = p.partial_ib_x + ((long long)(e * 2 + rank) * p.slots + mi) * p.G * 128;
   }
   return u;
 }
 
-template <int DT, int GATE, int E>
+// IB: the internal-bias variant (gated modes): S += bias before the gate, and the column sums of dS over
+// the tokens (the bias gradient) leave through a second set of per-CTA fp32 buffers: every gate warp
+// sums its 16 token rows with shuffles, the 8 warps of a 64-feature chunk meet in shared memory, are
+// added in a fixed order, and one thread per column stores (first tile) or adds (later tiles).
+template <int DT, int GATE, int E, bool IB>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(dadr::kThreads, 1)
 prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmRr,
                       const __grid_constant__ CUtensorMap tmRd, const __grid_constant__ CUtensorMap tmdC,
@@ -227,7 +238,8 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   uint8_t* smemDS = smemA + 2 * kTile;          // 2 buffers x 2 tiles [128 x 64]
   uint8_t* smemR = smemDS + 4 * kTile;          // rb buffers
   uint8_t* smemSt = smemR + p.rb * r_buf_bytes; // ns stages: dC tiles + B tile
-  DadrBarriers* bars = reinterpret_cast<DadrBarriers*>(smemSt + p.ns * St::kBytes);
+  float* smemIb = reinterpret_cast<float*>(smemSt + p.ns * St::kBytes);   // IB: [2][16 gate warps][64] column sums
+  DadrBarriers* bars = reinterpret_cast<DadrBarriers*>(smemSt + p.ns * St::kBytes + (IB ? 8192 : 0));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -255,6 +267,8 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     mbar_init(&bars->s_full, 1);
     mbar_init(&bars->s_free, 2 * kNumGateWarps);
     mbar_init(&bars->da_full, 1);
+    mbar_init(&bars->ib_full[0], kNumGateWarps);
+    mbar_init(&bars->ib_full[1], kNumGateWarps);
     fence_mbar_init();
   }
   if (warp == kWarpMma) {
@@ -476,6 +490,9 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const uint32_t tileA = smem_u32(smemA + ch * kTile);
     const uint32_t s_free_addr = mapa_shared(smem_u32(&bars->s_free), 0);
     const uint32_t gate_done_addr = mapa_shared(smem_u32(&bars->gate_done[0]), 0);
+    // internal bias: this warp's 64 columns of row 0 of the [G, K] bias, and how many of them lie inside K
+    const uint16_t* ib_row = nullptr;
+    int ib_valid = 0;
     float dacc[8][4];   // gate term of dA, 16 rows x 64 columns of this warp, whole tile
 #pragma unroll
     for (int i = 0; i < 8; ++i) { dacc[i][0] = dacc[i][1] = dacc[i][2] = dacc[i][3] = 0.f; }
@@ -485,6 +502,10 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const DadrUnit u = dadr_unit(p, pidx, (int)rank, k);
       const int f0 = u.f0;
       const int mt = u.mp * 2 + (int)rank;
+      if (IB) {
+        ib_row = reinterpret_cast<const uint16_t*>(p.ib) + f0 + ch * 64;
+        ib_valid = p.K - (f0 + ch * 64);
+      }
       if (!mbar_wait(&bars->a_full, tile_iter & 1)) { ok = false; break; }
       for (int g = 0; g < G && ok; ++g, ++gg) {
         const uint32_t hb = gg & 1, ph = (gg >> 1) & 1;
@@ -511,6 +532,25 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             tmem_ld_16x256b_x2(tdh + pc * 16, dh[i]);
           }
           tmem_ld_wait();
+          if (IB && kGated) {
+            // the rotation delivered S/2 (halved R): add half the bias
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const int c = (pass * 2 + i) * 16 + 2 * (lane & 3);
+              const uint16_t* ibp = ib_row + (long long)g * p.K;
+              float2 lo = make_float2(0.f, 0.f), hi = make_float2(0.f, 0.f);
+              if (c < ib_valid) lo = Elem<DT>::unpack(__ldg(reinterpret_cast<const uint32_t*>(ibp + c)));
+              if (c + 8 < ib_valid) hi = Elem<DT>::unpack(__ldg(reinterpret_cast<const uint32_t*>(ibp + c + 8)));
+              sv[i][0] = __float_as_uint(fmaf(lo.x, 0.5f, __uint_as_float(sv[i][0])));
+              sv[i][1] = __float_as_uint(fmaf(lo.y, 0.5f, __uint_as_float(sv[i][1])));
+              sv[i][2] = __float_as_uint(fmaf(lo.x, 0.5f, __uint_as_float(sv[i][2])));
+              sv[i][3] = __float_as_uint(fmaf(lo.y, 0.5f, __uint_as_float(sv[i][3])));
+              sv[i][4] = __float_as_uint(fmaf(hi.x, 0.5f, __uint_as_float(sv[i][4])));
+              sv[i][5] = __float_as_uint(fmaf(hi.y, 0.5f, __uint_as_float(sv[i][5])));
+              sv[i][6] = __float_as_uint(fmaf(hi.x, 0.5f, __uint_as_float(sv[i][6])));
+              sv[i][7] = __float_as_uint(fmaf(hi.y, 0.5f, __uint_as_float(sv[i][7])));
+            }
+          }
           if (kGated && pass == 1) {
             // this warp holds all its S values: the S buffer may be refilled for the next group
             tc_fence_before_sync();
@@ -547,6 +587,45 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 #pragma unroll
           for (int i = 0; i < 2; ++i)
             stmatrix_x4(tileDS + sw128_offset(a_row, (pass * 2 + i) * 2 + (mat >> 1)), dsf[i]);
+          if (IB && kGated) {
+            // column sums of (2 dS) over this warp's 16 token rows: rows r and r+8 of the thread, then the
+            // 8 lane groups; lanes 0-3 end up with columns 2 lane + {0,1} (+8) of each piece
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const float2 p0 = Elem<DT>::unpack(dsf[i][0]), p1 = Elem<DT>::unpack(dsf[i][1]);
+              const float2 p2 = Elem<DT>::unpack(dsf[i][2]), p3 = Elem<DT>::unpack(dsf[i][3]);
+              float c0 = p0.x + p1.x, c1 = p0.y + p1.y, c2 = p2.x + p3.x, c3 = p2.y + p3.y;
+#pragma unroll
+              for (int sh = 4; sh <= 16; sh <<= 1) {
+                c0 += __shfl_xor_sync(0xffffffffu, c0, sh);
+                c1 += __shfl_xor_sync(0xffffffffu, c1, sh);
+                c2 += __shfl_xor_sync(0xffffffffu, c2, sh);
+                c3 += __shfl_xor_sync(0xffffffffu, c3, sh);
+              }
+              if (lane < 4) {
+                float* dst = smemIb + ((gg & 1) * kNumGateWarps + gw) * 64 + (pass * 2 + i) * 16 + 2 * lane;
+                dst[0] = c0; dst[1] = c1; dst[8] = c2; dst[9] = c3;
+              }
+            }
+          }
+        }
+        if (IB && kGated) {
+          // the 8 warps of this 64-feature chunk (one per 16-token row group) are added in a fixed order
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->ib_full[gg & 1]);
+          if (!mbar_wait(&bars->ib_full[gg & 1], (gg >> 1) & 1)) { ok = false; break; }
+          if (lane < 8) {
+            const int rid = gw & 7, col = rid * 8 + lane;
+            const float* src = smemIb + ((gg & 1) * kNumGateWarps + ch * 8) * 64 + col;
+            float tsum = 0.f;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) tsum += src[r * 64];
+            if (f0 + ch * 64 + col < p.K) {
+              float* dst = u.part_ib + (long long)g * u.ld + ch * 64 + col;
+              if (u.first) *dst = tsum;
+              else asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst), "f"(tsum) : "memory");
+            }
+          }
         }
         fence_proxy_async_smem();   // dS is read by the dS . R MMAs through the async proxy
         tc_fence_before_sync();
@@ -720,6 +799,29 @@ __global__ void dr_reduce_kernel(const float* __restrict__ partial, const float*
     *reinterpret_cast<uint32_t*>(reinterpret_cast<uint16_t*>(dR_out) + (long long)row * lddr + k) = Elem<DT>::pack(acc.x * scale, acc.y * scale);
 }
 
+// d_ib[g, k] = cast( scale * sum of the CTAs' column sums of dS ), in the same fixed order as dR.
+template <int DT>
+__global__ void dib_reduce_kernel(const float* __restrict__ partial, const float* __restrict__ partial_x,
+                                  uint16_t* __restrict__ d_ib, int G, int K, long long ldib, int runs, int n_ft,
+                                  int n_main, int n_extra, int steal, int slots, float scale) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)G * K) return;
+  const int k = (int)(idx % K), g = (int)(idx / K);
+  float acc = 0.f;
+  for (int r = 0; r < 2 * runs; ++r) acc += partial[((long long)r * G + g) * K + k];
+  if (steal > 0) {
+    const int fx = k >> 7, kk = k & 127;
+    for (int run = 0; run < runs; ++run) {
+      const int m = run * n_ft + fx;
+      const int e = ((m + 1) * n_extra - 1) / n_main;
+      const int mi = m - e * n_main / n_extra;
+      for (int rank = 0; rank < 2; ++rank)
+        acc += partial_x[(((long long)(e * 2 + rank) * slots + mi) * G + g) * 128 + kk];
+    }
+  }
+  d_ib[(long long)g * ldib + k] = (uint16_t)(Elem<DT>::pack(acc * scale, 0.f) & 0xffffu);
+}
+
 // Grid of the dA+dR kernel.  runs: the number of main CTA pairs that share one feature column (each
 // walks every runs-th 256-token tile).  When the main pairs leave SM pairs idle and have enough
 // tiles each, the idle pairs become extra pairs and every main pair leaves its last `steal` tiles
@@ -772,12 +874,13 @@ void dadr_plan_grid(int M, int K, int num_sms, const int* cfg, DadrGrid* gr) {
 }
 
 template <int E>
-static int dadr_plan(DadrParams& p, int& smem_bytes) {
+static int dadr_plan(DadrParams& p, int& smem_bytes, bool ib) {
   using St = dadr::Stage<E>;
   p.rr_tile_bytes = ((E / 2 * 128) + 1023) / 1024 * 1024;
   p.rd_tile_bytes = ((E * 128) + 1023) / 1024 * 1024;
   p.rb = (E <= 16) ? 4 : 2;
-  const int fixed = 6 * dadr::kTile + p.rb * 2 * (p.rr_tile_bytes + p.rd_tile_bytes) + (int)sizeof(DadrBarriers) + 1024;
+  const int fixed = 6 * dadr::kTile + p.rb * 2 * (p.rr_tile_bytes + p.rd_tile_bytes) + (int)sizeof(DadrBarriers) + 1024 +
+                    (ib ? 8192 : 0);
   int ns = (227 * 1024 - 256 - fixed) / St::kBytes;
   if (ns > dadr::kMaxStages) ns = dadr::kMaxStages;
   if (ns < 2) return fail(PRISM_ERR_UNSUPPORTED, "bwd_dadr does not fit shared memory (E=%d)", E);
@@ -797,7 +900,9 @@ int launch_bwd_dadr(const DadrArgs& a) {
   p.scale = a.scale;
   p.dA = a.dA; p.ldda = a.ldda; p.partial = a.partial; p.err = a.err;
   int smem_bytes = 0;
-  int rc = (a.E == 16) ? dadr_plan<16>(p, smem_bytes) : (a.E == 32) ? dadr_plan<32>(p, smem_bytes) : dadr_plan<64>(p, smem_bytes);
+  const bool ib = a.ib != nullptr && a.gate != GATE_NONE;
+  p.ib = ib ? a.ib : nullptr; p.partial_ib = a.partial_ib; p.partial_ib_x = a.partial_ib_x;
+  int rc = (a.E == 16) ? dadr_plan<16>(p, smem_bytes, ib) : (a.E == 32) ? dadr_plan<32>(p, smem_bytes, ib) : dadr_plan<64>(p, smem_bytes, ib);
   if (rc) return rc;
   const int stage_out = 64;
 
@@ -810,9 +915,10 @@ int launch_bwd_dadr(const DadrArgs& a) {
 
   using KernT = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, DadrParams);
   KernT kern = nullptr;
-#define PRISM_PICK_G(DT_, E_)                                                                    \
-  (a.gate == GATE_SILU ? (KernT)prism_bwd_dadr_kernel<DT_, GATE_SILU, E_>                                       \
-                       : a.gate == GATE_SIGMOID ? (KernT)prism_bwd_dadr_kernel<DT_, GATE_SIGMOID, E_> : (KernT)prism_bwd_dadr_kernel<DT_, GATE_NONE, E_>)
+#define PRISM_PICK_G(DT_, E_)                                                                                \
+  (a.gate == GATE_SILU ? (ib ? (KernT)prism_bwd_dadr_kernel<DT_, GATE_SILU, E_, true> : (KernT)prism_bwd_dadr_kernel<DT_, GATE_SILU, E_, false>) \
+   : a.gate == GATE_SIGMOID ? (ib ? (KernT)prism_bwd_dadr_kernel<DT_, GATE_SIGMOID, E_, true> : (KernT)prism_bwd_dadr_kernel<DT_, GATE_SIGMOID, E_, false>) \
+                            : (KernT)prism_bwd_dadr_kernel<DT_, GATE_NONE, E_, false>)
 #define PRISM_PICK(E_) kern = (a.dtype == DT_BF16) ? PRISM_PICK_G(DT_BF16, E_) : PRISM_PICK_G(DT_F16, E_)
   if (a.E == 16) { PRISM_PICK(16); } else if (a.E == 32) { PRISM_PICK(32); } else { PRISM_PICK(64); }
 #undef PRISM_PICK_G
@@ -833,7 +939,17 @@ int launch_bwd_dadr(const DadrArgs& a) {
   if (a.dtype == DT_BF16) { if (a.dr_f32) PRISM_DR_REDUCE(DT_BF16, true); else PRISM_DR_REDUCE(DT_BF16, false); }
   else { if (a.dr_f32) PRISM_DR_REDUCE(DT_F16, true); else PRISM_DR_REDUCE(DT_F16, false); }
 #undef PRISM_DR_REDUCE
-  return check_launch("prism_bwd_dadr reduce");
+  if ((rc = check_launch("prism_bwd_dadr reduce"))) return rc;
+  if (ib) {
+    const long long n = (long long)p.G * a.K;
+    const long long nblocks = (n + threads - 1) / threads;
+    if (a.dtype == DT_BF16)
+      dib_reduce_kernel<DT_BF16><<<(unsigned)nblocks, threads, 0, a.stream>>>(a.partial_ib, a.partial_ib_x, reinterpret_cast<uint16_t*>(a.d_ib), p.G, a.K, a.K, p.runs, p.n_ft, p.n_main, p.n_extra, p.steal, p.slots, r_scale);
+    else
+      dib_reduce_kernel<DT_F16><<<(unsigned)nblocks, threads, 0, a.stream>>>(a.partial_ib, a.partial_ib_x, reinterpret_cast<uint16_t*>(a.d_ib), p.G, a.K, a.K, p.runs, p.n_ft, p.n_main, p.n_extra, p.steal, p.slots, r_scale);
+    return check_launch("prism_bwd_dadr internal-bias reduce");
+  }
+  return PRISM_OK;
 }
 
 }  // namespace prism

@@ -50,6 +50,7 @@ struct DbParams {
   int splits;
   int out_f32;        // 1: dB is fp32
   float scale;
+  const void* ib;     // internal bias [G, K] or null
   void* dB;
   long long lddb;
   float* partial;     // [splits][part_rows][K] when splits > 1
@@ -221,13 +222,18 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // S of rotation block b sits in columns [2E b, 2E b + 2E); this CTA's product in the rank-th half
     const uint32_t s_tmem = tmem_base + (r0 << 16) + kSCol0 + ft * (64 / E) * 2 * E + rank * E;
     const uint32_t s_free_addr = mapa_shared(smem_u32(&bars->s_free), 0);
+    // internal bias of this warp's 64 features (columns of A), the same for every token block
+    const int kcol = f0 + (int)ft * 64;
+    const int kvalid = p.K - kcol;
+    const uint16_t* ib = (p.ib != nullptr && kvalid > 0)
+                             ? reinterpret_cast<const uint16_t*>(p.ib) + (long long)g * p.K + kcol : nullptr;
     bool ok = true;
     Ring rs(p.ns);
     for (int j = 0; j < nb && ok; ++j, rs.next()) {
       if (!mbar_wait(&bars->s_full, j & 1)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t tile = smem_u32(smemSt + rs.idx * p.stage_bytes + ft * kTile);
-      gate_rows16_tmem_smem<DT, GATE, E>(s_tmem, 2 * E, tile, r0, lane, s_free_addr);
+      gate_rows16_tmem_smem<DT, GATE, E>(s_tmem, 2 * E, tile, r0, lane, s_free_addr, ib, kvalid);
       fence_proxy_async_smem();   // H was written by the generic proxy, the MMA reads it through the async proxy
       tc_fence_before_sync();
       __syncwarp();
@@ -340,7 +346,7 @@ int launch_bwd_db(const DbArgs& a) {
   p.n_tokblocks = (a.M + 127) / 128;
   p.dc_tiles = (a.BN / 2 + 63) / 64;   // per CTA: half of the tile's dC columns
   p.r_tile_bytes = ((a.E * 128) + 1023) / 1024 * 1024;
-  p.scale = a.scale; p.out_f32 = a.out_f32;
+  p.scale = a.scale; p.out_f32 = a.out_f32; p.ib = a.ib;
   p.dB = a.dB; p.lddb = a.lddb; p.partial = a.partial; p.err = a.err;
   if ((a.plan.splits > 1 || a.plan.tail_rows > 0) && a.partial == nullptr)
     return fail(PRISM_ERR_WORKSPACE, "bwd_db: split accumulation needs a partial-sum workspace");

@@ -675,6 +675,30 @@ __device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)
                : "memory");
 }
 
+// Internal bias of the gated modes: S[:, k] += factor * ib[k] before the gate.  `ib` points at the bias of
+// the warp's 64-column chunk (16-bit, row g of the [G, K] bias, 4-byte aligned), `kvalid` is the number
+// of columns of the chunk that lie inside K.  s[pc] holds piece pc (16 columns) in the accumulator
+// fragment layout: values 0-3 in columns 2(lane%4) + {0,1}, values 4-7 eight columns further on.
+template <int DT>
+__device__ __forceinline__ void add_internal_bias(uint32_t (&s)[4][8], const uint16_t* ib, int kvalid, int lane,
+                                                  float factor) {
+#pragma unroll
+  for (int pc = 0; pc < 4; ++pc) {
+    const int c = pc * 16 + 2 * (lane & 3);
+    float2 lo = make_float2(0.f, 0.f), hi = make_float2(0.f, 0.f);
+    if (c < kvalid) lo = Elem<DT>::unpack(__ldg(reinterpret_cast<const uint32_t*>(ib + c)));
+    if (c + 8 < kvalid) hi = Elem<DT>::unpack(__ldg(reinterpret_cast<const uint32_t*>(ib + c + 8)));
+    s[pc][0] = __float_as_uint(fmaf(lo.x, factor, __uint_as_float(s[pc][0])));
+    s[pc][1] = __float_as_uint(fmaf(lo.y, factor, __uint_as_float(s[pc][1])));
+    s[pc][2] = __float_as_uint(fmaf(lo.x, factor, __uint_as_float(s[pc][2])));
+    s[pc][3] = __float_as_uint(fmaf(lo.y, factor, __uint_as_float(s[pc][3])));
+    s[pc][4] = __float_as_uint(fmaf(hi.x, factor, __uint_as_float(s[pc][4])));
+    s[pc][5] = __float_as_uint(fmaf(hi.y, factor, __uint_as_float(s[pc][5])));
+    s[pc][6] = __float_as_uint(fmaf(hi.x, factor, __uint_as_float(s[pc][6])));
+    s[pc][7] = __float_as_uint(fmaf(hi.y, factor, __uint_as_float(s[pc][7])));
+  }
+}
+
 // Gate step when the rotation runs on tcgen05: one warp turns its 16 rows x 64 columns of
 // S = A . blockdiag(R_g)^T (fp32 in TMEM at s_tmem, lane field = the warp's first row) into H
 // (16-bit) and writes H to TMEM at h_tmem as the A operand of the dense MMA (8 columns per 16 K
@@ -684,9 +708,10 @@ __device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)
 // Nothing here touches the legacy tensor path: mma.sync shares the tensor cores with tcgen05.mma
 // and is starved while a burst of tcgen05.mma runs (measured: 13x slower), which would serialise
 // the gate warps with the dense product.
+// ib / kvalid: internal bias of the chunk (see add_internal_bias), or null.
 template <int DT, int GATE>
 __device__ __forceinline__ void gate_rows16_tmem(uint32_t s_tmem, uint32_t tile, uint32_t r0, int lane,
-                                                 uint32_t h_tmem) {
+                                                 uint32_t h_tmem, const uint16_t* ib = nullptr, int kvalid = 64) {
   const uint32_t mat = lane >> 3, l8 = lane & 7;
   const uint32_t a_row = r0 + l8 + (mat & 1) * 8;
   uint32_t s[4][8], af[4][4], h[4][4];
@@ -700,6 +725,7 @@ __device__ __forceinline__ void gate_rows16_tmem(uint32_t s_tmem, uint32_t tile,
     for (int pc = 0; pc < 4; ++pc) af[pc][0] = af[pc][1] = af[pc][2] = af[pc][3] = 0u;
   }
   tmem_ld_wait();
+  if (GATE != GATE_NONE && ib != nullptr) add_internal_bias<DT>(s, ib, kvalid, lane, 1.0f);
 #pragma unroll
   for (int pc = 0; pc < 4; ++pc) {
     h[pc][0] = gate_pair<DT, GATE, (PRISM_FWD_CVT_HW != 0) && GATE != GATE_NONE>(af[pc][0], __uint_as_float(s[pc][0]), __uint_as_float(s[pc][1]));
@@ -720,7 +746,8 @@ __device__ __forceinline__ void gate_rows16_tmem(uint32_t s_tmem, uint32_t tile,
 // values in registers: a single S buffer can then be refilled while the gate math still runs.
 template <int DT, int GATE, int E>
 __device__ __forceinline__ void gate_rows16_tmem_smem(uint32_t s_tmem, uint32_t blk_stride, uint32_t tile, uint32_t r0,
-                                                      int lane, uint32_t s_free) {
+                                                      int lane, uint32_t s_free, const uint16_t* ib = nullptr,
+                                                      int kvalid = 64) {
   constexpr int KS = E / 16;
   const uint32_t mat = lane >> 3, l8 = lane & 7;
   const uint32_t a_row = r0 + l8 + (mat & 1) * 8;
@@ -740,6 +767,7 @@ __device__ __forceinline__ void gate_rows16_tmem_smem(uint32_t s_tmem, uint32_t 
     __syncwarp();
     if (lane == 0) mbar_arrive_cluster(s_free);
   }
+  if (GATE != GATE_NONE && ib != nullptr) add_internal_bias<DT>(s, ib, kvalid, lane, 1.0f);
 #pragma unroll
   for (int pc = 0; pc < 4; ++pc) {
     h[pc][0] = gate_pair<DT, GATE, (PRISM_DB_CVT_HW != 0) && GATE != GATE_NONE>(af[pc][0], __uint_as_float(s[pc][0]), __uint_as_float(s[pc][1]));

@@ -58,6 +58,7 @@ struct FwdParams {
   int stage_bytes;
   int tma_store;        // 1: epilogue goes through TMA stores (BN multiple of 64)
   const void* bias;     // [N] or null
+  const void* ib;       // internal bias [G, K] or null
   void* C;
   long long ldc;
   int* err;
@@ -269,11 +270,31 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     Ring rs(p.ns);
     for (uint32_t i = 0; i < group; ++i) rs.next();
     bool ok = true;
+    // internal bias: group and K chunk of chunk j, followed without a division per chunk
+    const uint16_t* ibase = reinterpret_cast<const uint16_t*>(p.ib);
+    int tg = cid, kc = (int)group, gcur = 0;
+    if (ibase != nullptr && total > 0) {
+      while (kc >= nk) { kc -= nk; tg += n_clusters; }
+      int mt0, nt0;
+      tile_coords(p, tg, mt0, nt0);
+      gcur = nt0 / p.ntiles_per_group;
+    }
     for (uint32_t j = group; j < total; j += kGateGroups, rs.next(), rs.next()) {
       const uint32_t slot = j & (kSlots - 1);
       if (!mbar_wait(&bars->s_full[slot], (j / kSlots) & 1)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t s_tmem = tmem_base + (r0 << 16) + kSlotCol0 + slot * 64;
+      const uint16_t* ib = nullptr;
+      if (ibase != nullptr) {
+        ib = ibase + (long long)gcur * p.K + kc * 64;
+        const int kv = p.K - kc * 64;
+        gate_rows16_tmem<DT, GATE>(s_tmem, smem_u32(smemSt + rs.idx * p.stage_bytes), r0, lane, s_tmem, ib, kv);
+        kc += kGateGroups;
+        if (kc >= nk) {
+          while (kc >= nk) { kc -= nk; tg += n_clusters; }
+          if (tg < p.n_tiles) { int mt1, nt1; tile_coords(p, tg, mt1, nt1); gcur = nt1 / p.ntiles_per_group; }
+        }
+      } else
       gate_rows16_tmem<DT, GATE>(s_tmem, smem_u32(smemSt + rs.idx * p.stage_bytes), r0, lane, s_tmem);
       tmem_st_wait();
       tc_fence_before_sync();
@@ -393,7 +414,7 @@ int launch_fwd(const FwdArgs& a) {
   p.n_kchunks = (a.K + 63) / 64;
   p.r_tile_bytes = ((a.E / 2 * 128) + 1023) / 1024 * 1024;   // this CTA's E/2 rows of the R tile
   p.tma_store = (a.BN % 64 == 0) ? 1 : 0;
-  p.bias = a.bias; p.C = a.C; p.ldc = a.ldc; p.err = a.err;
+  p.bias = a.bias; p.ib = a.ib; p.C = a.C; p.ldc = a.ldc; p.err = a.err;
 
   const int budget = 227 * 1024 - 1024 - (int)sizeof(FwdBarriers) - 256 - fwd::kNumEpiWarps * fwd::kEpiStageBytes;
   p.stage_bytes = fwd::kATileBytes + p.r_tile_bytes + a.BN * 64;   // A tile, halves of the R and B tiles

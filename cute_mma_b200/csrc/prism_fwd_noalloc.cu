@@ -86,7 +86,7 @@ extern "C" int prism_fwd_noalloc(const void* A, const void* B, const void* R, co
   // the status word must start at zero; the array still holds whatever the last call left
   cudaError_t e = cudaMemsetAsync(scratch, 0, PRISM_WORKSPACE_HEADER_BYTES, s);
   if (e != cudaSuccess) return fail(PRISM_ERR_CUDA, "prism_fwd_noalloc: clearing the status word: %s", cudaGetErrorString(e));
-  rc = prism_fwd(A, B, R, bias, C, M, N, K, group_size, reconn_sz, dtype, gate, lda, ldb, ldr, ldc, cfg,
+  rc = prism_fwd(A, B, R, bias, nullptr, C, M, N, K, group_size, reconn_sz, dtype, gate, lda, ldb, ldr, ldc, cfg,
                  scratch, (size_t)PRISM_NOALLOC_SCRATCH_BYTES, stream);
   if (rc) return rc;
   if (device_status != nullptr) {

@@ -49,6 +49,7 @@ struct FwdSmallParams {
   int pmax;            // partial slots per group
   int ns, stage_bytes, a_off, r_off, b_off;
   const void* bias;
+  const void* ib;      // internal bias [G, K] or null
   void* C;
   long long ldc;
   float* partial;      // [G][pmax][Mp][gs] fp32
@@ -237,13 +238,17 @@ prism_fwd_small_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       Ring rs(p.ns);
       bool ok = true;
       const int n = u1 - u0;
+      const uint16_t* ibase = reinterpret_cast<const uint16_t*>(p.ib);
+      int g = u0 / p.nk, kc = u0 - g * p.nk;
       for (int i = 0; i < n; ++i, rs.next()) {
         const uint32_t slot = (uint32_t)i & 1u;
         if (!mbar_wait(&bars->s_full[slot], ((uint32_t)i >> 1) & 1)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t tile = smem_u32(smemSt + rs.idx * p.stage_bytes + p.a_off);
+        const uint16_t* ib = ibase != nullptr ? ibase + (long long)g * p.K + kc * 64 : nullptr;
         gate_rows16_tmem_smem<DT, GATE, E>(tmem_base + (r0 << 16) + kSCol0 + slot * 64, E, tile, r0, lane,
-                                           smem_u32(&bars->s_free[slot]));
+                                           smem_u32(&bars->s_free[slot]), ib, p.K - kc * 64);
+        if (++kc == p.nk) { kc = 0; ++g; }
         fence_proxy_async_smem();   // H was written by the generic proxy, the MMA reads it through the async proxy
         tc_fence_before_sync();
         __syncwarp();
@@ -364,7 +369,7 @@ int launch_fwd_small(const FwdArgs& a, void* scratch) {
   p.nrt = a.gs / 128;
   p.nk = (a.K + 63) / 64;
   fwd_small_partition(p.G, p.nk, a.num_sms, &p.units, &p.ncta, &p.pmax);
-  p.bias = a.bias; p.C = a.C; p.ldc = a.ldc; p.err = a.err;
+  p.bias = a.bias; p.ib = a.ib; p.C = a.C; p.ldc = a.ldc; p.err = a.err;
   p.partial = reinterpret_cast<float*>(scratch);
   // stage: A tile (Mp rows), R tile, B tiles, each on a 1024-byte boundary (128-byte swizzle atoms)
   p.a_off = 0;

@@ -13,6 +13,7 @@ struct FwdArgs {
   const void* B;      // [N, K]
   const void* R_eff;  // [(N/gs)*E, K]  rotation blocks padded to E x E
   const void* bias;   // [N] or null
+  const void* ib;     // internal bias [N/gs, K] (gated modes) or null
   void* C;            // [M, N]
   int M, N, K, gs, E;
   int dtype, gate;
@@ -49,6 +50,7 @@ struct DbArgs {
   const void* dC;     // [M, N]
   const void* A;      // [M, K]
   const void* R_eff;  // [(N/gs)*E, K]
+  const void* ib;     // internal bias [N/gs, K] (gated modes) or null
   void* dB;           // [N, K], 16-bit like the inputs or fp32 (out_f32)
   int M, N, K, gs, E;
   int dtype, gate;
@@ -81,6 +83,10 @@ struct DadrArgs {
   const void* R_eff;  // [(N/gs)*E, K]
   void* dA;           // [M, K]
   void* dR;           // [(N/gs)*rs, K], 16-bit like the inputs or fp32 (dr_f32)
+  const void* ib;     // internal bias [N/gs, K] (gated modes) or null
+  void* d_ib;         // its gradient [N/gs, K] (same dtype as the inputs), when ib is given
+  float* partial_ib;  // fp32 column sums of dS per main CTA: [2*runs][N/gs][K]
+  float* partial_ib_x;  // ... and per slab of the extra pairs' CTAs: [2*n_extra][slots][N/gs][128]
   int M, N, K, gs, rs, E;
   int dtype, gate;
   int dr_f32;         // 1: dR is written as fp32

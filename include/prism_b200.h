@@ -52,6 +52,7 @@ extern "C" {
 #define PRISM_KIND_BWD_DADR 1
 #define PRISM_KIND_BWD_DB 2
 #define PRISM_KIND_DBIAS 3
+#define PRISM_KIND_BWD_DADR_IB 4   /* prism_bwd_dadr with an internal bias (more scratch) */
 
 /* element types: the 16-bit input types, and fp32 for gradient outputs that should leave unrounded */
 #define PRISM_DTYPE_F16 0
@@ -63,13 +64,15 @@ extern "C" {
 /* size of the library's built-in scratch array used by prism_fwd_noalloc: 8 MiB + the status header */
 #define PRISM_NOALLOC_SCRATCH_BYTES (8 * 1024 * 1024 + 256)
 
-/* Forward.  bias: [N] in the same dtype, or NULL.  cfg (4 ints, 0 = default): {BN, PM, stages, path}:
+/* Forward.  bias: [N] in the same dtype, or NULL.  internal_bias: [N/group_size, K] in the same dtype
+ * (contiguous rows), or NULL: added to A.blockdiag(R_g)^T before the gate (gated modes only; reference:
+ * src/cute_prism/_pytorch_backend.py:154-156, cute_prism_coop_pc.cu:250-301).  cfg (4 ints, 0 = default): {BN, PM, stages, path}:
  * N tile (divides group_size, <= 256), row tiles per rasterisation panel, shared-memory stages, and the
  * kernel: 0 = by shape, 1 = the general tiled kernel, 2 = the few-token streaming kernel (M <= 128 and
  * group_size a multiple of 128; picked by default up to 48 tokens).  The streaming kernel cuts B into
  * equal shares for all SMs, keeps fp32 partial sums of the shares in the workspace and adds them in a
  * fixed order, so its result is bit-stable; ask prism_workspace_bytes with the same cfg. */
-int prism_fwd(const void* A, const void* B, const void* R, const void* bias, void* C,
+int prism_fwd(const void* A, const void* B, const void* R, const void* bias, const void* internal_bias, void* C,
               int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
               long long lda, long long ldb, long long ldr, long long ldc,
               const int* cfg, void* workspace, size_t workspace_bytes, void* stream);
@@ -100,9 +103,11 @@ int prism_fwd_noalloc(const void* A, const void* B, const void* R, const void* b
  * main pair (steal < 0: never).  Each CTA accumulates dR into fp32 memory of its own
  * in the workspace in a fixed order and a second kernel adds the buffers in a fixed order: dR is
  * bit-identical from run to run.  The workspace also holds the kernel's copy of R (widened for
- * reconn_sz = 8, halved in the gated mode). */
-int prism_bwd_dadr(const void* dC, const void* A, const void* B, const void* R, void* dA, void* dR,
-                   int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
+ * reconn_sz = 8, halved in the gated mode).  internal_bias (or NULL): as in prism_fwd; then
+ * d_internal_bias [N/group_size, K] (input dtype) receives dc_scale * sum over tokens of dS, summed in a
+ * fixed order like dR, and the workspace is sized with PRISM_KIND_BWD_DADR_IB. */
+int prism_bwd_dadr(const void* dC, const void* A, const void* B, const void* R, const void* internal_bias,
+                   void* dA, void* dR, void* d_internal_bias, int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
                    int dr_dtype, float dc_scale, long long lddc, long long lda, long long ldb, long long ldr,
                    long long ldda, long long lddr,
                    const int* cfg, void* workspace, size_t workspace_bytes, void* stream);
@@ -114,7 +119,7 @@ int prism_bwd_dadr(const void* dC, const void* A, const void* B, const void* R, 
  * several CTA pairs whose fp32 partial sums (in the workspace) are added in a fixed order, so the
  * result is deterministic; splits < 0 never splits.  By default only the n-tile rows of a mostly
  * empty last wave are split (in a second launch). */
-int prism_bwd_db(const void* dC, const void* A, const void* R, void* dB,
+int prism_bwd_db(const void* dC, const void* A, const void* R, const void* internal_bias, void* dB,
                  int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
                  int db_dtype, float dc_scale, long long lddc, long long lda, long long ldr, long long lddb,
                  const int* cfg, void* workspace, size_t workspace_bytes, void* stream);

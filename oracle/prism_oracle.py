@@ -19,7 +19,7 @@ Parity pin: ``tests/golden/make_golden.py`` imports the reference package itself
 runs its pytorch backend on seeded inputs and stores inputs + outputs under
 ``tests/golden/``; ``tests/test_oracle.py`` checks this file against those vectors
 (and against torch autograd in float64).  Only the features on the accelerated path
-are restated: mode ``ar`` with ``silu_gate`` / ``sigmoid_gate``; no dropout, shuffle, internal bias or rw mode.
+are restated: mode ``ar`` with ``silu_gate`` / ``sigmoid_gate`` and the internal bias; no dropout, shuffle or rw mode.
 """
 from __future__ import annotations
 
@@ -60,8 +60,9 @@ def _gate(S, activation):
     return 2.0 * sig, 2.0 * sig * (1.0 - sig)
 
 
-def prism_forward(A, B, R, group_size, reconn_sz, activation=None, bias=None):
-    """C (M, N) in the dtype of A.  Follows ``pytorch_forward`` (ar mode, optional gate)."""
+def prism_forward(A, B, R, group_size, reconn_sz, activation=None, bias=None, internal_bias=None):
+    """C (M, N) in the dtype of A.  Follows ``pytorch_forward`` (ar mode, optional gate; the internal bias
+    (G, K) is added to S before the gate, lines 154-156)."""
     if activation not in GATES:
         raise ValueError(f"oracle restates {GATES} only, got {activation!r}")
     M, K = A.shape
@@ -71,6 +72,8 @@ def prism_forward(A, B, R, group_size, reconn_sz, activation=None, bias=None):
     C = torch.empty(M, N, dtype=A.dtype, device=A.device)
     for g in range(G):
         S = rotate(A, Rb[g])
+        if activation is not None and internal_bias is not None:
+            S = S + internal_bias[g]
         H = A * _gate(S, activation)[0] if activation is not None else S
         C[:, g * group_size:(g + 1) * group_size] = H @ B[g * group_size:(g + 1) * group_size].T
     if bias is not None:
@@ -78,8 +81,9 @@ def prism_forward(A, B, R, group_size, reconn_sz, activation=None, bias=None):
     return C
 
 
-def prism_backward(dC, A, B, R, group_size, reconn_sz, activation=None):
-    """(dA, dR, dB-or-None).  Follows ``pytorch_backward``."""
+def prism_backward(dC, A, B, R, group_size, reconn_sz, activation=None, internal_bias=None):
+    """(dA, dR, dB-or-None), plus d_internal_bias (G, K) = sum over tokens of dS as a fourth element when an
+    internal bias is given (lines 246-248, 271-272).  Follows ``pytorch_backward``."""
     if activation not in GATES:
         raise ValueError(f"oracle restates {GATES} only, got {activation!r}")
     M, K = A.shape
@@ -92,6 +96,7 @@ def prism_backward(dC, A, B, R, group_size, reconn_sz, activation=None):
     dA = torch.zeros_like(A)
     dR = torch.empty_like(R)
     dB = torch.empty_like(B) if gated else None
+    d_ib = torch.empty_like(internal_bias) if (gated and internal_bias is not None) else None
     Ab = A.reshape(M, nb, rs)
     for g in range(G):
         sl = slice(g * group_size, (g + 1) * group_size)
@@ -99,9 +104,13 @@ def prism_backward(dC, A, B, R, group_size, reconn_sz, activation=None):
         dH = dC_g @ B[sl]
         if gated:
             S = rotate(A, Rb[g])
+            if internal_bias is not None:
+                S = S + internal_bias[g]
             gate, gate_d = _gate(S, activation)
             dB[sl] = dC_g.T @ (A * gate)
             dS = dH * A * gate_d
+            if d_ib is not None:
+                d_ib[g] = dS.sum(dim=0)
             dA += dH * gate
         else:
             dS = dH
@@ -109,6 +118,8 @@ def prism_backward(dC, A, B, R, group_size, reconn_sz, activation=None):
         # dR block (g, b)[i, j] = sum_m dS[m, b*rs+i] * A[m, b*rs+j]
         dRg = torch.einsum("mbi,mbj->ibj", dS.reshape(M, nb, rs), Ab)
         dR[g * rs:(g + 1) * rs] = dRg.reshape(rs, K)
+    if d_ib is not None:
+        return dA, dR, dB, d_ib
     return dA, dR, dB
 
 

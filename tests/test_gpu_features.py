@@ -187,7 +187,7 @@ def test_bounded_wait_runs_out_and_is_reported():
     assert int(ws[:4].view(torch.int32).item()) == 0
     C = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
     p = lambda t: ctypes.c_void_p(t.data_ptr())
-    _lib.check(L.prism_fwd(p(A), p(B), p(R), None, p(C), M, N, K, gs, rs, 1, 1, K, K, K, N, None,
+    _lib.check(L.prism_fwd(p(A), p(B), p(R), None, None, p(C), M, N, K, gs, rs, 1, 1, K, K, K, N, None,
                            p(ws), ws.numel(), stream))
     assert L.prism_status(p(ws), stream) == 0
     assert O.rel_err(C.float(), O.prism_forward(A.float(), B.float(), R.float(), gs, rs, "silu_gate")) < TOL
@@ -309,4 +309,51 @@ def test_library_calls_can_be_captured_in_a_cuda_graph():
     torch.cuda.synchronize()
     assert torch.equal(y_static, y_eager) and torch.equal(x.grad, gx)
     assert torch.equal(layer.reconn.grad, gr) and torch.equal(layer.bias.grad, gb)
+    cp.check_device_status()
+
+
+@pytest.mark.parametrize("shape", [(1024, 256, 1024, 256, 8), (300, 208, 256, 128, 16), (2048, 512, 512, 256, 16),
+                                   (16, 256, 512, 256, 16), (512, 512, 256, 64, 32)], ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("act", ["silu_gate", "sigmoid_gate"])
+def test_internal_bias_forward_and_backward(shape, act):
+    """S = A . blockdiag(R_g)^T + internal_bias[g] before the gate; d_internal_bias = sum over tokens of dS
+    (reference: src/cute_prism/_pytorch_backend.py:154-156, 271-272), bit-stable like dR."""
+    M, K, N, gs, rs = shape
+    dt = torch.bfloat16 if rs != 8 else torch.float16
+    A, B, R, dC = _inputs(M, K, N, gs, rs, dt, seed=71)
+    ib = (torch.randn(N // gs, K, device=DEV) * 0.5).to(dt)
+    C, _ = cp.forward(A, B, R, gs, rs, activation=act, internal_bias=ib)
+    dA, dR, dB, d_ib = cp.backward(dC, A, B, R, gs, rs, activation=act, internal_bias=ib)
+    cp.check_device_status()
+    Af, Bf, Rf, ibf = A.float(), B.float(), R.float(), ib.float()
+    rC = O.prism_forward(Af, Bf, Rf, gs, rs, act, internal_bias=ibf)
+    rA, rR, rB, r_ib = O.prism_backward(dC.float(), Af, Bf, Rf, gs, rs, act, internal_bias=ibf)
+    for name, val, ref in (("C", C, rC), ("dA", dA, rA), ("dR", dR, rR), ("dB", dB, rB), ("d_ib", d_ib, r_ib)):
+        assert torch.isfinite(val).all(), name
+        assert O.rel_err(val.float(), ref) < TOL, (name, O.rel_err(val.float(), ref))
+    # the bias really takes part: without it the forward differs
+    C0, _ = cp.forward(A, B, R, gs, rs, activation=act)
+    assert O.rel_err(C0.float(), rC) > 5e-2
+    for _ in range(3):
+        dA2, dR2, dB2, d_ib2 = cp.backward(dC, A, B, R, gs, rs, activation=act, internal_bias=ib)
+        assert torch.equal(d_ib2, d_ib) and torch.equal(dR2, dR) and torch.equal(dA2, dA)
+    with pytest.raises(ValueError):
+        cp.forward(A, B, R, gs, rs, internal_bias=ib)   # plain mode
+
+
+def test_prism_linear_with_internal_bias_trains():
+    torch.manual_seed(3)
+    layer = cp.PrismLinear(256, 512, group_size=256, reconn_sz=16, activation="silu_gate", internal_bias=True)
+    layer = layer.to(DEV).to(torch.bfloat16)
+    x = torch.randn(4, 96, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = layer(x)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    A = x.detach().reshape(-1, 256)
+    s = layer._bwd_scale
+    rA, rR, rB, r_ib = O.prism_backward(dy.reshape(-1, 512).float() * s, A.float(), layer.weight.detach().float(),
+                                        layer.reconn.detach().float(), 256, 16, "silu_gate",
+                                        internal_bias=layer._internal_bias.detach().float())
+    assert O.rel_err(layer._internal_bias.grad.float(), r_ib) < TOL
+    assert O.rel_err(x.grad.reshape(-1, 256).float(), rA) < TOL and O.rel_err(layer.weight.grad.float(), rB) < TOL
     cp.check_device_status()

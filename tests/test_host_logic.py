@@ -34,8 +34,10 @@ def test_forward_rejects_cpu_and_bad_options():
         cp.forward(A, B, R, 32, 8, mode="wr")
     with pytest.raises(ValueError, match="gated"):
         cp.forward(A, B, R, 32, 8, mode="rw", activation="silu_gate")
-    with pytest.raises(ValueError, match="internal_bias"):
-        cp.forward(A, B, R, 32, 8, activation="silu_gate", internal_bias=torch.zeros(2, 64))
+    with pytest.raises(ValueError, match="gated"):
+        F._check_internal_bias(torch.zeros(2, 64), A, 64, 64, 32, 0)      # plain mode has no internal bias
+    with pytest.raises(ValueError, match="internal_bias must"):
+        F._check_internal_bias(torch.zeros(3, 64), A, 64, 64, 32, 1)      # wrong shape
     with pytest.raises(ValueError):
         cp.backward(torch.randn(8, 64), A, B, R, 32, 12)
 
@@ -77,8 +79,10 @@ def test_prism_linear_construction_and_state():
     assert torch.equal(m2.weight, m.weight)
     sg = cp.PrismLinear(64, 128, group_size=32, reconn_sz=16, activation="sigmoid_gate")
     assert sg.weight.requires_grad and abs(sg._bwd_scale - 1 / 1.15) < 1e-12
-    for bad in (dict(input_shuffle=True), dict(dropout=0.1),
-                dict(internal_bias=True), dict(activation="tanh")):
+    ibl = cp.PrismLinear(64, 128, group_size=32, reconn_sz=16, activation="silu_gate", internal_bias=True)
+    assert ibl._internal_bias.shape == (4, 64) and "_internal_bias" in ibl.state_dict()
+    assert cp.PrismLinear(64, 128, group_size=32, reconn_sz=16, internal_bias=True)._internal_bias is None   # plain mode: none
+    for bad in (dict(input_shuffle=True), dict(dropout=0.1), dict(activation="tanh")):
         with pytest.raises(ValueError):
             cp.PrismLinear(64, 128, 32, 16, **bad)
     with pytest.raises(ValueError):

@@ -36,6 +36,18 @@ def test_oracle_matches_reference_small(path):
             assert O.rel_err(dB, _t(z[f"dB_{tag}"])) < tol
 
 
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLD, "small_*.npz"))), ids=os.path.basename)
+def test_oracle_matches_reference_internal_bias(path):
+    z = np.load(path)
+    M, K, N, gs, rs = [int(v) for v in z["meta"]]
+    A, B, R, dC, ib = _t(z["A"]), _t(z["B"]), _t(z["R"]), _t(z["dC"]), _t(z["ib"])
+    tol = 1e-12 if A.dtype == torch.float64 else 2e-5
+    C = O.prism_forward(A, B, R, gs, rs, "silu_gate", internal_bias=ib)
+    dA, dR, dB, d_ib = O.prism_backward(dC, A, B, R, gs, rs, "silu_gate", internal_bias=ib)
+    for val, key in ((C, "C_ib"), (dA, "dA_ib"), (dR, "dR_ib"), (dB, "dB_ib"), (d_ib, "dib_ib")):
+        assert O.rel_err(val, _t(z[key])) < tol, key
+
+
 @pytest.mark.parametrize("seed", [0, 1])
 def test_oracle_matches_reference_config0(seed):
     z = np.load(os.path.join(GOLD, f"config0_seed{seed}.npz"))

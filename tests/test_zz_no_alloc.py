@@ -32,7 +32,7 @@ def _call_pair(L, M, K, N, gs, rs, dt, act, seed):
     need = L.prism_workspace_bytes(0, M, N, K, gs, rs, code, None)
     ws = torch.zeros(need, dtype=torch.uint8, device=DEV)
     C_ref = torch.empty(M, N, dtype=dt, device=DEV)
-    _lib.check(L.prism_fwd(_p(A), _p(B), _p(R), None, _p(C_ref), M, N, K, gs, rs, code, gate,
+    _lib.check(L.prism_fwd(_p(A), _p(B), _p(R), None, None, _p(C_ref), M, N, K, gs, rs, code, gate,
                            K, K, K, N, None, _p(ws), need, stream))
     # the variant that brings its own scratch
     C = torch.full((M, N), float("nan"), dtype=dt, device=DEV)
