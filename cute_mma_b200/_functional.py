@@ -172,6 +172,27 @@ def _check_internal_bias(internal_bias, A, N, K, group_size, gate):
     return internal_bias.contiguous()
 
 
+def _check_dropout(dropout_p, reconn_sz):
+    if not 0.0 <= dropout_p < 1.0:
+        raise ValueError(f"dropout_p must be in [0, 1), got {dropout_p}")
+    if reconn_sz not in (8, 16):
+        raise ValueError("dropout is supported for reconn_sz 8 and 16")
+
+
+def _check_seeds(seeds, A, n_groups):
+    """Per-group dropout seeds as the kernels take them: an int64 tensor (n_groups,) on A's device.  Accepts
+    what the reference's forward returns as well (a one-element list holding that tensor)."""
+    if isinstance(seeds, (list, tuple)):
+        if len(seeds) == 0:
+            return None
+        seeds = seeds[0] if isinstance(seeds[0], torch.Tensor) else torch.tensor(list(seeds), dtype=torch.int64)
+    if seeds.numel() == 0:
+        return None
+    if seeds.dtype != torch.int64 or seeds.shape != (n_groups,):
+        raise ValueError(f"dropout_seeds must be an int64 tensor of shape ({n_groups},)")
+    return seeds.to(A.device).contiguous()
+
+
 def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else None
 
@@ -185,12 +206,14 @@ def _reject_unsupported(**kw):
 def forward(A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=None, mode: str = "ar",
             comp_params=None, activation=None, autotuning: bool = False, autotuning_search_space=None,
             force_rebenchmark: bool = False, internal_bias=None, dropout_p: float = 0.0,
-            training: bool = False, shuffle_masks=None, *, bias=None, tile_cfg=None):
+            training: bool = False, shuffle_masks=None, *, bias=None, tile_cfg=None, dropout_seeds=None):
     """C = per-group (A . blockdiag(R_g)^T) @ B_g^T, or a gated form (``activation="silu_gate"``:
     ``(A * silu(A . blockdiag(R_g)^T)) @ B_g^T``; ``"sigmoid_gate"``: ``(A * 2 sigmoid(...)) @ B_g^T``);
     returns ``(C, [])``.
 
-    ``bias`` (keyword-only, [N], same dtype) is added in the kernel epilogue.
+    ``bias`` (keyword-only, [N], same dtype) is added in the kernel epilogue.  With ``training=True`` and
+    ``dropout_p > 0`` (gated modes) the gated activation goes through hash dropout and the second return
+    value is ``[seeds]`` (int64, one per group) for ``backward(dropout_seeds=..., dropout_p=...)``.
     """
     if mode not in ("ar", "rw"):
         raise ValueError(f"Unknown mode {mode!r}, must be 'ar' or 'rw'")
@@ -204,17 +227,25 @@ def forward(A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=None, mo
         validate_tensor_params(A, B, R, group_size, reconn_sz)
         C = torch.matmul(A, fold_weight(B, R, group_size, reconn_sz).t())
         return (C if bias is None else C + bias), []
-    _reject_unsupported(shuffle_masks=shuffle_masks, dropout_p=(dropout_p if training else 0.0))
+    _reject_unsupported(shuffle_masks=shuffle_masks)
     validate_tensor_params(A, B, R, group_size, reconn_sz)
     M, K = A.shape
     N = B.shape[0]
     internal_bias = _check_internal_bias(internal_bias, A, N, K, group_size, gate)
+    # hash dropout of the gated activation, training only (reference: src/cute_prism/__init__.py:242-261): one
+    # int64 seed per group, drawn here (or given as `dropout_seeds`) and returned for the backward
+    seeds = None
+    if gate and training and dropout_p > 0.0:
+        _check_dropout(dropout_p, reconn_sz)
+        seeds = dropout_seeds if dropout_seeds is not None else torch.randint(
+            1, 1 << 62, (N // group_size,), dtype=torch.int64, device=A.device)
+        seeds = _check_seeds(seeds, A, N // group_size)
     if bias is not None:
         if bias.dtype != A.dtype or bias.shape != (N,) or not bias.is_contiguous() or bias.device != A.device:
             raise ValueError("bias must be a contiguous (N,) tensor of the same dtype and device as A")
     C = torch.empty(M, N, dtype=A.dtype, device=A.device)
     if M == 0:
-        return C, []
+        return C, ([seeds] if seeds is not None else [])
     L = _lib.lib()
     cfg = tile_cfg if tile_cfg is not None else _tile_lookup("fwd", A.dtype, gate, M, N, K, group_size, reconn_sz)
     cfg_arr = _cfg_array(cfg)
@@ -222,12 +253,13 @@ def forward(A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=None, mo
     with torch.cuda.device(A.device):
         need = L.prism_workspace_bytes(KIND_FWD, M, N, K, group_size, reconn_sz, dt, cfg_arr)
         ws = _workspace.get(A.device, need)
-        _lib.check(L.prism_fwd(
+        _lib.check(L.prism_fwd_dropout(
             ctypes.c_void_p(A.data_ptr()), ctypes.c_void_p(B.data_ptr()), ctypes.c_void_p(R.data_ptr()),
             _ptr(bias), _ptr(internal_bias), ctypes.c_void_p(C.data_ptr()),
             M, N, K, group_size, reconn_sz, dt, gate, A.stride(0), B.stride(0), R.stride(0), C.stride(0),
+            _ptr(seeds), ctypes.c_float(dropout_p if seeds is not None else 0.0),
             cfg_arr, ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(A.device)))
-    return C, []
+    return C, ([seeds] if seeds is not None else [])
 
 
 def _grad_dtype(out_dtype, in_dtype, name):
@@ -285,7 +317,7 @@ def cayley_backward(M, dR, reconn_sz: int):
 
 
 def _backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=None, out_dtype=None,
-                 internal_bias=None):
+                 internal_bias=None, dropout_seeds=None, dropout_p=0.0):
     """dB = dc_scale * dC^T . H  through ``prism_bwd_db`` (H recomputed on chip); with
     ``out_dtype=torch.float32`` the kernel's fp32 sums are returned unrounded."""
     M, K = A.shape
@@ -303,12 +335,12 @@ def _backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=N
             ctypes.c_void_p(dC.data_ptr()), ctypes.c_void_p(A.data_ptr()), ctypes.c_void_p(R.data_ptr()),
             _ptr(internal_bias), ctypes.c_void_p(dB.data_ptr()), M, N, K, group_size, reconn_sz, dt, gate, out_code,
             ctypes.c_float(dc_scale), dC.stride(0), A.stride(0), R.stride(0), dB.stride(0),
-            cfg_arr, ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(A.device)))
+            _ptr(dropout_seeds), ctypes.c_float(dropout_p if dropout_seeds is not None else 0.0), cfg_arr, ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(A.device)))
     return dB
 
 
 def _backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=None, dR_dtype=None,
-                   internal_bias=None):
+                   internal_bias=None, dropout_seeds=None, dropout_p=0.0):
     """(dA, dR), both scaled by ``dc_scale``, through ``prism_bwd_dadr``; with
     ``dR_dtype=torch.float32`` the fp32 sums of the dR reduction are returned unrounded.  With an
     ``internal_bias`` the result is ``(dA, dR, d_internal_bias)``."""
@@ -332,7 +364,7 @@ def _backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_
             ctypes.c_void_p(dR.data_ptr()), _ptr(d_ib),
             M, N, K, group_size, reconn_sz, dt, gate, dr_code, ctypes.c_float(dc_scale),
             dC.stride(0), A.stride(0), B.stride(0), R.stride(0), dA.stride(0), dR.stride(0),
-            cfg_arr, ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(A.device)))
+            _ptr(dropout_seeds), ctypes.c_float(dropout_p if dropout_seeds is not None else 0.0), cfg_arr, ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream_ptr(A.device)))
     if internal_bias is not None:
         return dA, dR, d_ib
     return dA, dR
@@ -353,16 +385,21 @@ def backward(dC, A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=Non
     """
     gate = _gate_code(activation)
     validate_kernel_params(group_size, reconn_sz)
-    _reject_unsupported(shuffle_masks=shuffle_masks, dropout_seeds=dropout_seeds if dropout_p > 0.0 else None)
+    _reject_unsupported(shuffle_masks=shuffle_masks)
     validate_tensor_params(A, B, R, group_size, reconn_sz)
     M, K = A.shape
     N = B.shape[0]
     if dC.shape != (M, N) or dC.dtype != A.dtype or dC.device != A.device or not dC.is_contiguous():
         raise ValueError(f"dC must be a contiguous ({M}, {N}) tensor of the same dtype and device as A")
     internal_bias = _check_internal_bias(internal_bias, A, N, K, group_size, gate)
-    out = _backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, dc_scale, tile_cfg_dadr, dR_dtype, internal_bias)
-    dB = (_backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale, tile_cfg_db, dB_dtype, internal_bias)
-          if gate else None)
+    seeds = None
+    if gate and dropout_seeds is not None and dropout_p > 0.0:
+        _check_dropout(dropout_p, reconn_sz)
+        seeds = _check_seeds(dropout_seeds, A, N // group_size)
+    out = _backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, dc_scale, tile_cfg_dadr, dR_dtype, internal_bias,
+                         seeds, dropout_p)
+    dB = (_backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale, tile_cfg_db, dB_dtype, internal_bias,
+                       seeds, dropout_p) if gate else None)
     return out[0], out[1], dB, (out[2] if internal_bias is not None else None)
 
 

@@ -15,8 +15,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.environ.get("PRISM_B200_LIB", os.path.join(_HERE, "libprism_b200.so"))
 SOURCES = ["prism_abi.cu", "prism_fwd.cu", "prism_fwd_small.cu", "prism_bwd_db.cu", "prism_bwd_dadr.cu",
-           "prism_fwd_noalloc.cu", "prism_cayley.cu"]
-HEADERS = ["prism_common.cuh", "prism_host.cuh", "prism_kernels.cuh"]
+           "prism_bwd_dadr_f16.cu", "prism_bwd_dadr_bf16.cu", "prism_fwd_noalloc.cu", "prism_cayley.cu"]
+HEADERS = ["prism_common.cuh", "prism_host.cuh", "prism_kernels.cuh", "prism_bwd_dadr_kernel.cuh"]
 PUBLIC_HEADER = os.path.join(os.path.dirname(_HERE), "include", "prism_b200.h")
 
 NVCC_FLAGS = [
@@ -26,12 +26,12 @@ NVCC_FLAGS = [
 
 # every symbol include/prism_b200.h declares
 EXPORTS = [
-    "prism_fwd", "prism_fwd_noalloc", "prism_bwd_dadr", "prism_bwd_db", "prism_dbias", "prism_fold_weight", "prism_cayley", "prism_cayley_bwd", "prism_workspace_bytes",
+    "prism_fwd", "prism_fwd_dropout", "prism_fwd_noalloc", "prism_bwd_dadr", "prism_bwd_db", "prism_dbias", "prism_fold_weight", "prism_cayley", "prism_cayley_bwd", "prism_workspace_bytes",
     "prism_status",
     "prism_last_error_string", "prism_abi_version", "prism_launch_count",
 ]
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 _lock = threading.Lock()
 _lib = None
@@ -109,16 +109,19 @@ def lib() -> ctypes.CDLL:
             ip = ctypes.POINTER(ctypes.c_int)
             L.prism_fwd.restype = i
             L.prism_fwd.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, ll, ll, ll, ll, ip, vp, sz, vp]
+            L.prism_fwd_dropout.restype = i
+            L.prism_fwd_dropout.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, ll, ll, ll, ll, vp, ctypes.c_float,
+                                            ip, vp, sz, vp]
             L.prism_fwd_noalloc.restype = i
             L.prism_fwd_noalloc.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, i, ll, ll, ll, ll, ip, vp, vp]
             if hasattr(L, "prism_bwd_dadr"):
                 L.prism_bwd_dadr.restype = i
                 L.prism_bwd_dadr.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, i, ctypes.c_float,
-                                             ll, ll, ll, ll, ll, ll, ip, vp, sz, vp]
+                                             ll, ll, ll, ll, ll, ll, vp, ctypes.c_float, ip, vp, sz, vp]
             if hasattr(L, "prism_bwd_db"):
                 L.prism_bwd_db.restype = i
                 L.prism_bwd_db.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, i, i, i, ctypes.c_float,
-                                           ll, ll, ll, ll, ip, vp, sz, vp]
+                                           ll, ll, ll, ll, vp, ctypes.c_float, ip, vp, sz, vp]
             L.prism_dbias.restype = i
             L.prism_dbias.argtypes = [vp, vp, i, i, i, i, ll, vp, sz, vp]
             L.prism_fold_weight.restype = i

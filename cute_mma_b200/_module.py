@@ -18,8 +18,9 @@ Differences, all on the fast path:
   library's batched kernel (fp32 inside, its own backward); elsewhere it is solved by
   ``torch.linalg.solve`` in fp32 for fp16/bf16 parameters (which has no 16-bit kernels) and cast back;
 * the internal bias (``internal_bias=True``, gated modes) is added inside the kernels and its gradient
-  comes out of the dA+dR kernel; input shuffle and dropout are not part of the accelerated path and
-  raise ``ValueError`` at construction.
+  comes out of the dA+dR kernel; ``dropout`` (gated modes, training) is the reference kernels' hash
+  dropout, regenerated in the backward from per-group seeds; input shuffle is not part of the
+  accelerated path and raises ``ValueError`` at construction.
 """
 from __future__ import annotations
 
@@ -36,39 +37,49 @@ _GATED_SIGMOID_BWD_GAIN = 1.15
 _GATED = ("silu_gate", "sigmoid_gate")
 
 
+def gated_name(activation) -> bool:
+    return activation in _GATED
+
+
 # ---------------------------------------------------------------------------
 # custom ops: opaque to torch.compile, with fake-tensor and autograd support
 # ---------------------------------------------------------------------------
 @torch.library.custom_op("prism_b200::forward", mutates_args=())
 def _prism_forward_op(A: torch.Tensor, B: torch.Tensor, R: torch.Tensor, bias: torch.Tensor | None,
                       group_size: int, reconn_sz: int, activation: str, bwd_scale: float,
-                      internal_bias: torch.Tensor | None = None) -> torch.Tensor:
+                      internal_bias: torch.Tensor | None = None,
+                      dropout_seeds: torch.Tensor | None = None, dropout_p: float = 0.0) -> torch.Tensor:
     C, _ = F.forward(A.contiguous(), B.contiguous(), R.contiguous(), group_size, reconn_sz,
-                     activation=activation or None, bias=bias, internal_bias=internal_bias)
+                     activation=activation or None, bias=bias, internal_bias=internal_bias,
+                     dropout_p=dropout_p, training=dropout_seeds is not None, dropout_seeds=dropout_seeds)
     return C
 
 
 @_prism_forward_op.register_fake
-def _(A, B, R, bias, group_size, reconn_sz, activation, bwd_scale, internal_bias=None):
+def _(A, B, R, bias, group_size, reconn_sz, activation, bwd_scale, internal_bias=None, dropout_seeds=None,
+      dropout_p=0.0):
     return A.new_empty(A.shape[0], B.shape[0])
 
 
 @torch.library.custom_op("prism_b200::backward", mutates_args=())
 def _prism_backward_op(dC: torch.Tensor, A: torch.Tensor, B: torch.Tensor, R: torch.Tensor,
                        group_size: int, reconn_sz: int, activation: str, bwd_scale: float,
-                       need_dB: bool, need_dbias: bool, internal_bias: torch.Tensor | None = None
+                       need_dB: bool, need_dbias: bool, internal_bias: torch.Tensor | None = None,
+                       dropout_seeds: torch.Tensor | None = None, dropout_p: float = 0.0
                        ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     dC = dC.contiguous()
     A, B, R = A.contiguous(), B.contiguous(), R.contiguous()
     gate = F._gate_code(activation or None)
     ib = internal_bias.contiguous() if internal_bias is not None else None
-    out = F._backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, bwd_scale, internal_bias=ib)
+    out = F._backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, bwd_scale, internal_bias=ib,
+                           dropout_seeds=dropout_seeds, dropout_p=dropout_p)
     dA, dR = out[0], out[1]
     d_ib = out[2] if ib is not None else dC.new_empty(0)
     if not need_dB:
         dB = B.new_empty(0)
     elif gate:
-        dB = F._backward_db(dC, A, R, group_size, reconn_sz, gate, bwd_scale, internal_bias=ib)
+        dB = F._backward_db(dC, A, R, group_size, reconn_sz, gate, bwd_scale, internal_bias=ib,
+                            dropout_seeds=dropout_seeds, dropout_p=dropout_p)
     else:
         dB = torch.zeros_like(B)  # frozen-B contract of the reference's plain mode
     # the bias is added after the rescale point: its gradient is the plain column sum of dC
@@ -77,7 +88,8 @@ def _prism_backward_op(dC: torch.Tensor, A: torch.Tensor, B: torch.Tensor, R: to
 
 
 @_prism_backward_op.register_fake
-def _(dC, A, B, R, group_size, reconn_sz, activation, bwd_scale, need_dB, need_dbias, internal_bias=None):
+def _(dC, A, B, R, group_size, reconn_sz, activation, bwd_scale, need_dB, need_dbias, internal_bias=None,
+      dropout_seeds=None, dropout_p=0.0):
     return (A.new_empty(A.shape), R.new_empty(R.shape), (B.new_empty(B.shape) if need_dB else B.new_empty(0)),
             (dC.new_empty(dC.shape[1]) if need_dbias else dC.new_empty(0)),
             (internal_bias.new_empty(internal_bias.shape) if internal_bias is not None else dC.new_empty(0)))
@@ -117,9 +129,10 @@ _cayley_op.register_autograd(_cayley_backward, setup_context=_cayley_setup)
 
 
 def _setup_context(ctx, inputs, output):
-    A, B, R, bias, group_size, reconn_sz, activation, bwd_scale, internal_bias = inputs
+    A, B, R, bias, group_size, reconn_sz, activation, bwd_scale, internal_bias, dropout_seeds, dropout_p = inputs
     ctx.save_for_backward(A, B, R, *(() if internal_bias is None else (internal_bias,)))
     ctx.has_ib = internal_bias is not None
+    ctx.dropout_seeds, ctx.dropout_p = dropout_seeds, dropout_p
     ctx.has_bias = bias is not None
     ctx.group_size, ctx.reconn_sz = group_size, reconn_sz
     ctx.activation, ctx.bwd_scale = activation, bwd_scale
@@ -131,19 +144,22 @@ def _backward(ctx, dC):
     need_dB = bool(ctx.needs_input_grad[1])
     need_dbias = bool(ctx.has_bias and ctx.needs_input_grad[3])
     dA, dR, dB, dbias, d_ib = _prism_backward_op(dC, A, B, R, ctx.group_size, ctx.reconn_sz, ctx.activation,
-                                                 ctx.bwd_scale, need_dB, need_dbias, ib)
+                                                 ctx.bwd_scale, need_dB, need_dbias, ib, ctx.dropout_seeds,
+                                                 ctx.dropout_p)
     return (dA, (dB if need_dB else None), dR, (dbias if need_dbias else None), None, None, None, None,
-            (d_ib if ctx.has_ib else None))
+            (d_ib if ctx.has_ib else None), None, None)
 
 
 _prism_forward_op.register_autograd(_backward, setup_context=_setup_context)
 
 
 def prism_linear(A, B, R, bias=None, group_size=256, reconn_sz=8, activation=None, bwd_scale=1.0,
-                 internal_bias=None):
+                 internal_bias=None, dropout_seeds=None, dropout_p=0.0):
     """Differentiable functional form: C = prism(A, B, R) + bias; gradients of A/B/R (and of the
-    internal bias) are multiplied by ``bwd_scale`` (the output-bias gradient is not)."""
-    return _prism_forward_op(A, B, R, bias, group_size, reconn_sz, activation or "", float(bwd_scale), internal_bias)
+    internal bias) are multiplied by ``bwd_scale`` (the output-bias gradient is not).  ``dropout_seeds``
+    (int64, one per group) switches the hash dropout of the gated activation on."""
+    return _prism_forward_op(A, B, R, bias, group_size, reconn_sz, activation or "", float(bwd_scale), internal_bias,
+                             dropout_seeds, float(dropout_p))
 
 
 # ---------------------------------------------------------------------------
@@ -169,8 +185,11 @@ class PrismLinear(nn.Module):
         super().__init__()
         if activation not in (None,) + _GATED:
             raise ValueError(f"Unknown activation {activation!r}, must be one of (None, 'silu_gate', 'sigmoid_gate')")
-        if input_shuffle or dropout > 0.0:
-            raise ValueError("input_shuffle and dropout are not supported by the sm_100a kernels")
+        if input_shuffle:
+            raise ValueError("input_shuffle is not supported by the sm_100a kernels")
+        if dropout > 0.0 and gated_name(activation) and reconn_sz not in (8, 16):
+            raise ValueError("dropout is supported for reconn_sz 8 and 16")
+        self.dropout = float(dropout)
         if out_features % group_size != 0:
             raise ValueError(f"out_features ({out_features}) must be divisible by group_size ({group_size})")
         if in_features % reconn_sz != 0:
@@ -284,8 +303,14 @@ class PrismLinear(nn.Module):
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:
         A = input.reshape(-1, self.in_features)
+        seeds = None
+        if self.training and self.dropout > 0.0 and self.activation in _GATED:
+            # one seed per group and call; forward and backward regenerate the mask from them
+            seeds = torch.randint(1, 1 << 62, (self.out_features // self.group_size,), dtype=torch.int64,
+                                  device=A.device)
         C = _prism_forward_op(A, self.weight, self._build_R(), self.bias, self.group_size, self.reconn_sz,
-                              self.activation or "", float(self._bwd_scale), self._internal_bias)
+                              self.activation or "", float(self._bwd_scale), self._internal_bias, seeds,
+                              self.dropout)
         return C.reshape(input.shape[:-1] + (self.out_features,))
 
     def extra_repr(self) -> str:

@@ -201,6 +201,15 @@ static int check_ib(const char* fn, const void* ib, int gate) {
   return PRISM_OK;
 }
 
+// dropout: per-group seeds [N/gs] (int64) with a probability in (0, 1), gated modes only; null seeds = none
+static int check_dropout(const char* fn, const void* seeds, float p, int gate) {
+  if (seeds == nullptr) return PRISM_OK;
+  if (gate == GATE_NONE) return fail(PRISM_ERR_BAD_ARG, "%s: dropout requires a gated mode", fn);
+  if (!(p >= 0.f && p < 1.f)) return fail(PRISM_ERR_BAD_ARG, "%s: dropout_p must be in [0, 1), got %g", fn, (double)p);
+  if (reinterpret_cast<uintptr_t>(seeds) % 8 != 0) return fail(PRISM_ERR_BAD_ARG, "%s: dropout_seeds must be 8-byte aligned", fn);
+  return PRISM_OK;
+}
+
 static int check_ptr(const char* fn, const char* name, const void* p, long long ld, int min_ld) {
   if (p == nullptr) return fail(PRISM_ERR_BAD_ARG, "%s: %s is null", fn, name);
   if (reinterpret_cast<uintptr_t>(p) % 16 != 0) return fail(PRISM_ERR_BAD_ARG, "%s: %s must be 16-byte aligned", fn, name);
@@ -213,7 +222,7 @@ static int check_ptr(const char* fn, const char* name, const void* p, long long 
 
 using namespace prism;
 
-extern "C" int prism_abi_version(void) { return 3; }
+extern "C" int prism_abi_version(void) { return 4; }
 
 extern "C" long long prism_launch_count(void) { return launch_counter().load(std::memory_order_relaxed); }
 
@@ -279,10 +288,25 @@ extern "C" int prism_status(void* workspace, void* stream) {
   return PRISM_OK;
 }
 
+extern "C" int prism_fwd_dropout(const void* A, const void* B, const void* R, const void* bias, const void* internal_bias,
+                                 void* C, int M, int N, int K, int gs, int rs, int dtype, int gate,
+                                 long long lda, long long ldb, long long ldr, long long ldc,
+                                 const long long* dropout_seeds, float dropout_p,
+                                 const int* cfg, void* workspace, size_t workspace_bytes, void* stream);
+
 extern "C" int prism_fwd(const void* A, const void* B, const void* R, const void* bias, const void* internal_bias, void* C,
                          int M, int N, int K, int gs, int rs, int dtype, int gate,
                          long long lda, long long ldb, long long ldr, long long ldc,
                          const int* cfg, void* workspace, size_t workspace_bytes, void* stream) {
+  return prism_fwd_dropout(A, B, R, bias, internal_bias, C, M, N, K, gs, rs, dtype, gate, lda, ldb, ldr, ldc, nullptr, 0.f, cfg,
+                           workspace, workspace_bytes, stream);
+}
+
+extern "C" int prism_fwd_dropout(const void* A, const void* B, const void* R, const void* bias, const void* internal_bias,
+                                 void* C, int M, int N, int K, int gs, int rs, int dtype, int gate,
+                                 long long lda, long long ldb, long long ldr, long long ldc,
+                                 const long long* dropout_seeds, float dropout_p,
+                                 const int* cfg, void* workspace, size_t workspace_bytes, void* stream) {
   const char* fn = "prism_fwd";
   int rc;
   if ((rc = check_common(fn, M, N, K, gs, rs, dtype, gate))) return rc;
@@ -295,6 +319,7 @@ extern "C" int prism_fwd(const void* A, const void* B, const void* R, const void
   if (bias != nullptr && reinterpret_cast<uintptr_t>(bias) % 4 != 0)
     return fail(PRISM_ERR_BAD_ARG, "%s: bias must be 4-byte aligned", fn);
   if ((rc = check_ib(fn, internal_bias, gate))) return rc;
+  if ((rc = check_dropout(fn, dropout_seeds, dropout_p, gate))) return rc;
   const size_t need = prism_workspace_bytes(PRISM_KIND_FWD, M, N, K, gs, rs, dtype, cfg);
   if (workspace == nullptr || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
     return fail(PRISM_ERR_WORKSPACE, "%s: workspace must be 256-byte aligned and >= %zu bytes (got %zu)", fn, need, workspace_bytes);
@@ -302,6 +327,7 @@ extern "C" int prism_fwd(const void* A, const void* B, const void* R, const void
 
   FwdArgs a;
   a.A = A; a.B = B; a.bias = bias; a.ib = internal_bias; a.C = C;
+  a.drop_seeds = dropout_seeds; a.drop_p = dropout_p;
   a.M = M; a.N = N; a.K = K; a.gs = gs; a.E = effective_block(rs);
   a.dtype = dtype; a.gate = gate;
   a.lda = lda; a.ldb = ldb; a.ldc = ldc;
@@ -333,6 +359,7 @@ extern "C" int prism_fwd(const void* A, const void* B, const void* R, const void
 extern "C" int prism_bwd_db(const void* dC, const void* A, const void* R, const void* internal_bias, void* dB,
                             int M, int N, int K, int gs, int rs, int dtype, int gate, int db_dtype, float dc_scale,
                             long long lddc, long long lda, long long ldr, long long lddb,
+                            const long long* dropout_seeds, float dropout_p,
                             const int* cfg, void* workspace, size_t workspace_bytes, void* stream) {
   const char* fn = "prism_bwd_db";
   int rc;
@@ -342,6 +369,7 @@ extern "C" int prism_bwd_db(const void* dC, const void* A, const void* R, const 
   if (K % 8 != 0) return fail(PRISM_ERR_BAD_ARG, "%s: K must be a multiple of 8", fn);
   if ((rc = check_ptr(fn, "dB", dB, lddb, K))) return rc;
   if ((rc = check_ib(fn, internal_bias, gate))) return rc;
+  if ((rc = check_dropout(fn, dropout_seeds, dropout_p, gate))) return rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (M == 0) {  // no tokens: the gradient is zero
     const size_t es = db_f32 ? 4 : 2;
@@ -356,7 +384,7 @@ extern "C" int prism_bwd_db(const void* dC, const void* A, const void* R, const 
     return fail(PRISM_ERR_WORKSPACE, "%s: workspace must be 256-byte aligned and >= %zu bytes (got %zu)", fn, need, workspace_bytes);
 
   DbArgs a;
-  a.dC = dC; a.A = A; a.dB = dB; a.ib = internal_bias;
+  a.dC = dC; a.A = A; a.dB = dB; a.ib = internal_bias; a.drop_seeds = dropout_seeds; a.drop_p = dropout_p;
   a.M = M; a.N = N; a.K = K; a.gs = gs; a.E = effective_block(rs);
   a.dtype = dtype; a.gate = gate; a.scale = dc_scale; a.out_f32 = db_f32;
   a.lddc = lddc; a.lda = lda; a.lddb = lddb;
@@ -381,7 +409,8 @@ extern "C" int prism_bwd_db(const void* dC, const void* A, const void* R, const 
 extern "C" int prism_bwd_dadr(const void* dC, const void* A, const void* B, const void* R, const void* internal_bias,
                               void* dA, void* dR, void* d_internal_bias, int M, int N, int K, int gs, int rs, int dtype, int gate,
                               int dr_dtype, float dc_scale, long long lddc, long long lda, long long ldb,
-                              long long ldr, long long ldda, long long lddr, const int* cfg,
+                              long long ldr, long long ldda, long long lddr,
+                              const long long* dropout_seeds, float dropout_p, const int* cfg,
                               void* workspace, size_t workspace_bytes, void* stream) {
   const char* fn = "prism_bwd_dadr";
   int rc;
@@ -391,6 +420,7 @@ extern "C" int prism_bwd_dadr(const void* dC, const void* A, const void* B, cons
   if (K % 8 != 0) return fail(PRISM_ERR_BAD_ARG, "%s: K must be a multiple of 8", fn);
   if ((rc = check_ptr(fn, "dR", dR, lddr, K))) return rc;
   if ((rc = check_ib(fn, internal_bias, gate))) return rc;
+  if ((rc = check_dropout(fn, dropout_seeds, dropout_p, gate))) return rc;
   const bool with_ib = internal_bias != nullptr;
   if (with_ib && d_internal_bias == nullptr) return fail(PRISM_ERR_BAD_ARG, "%s: d_internal_bias is null", fn);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
@@ -411,6 +441,7 @@ extern "C" int prism_bwd_dadr(const void* dC, const void* A, const void* B, cons
 
   DadrArgs a;
   a.dC = dC; a.A = A; a.B = B; a.dA = dA; a.dR = dR; a.ib = internal_bias; a.d_ib = d_internal_bias;
+  a.drop_seeds = dropout_seeds; a.drop_p = dropout_p;
   a.M = M; a.N = N; a.K = K; a.gs = gs; a.rs = rs; a.E = effective_block(rs);
   a.dtype = dtype; a.gate = gate; a.scale = dc_scale; a.dr_f32 = dr_f32;
   a.lddc = lddc; a.lda = lda; a.ldb = ldb; a.ldda = ldda; a.lddr = lddr;

@@ -1,0 +1,6 @@
+// fp16 instances of the dA+dR kernel (a translation unit of their own: they compile side by side with the bf16 ones)
+#include "prism_bwd_dadr_kernel.cuh"
+
+namespace prism {
+PRISM_DADR_DEFINE_PICKER(dadr_kernel_f16, DT_F16)
+}  // namespace prism

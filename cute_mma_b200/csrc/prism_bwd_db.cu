@@ -51,6 +51,8 @@ struct DbParams {
   int out_f32;        // 1: dB is fp32
   float scale;
   const void* ib;     // internal bias [G, K] or null
+  const long long* drop_seeds;   // per-group dropout seeds (DROP kernels)
+  float drop_p, drop_inv_keep;
   void* dB;
   long long lddb;
   float* partial;     // [splits][part_rows][K] when splits > 1
@@ -70,7 +72,7 @@ struct DbBarriers {
   uint32_t tmem_base;
 };
 
-template <int DT, int GATE, int E>
+template <int DT, int GATE, int E, bool DROP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(db::kThreads, 1)
 prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmR,
                     const __grid_constant__ CUtensorMap tmdC, const DbParams p) {
@@ -227,13 +229,22 @@ prism_bwd_db_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int kvalid = p.K - kcol;
     const uint16_t* ib = (p.ib != nullptr && kvalid > 0)
                              ? reinterpret_cast<const uint16_t*>(p.ib) + (long long)g * p.K + kcol : nullptr;
+    const uint64_t drop_h1 = DROP ? drop_group_hash(p.drop_seeds, g) : 0ull;
     bool ok = true;
     Ring rs(p.ns);
     for (int j = 0; j < nb && ok; ++j, rs.next()) {
       if (!mbar_wait(&bars->s_full, j & 1)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t tile = smem_u32(smemSt + rs.idx * p.stage_bytes + ft * kTile);
-      gate_rows16_tmem_smem<DT, GATE, E>(s_tmem, 2 * E, tile, r0, lane, s_free_addr, ib, kvalid);
+      DropCtx dc;
+      if (DROP) {
+        dc.h1 = drop_h1;
+        dc.base = (long long)((tb0 + j) * 128 + (int)r0 + (lane >> 2)) * p.K + kcol + 2 * (lane & 3);
+        dc.row8 = 8ll * p.K;
+        dc.p = p.drop_p;
+        dc.inv_keep = p.drop_inv_keep;
+      }
+      gate_rows16_tmem_smem<DT, GATE, E, DROP>(s_tmem, 2 * E, tile, r0, lane, s_free_addr, ib, kvalid, &dc);
       fence_proxy_async_smem();   // H was written by the generic proxy, the MMA reads it through the async proxy
       tc_fence_before_sync();
       __syncwarp();
@@ -347,6 +358,9 @@ int launch_bwd_db(const DbArgs& a) {
   p.dc_tiles = (a.BN / 2 + 63) / 64;   // per CTA: half of the tile's dC columns
   p.r_tile_bytes = ((a.E * 128) + 1023) / 1024 * 1024;
   p.scale = a.scale; p.out_f32 = a.out_f32; p.ib = a.ib;
+  const bool drop = a.drop_seeds != nullptr && a.drop_p > 0.f && a.gate != GATE_NONE;
+  p.drop_seeds = a.drop_seeds; p.drop_p = a.drop_p; p.drop_inv_keep = drop ? 1.f / (1.f - a.drop_p) : 1.f;
+  if (drop && a.E != 16) return fail(PRISM_ERR_UNSUPPORTED, "bwd_db: dropout needs reconn_sz 8 or 16");
   p.dB = a.dB; p.lddb = a.lddb; p.partial = a.partial; p.err = a.err;
   if ((a.plan.splits > 1 || a.plan.tail_rows > 0) && a.partial == nullptr)
     return fail(PRISM_ERR_WORKSPACE, "bwd_db: split accumulation needs a partial-sum workspace");
@@ -368,11 +382,12 @@ int launch_bwd_db(const DbArgs& a) {
 
   using KernT = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, DbParams);
   KernT kern = nullptr;
-#define PRISM_PICK_G(DT_, E_)                                                                    \
-  (a.gate == GATE_SILU ? (KernT)prism_bwd_db_kernel<DT_, GATE_SILU, E_>                                       \
-                       : a.gate == GATE_SIGMOID ? (KernT)prism_bwd_db_kernel<DT_, GATE_SIGMOID, E_> : (KernT)prism_bwd_db_kernel<DT_, GATE_NONE, E_>)
-#define PRISM_PICK(E_) kern = (a.dtype == DT_BF16) ? PRISM_PICK_G(DT_BF16, E_) : PRISM_PICK_G(DT_F16, E_)
-  if (a.E == 16) { PRISM_PICK(16); } else if (a.E == 32) { PRISM_PICK(32); } else { PRISM_PICK(64); }
+#define PRISM_PICK_G(DT_, E_, DROP_)                                                                    \
+  (a.gate == GATE_SILU ? (KernT)prism_bwd_db_kernel<DT_, GATE_SILU, E_, DROP_>                           \
+                       : a.gate == GATE_SIGMOID ? (KernT)prism_bwd_db_kernel<DT_, GATE_SIGMOID, E_, DROP_> : (KernT)prism_bwd_db_kernel<DT_, GATE_NONE, E_, false>)
+#define PRISM_PICK(E_) kern = (a.dtype == DT_BF16) ? PRISM_PICK_G(DT_BF16, E_, false) : PRISM_PICK_G(DT_F16, E_, false)
+  if (drop) { kern = (a.dtype == DT_BF16) ? PRISM_PICK_G(DT_BF16, 16, true) : PRISM_PICK_G(DT_F16, 16, true); }
+  else if (a.E == 16) { PRISM_PICK(16); } else if (a.E == 32) { PRISM_PICK(32); } else { PRISM_PICK(64); }
 #undef PRISM_PICK_G
 #undef PRISM_PICK
   if ((rc = set_max_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes, "bwd_db"))) return rc;

@@ -32,6 +32,30 @@ template <> struct CIo<CT_BF16> {
   __device__ static void st(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 };
 
+// 8 x 8 blocks are handled entirely in registers (every loop unrolled); for 16 x 16 the outermost loop of
+// each step stays a loop (arrays in local memory): the unrolled form takes minutes to compile and these
+// launches last microseconds either way.
+#define PRISM_CAYLEY_OUTER(RS_, VAR_, ...)                                          \
+  if constexpr ((RS_) <= 8) {                                                       \
+    _Pragma("unroll") for (int VAR_ = 0; VAR_ < (RS_); ++VAR_) { __VA_ARGS__ }      \
+  } else {                                                                          \
+    _Pragma("unroll 1") for (int VAR_ = 0; VAR_ < (RS_); ++VAR_) { __VA_ARGS__ }    \
+  }
+
+template <int RS>
+__device__ __forceinline__ void cayley_eliminate(float (&a)[RS][RS], float (&P)[RS][RS], int c) {
+  const float inv = 1.f / a[c][c];
+#pragma unroll
+  for (int j = 0; j < RS; ++j) { a[c][j] *= inv; P[c][j] *= inv; }
+#pragma unroll
+  for (int r = 0; r < RS; ++r) {
+    if (r == c) continue;
+    const float f = a[r][c];
+#pragma unroll
+    for (int j = 0; j < RS; ++j) { a[r][j] -= f * a[c][j]; P[r][j] -= f * P[c][j]; }
+  }
+}
+
 // P = (I - S)^-1 for S = M - M^T, by Gauss-Jordan on [I - S | I]
 template <int RS>
 __device__ __forceinline__ void cayley_inverse(const float (&S)[RS][RS], float (&P)[RS][RS]) {
@@ -43,18 +67,19 @@ __device__ __forceinline__ void cayley_inverse(const float (&S)[RS][RS], float (
       a[i][j] = (i == j ? 1.f : 0.f) - S[i][j];
       P[i][j] = (i == j ? 1.f : 0.f);
     }
+  PRISM_CAYLEY_OUTER(RS, c, cayley_eliminate<RS>(a, P, c);)
+}
+
+// out[i][:] = sum_k X[i][k] * Y[k][:] (TRANS_X: X[k][i]; TRANS_Y: Y[:][k]) + (ADD_X ? X[i][:] : 0) + (ADD_I ? e_i : 0)
+template <int RS, bool TRANS_X, bool TRANS_Y, bool ADD_X, bool ADD_I>
+__device__ __forceinline__ void cayley_matmul_row(const float (&X)[RS][RS], const float (&Y)[RS][RS], float (&out)[RS][RS],
+                                                  int i) {
 #pragma unroll
-  for (int c = 0; c < RS; ++c) {
-    const float inv = 1.f / a[c][c];
+  for (int j = 0; j < RS; ++j) {
+    float acc = (ADD_X ? X[i][j] : 0.f) + ((ADD_I && i == j) ? 1.f : 0.f);
 #pragma unroll
-    for (int j = 0; j < RS; ++j) { a[c][j] *= inv; P[c][j] *= inv; }
-#pragma unroll
-    for (int r = 0; r < RS; ++r) {
-      if (r == c) continue;
-      const float f = a[r][c];
-#pragma unroll
-      for (int j = 0; j < RS; ++j) { a[r][j] -= f * a[c][j]; P[r][j] -= f * P[c][j]; }
-    }
+    for (int k = 0; k < RS; ++k) acc = fmaf(TRANS_X ? X[k][i] : X[i][k], TRANS_Y ? Y[j][k] : Y[k][j], acc);
+    out[i][j] = acc;
   }
 }
 
@@ -76,15 +101,11 @@ __global__ void cayley_fwd_kernel(const typename CIo<CT>::T* __restrict__ M, typ
     for (int j = 0; j < RS; ++j) S[i][j] = Mv[i][j] - Mv[j][i];
   cayley_inverse<RS>(S, P);
   typename CIo<CT>::T* r = R + (long long)g * RS * ldr + (long long)b * RS;
+  PRISM_CAYLEY_OUTER(RS, i, cayley_matmul_row<RS, false, false, true, false>(P, S, Mv, i);)   // P (I + S) = P + P S
 #pragma unroll
   for (int i = 0; i < RS; ++i)
 #pragma unroll
-    for (int j = 0; j < RS; ++j) {
-      float acc = P[i][j];                                   // P (I + S) = P + P S
-#pragma unroll
-      for (int k = 0; k < RS; ++k) acc = fmaf(P[i][k], S[k][j], acc);
-      CIo<CT>::st(r + i * ldr + j, acc);
-    }
+    for (int j = 0; j < RS; ++j) CIo<CT>::st(r + i * ldr + j, Mv[i][j]);
 }
 
 template <int CT, int RS>
@@ -107,38 +128,14 @@ __global__ void cayley_bwd_kernel(const typename CIo<CT>::T* __restrict__ M, con
     for (int j = 0; j < RS; ++j) S[i][j] = X[i][j] - X[j][i];
   cayley_inverse<RS>(S, P);
   // Y = R + I = P (I + S) + I
+  PRISM_CAYLEY_OUTER(RS, i, cayley_matmul_row<RS, false, false, true, true>(P, S, Y, i);)
+  // S <- G (the incoming gradient), X = G Y^T, then T = P^T X (kept in S)
 #pragma unroll
   for (int i = 0; i < RS; ++i)
 #pragma unroll
-    for (int j = 0; j < RS; ++j) {
-      float acc = P[i][j] + (i == j ? 1.f : 0.f);
-#pragma unroll
-      for (int k = 0; k < RS; ++k) acc = fmaf(P[i][k], S[k][j], acc);
-      Y[i][j] = acc;
-    }
-  // X = G Y^T, then T = P^T X
-#pragma unroll
-  for (int i = 0; i < RS; ++i) {
-    float grow[RS];
-#pragma unroll
-    for (int k = 0; k < RS; ++k) grow[k] = CIo<CT>::ld(gr + i * lddr + k);
-#pragma unroll
-    for (int j = 0; j < RS; ++j) {
-      float acc = 0.f;
-#pragma unroll
-      for (int k = 0; k < RS; ++k) acc = fmaf(grow[k], Y[j][k], acc);
-      X[i][j] = acc;
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < RS; ++i)
-#pragma unroll
-    for (int j = 0; j < RS; ++j) {
-      float acc = 0.f;
-#pragma unroll
-      for (int k = 0; k < RS; ++k) acc = fmaf(P[k][i], X[k][j], acc);
-      S[i][j] = acc;   // S now holds T = dL/dS
-    }
+    for (int j = 0; j < RS; ++j) S[i][j] = CIo<CT>::ld(gr + i * lddr + j);
+  PRISM_CAYLEY_OUTER(RS, i, cayley_matmul_row<RS, false, true, false, false>(S, Y, X, i);)
+  PRISM_CAYLEY_OUTER(RS, i, cayley_matmul_row<RS, true, false, false, false>(P, X, S, i);)
   typename CIo<CT>::T* o = dM + (long long)g * RS * lddm + (long long)b * RS;
 #pragma unroll
   for (int i = 0; i < RS; ++i)

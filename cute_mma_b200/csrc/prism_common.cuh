@@ -648,22 +648,59 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t (&a)[
 }
 
 
+// ----------------------------------------------------------------------------
+// Hash dropout of the gated modes (training): element (m, k) of group g is kept iff
+//   u = top24(splitmix64(splitmix64(seed_g + 0xdeadbeef) ^ splitmix64(m*K + k))) / 2^24  >=  p
+// and kept elements are scaled by 1 / (1 - p): the same counter-based mask as the reference's kernels
+// (cute_prism_dtype.hpp:28-40, applied to H in the forward and dB kernels, cute_prism_coop_pc.cu:250-301,
+// and to dH in the dA+dR kernel), so that forward and backward regenerate it from the per-group seeds.
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
+  x += 0x9e3779b97f4a7c15ull;
+  x = (x ^ (x >> 30)) * 0xbf58476d1ce4e5b9ull;
+  x = (x ^ (x >> 27)) * 0x94d049bb133111ebull;
+  return x ^ (x >> 31);
+}
+struct DropCtx {
+  uint64_t h1;       // splitmix64(seed_g + 0xdeadbeef)
+  long long base;    // m*K + k of this thread's first element: row r0 + lane/4 of the warp, column 2 (lane%4) of the chunk
+  long long row8;    // 8 * K: the thread's second row
+  float p, inv_keep;
+  // multiplier of the element `rsel` rows of 8 down and `col` columns to the right
+  __device__ __forceinline__ float mul(int rsel, int col) const {
+    const uint64_t h = splitmix64(h1 ^ splitmix64((uint64_t)(base + rsel * row8 + col)));
+    const float u = (float)((h >> 40) & 0xFFFFFFull) * (1.0f / 16777216.0f);
+    return u >= p ? inv_keep : 0.f;
+  }
+};
+__device__ __forceinline__ uint64_t drop_group_hash(const long long* seeds, int g) {
+  return splitmix64((uint64_t)__ldg(seeds + g) + 0xdeadbeefull);
+}
+
 // H for one pair of elements from fp32 S and packed 16-bit A: A*silu(S), A*2*sigmoid(S), or S in
 // plain mode.  With hs = s/2 and t = tanh(hs): silu(s) = hs + hs t and 2 sigmoid(s) = 1 + t: one
 // special-function operation per element, no division.
-template <int DT, int GATE, bool HW = false>
-__device__ __forceinline__ uint32_t gate_pair(uint32_t a2, float s0, float s1) {
+// DROP: the pair is multiplied by (m0, m1), the dropout multipliers (0 or 1 / (1 - p)).
+template <int DT, int GATE, bool HW = false, bool DROP = false>
+__device__ __forceinline__ uint32_t gate_pair(uint32_t a2, float s0, float s1, float m0 = 1.f, float m1 = 1.f) {
   if (GATE == GATE_NONE) return Pk<DT>::cvt(s0, s1);
   if (gate_in_f32<DT>()) {
     const float2 hs = mul2(make_float2(s0, s1), make_float2(0.5f, 0.5f));
     const float2 t = make_float2(tanh_approx(hs.x), tanh_approx(hs.y));
     const float2 a = Elem<DT>::unpack(a2);
-    const float2 h = (GATE == GATE_SILU) ? mul2(a, fma2(hs, t, hs)) : fma2(a, t, a);
+    float2 h = (GATE == GATE_SILU) ? mul2(a, fma2(hs, t, hs)) : fma2(a, t, a);
+    if (DROP) h = mul2(h, make_float2(m0, m1));
     return Pk<DT>::cvt_hw(h.x, h.y);
   }
-  if (GATE == GATE_SILU) return Pk<DT>::mul(a2, silu_pair<DT, HW>(s0, s1));
-  const uint32_t hs = Pk<DT>::mul(HW ? Pk<DT>::cvt_hw(s0, s1) : Pk<DT>::cvt(s0, s1), Pk<DT>::kHalf);
-  return Pk<DT>::fma(a2, Pk<DT>::tanh(hs), a2);
+  uint32_t h;
+  if (GATE == GATE_SILU) {
+    h = Pk<DT>::mul(a2, silu_pair<DT, HW>(s0, s1));
+  } else {
+    const uint32_t hs = Pk<DT>::mul(HW ? Pk<DT>::cvt_hw(s0, s1) : Pk<DT>::cvt(s0, s1), Pk<DT>::kHalf);
+    h = Pk<DT>::fma(a2, Pk<DT>::tanh(hs), a2);
+  }
+  if (DROP) h = Pk<DT>::mul(h, Pk<DT>::cvt_hw(m0, m1));
+  return h;
 }
 
 // TMEM -> registers in the mma.sync accumulator layout: 16 lanes x 16 columns; thread t gets
@@ -709,9 +746,11 @@ __device__ __forceinline__ void add_internal_bias(uint32_t (&s)[4][8], const uin
 // and is starved while a burst of tcgen05.mma runs (measured: 13x slower), which would serialise
 // the gate warps with the dense product.
 // ib / kvalid: internal bias of the chunk (see add_internal_bias), or null.
-template <int DT, int GATE>
+// DROP / drop: hash dropout of H (see DropCtx).
+template <int DT, int GATE, bool DROP = false>
 __device__ __forceinline__ void gate_rows16_tmem(uint32_t s_tmem, uint32_t tile, uint32_t r0, int lane,
-                                                 uint32_t h_tmem, const uint16_t* ib = nullptr, int kvalid = 64) {
+                                                 uint32_t h_tmem, const uint16_t* ib = nullptr, int kvalid = 64,
+                                                 const DropCtx* drop = nullptr) {
   const uint32_t mat = lane >> 3, l8 = lane & 7;
   const uint32_t a_row = r0 + l8 + (mat & 1) * 8;
   uint32_t s[4][8], af[4][4], h[4][4];
@@ -728,10 +767,17 @@ __device__ __forceinline__ void gate_rows16_tmem(uint32_t s_tmem, uint32_t tile,
   if (GATE != GATE_NONE && ib != nullptr) add_internal_bias<DT>(s, ib, kvalid, lane, 1.0f);
 #pragma unroll
   for (int pc = 0; pc < 4; ++pc) {
-    h[pc][0] = gate_pair<DT, GATE, (PRISM_FWD_CVT_HW != 0) && GATE != GATE_NONE>(af[pc][0], __uint_as_float(s[pc][0]), __uint_as_float(s[pc][1]));
-    h[pc][1] = gate_pair<DT, GATE, (PRISM_FWD_CVT_HW != 0) && GATE != GATE_NONE>(af[pc][1], __uint_as_float(s[pc][2]), __uint_as_float(s[pc][3]));
-    h[pc][2] = gate_pair<DT, GATE, (PRISM_FWD_CVT_HW != 0) && GATE != GATE_NONE>(af[pc][2], __uint_as_float(s[pc][4]), __uint_as_float(s[pc][5]));
-    h[pc][3] = gate_pair<DT, GATE, (PRISM_FWD_CVT_HW != 0) && GATE != GATE_NONE>(af[pc][3], __uint_as_float(s[pc][6]), __uint_as_float(s[pc][7]));
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      // pair e: row r (e even) or r + 8 (e odd), columns pc*16 + 2(lane%4) + {0,1}, eight further on for e >= 2
+      float m0 = 1.f, m1 = 1.f;
+      if (DROP && GATE != GATE_NONE) {
+        m0 = drop->mul(e & 1, pc * 16 + (e >> 1) * 8);
+        m1 = drop->mul(e & 1, pc * 16 + (e >> 1) * 8 + 1);
+      }
+      h[pc][e] = gate_pair<DT, GATE, (PRISM_FWD_CVT_HW != 0) && GATE != GATE_NONE, DROP>(
+          af[pc][e], __uint_as_float(s[pc][2 * e]), __uint_as_float(s[pc][2 * e + 1]), m0, m1);
+    }
   }
 #pragma unroll
   for (int pc = 0; pc < 4; ++pc) tmem_st_frag16x16(h_tmem + pc * 8, h[pc]);
@@ -744,10 +790,10 @@ __device__ __forceinline__ void gate_rows16_tmem(uint32_t s_tmem, uint32_t tile,
 // starts at b * blk_stride + np * 16.
 // s_free (a shared::cluster barrier address, or 0) is arrived on as soon as this warp holds its S
 // values in registers: a single S buffer can then be refilled while the gate math still runs.
-template <int DT, int GATE, int E>
+template <int DT, int GATE, int E, bool DROP = false>
 __device__ __forceinline__ void gate_rows16_tmem_smem(uint32_t s_tmem, uint32_t blk_stride, uint32_t tile, uint32_t r0,
                                                       int lane, uint32_t s_free, const uint16_t* ib = nullptr,
-                                                      int kvalid = 64) {
+                                                      int kvalid = 64, const DropCtx* drop = nullptr) {
   constexpr int KS = E / 16;
   const uint32_t mat = lane >> 3, l8 = lane & 7;
   const uint32_t a_row = r0 + l8 + (mat & 1) * 8;
@@ -770,10 +816,16 @@ __device__ __forceinline__ void gate_rows16_tmem_smem(uint32_t s_tmem, uint32_t 
   if (GATE != GATE_NONE && ib != nullptr) add_internal_bias<DT>(s, ib, kvalid, lane, 1.0f);
 #pragma unroll
   for (int pc = 0; pc < 4; ++pc) {
-    h[pc][0] = gate_pair<DT, GATE, (PRISM_DB_CVT_HW != 0) && GATE != GATE_NONE>(af[pc][0], __uint_as_float(s[pc][0]), __uint_as_float(s[pc][1]));
-    h[pc][1] = gate_pair<DT, GATE, (PRISM_DB_CVT_HW != 0) && GATE != GATE_NONE>(af[pc][1], __uint_as_float(s[pc][2]), __uint_as_float(s[pc][3]));
-    h[pc][2] = gate_pair<DT, GATE, (PRISM_DB_CVT_HW != 0) && GATE != GATE_NONE>(af[pc][2], __uint_as_float(s[pc][4]), __uint_as_float(s[pc][5]));
-    h[pc][3] = gate_pair<DT, GATE, (PRISM_DB_CVT_HW != 0) && GATE != GATE_NONE>(af[pc][3], __uint_as_float(s[pc][6]), __uint_as_float(s[pc][7]));
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float m0 = 1.f, m1 = 1.f;
+      if (DROP && GATE != GATE_NONE) {
+        m0 = drop->mul(e & 1, pc * 16 + (e >> 1) * 8);
+        m1 = drop->mul(e & 1, pc * 16 + (e >> 1) * 8 + 1);
+      }
+      h[pc][e] = gate_pair<DT, GATE, (PRISM_DB_CVT_HW != 0) && GATE != GATE_NONE, DROP>(
+          af[pc][e], __uint_as_float(s[pc][2 * e]), __uint_as_float(s[pc][2 * e + 1]), m0, m1);
+    }
   }
 #pragma unroll
   for (int pc = 0; pc < 4; ++pc) stmatrix_x4(tile + sw128_offset(a_row, pc * 2 + (mat >> 1)), h[pc]);

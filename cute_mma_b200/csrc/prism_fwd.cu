@@ -59,6 +59,8 @@ struct FwdParams {
   int tma_store;        // 1: epilogue goes through TMA stores (BN multiple of 64)
   const void* bias;     // [N] or null
   const void* ib;       // internal bias [G, K] or null
+  const long long* drop_seeds;   // per-group dropout seeds (DROP kernels)
+  float drop_p, drop_inv_keep;
   void* C;
   long long ldc;
   int* err;
@@ -84,7 +86,7 @@ __device__ __forceinline__ void tile_coords(const FwdParams& p, int t, int& mt, 
   mt = m0 + (rem - nt * pm);
 }
 
-template <int DT, int GATE, int E>
+template <int DT, int GATE, int E, bool DROP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(fwd::kThreads, 1)
 prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmR,
                  const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
@@ -270,13 +272,14 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     Ring rs(p.ns);
     for (uint32_t i = 0; i < group; ++i) rs.next();
     bool ok = true;
-    // internal bias: group and K chunk of chunk j, followed without a division per chunk
+    // internal bias / dropout: tile, group and K chunk of chunk j, followed without a division per chunk
     const uint16_t* ibase = reinterpret_cast<const uint16_t*>(p.ib);
-    int tg = cid, kc = (int)group, gcur = 0;
-    if (ibase != nullptr && total > 0) {
+    const bool track = (ibase != nullptr) || DROP;
+    int tg = cid, kc = (int)group, gcur = 0, mtcur = 0;
+    if (track && total > 0) {
       while (kc >= nk) { kc -= nk; tg += n_clusters; }
-      int mt0, nt0;
-      tile_coords(p, tg, mt0, nt0);
+      int nt0;
+      tile_coords(p, tg, mtcur, nt0);
       gcur = nt0 / p.ntiles_per_group;
     }
     for (uint32_t j = group; j < total; j += kGateGroups, rs.next(), rs.next()) {
@@ -284,18 +287,26 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!mbar_wait(&bars->s_full[slot], (j / kSlots) & 1)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t s_tmem = tmem_base + (r0 << 16) + kSlotCol0 + slot * 64;
-      const uint16_t* ib = nullptr;
-      if (ibase != nullptr) {
-        ib = ibase + (long long)gcur * p.K + kc * 64;
-        const int kv = p.K - kc * 64;
-        gate_rows16_tmem<DT, GATE>(s_tmem, smem_u32(smemSt + rs.idx * p.stage_bytes), r0, lane, s_tmem, ib, kv);
+      if (track) {
+        const uint16_t* ib = ibase != nullptr ? ibase + (long long)gcur * p.K + kc * 64 : nullptr;
+        DropCtx dc;
+        if (DROP) {
+          dc.h1 = drop_group_hash(p.drop_seeds, gcur);
+          dc.base = (long long)((mtcur * 2 + (int)rank) * 128 + (int)r0 + (lane >> 2)) * p.K + kc * 64 + 2 * (lane & 3);
+          dc.row8 = 8ll * p.K;
+          dc.p = p.drop_p;
+          dc.inv_keep = p.drop_inv_keep;
+        }
+        gate_rows16_tmem<DT, GATE, DROP>(s_tmem, smem_u32(smemSt + rs.idx * p.stage_bytes), r0, lane, s_tmem, ib,
+                                         p.K - kc * 64, &dc);
         kc += kGateGroups;
         if (kc >= nk) {
           while (kc >= nk) { kc -= nk; tg += n_clusters; }
-          if (tg < p.n_tiles) { int mt1, nt1; tile_coords(p, tg, mt1, nt1); gcur = nt1 / p.ntiles_per_group; }
+          if (tg < p.n_tiles) { int nt1; tile_coords(p, tg, mtcur, nt1); gcur = nt1 / p.ntiles_per_group; }
         }
-      } else
-      gate_rows16_tmem<DT, GATE>(s_tmem, smem_u32(smemSt + rs.idx * p.stage_bytes), r0, lane, s_tmem);
+      } else {
+        gate_rows16_tmem<DT, GATE>(s_tmem, smem_u32(smemSt + rs.idx * p.stage_bytes), r0, lane, s_tmem);
+      }
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
@@ -415,6 +426,9 @@ int launch_fwd(const FwdArgs& a) {
   p.r_tile_bytes = ((a.E / 2 * 128) + 1023) / 1024 * 1024;   // this CTA's E/2 rows of the R tile
   p.tma_store = (a.BN % 64 == 0) ? 1 : 0;
   p.bias = a.bias; p.ib = a.ib; p.C = a.C; p.ldc = a.ldc; p.err = a.err;
+  const bool drop = a.drop_seeds != nullptr && a.drop_p > 0.f && a.gate != GATE_NONE;
+  p.drop_seeds = a.drop_seeds; p.drop_p = a.drop_p; p.drop_inv_keep = drop ? 1.f / (1.f - a.drop_p) : 1.f;
+  if (drop && a.E != 16) return fail(PRISM_ERR_UNSUPPORTED, "forward: dropout needs reconn_sz 8 or 16");
 
   const int budget = 227 * 1024 - 1024 - (int)sizeof(FwdBarriers) - 256 - fwd::kNumEpiWarps * fwd::kEpiStageBytes;
   p.stage_bytes = fwd::kATileBytes + p.r_tile_bytes + a.BN * 64;   // A tile, halves of the R and B tiles
@@ -440,11 +454,12 @@ int launch_fwd(const FwdArgs& a) {
 
   using KernT = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, FwdParams);
   KernT kern = nullptr;
-#define PRISM_PICK_G(DT_, E_)                                                                    \
-  (a.gate == GATE_SILU ? (KernT)prism_fwd_kernel<DT_, GATE_SILU, E_>                                       \
-                       : a.gate == GATE_SIGMOID ? (KernT)prism_fwd_kernel<DT_, GATE_SIGMOID, E_> : (KernT)prism_fwd_kernel<DT_, GATE_NONE, E_>)
-#define PRISM_PICK(E_) kern = (a.dtype == DT_BF16) ? PRISM_PICK_G(DT_BF16, E_) : PRISM_PICK_G(DT_F16, E_)
-  if (a.E == 16) { PRISM_PICK(16); } else if (a.E == 32) { PRISM_PICK(32); } else { PRISM_PICK(64); }
+#define PRISM_PICK_G(DT_, E_, DROP_)                                                                    \
+  (a.gate == GATE_SILU ? (KernT)prism_fwd_kernel<DT_, GATE_SILU, E_, DROP_>                              \
+                       : a.gate == GATE_SIGMOID ? (KernT)prism_fwd_kernel<DT_, GATE_SIGMOID, E_, DROP_> : (KernT)prism_fwd_kernel<DT_, GATE_NONE, E_, false>)
+#define PRISM_PICK(E_) kern = (a.dtype == DT_BF16) ? PRISM_PICK_G(DT_BF16, E_, false) : PRISM_PICK_G(DT_F16, E_, false)
+  if (drop) { kern = (a.dtype == DT_BF16) ? PRISM_PICK_G(DT_BF16, 16, true) : PRISM_PICK_G(DT_F16, 16, true); }
+  else if (a.E == 16) { PRISM_PICK(16); } else if (a.E == 32) { PRISM_PICK(32); } else { PRISM_PICK(64); }
 #undef PRISM_PICK_G
 #undef PRISM_PICK
   if ((rc = set_max_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes, "forward"))) return rc;

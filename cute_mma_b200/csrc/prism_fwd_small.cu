@@ -50,6 +50,8 @@ struct FwdSmallParams {
   int ns, stage_bytes, a_off, r_off, b_off;
   const void* bias;
   const void* ib;      // internal bias [G, K] or null
+  const long long* drop_seeds;   // per-group dropout seeds (DROP kernels)
+  float drop_p, drop_inv_keep;
   void* C;
   long long ldc;
   float* partial;      // [G][pmax][Mp][gs] fp32
@@ -72,7 +74,7 @@ __device__ __host__ __forceinline__ int fsm_owner(long long x, int units, int nc
   return (int)(((x + 1) * ncta + units - 1) / units) - 1;
 }
 
-template <int DT, int GATE, int E>
+template <int DT, int GATE, int E, bool DROP>
 __global__ void __launch_bounds__(fsm::kThreads, 1)
 prism_fwd_small_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmR,
                        const __grid_constant__ CUtensorMap tmB, const FwdSmallParams p) {
@@ -246,8 +248,16 @@ prism_fwd_small_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         tc_fence_after_sync();
         const uint32_t tile = smem_u32(smemSt + rs.idx * p.stage_bytes + p.a_off);
         const uint16_t* ib = ibase != nullptr ? ibase + (long long)g * p.K + kc * 64 : nullptr;
-        gate_rows16_tmem_smem<DT, GATE, E>(tmem_base + (r0 << 16) + kSCol0 + slot * 64, E, tile, r0, lane,
-                                           smem_u32(&bars->s_free[slot]), ib, p.K - kc * 64);
+        DropCtx dc;
+        if (DROP) {
+          dc.h1 = drop_group_hash(p.drop_seeds, g);
+          dc.base = (long long)((int)r0 + (lane >> 2)) * p.K + kc * 64 + 2 * (lane & 3);
+          dc.row8 = 8ll * p.K;
+          dc.p = p.drop_p;
+          dc.inv_keep = p.drop_inv_keep;
+        }
+        gate_rows16_tmem_smem<DT, GATE, E, DROP>(tmem_base + (r0 << 16) + kSCol0 + slot * 64, E, tile, r0, lane,
+                                                 smem_u32(&bars->s_free[slot]), ib, p.K - kc * 64, &dc);
         if (++kc == p.nk) { kc = 0; ++g; }
         fence_proxy_async_smem();   // H was written by the generic proxy, the MMA reads it through the async proxy
         tc_fence_before_sync();
@@ -370,6 +380,9 @@ int launch_fwd_small(const FwdArgs& a, void* scratch) {
   p.nk = (a.K + 63) / 64;
   fwd_small_partition(p.G, p.nk, a.num_sms, &p.units, &p.ncta, &p.pmax);
   p.bias = a.bias; p.ib = a.ib; p.C = a.C; p.ldc = a.ldc; p.err = a.err;
+  const bool drop = a.drop_seeds != nullptr && a.drop_p > 0.f && a.gate != GATE_NONE;
+  p.drop_seeds = a.drop_seeds; p.drop_p = a.drop_p; p.drop_inv_keep = drop ? 1.f / (1.f - a.drop_p) : 1.f;
+  if (drop && a.E != 16) return fail(PRISM_ERR_UNSUPPORTED, "forward: dropout needs reconn_sz 8 or 16");
   p.partial = reinterpret_cast<float*>(scratch);
   // stage: A tile (Mp rows), R tile, B tiles, each on a 1024-byte boundary (128-byte swizzle atoms)
   p.a_off = 0;
@@ -391,11 +404,12 @@ int launch_fwd_small(const FwdArgs& a, void* scratch) {
 
   using KernT = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, FwdSmallParams);
   KernT kern = nullptr;
-#define PRISM_PICK_G(DT_, E_)                                                                    \
-  (a.gate == GATE_SILU ? (KernT)prism_fwd_small_kernel<DT_, GATE_SILU, E_>                                       \
-                       : a.gate == GATE_SIGMOID ? (KernT)prism_fwd_small_kernel<DT_, GATE_SIGMOID, E_> : (KernT)prism_fwd_small_kernel<DT_, GATE_NONE, E_>)
-#define PRISM_PICK(E_) kern = (a.dtype == DT_BF16) ? PRISM_PICK_G(DT_BF16, E_) : PRISM_PICK_G(DT_F16, E_)
-  if (a.E == 16) { PRISM_PICK(16); } else if (a.E == 32) { PRISM_PICK(32); } else { PRISM_PICK(64); }
+#define PRISM_PICK_G(DT_, E_, DROP_)                                                                    \
+  (a.gate == GATE_SILU ? (KernT)prism_fwd_small_kernel<DT_, GATE_SILU, E_, DROP_>                        \
+                       : a.gate == GATE_SIGMOID ? (KernT)prism_fwd_small_kernel<DT_, GATE_SIGMOID, E_, DROP_> : (KernT)prism_fwd_small_kernel<DT_, GATE_NONE, E_, false>)
+#define PRISM_PICK(E_) kern = (a.dtype == DT_BF16) ? PRISM_PICK_G(DT_BF16, E_, false) : PRISM_PICK_G(DT_F16, E_, false)
+  if (drop) { kern = (a.dtype == DT_BF16) ? PRISM_PICK_G(DT_BF16, 16, true) : PRISM_PICK_G(DT_F16, 16, true); }
+  else if (a.E == 16) { PRISM_PICK(16); } else if (a.E == 32) { PRISM_PICK(32); } else { PRISM_PICK(64); }
 #undef PRISM_PICK_G
 #undef PRISM_PICK
   if ((rc = set_max_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes, "small-M forward"))) return rc;

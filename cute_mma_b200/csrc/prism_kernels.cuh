@@ -14,6 +14,8 @@ struct FwdArgs {
   const void* R_eff;  // [(N/gs)*E, K]  rotation blocks padded to E x E
   const void* bias;   // [N] or null
   const void* ib;     // internal bias [N/gs, K] (gated modes) or null
+  const long long* drop_seeds;  // [N/gs] per-group dropout seeds, or null (no dropout)
+  float drop_p;       // dropout probability (with drop_seeds)
   void* C;            // [M, N]
   int M, N, K, gs, E;
   int dtype, gate;
@@ -51,6 +53,8 @@ struct DbArgs {
   const void* A;      // [M, K]
   const void* R_eff;  // [(N/gs)*E, K]
   const void* ib;     // internal bias [N/gs, K] (gated modes) or null
+  const long long* drop_seeds;  // [N/gs] per-group dropout seeds, or null
+  float drop_p;
   void* dB;           // [N, K], 16-bit like the inputs or fp32 (out_f32)
   int M, N, K, gs, E;
   int dtype, gate;
@@ -84,6 +88,8 @@ struct DadrArgs {
   void* dA;           // [M, K]
   void* dR;           // [(N/gs)*rs, K], 16-bit like the inputs or fp32 (dr_f32)
   const void* ib;     // internal bias [N/gs, K] (gated modes) or null
+  const long long* drop_seeds;  // [N/gs] per-group dropout seeds, or null
+  float drop_p;
   void* d_ib;         // its gradient [N/gs, K] (same dtype as the inputs), when ib is given
   float* partial_ib;  // fp32 column sums of dS per main CTA: [2*runs][N/gs][K]
   float* partial_ib_x;  // ... and per slab of the extra pairs' CTAs: [2*n_extra][slots][N/gs][128]

@@ -77,6 +77,19 @@ int prism_fwd(const void* A, const void* B, const void* R, const void* bias, con
               long long lda, long long ldb, long long ldr, long long ldc,
               const int* cfg, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Forward with hash dropout of the gated activation (training): element (m, k) of group g of
+ * H = A * gate(S) is kept iff top24(splitmix64(splitmix64(seed_g + 0xdeadbeef) ^ splitmix64(m*K + k))) / 2^24
+ * >= dropout_p, and kept elements are scaled by 1 / (1 - dropout_p): the counter-based mask of the
+ * reference's kernels (cute_prism_dtype.hpp:28-40).  dropout_seeds: [N/group_size] int64 on the device,
+ * chosen by the caller (the reference draws them in [1, 2^62), src/cute_prism/__init__.py:242-250) and
+ * passed again to the two backward calls, which regenerate the mask.  Gated modes, reconn_sz 8 or 16.
+ * dropout_seeds = NULL: no dropout (prism_fwd is this call without dropout). */
+int prism_fwd_dropout(const void* A, const void* B, const void* R, const void* bias, const void* internal_bias,
+                      void* C, int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
+                      long long lda, long long ldb, long long ldr, long long ldc,
+                      const long long* dropout_seeds, float dropout_p,
+                      const int* cfg, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Forward for callers that cannot allocate device memory and therefore cannot supply a workspace.
  * (No counterpart in the reference: its bindings allocate outputs and scratch themselves.)
  * Same arguments and results as prism_fwd, except that the scratch is a fixed array of
@@ -105,11 +118,12 @@ int prism_fwd_noalloc(const void* A, const void* B, const void* R, const void* b
  * bit-identical from run to run.  The workspace also holds the kernel's copy of R (widened for
  * reconn_sz = 8, halved in the gated mode).  internal_bias (or NULL): as in prism_fwd; then
  * d_internal_bias [N/group_size, K] (input dtype) receives dc_scale * sum over tokens of dS, summed in a
- * fixed order like dR, and the workspace is sized with PRISM_KIND_BWD_DADR_IB. */
+ * fixed order like dR, and the workspace is sized with PRISM_KIND_BWD_DADR_IB.  dropout_seeds /
+ * dropout_p: the forward's (prism_fwd_dropout), or NULL / 0: dH is multiplied by the same mask. */
 int prism_bwd_dadr(const void* dC, const void* A, const void* B, const void* R, const void* internal_bias,
                    void* dA, void* dR, void* d_internal_bias, int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
                    int dr_dtype, float dc_scale, long long lddc, long long lda, long long ldb, long long ldr,
-                   long long ldda, long long lddr,
+                   long long ldda, long long lddr, const long long* dropout_seeds, float dropout_p,
                    const int* cfg, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Weight gradient dB [N,K] = dc_scale * dC^T . H (H recomputed from A and R; B is not needed).
@@ -122,6 +136,7 @@ int prism_bwd_dadr(const void* dC, const void* A, const void* B, const void* R, 
 int prism_bwd_db(const void* dC, const void* A, const void* R, const void* internal_bias, void* dB,
                  int M, int N, int K, int group_size, int reconn_sz, int dtype, int gate,
                  int db_dtype, float dc_scale, long long lddc, long long lda, long long ldr, long long lddb,
+                 const long long* dropout_seeds, float dropout_p,
                  const int* cfg, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Output-bias gradient dbias [N] = sum over the M token rows of dC [M,N] (not scaled: the bias is

@@ -19,7 +19,8 @@ Parity pin: ``tests/golden/make_golden.py`` imports the reference package itself
 runs its pytorch backend on seeded inputs and stores inputs + outputs under
 ``tests/golden/``; ``tests/test_oracle.py`` checks this file against those vectors
 (and against torch autograd in float64).  Only the features on the accelerated path
-are restated: mode ``ar`` with ``silu_gate`` / ``sigmoid_gate`` and the internal bias; no dropout, shuffle or rw mode.
+are restated: mode ``ar`` with ``silu_gate`` / ``sigmoid_gate``, the internal bias and the kernels' hash dropout
+(the pytorch backend's own dropout draws its masks with torch.rand instead); no shuffle or rw mode.
 """
 from __future__ import annotations
 
@@ -60,7 +61,49 @@ def _gate(S, activation):
     return 2.0 * sig, 2.0 * sig * (1.0 - sig)
 
 
-def prism_forward(A, B, R, group_size, reconn_sz, activation=None, bias=None, internal_bias=None):
+_M64 = (1 << 64) - 1
+
+
+def _splitmix64_int(x: int) -> int:
+    """splitmix64 on Python integers (the published mixer; the reference's mirror is
+    tests/test_cublas_backend.py:40-44)."""
+    x = (x + 0x9E3779B97F4A7C15) & _M64
+    x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+    x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & _M64
+    return (x ^ (x >> 31)) & _M64
+
+
+def _srl(x, n):
+    """logical right shift of int64 tensors holding uint64 bit patterns"""
+    return (x >> n) & ((1 << (64 - n)) - 1)
+
+
+def _as_i64(v: int) -> int:
+    return v - (1 << 64) if v >= (1 << 63) else v
+
+
+def _splitmix64_t(x):
+    """splitmix64 on an int64 tensor (two's-complement wrap-around = arithmetic mod 2^64)"""
+    x = x + _as_i64(0x9E3779B97F4A7C15)
+    x = (x ^ _srl(x, 30)) * _as_i64(0xBF58476D1CE4E5B9)
+    x = (x ^ _srl(x, 27)) * _as_i64(0x94D049BB133111EB)
+    return x ^ _srl(x, 31)
+
+
+def dropout_multiplier(seed: int, M: int, K: int, p: float, device="cpu"):
+    """(M, K) fp32 multipliers of the reference kernels' hash dropout (cute_prism_dtype.hpp:28-40,
+    cute_prism_coop_pc.cu:294-298): 1/(1-p) where u >= p, else 0, with
+    u = top24(splitmix64(splitmix64(seed + 0xdeadbeef) ^ splitmix64(m*K + k))) / 2^24."""
+    h1 = _as_i64(_splitmix64_int((int(seed) + 0xDEADBEEF) & _M64))
+    idx = torch.arange(M * K, dtype=torch.int64, device=device)
+    h = _splitmix64_t(_splitmix64_t(idx) ^ h1)
+    u = (_srl(h, 40) & 0xFFFFFF).to(torch.float32) * (1.0 / 16777216.0)
+    keep = u >= torch.tensor(p, dtype=torch.float32, device=device)
+    return (keep.to(torch.float32) * (1.0 / (1.0 - p))).reshape(M, K)
+
+
+def prism_forward(A, B, R, group_size, reconn_sz, activation=None, bias=None, internal_bias=None,
+                  dropout_seeds=None, dropout_p=0.0):
     """C (M, N) in the dtype of A.  Follows ``pytorch_forward`` (ar mode, optional gate; the internal bias
     (G, K) is added to S before the gate, lines 154-156)."""
     if activation not in GATES:
@@ -75,13 +118,16 @@ def prism_forward(A, B, R, group_size, reconn_sz, activation=None, bias=None, in
         if activation is not None and internal_bias is not None:
             S = S + internal_bias[g]
         H = A * _gate(S, activation)[0] if activation is not None else S
+        if activation is not None and dropout_seeds is not None and dropout_p > 0.0:
+            H = H * dropout_multiplier(int(dropout_seeds[g]), M, K, dropout_p, A.device).to(H.dtype)
         C[:, g * group_size:(g + 1) * group_size] = H @ B[g * group_size:(g + 1) * group_size].T
     if bias is not None:
         C = C + bias
     return C
 
 
-def prism_backward(dC, A, B, R, group_size, reconn_sz, activation=None, internal_bias=None):
+def prism_backward(dC, A, B, R, group_size, reconn_sz, activation=None, internal_bias=None,
+                   dropout_seeds=None, dropout_p=0.0):
     """(dA, dR, dB-or-None), plus d_internal_bias (G, K) = sum over tokens of dS as a fourth element when an
     internal bias is given (lines 246-248, 271-272).  Follows ``pytorch_backward``."""
     if activation not in GATES:
@@ -107,7 +153,12 @@ def prism_backward(dC, A, B, R, group_size, reconn_sz, activation=None, internal
             if internal_bias is not None:
                 S = S + internal_bias[g]
             gate, gate_d = _gate(S, activation)
-            dB[sl] = dC_g.T @ (A * gate)
+            H = A * gate
+            if dropout_seeds is not None and dropout_p > 0.0:   # the forward's mask on H and on dH (lines 264-276)
+                mult = dropout_multiplier(int(dropout_seeds[g]), M, K, dropout_p, A.device).to(H.dtype)
+                H = H * mult
+                dH = dH * mult
+            dB[sl] = dC_g.T @ H
             dS = dH * A * gate_d
             if d_ib is not None:
                 d_ib[g] = dS.sum(dim=0)

@@ -24,7 +24,7 @@ def test_header_and_loader_agree():
 def test_library_exports_every_declared_symbol(built_lib):
     for name in _declared_symbols():
         assert hasattr(built_lib, name), name
-    assert built_lib.prism_abi_version() == _lib.ABI_VERSION == 3
+    assert built_lib.prism_abi_version() == _lib.ABI_VERSION == 4
 
 
 def _call_fwd(L, M, N, K, gs, rs, dtype=1, gate=0, ptr=0x1000, ws=0x1000, ws_bytes=1 << 20):
@@ -52,7 +52,7 @@ def test_bad_arguments_are_rejected_without_a_gpu(built_lib, args, code):
 
 def test_gradient_dtype_codes_are_checked(built_lib):
     p = ctypes.c_void_p(0x1000)
-    rc = built_lib.prism_bwd_db(p, p, p, None, p, 16, 64, 64, 32, 8, 1, 1, 0, ctypes.c_float(1.0), 64, 64, 64, 64, None,
+    rc = built_lib.prism_bwd_db(p, p, p, None, p, 16, 64, 64, 32, 8, 1, 1, 0, ctypes.c_float(1.0), 64, 64, 64, 64, None, ctypes.c_float(0.0), None,
                                 p, 1 << 20, None)
     assert rc == 1 and b"db_dtype" in built_lib.prism_last_error_string()   # fp16 gradient of bf16 inputs
     rc = built_lib.prism_dbias(p, p, 16, 60, 1, -1, 64, p, 1 << 20, None)

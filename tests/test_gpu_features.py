@@ -357,3 +357,58 @@ def test_prism_linear_with_internal_bias_trains():
     assert O.rel_err(layer._internal_bias.grad.float(), r_ib) < TOL
     assert O.rel_err(x.grad.reshape(-1, 256).float(), rA) < TOL and O.rel_err(layer.weight.grad.float(), rB) < TOL
     cp.check_device_status()
+
+
+@pytest.mark.parametrize("shape", [(1024, 256, 1024, 256, 8), (300, 208, 256, 128, 16), (24, 512, 512, 256, 16),
+                                   (2048, 512, 768, 256, 16)], ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("act", ["silu_gate", "sigmoid_gate"])
+def test_hash_dropout_forward_and_backward(shape, act):
+    """Training-mode dropout of the gated activation: the kernels' mask is the reference kernels' hash mask
+    (regenerated in both backward kernels from the per-group seeds); checked against the oracle with the
+    same seeds, together with an internal bias."""
+    M, K, N, gs, rs = shape
+    dt = torch.bfloat16 if rs != 8 else torch.float16
+    p = 0.25
+    A, B, R, dC = _inputs(M, K, N, gs, rs, dt, seed=83)
+    ib = (torch.randn(N // gs, K, device=DEV) * 0.5).to(dt)
+    C, seeds = cp.forward(A, B, R, gs, rs, activation=act, internal_bias=ib, dropout_p=p, training=True)
+    assert len(seeds) == 1 and seeds[0].dtype == torch.int64 and seeds[0].shape == (N // gs,)
+    dA, dR, dB, d_ib = cp.backward(dC, A, B, R, gs, rs, activation=act, internal_bias=ib, dropout_seeds=seeds,
+                                   dropout_p=p)
+    cp.check_device_status()
+    Af, Bf, Rf, ibf = A.float(), B.float(), R.float(), ib.float()
+    sl = seeds[0].tolist()
+    rC = O.prism_forward(Af, Bf, Rf, gs, rs, act, internal_bias=ibf, dropout_seeds=sl, dropout_p=p)
+    rA, rR, rB, r_ib = O.prism_backward(dC.float(), Af, Bf, Rf, gs, rs, act, internal_bias=ibf, dropout_seeds=sl,
+                                        dropout_p=p)
+    for name, val, ref in (("C", C, rC), ("dA", dA, rA), ("dR", dR, rR), ("dB", dB, rB), ("d_ib", d_ib, r_ib)):
+        assert torch.isfinite(val).all(), name
+        assert O.rel_err(val.float(), ref) < TOL, (name, O.rel_err(val.float(), ref))
+    # same seeds, same result; eval mode (training=False) is the plain gated forward
+    C2, _ = cp.forward(A, B, R, gs, rs, activation=act, internal_bias=ib, dropout_p=p, training=True,
+                       dropout_seeds=seeds[0])
+    assert torch.equal(C2, C)
+    Ce, se = cp.forward(A, B, R, gs, rs, activation=act, internal_bias=ib, dropout_p=p, training=False)
+    assert se == [] and O.rel_err(Ce.float(), O.prism_forward(Af, Bf, Rf, gs, rs, act, internal_bias=ibf)) < TOL
+    assert O.rel_err(Ce.float(), rC) > 5e-2      # the mask really changed the result
+
+
+def test_prism_linear_dropout_train_and_eval():
+    torch.manual_seed(5)
+    layer = cp.PrismLinear(256, 512, group_size=256, reconn_sz=16, activation="silu_gate", dropout=0.5)
+    layer = layer.to(DEV).to(torch.bfloat16)
+    x = torch.randn(256, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    layer.eval()
+    y_eval = layer(x)
+    layer.train()
+    y1, y2 = layer(x), layer(x)
+    assert not torch.equal(y1, y2) and not torch.equal(y1, y_eval)       # fresh seeds per call
+    y1.float().pow(2).mean().backward()
+    assert torch.isfinite(x.grad).all() and torch.isfinite(layer.reconn.grad).all()
+    # expectation over masks is the eval output: the mean over many draws approaches it
+    acc = torch.zeros_like(y_eval, dtype=torch.float32)
+    with torch.no_grad():
+        for _ in range(64):
+            acc += layer(x).float()
+    assert O.rel_err(acc / 64, y_eval.float()) < 0.35
+    cp.check_device_status()

@@ -82,7 +82,11 @@ def test_prism_linear_construction_and_state():
     ibl = cp.PrismLinear(64, 128, group_size=32, reconn_sz=16, activation="silu_gate", internal_bias=True)
     assert ibl._internal_bias.shape == (4, 64) and "_internal_bias" in ibl.state_dict()
     assert cp.PrismLinear(64, 128, group_size=32, reconn_sz=16, internal_bias=True)._internal_bias is None   # plain mode: none
-    for bad in (dict(input_shuffle=True), dict(dropout=0.1), dict(activation="tanh")):
+    dl = cp.PrismLinear(64, 128, group_size=32, reconn_sz=16, activation="silu_gate", dropout=0.1)
+    assert dl.dropout == pytest.approx(0.1)
+    with pytest.raises(ValueError):
+        cp.PrismLinear(64, 128, group_size=32, reconn_sz=32, activation="silu_gate", dropout=0.1)   # 8 / 16 only
+    for bad in (dict(input_shuffle=True), dict(activation="tanh")):
         with pytest.raises(ValueError):
             cp.PrismLinear(64, 128, 32, 16, **bad)
     with pytest.raises(ValueError):

@@ -103,3 +103,29 @@ def test_known_answers():
 def test_flop_model():
     f, d, b = O.flops(16384, 4096, 14336, 256, 16)
     assert abs(f / 1e9 - 2044.4) < 0.5 and abs(d / 1e9 - 2164.7) < 0.5 and abs(b / 1e9 - 1924.2) < 0.5
+
+
+def test_dropout_hash_matches_the_scalar_definition():
+    """The vectorised mask of the oracle against the scalar definition of the reference's kernels
+    (cute_prism_dtype.hpp:28-40; the reference's own Python mirror is tests/test_cublas_backend.py:40-51):
+    u = top24(splitmix64(splitmix64(seed + 0xdeadbeef) ^ splitmix64(idx))) / 2^24, keep iff u >= p."""
+    M64 = (1 << 64) - 1
+
+    def splitmix64(x):
+        x = (x + 0x9E3779B97F4A7C15) & M64
+        x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & M64
+        x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & M64
+        return (x ^ (x >> 31)) & M64
+
+    assert splitmix64(0) == 0xE220A8397B1DCDAF          # first output of the published generator seeded with 0
+    for seed, M, K, p in ((1, 3, 16, 0.1), (0x0123456789ABCDEF, 7, 24, 0.5), ((1 << 62) - 1, 2, 40, 0.9)):
+        mult = O.dropout_multiplier(seed, M, K, p)
+        h1 = splitmix64((seed + 0xDEADBEEF) & M64)
+        for m in range(M):
+            for k in range(K):
+                h = splitmix64(h1 ^ splitmix64(m * K + k))
+                u = ((h >> 40) & 0xFFFFFF) * (1.0 / 16777216.0)
+                want = 1.0 / (1.0 - p) if np.float32(u) >= np.float32(p) else 0.0
+                assert abs(mult[m, k].item() - want) < 1e-6, (seed, m, k)
+    big = O.dropout_multiplier(12345, 256, 256, 0.25)
+    assert abs((big > 0).float().mean().item() - 0.75) < 0.01
