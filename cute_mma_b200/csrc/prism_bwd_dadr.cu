@@ -152,7 +152,8 @@ int launch_bwd_dadr(const DadrArgs& a) {
   p.dA = a.dA; p.ldda = a.ldda; p.partial = a.partial; p.err = a.err;
   int smem_bytes = 0;
   const bool ib = a.ib != nullptr && a.gate != GATE_NONE;
-  p.ib = ib ? a.ib : nullptr; p.partial_ib = a.partial_ib; p.partial_ib_x = a.partial_ib_x;
+  DadrExtra x;
+  x.ib = ib ? a.ib : nullptr; x.partial_ib = a.partial_ib; x.partial_ib_x = a.partial_ib_x;
   int rc = (a.E == 16) ? dadr_plan<16>(p, smem_bytes, ib) : (a.E == 32) ? dadr_plan<32>(p, smem_bytes, ib) : dadr_plan<64>(p, smem_bytes, ib);
   if (rc) return rc;
   const int stage_out = 64;
@@ -166,11 +167,11 @@ int launch_bwd_dadr(const DadrArgs& a) {
 
   const bool drop = a.drop_seeds != nullptr && a.drop_p > 0.f && a.gate != GATE_NONE;
   if (drop && a.E != 16) return fail(PRISM_ERR_UNSUPPORTED, "bwd_dadr: dropout needs reconn_sz 8 or 16");
-  p.drop_seeds = a.drop_seeds; p.drop_p = a.drop_p; p.drop_inv_keep = drop ? 1.f / (1.f - a.drop_p) : 1.f;
+  x.drop_seeds = a.drop_seeds; x.drop_p = a.drop_p; x.drop_inv_keep = drop ? 1.f / (1.f - a.drop_p) : 1.f;
   DadrKernel kern = (a.dtype == DT_BF16) ? dadr_kernel_bf16(a.gate, a.E, ib, drop) : dadr_kernel_f16(a.gate, a.E, ib, drop);
   if ((rc = set_max_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes, "bwd_dadr"))) return rc;
   dim3 grid(2 * (p.n_main + p.n_extra), 1, 1);   // the two CTAs of a pair are neighbours
-  kern<<<grid, dadr::kThreads, smem_bytes, a.stream>>>(tmA, tmRr, tmRd, tmdC, tmB, p);
+  kern<<<grid, dadr::kThreads, smem_bytes, a.stream>>>(tmA, tmRr, tmRd, tmdC, tmB, p, x);
   if ((rc = check_launch("prism_bwd_dadr"))) return rc;
 
   // gated mode: the kernel formed 2 dS against the halved R tiles, so the dR partials are doubled

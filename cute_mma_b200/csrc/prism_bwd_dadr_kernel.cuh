@@ -76,12 +76,17 @@ struct DadrParams {
   long long ldda;
   float* partial;      // [2*runs][G*E][K] fp32: one buffer per CTA of every main pair
   float* partial_x;    // [2*n_extra][slots][G*E][128] fp32: slabs of the extra pairs' CTAs
+  int* err;
+};
+
+// Arguments of the internal-bias and dropout instances only.  A kernel parameter of its own: with these
+// fields inside DadrParams the instance without either (the benchmarked one) compiled to more spills.
+struct DadrExtra {
   const long long* drop_seeds;   // per-group dropout seeds (DROP kernels)
   float drop_p, drop_inv_keep;
   const void* ib;      // internal bias [G, K] (gated modes, IB kernels) or null
   float* partial_ib;   // [2*runs][G][K] fp32: column sums of dS of the main CTAs
   float* partial_ib_x; // [2*n_extra][slots][G][128] fp32: ... of the extra pairs' CTAs
-  int* err;
 };
 
 struct DadrBarriers {
@@ -179,7 +184,6 @@ struct DadrUnit {
   bool first;     // first tile that touches this dR slab: store, do not add
   float* part;    // dR slab of this CTA for the tile's column (row 0, feature f0)
   long long ld;   // its row pitch
-  float* part_ib; // d(internal bias) slab of this CTA for the tile's column (group 0, feature f0), same pitch
 };
 __device__ __forceinline__ int dadr_tiles_of_run(const DadrParams& p, int run) {
   return ((p.n_mtiles + 1) / 2 - run + p.runs - 1) / p.runs;
@@ -199,7 +203,6 @@ __device__ __forceinline__ DadrUnit dadr_unit(const DadrParams& p, int pidx, int
     u.first = (k == 0);
     u.part = p.partial + (long long)(run * 2 + rank) * GE * p.K + u.f0;
     u.ld = p.K;
-    u.part_ib = p.partial_ib + (long long)(run * 2 + rank) * p.G * p.K + u.f0;
   } else {
     const int e = pidx - p.n_main;
     const int m_lo = e * p.n_main / p.n_extra;
@@ -212,9 +215,20 @@ __device__ __forceinline__ DadrUnit dadr_unit(const DadrParams& p, int pidx, int
     u.first = (j == 0);
     u.part = p.partial_x + ((long long)(e * 2 + rank) * p.slots + mi) * GE * 128;
     u.ld = 128;
-    u.part_ib = p.partial_ib_x + ((long long)(e * 2 + rank) * p.slots + mi) * p.G * 128;
   }
   return u;
+}
+// d(internal bias) slab of this CTA for unit k's column (group 0, feature f0); row pitch as the dR slab's
+__device__ __forceinline__ float* dadr_unit_ib(const DadrParams& p, const DadrExtra& x, int pidx, int rank, int k) {
+  if (pidx < p.n_main) {
+    const int fx = pidx % p.n_ft, run = pidx / p.n_ft;
+    return x.partial_ib + (long long)(run * 2 + rank) * p.G * p.K + fx * 128;
+  }
+  const int e = pidx - p.n_main;
+  const int m_lo = e * p.n_main / p.n_extra;
+  const int cnt = (e + 1) * p.n_main / p.n_extra - m_lo;
+  const int mi = k % cnt;
+  return x.partial_ib_x + ((long long)(e * 2 + rank) * p.slots + mi) * p.G * 128;
 }
 
 // IB: the internal-bias variant (gated modes): S += bias before the gate, and the column sums of dS over
@@ -226,7 +240,7 @@ template <int DT, int GATE, int E, bool IB, bool DROP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(dadr::kThreads, 1)
 prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmRr,
                       const __grid_constant__ CUtensorMap tmRd, const __grid_constant__ CUtensorMap tmdC,
-                      const __grid_constant__ CUtensorMap tmB, const DadrParams p) {
+                      const __grid_constant__ CUtensorMap tmB, const DadrParams p, const DadrExtra ex) {
   using namespace dadr;
   using St = Stage<E>;
   constexpr int KS = E / 16;       // 16-wide steps per rotation block
@@ -507,8 +521,10 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const DadrUnit u = dadr_unit(p, pidx, (int)rank, k);
       const int f0 = u.f0;
       const int mt = u.mp * 2 + (int)rank;
+      float* part_ib = nullptr;
       if (IB) {
-        ib_row = reinterpret_cast<const uint16_t*>(p.ib) + f0 + ch * 64;
+        part_ib = dadr_unit_ib(p, ex, pidx, (int)rank, k);
+        ib_row = reinterpret_cast<const uint16_t*>(ex.ib) + f0 + ch * 64;
         ib_valid = p.K - (f0 + ch * 64);
       }
       if (!mbar_wait(&bars->a_full, tile_iter & 1)) { ok = false; break; }
@@ -522,11 +538,11 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         tc_fence_after_sync();
         DropCtx dctx;
         if (DROP && kGated) {
-          dctx.h1 = drop_group_hash(p.drop_seeds, g);
+          dctx.h1 = drop_group_hash(ex.drop_seeds, g);
           dctx.base = (long long)(mt * 128 + (int)r0 + (lane >> 2)) * p.K + f0 + ch * 64 + 2 * (lane & 3);
           dctx.row8 = 8ll * p.K;
-          dctx.p = p.drop_p;
-          dctx.inv_keep = p.drop_inv_keep;
+          dctx.p = ex.drop_p;
+          dctx.inv_keep = ex.drop_inv_keep;
         }
         const uint32_t tileDS = smem_u32(smemDS + hb * 2 * kTile + ch * kTile);
         const uint32_t tdh = tmem_base + lane_base + kDhCol0 + hb * 128 + ch * 64;
@@ -638,7 +654,7 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 #pragma unroll
             for (int r = 0; r < 8; ++r) tsum += src[r * 64];
             if (f0 + ch * 64 + col < p.K) {
-              float* dst = u.part_ib + (long long)g * u.ld + ch * 64 + col;
+              float* dst = part_ib + (long long)g * u.ld + ch * 64 + col;
               if (u.first) *dst = tsum;
               else asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst), "f"(tsum) : "memory");
             }
@@ -771,7 +787,7 @@ prism_bwd_dadr_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   if (warp == kWarpMma) tmem_dealloc_pair(tmem_base, 512);
 }
 
-using DadrKernel = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, DadrParams);
+using DadrKernel = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, DadrParams, DadrExtra);
 // kernel instance for (gate, E, internal-bias variant), one function per data type and translation unit
 DadrKernel dadr_kernel_f16(int gate, int E, bool ib, bool drop);
 DadrKernel dadr_kernel_bf16(int gate, int E, bool ib, bool drop);

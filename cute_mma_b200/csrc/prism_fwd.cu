@@ -86,7 +86,8 @@ __device__ __forceinline__ void tile_coords(const FwdParams& p, int t, int& mt, 
   mt = m0 + (rem - nt * pm);
 }
 
-template <int DT, int GATE, int E, bool DROP>
+// EXTRA: 0 the plain gate warps; 1 internal bias (a null bias is allowed); 2 hash dropout (+ optional bias)
+template <int DT, int GATE, int E, int EXTRA>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(fwd::kThreads, 1)
 prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmR,
                  const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC,
@@ -274,7 +275,8 @@ prism_fwd_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     bool ok = true;
     // internal bias / dropout: tile, group and K chunk of chunk j, followed without a division per chunk
     const uint16_t* ibase = reinterpret_cast<const uint16_t*>(p.ib);
-    const bool track = (ibase != nullptr) || DROP;
+    constexpr bool DROP = (EXTRA == 2);
+    constexpr bool track = (EXTRA != 0);
     int tg = cid, kc = (int)group, gcur = 0, mtcur = 0;
     if (track && total > 0) {
       while (kc >= nk) { kc -= nk; tg += n_clusters; }
@@ -454,12 +456,14 @@ int launch_fwd(const FwdArgs& a) {
 
   using KernT = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, FwdParams);
   KernT kern = nullptr;
-#define PRISM_PICK_G(DT_, E_, DROP_)                                                                    \
-  (a.gate == GATE_SILU ? (KernT)prism_fwd_kernel<DT_, GATE_SILU, E_, DROP_>                              \
-                       : a.gate == GATE_SIGMOID ? (KernT)prism_fwd_kernel<DT_, GATE_SIGMOID, E_, DROP_> : (KernT)prism_fwd_kernel<DT_, GATE_NONE, E_, false>)
-#define PRISM_PICK(E_) kern = (a.dtype == DT_BF16) ? PRISM_PICK_G(DT_BF16, E_, false) : PRISM_PICK_G(DT_F16, E_, false)
-  if (drop) { kern = (a.dtype == DT_BF16) ? PRISM_PICK_G(DT_BF16, 16, true) : PRISM_PICK_G(DT_F16, 16, true); }
-  else if (a.E == 16) { PRISM_PICK(16); } else if (a.E == 32) { PRISM_PICK(32); } else { PRISM_PICK(64); }
+#define PRISM_PICK_G(DT_, E_, X_)                                                                       \
+  (a.gate == GATE_SILU ? (KernT)prism_fwd_kernel<DT_, GATE_SILU, E_, X_>                                 \
+                       : a.gate == GATE_SIGMOID ? (KernT)prism_fwd_kernel<DT_, GATE_SIGMOID, E_, X_> : (KernT)prism_fwd_kernel<DT_, GATE_NONE, E_, 0>)
+#define PRISM_PICK(E_, X_) kern = (a.dtype == DT_BF16) ? PRISM_PICK_G(DT_BF16, E_, X_) : PRISM_PICK_G(DT_F16, E_, X_)
+  const bool ib = a.ib != nullptr && a.gate != GATE_NONE;
+  if (drop) { PRISM_PICK(16, 2); }
+  else if (ib) { if (a.E == 16) { PRISM_PICK(16, 1); } else if (a.E == 32) { PRISM_PICK(32, 1); } else { PRISM_PICK(64, 1); } }
+  else if (a.E == 16) { PRISM_PICK(16, 0); } else if (a.E == 32) { PRISM_PICK(32, 0); } else { PRISM_PICK(64, 0); }
 #undef PRISM_PICK_G
 #undef PRISM_PICK
   if ((rc = set_max_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes, "forward"))) return rc;
