@@ -793,10 +793,14 @@ __device__ __forceinline__ void gate_rows16_tmem(uint32_t s_tmem, uint32_t tile,
 template <int DT, int GATE, int E, bool DROP = false>
 __device__ __forceinline__ void gate_rows16_tmem_smem(uint32_t s_tmem, uint32_t blk_stride, uint32_t tile, uint32_t r0,
                                                       int lane, uint32_t s_free, const uint16_t* ib = nullptr,
-                                                      int kvalid = 64, const DropCtx* drop = nullptr) {
+                                                      int kvalid = 64, const DropCtx* drop = nullptr,
+                                                      uint32_t h_tile = 0, uint32_t h_r0 = 0) {
   constexpr int KS = E / 16;
   const uint32_t mat = lane >> 3, l8 = lane & 7;
   const uint32_t a_row = r0 + l8 + (mat & 1) * 8;
+  // H goes back over the A rows, or (h_tile != 0) to rows h_r0 ... of a tile of its own
+  const uint32_t h_row = (h_tile != 0) ? h_r0 + l8 + (mat & 1) * 8 : a_row;
+  if (h_tile == 0) h_tile = tile;
   uint32_t s[4][8], af[4][4], h[4][4];
 #pragma unroll
   for (int pc = 0; pc < 4; ++pc) tmem_ld_16x256b_x2(s_tmem + (pc / KS) * blk_stride + (pc % KS) * 16, s[pc]);
@@ -828,7 +832,7 @@ __device__ __forceinline__ void gate_rows16_tmem_smem(uint32_t s_tmem, uint32_t 
     }
   }
 #pragma unroll
-  for (int pc = 0; pc < 4; ++pc) stmatrix_x4(tile + sw128_offset(a_row, pc * 2 + (mat >> 1)), h[pc]);
+  for (int pc = 0; pc < 4; ++pc) stmatrix_x4(h_tile + sw128_offset(h_row, pc * 2 + (mat >> 1)), h[pc]);
 }
 
 }  // namespace prism
