@@ -97,6 +97,9 @@ prism_fwd_small_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   const int n_gate = p.Mp / 16;   // gate warps with token rows
 
   if (threadIdx.x == 0) {
+    // the reduction kernel (launched with programmatic stream serialisation) may be scheduled from now on:
+    // its blocks sit in their dependency wait until this grid has finished, so its launch latency is hidden
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     for (int i = 0; i < kMaxStages; ++i) {
       mbar_init(&bars->full[i], 1);
       mbar_init(&bars->empty[i], 1);
