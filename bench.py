@@ -41,6 +41,10 @@ WORKLOADS = {
     "cfg2_m16384": dict(M=16384, K=4096, N=14336, gs=256, rs=16, dtype="bf16", act="silu_gate", dc_std=1.0),
     "cfg2_m4096": dict(M=4096, K=4096, N=14336, gs=256, rs=16, dtype="bf16", act="silu_gate", dc_std=1.0),
     "cfg2_m2048": dict(M=2048, K=4096, N=14336, gs=256, rs=16, dtype="bf16", act="silu_gate", dc_std=1.0),
+    # cfg 2 with the input shuffle: every group's permutation folded into the parameters, i.e. the kernels run a
+    # 64-wide rotation (rs) while the layer's algorithmic work is that of its 16-wide blocks (rs_algo)
+    "cfg2_m16384_shuffle": dict(M=16384, K=4096, N=14336, gs=256, rs=64, rs_algo=16, shuffle=True, dtype="bf16",
+                                act="silu_gate", dc_std=1.0),
     "cfg3_m8192": dict(M=8192, K=1024, N=16384, gs=256, rs=8, dtype="fp16", act="silu_gate", dc_std=0.1),
     "cfg1": dict(M=1024, K=256, N=1024, gs=256, rs=8, dtype="fp16", act="silu_gate", dc_std=1.0),
 }
@@ -51,7 +55,7 @@ NCCL_CTAS = 8   # CTAs NCCL uses per collective: the all-reduce of dB runs besid
 
 def flops(w):
     dense = 2.0 * w["M"] * w["N"] * w["K"]
-    bd = 2.0 * w["M"] * w["K"] * w["rs"] * (w["N"] // w["gs"])
+    bd = 2.0 * w["M"] * w["K"] * w.get("rs_algo", w["rs"]) * (w["N"] // w["gs"])
     gated = w["act"] is not None
     return {"fwd": dense + bd, "dadr": dense + 2 * bd, "db": dense if gated else 0.0}
 
@@ -278,7 +282,12 @@ def make_inputs(w, dev, rank, M=None):
     gen = torch.Generator(device=dev).manual_seed(1234 + rank)
     A = torch.randn(M, K, device=dev, generator=gen).to(dt)
     B = (torch.randn(N, K, device=dev, generator=torch.Generator(device=dev).manual_seed(7)) * K ** -0.5).to(dt)
-    R = O.orthogonal_R(N // gs, K, rs, torch.Generator().manual_seed(0)).to(dt).to(dev)
+    R = O.orthogonal_R(N // gs, K, w.get("rs_algo", rs), torch.Generator().manual_seed(0)).to(dt).to(dev)
+    if w.get("shuffle"):
+        from cute_mma_b200 import _shuffle
+        masks, _ = _shuffle.build_shuffle_masks(K, N, gs, w["rs_algo"])
+        fold = _shuffle.ShuffleFold(masks, K, gs, w["rs_algo"], dev)
+        B, R = fold.fold_cols(B, gs), fold.fold_R(R)
     dC = (torch.randn(M, N, device=dev, generator=gen) * w["dc_std"]).to(dt)
     return A, B, R, dC
 

@@ -203,6 +203,23 @@ def _reject_unsupported(**kw):
             raise ValueError(f"{name} is not supported by the sm_100a kernels")
 
 
+_fold_cache: dict = {}
+
+
+def _shuffle_fold(shuffle_masks, K, group_size, reconn_sz, device):
+    """Index maps of a set of shuffle masks (see ``_shuffle``), kept for repeated calls with the same tensor."""
+    from ._shuffle import ShuffleFold
+    if not isinstance(shuffle_masks, torch.Tensor) or shuffle_masks.dim() != 3 or shuffle_masks.dtype != torch.int64:
+        raise ValueError("shuffle_masks must be an int64 tensor of shape (n_groups, K / 64, rounds)")
+    key = (shuffle_masks.data_ptr(), shuffle_masks._version, tuple(shuffle_masks.shape), K, group_size, str(device))
+    fold = _fold_cache.get(key)
+    if fold is None:
+        if len(_fold_cache) >= 16:
+            _fold_cache.clear()
+        fold = _fold_cache[key] = ShuffleFold(shuffle_masks, K, group_size, reconn_sz, device)
+    return fold
+
+
 def forward(A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=None, mode: str = "ar",
             comp_params=None, activation=None, autotuning: bool = False, autotuning_search_space=None,
             force_rebenchmark: bool = False, internal_bias=None, dropout_p: float = 0.0,
@@ -214,6 +231,10 @@ def forward(A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=None, mo
     ``bias`` (keyword-only, [N], same dtype) is added in the kernel epilogue.  With ``training=True`` and
     ``dropout_p > 0`` (gated modes) the gated activation goes through hash dropout and the second return
     value is ``[seeds]`` (int64, one per group) for ``backward(dropout_seeds=..., dropout_p=...)``.
+    ``shuffle_masks`` (reconn_sz 16, chunks of 64 features): every group sees its own butterfly permutation
+    of the input features (reference: src/cute_prism/__init__.py:114-117); served by the 64-wide rotation of
+    the same kernels on folded parameters (``_shuffle``), not combined with dropout (the hash mask is
+    indexed by physical feature there, by permuted feature in the reference).
     """
     if mode not in ("ar", "rw"):
         raise ValueError(f"Unknown mode {mode!r}, must be 'ar' or 'rw'")
@@ -227,10 +248,17 @@ def forward(A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=None, mo
         validate_tensor_params(A, B, R, group_size, reconn_sz)
         C = torch.matmul(A, fold_weight(B, R, group_size, reconn_sz).t())
         return (C if bias is None else C + bias), []
-    _reject_unsupported(shuffle_masks=shuffle_masks)
     validate_tensor_params(A, B, R, group_size, reconn_sz)
     M, K = A.shape
     N = B.shape[0]
+    if shuffle_masks is not None:
+        if training and dropout_p > 0.0:
+            raise ValueError("input shuffle together with dropout is not supported by the sm_100a kernels")
+        internal_bias = _check_internal_bias(internal_bias, A, N, K, group_size, gate)
+        fold = _shuffle_fold(shuffle_masks, K, group_size, reconn_sz, A.device)
+        return forward(A, fold.fold_cols(B, group_size), fold.fold_R(R), group_size, 64, activation=activation,
+                       internal_bias=None if internal_bias is None else fold.fold_cols(internal_bias, 1),
+                       bias=bias, tile_cfg=tile_cfg)
     internal_bias = _check_internal_bias(internal_bias, A, N, K, group_size, gate)
     # hash dropout of the gated activation, training only (reference: src/cute_prism/__init__.py:242-261): one
     # int64 seed per group, drawn here (or given as `dropout_seeds`) and returned for the backward
@@ -385,10 +413,23 @@ def backward(dC, A, B, R, group_size: int = 256, reconn_sz: int = 8, backend=Non
     """
     gate = _gate_code(activation)
     validate_kernel_params(group_size, reconn_sz)
-    _reject_unsupported(shuffle_masks=shuffle_masks)
     validate_tensor_params(A, B, R, group_size, reconn_sz)
     M, K = A.shape
     N = B.shape[0]
+    if shuffle_masks is not None:
+        # the same kernels on the folded parameters (64-wide rotation); the parameter gradients come back through
+        # the fold's index maps, dA needs none
+        if dropout_seeds is not None and dropout_p > 0.0:
+            raise ValueError("input shuffle together with dropout is not supported by the sm_100a kernels")
+        internal_bias = _check_internal_bias(internal_bias, A, N, K, group_size, gate)
+        fold = _shuffle_fold(shuffle_masks, K, group_size, reconn_sz, A.device)
+        dA, dR64, dB2, d_ib2 = backward(
+            dC, A, fold.fold_cols(B, group_size), fold.fold_R(R), group_size, 64, activation=activation,
+            dR_dtype=dR_dtype, dB_dtype=dB_dtype,
+            internal_bias=None if internal_bias is None else fold.fold_cols(internal_bias, 1),
+            dc_scale=dc_scale, tile_cfg_dadr=tile_cfg_dadr, tile_cfg_db=tile_cfg_db)
+        return (dA, fold.unfold_dR(dR64), None if dB2 is None else fold.unfold_cols(dB2, group_size),
+                None if d_ib2 is None else fold.unfold_cols(d_ib2, 1))
     if dC.shape != (M, N) or dC.dtype != A.dtype or dC.device != A.device or not dC.is_contiguous():
         raise ValueError(f"dC must be a contiguous ({M}, {N}) tensor of the same dtype and device as A")
     internal_bias = _check_internal_bias(internal_bias, A, N, K, group_size, gate)

@@ -19,8 +19,10 @@ Differences, all on the fast path:
   ``torch.linalg.solve`` in fp32 for fp16/bf16 parameters (which has no 16-bit kernels) and cast back;
 * the internal bias (``internal_bias=True``, gated modes) is added inside the kernels and its gradient
   comes out of the dA+dR kernel; ``dropout`` (gated modes, training) is the reference kernels' hash
-  dropout, regenerated in the backward from per-group seeds; input shuffle is not part of the
-  accelerated path and raises ``ValueError`` at construction.
+  dropout, regenerated in the backward from per-group seeds;
+* ``input_shuffle=True`` (``reconn_sz`` 16, chunks of 64 features, no dropout) builds the reference's per-group
+  butterfly masks and folds every group's permutation into a 64-wide rotation and a column order of the
+  weight (``_shuffle``): the same kernels, no per-group copy of the input.
 """
 from __future__ import annotations
 
@@ -186,7 +188,15 @@ class PrismLinear(nn.Module):
         if activation not in (None,) + _GATED:
             raise ValueError(f"Unknown activation {activation!r}, must be one of (None, 'silu_gate', 'sigmoid_gate')")
         if input_shuffle:
-            raise ValueError("input_shuffle is not supported by the sm_100a kernels")
+            # reference: src/cute_prism/_module.py:368-375; here additionally chunks of 64 features and no dropout
+            if reconn_sz != 16:
+                raise ValueError("input_shuffle requires reconn_sz=16")
+            if shuffle_blk_k != 64:
+                raise ValueError("input_shuffle is built for shuffle_blk_k=64")
+            if in_features % shuffle_blk_k != 0:
+                raise ValueError(f"in_features ({in_features}) must be divisible by shuffle_blk_k ({shuffle_blk_k})")
+            if dropout > 0.0:
+                raise ValueError("input_shuffle together with dropout is not supported by the sm_100a kernels")
         if dropout > 0.0 and gated_name(activation) and reconn_sz not in (8, 16):
             raise ValueError("dropout is supported for reconn_sz 8 and 16")
         self.dropout = float(dropout)
@@ -198,6 +208,12 @@ class PrismLinear(nn.Module):
 
         self.in_features, self.out_features = in_features, out_features
         self.group_size, self.reconn_sz = group_size, reconn_sz
+        self.input_shuffle, self.shuffle_blk_k = bool(input_shuffle), shuffle_blk_k
+        self._shuffle_fold = None
+        if input_shuffle:
+            from ._shuffle import build_shuffle_masks
+            masks, self._shuffle_deltas = build_shuffle_masks(in_features, out_features, group_size, reconn_sz, shuffle_blk_k)
+            self.register_buffer("_shuffle_masks", masks)
         self.activation = activation
         self.cayley_order = cayley_order
         self.r_init_scale = r_init_scale
@@ -308,8 +324,19 @@ class PrismLinear(nn.Module):
             # one seed per group and call; forward and backward regenerate the mask from them
             seeds = torch.randint(1, 1 << 62, (self.out_features // self.group_size,), dtype=torch.int64,
                                   device=A.device)
-        C = _prism_forward_op(A, self.weight, self._build_R(), self.bias, self.group_size, self.reconn_sz,
-                              self.activation or "", float(self._bwd_scale), self._internal_bias, seeds,
+        weight, R, rs, ib = self.weight, self._build_R(), self.reconn_sz, self._internal_bias
+        if self.input_shuffle:
+            # every group's permutation of the input features, folded into the parameters: a 64-wide rotation
+            # on the same kernels (``_shuffle``); autograd carries dR, dB and the bias gradient back through the fold
+            fold = self._shuffle_fold
+            if fold is None or fold.perm.device != A.device:
+                from ._shuffle import ShuffleFold
+                fold = self._shuffle_fold = ShuffleFold(self._shuffle_masks, self.in_features, self.group_size,
+                                                        self.reconn_sz, A.device)
+            weight, R, rs = fold.fold_cols(weight, self.group_size), fold.fold_R(R), 64
+            ib = None if ib is None else fold.fold_cols(ib, 1)
+        C = _prism_forward_op(A, weight, R, self.bias, self.group_size, rs,
+                              self.activation or "", float(self._bwd_scale), ib, seeds,
                               self.dropout)
         return C.reshape(input.shape[:-1] + (self.out_features,))
 
@@ -319,6 +346,8 @@ class PrismLinear(nn.Module):
                  f"bias={self.bias is not None}"]
         if self._internal_bias is not None:
             parts.append("internal_bias=True")
+        if self.input_shuffle:
+            parts.append(f"input_shuffle=True, shuffle_blk_k={self.shuffle_blk_k}")
         if self.activation is not None:
             parts.append(f"activation={self.activation!r}")
         else:

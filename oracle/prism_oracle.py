@@ -102,8 +102,42 @@ def dropout_multiplier(seed: int, M: int, K: int, p: float, device="cpu"):
     return (keep.to(torch.float32) * (1.0 / (1.0 - p))).reshape(M, K)
 
 
+SHUFFLE_SEGMENT_SZ = 2   # src/cute_prism/_pytorch_backend.py:12
+
+
+def shuffle_elem_perm(masks_g, K, reconn_sz):
+    """One group's element permutation, ``A_g[:, i] = A[:, perm[i]]``: inside every chunk of
+    K / n_chunks features the 2-element segments go through one round of XOR-partner swaps per delta (the
+    powers of two from the block size in segments up), pair p of a round swapped when bit p of the round's
+    mask is set (src/cute_prism/_pytorch_backend.py:25-76).  Plain loops: test infrastructure."""
+    n_chunks, n_rounds = masks_g.shape
+    blk = K // n_chunks
+    n_seg = blk // SHUFFLE_SEGMENT_SZ
+    block_size = reconn_sz // SHUFFLE_SEGMENT_SZ
+    deltas = [1 << r for r in range(n_seg.bit_length() - 1) if (1 << r) >= block_size]
+    assert len(deltas) == n_rounds
+    perm = list(range(K))
+    for c in range(n_chunks):
+        seg = list(range(n_seg))
+        for r, delta in enumerate(deltas):
+            bits = int(masks_g[c, r])
+            new = list(seg)
+            pair = 0
+            for i in range(n_seg):
+                partner = i ^ delta
+                if partner > i and partner < n_seg:
+                    if (bits >> pair) & 1:
+                        new[i], new[partner] = new[partner], new[i]
+                    pair += 1
+            seg = new
+        for dst, src in enumerate(seg):
+            for e in range(SHUFFLE_SEGMENT_SZ):
+                perm[c * blk + dst * SHUFFLE_SEGMENT_SZ + e] = c * blk + src * SHUFFLE_SEGMENT_SZ + e
+    return torch.tensor(perm, dtype=torch.long)
+
+
 def prism_forward(A, B, R, group_size, reconn_sz, activation=None, bias=None, internal_bias=None,
-                  dropout_seeds=None, dropout_p=0.0):
+                  dropout_seeds=None, dropout_p=0.0, shuffle_masks=None):
     """C (M, N) in the dtype of A.  Follows ``pytorch_forward`` (ar mode, optional gate; the internal bias
     (G, K) is added to S before the gate, lines 154-156)."""
     if activation not in GATES:
@@ -113,7 +147,10 @@ def prism_forward(A, B, R, group_size, reconn_sz, activation=None, bias=None, in
     G = N // group_size
     Rb = _blocks(R, G, reconn_sz)
     C = torch.empty(M, N, dtype=A.dtype, device=A.device)
+    A_in = A
     for g in range(G):
+        if shuffle_masks is not None:   # this group's permuted view of the input (lines 143-149); all that follows lives in it
+            A = A_in.index_select(1, shuffle_elem_perm(shuffle_masks[g].cpu(), K, reconn_sz).to(A_in.device))
         S = rotate(A, Rb[g])
         if activation is not None and internal_bias is not None:
             S = S + internal_bias[g]
@@ -127,7 +164,7 @@ def prism_forward(A, B, R, group_size, reconn_sz, activation=None, bias=None, in
 
 
 def prism_backward(dC, A, B, R, group_size, reconn_sz, activation=None, internal_bias=None,
-                   dropout_seeds=None, dropout_p=0.0):
+                   dropout_seeds=None, dropout_p=0.0, shuffle_masks=None):
     """(dA, dR, dB-or-None), plus d_internal_bias (G, K) = sum over tokens of dS as a fourth element when an
     internal bias is given (lines 246-248, 271-272).  Follows ``pytorch_backward``."""
     if activation not in GATES:
@@ -143,11 +180,18 @@ def prism_backward(dC, A, B, R, group_size, reconn_sz, activation=None, internal
     dR = torch.empty_like(R)
     dB = torch.empty_like(B) if gated else None
     d_ib = torch.empty_like(internal_bias) if (gated and internal_bias is not None) else None
+    A_in = A
     Ab = A.reshape(M, nb, rs)
     for g in range(G):
         sl = slice(g * group_size, (g + 1) * group_size)
         dC_g = dC[:, sl]
         dH = dC_g @ B[sl]
+        perm = None
+        if shuffle_masks is not None:   # gradients in the group's permuted space, dA added back through the permutation (lines 233-240, 300-304)
+            perm = shuffle_elem_perm(shuffle_masks[g].cpu(), K, reconn_sz).to(A_in.device)
+            A = A_in.index_select(1, perm)
+            Ab = A.reshape(M, nb, rs)
+        dA_g = torch.zeros_like(A)
         if gated:
             S = rotate(A, Rb[g])
             if internal_bias is not None:
@@ -162,10 +206,14 @@ def prism_backward(dC, A, B, R, group_size, reconn_sz, activation=None, internal
             dS = dH * A * gate_d
             if d_ib is not None:
                 d_ib[g] = dS.sum(dim=0)
-            dA += dH * gate
+            dA_g += dH * gate
         else:
             dS = dH
-        dA += rotate_t(dS, Rb[g])
+        dA_g += rotate_t(dS, Rb[g])
+        if perm is None:
+            dA += dA_g
+        else:
+            dA.index_add_(1, perm, dA_g)
         # dR block (g, b)[i, j] = sum_m dS[m, b*rs+i] * A[m, b*rs+j]
         dRg = torch.einsum("mbi,mbj->ibj", dS.reshape(M, nb, rs), Ab)
         dR[g * rs:(g + 1) * rs] = dRg.reshape(rs, K)

@@ -412,3 +412,69 @@ def test_prism_linear_dropout_train_and_eval():
             acc += layer(x).float()
     assert O.rel_err(acc / 64, y_eval.float()) < 0.35
     cp.check_device_status()
+
+
+@pytest.mark.parametrize("shape", [(512, 256, 512, 256), (300, 192, 384, 128), (16, 512, 1024, 256), (2048, 1024, 768, 256)],
+                         ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("act", [None, "silu_gate", "sigmoid_gate"])
+def test_input_shuffle_forward_and_backward(shape, act):
+    """Every group sees its own butterfly permutation of the input features (reference:
+    src/cute_prism/_module.py:236-270, _pytorch_backend.py:31-76): served by the 64-wide rotation of the same
+    kernels on folded parameters, checked against the oracle's per-group gather, with an internal bias."""
+    from cute_mma_b200 import _shuffle as S
+    M, K, N, gs = shape
+    rs = 16
+    dt = torch.bfloat16 if M % 32 == 0 else torch.float16
+    A, B, R, dC = _inputs(M, K, N, gs, rs, dt, seed=91)
+    masks, _ = S.build_shuffle_masks(K, N, gs, rs)
+    masks = masks.to(DEV)
+    ib = (torch.randn(N // gs, K, device=DEV) * 0.5).to(dt) if act else None
+    C, seeds = cp.forward(A, B, R, gs, rs, activation=act, internal_bias=ib, shuffle_masks=masks)
+    dA, dR, dB, d_ib = cp.backward(dC, A, B, R, gs, rs, activation=act, internal_bias=ib, shuffle_masks=masks)
+    cp.check_device_status()
+    assert seeds == [] and dR.shape == R.shape and dR.dtype == dt
+    Af, Bf, Rf = A.float(), B.float(), R.float()
+    ibf = None if ib is None else ib.float()
+    rC = O.prism_forward(Af, Bf, Rf, gs, rs, act, internal_bias=ibf, shuffle_masks=masks)
+    ref = O.prism_backward(dC.float(), Af, Bf, Rf, gs, rs, act, internal_bias=ibf, shuffle_masks=masks)
+    pairs = [("C", C, rC), ("dA", dA, ref[0]), ("dR", dR, ref[1])]
+    if act:
+        pairs += [("dB", dB, ref[2]), ("d_ib", d_ib, ref[3])]
+    else:
+        assert dB is None and d_ib is None
+    for name, val, r in pairs:
+        assert torch.isfinite(val).all(), name
+        assert O.rel_err(val.float(), r) < TOL, (name, O.rel_err(val.float(), r))
+    # without the masks the result is another one (groups 1.. are permuted)
+    C0, _ = cp.forward(A, B, R, gs, rs, activation=act, internal_bias=ib)
+    assert O.rel_err(C0.float(), rC) > 5e-2
+    with pytest.raises(ValueError):
+        cp.forward(A, B, R, gs, rs, activation="silu_gate", shuffle_masks=masks, dropout_p=0.1, training=True)
+
+
+def test_prism_linear_input_shuffle_trains():
+    """PrismLinear(input_shuffle=True): forward and all parameter gradients through autograd (the fold is made
+    of differentiable index operations) against the oracle with the module's own masks."""
+    torch.manual_seed(3)
+    K, N, gs, rs, M = 256, 512, 128, 16, 192
+    layer = cp.PrismLinear(K, N, group_size=gs, reconn_sz=rs, activation="silu_gate", input_shuffle=True,
+                           internal_bias=True).to(DEV, torch.bfloat16)
+    with torch.no_grad():
+        layer._internal_bias.normal_(0, 0.3)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16).requires_grad_(True)
+    y = layer(x)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    cp.check_device_status()
+    R = layer._build_R().detach().float()
+    W, ib, bias = layer.weight.detach().float(), layer._internal_bias.detach().float(), layer.bias.detach().float()
+    masks = layer._shuffle_masks
+    rC = O.prism_forward(x.detach().float(), W, R, gs, rs, "silu_gate", bias=bias, internal_bias=ib, shuffle_masks=masks)
+    scale = float(layer._bwd_scale)
+    rA, rR, rB, r_ib = O.prism_backward(dy.float() * scale, x.detach().float(), W, R, gs, rs, "silu_gate",
+                                        internal_bias=ib, shuffle_masks=masks)
+    assert O.rel_err(y.float(), rC) < TOL
+    assert O.rel_err(x.grad.float(), rA) < TOL
+    assert O.rel_err(layer.weight.grad.float(), rB) < TOL
+    assert O.rel_err(layer._internal_bias.grad.float(), r_ib) < TOL
+    assert layer.reconn.grad is not None and torch.isfinite(layer.reconn.grad).all() and layer.reconn.grad.abs().sum() > 0

@@ -13,6 +13,7 @@ import torch.multiprocessing as mp
 import cute_mma_b200 as cp
 from cute_mma_b200 import _functional as F
 from cute_mma_b200 import _tile_table
+from oracle import prism_oracle as O
 
 
 def test_validate_kernel_params():
@@ -86,9 +87,15 @@ def test_prism_linear_construction_and_state():
     assert dl.dropout == pytest.approx(0.1)
     with pytest.raises(ValueError):
         cp.PrismLinear(64, 128, group_size=32, reconn_sz=32, activation="silu_gate", dropout=0.1)   # 8 / 16 only
-    for bad in (dict(input_shuffle=True), dict(activation="tanh")):
+    sh = cp.PrismLinear(128, 128, group_size=32, reconn_sz=16, activation="silu_gate", input_shuffle=True)
+    assert sh._shuffle_masks.shape == (4, 2, 2) and "_shuffle_masks" in sh.state_dict()
+    assert int(sh._shuffle_masks[0].abs().sum()) == 0          # group 0 keeps the natural order
+    for bad in (dict(input_shuffle=True, reconn_sz=8), dict(input_shuffle=True, shuffle_blk_k=32),
+                dict(input_shuffle=True, activation="silu_gate", dropout=0.1), dict(activation="tanh")):
+        kw = dict(reconn_sz=16)
+        kw.update(bad)
         with pytest.raises(ValueError):
-            cp.PrismLinear(64, 128, 32, 16, **bad)
+            cp.PrismLinear(128, 128, 32, **kw)
     with pytest.raises(ValueError):
         cp.PrismLinear(64, 100, 32, 8)
 
@@ -171,3 +178,40 @@ def test_allreduce_is_a_noop_without_process_group():
     t = torch.ones(3)
     assert cp.allreduce_grads([t]) is None
     assert torch.equal(t, torch.ones(3))
+
+
+def test_input_shuffle_fold_is_the_reference_shuffle():
+    """The per-group butterfly permutation folded into a 64-wide rotation and a column order of B (what the
+    kernels are given) is the shuffled layer itself: checked with the oracle in float64 on the CPU, forward and
+    every gradient, against the oracle's own per-group gather (which follows the reference)."""
+    from cute_mma_b200 import _shuffle as S
+    M, K, N, gs, rs = 20, 192, 384, 128, 16
+    masks, deltas = S.build_shuffle_masks(K, N, gs, rs)
+    assert deltas == [8, 16] and masks.shape == (3, 3, 2) and int(masks[1:].abs().sum()) > 0
+    fold = S.ShuffleFold(masks, K, gs, rs, "cpu")
+    for g in range(3):
+        assert torch.equal(fold.perm[g], O.shuffle_elem_perm(masks[g], K, rs))
+        assert torch.equal(fold.perm[g][fold.inv[g]], torch.arange(K))
+    gen = torch.Generator().manual_seed(5)
+    A = torch.randn(M, K, generator=gen, dtype=torch.float64)
+    B = torch.randn(N, K, generator=gen, dtype=torch.float64) * K ** -0.5
+    R = O.orthogonal_R(N // gs, K, rs, gen).double()
+    dC = torch.randn(M, N, generator=gen, dtype=torch.float64)
+    ib = torch.randn(N // gs, K, generator=gen, dtype=torch.float64) * 0.3
+    for act in (None, "silu_gate", "sigmoid_gate"):
+        ibx = ib if act else None
+        C = O.prism_forward(A, B, R, gs, rs, act, internal_bias=ibx, shuffle_masks=masks)
+        grads = O.prism_backward(dC, A, B, R, gs, rs, act, internal_bias=ibx, shuffle_masks=masks)
+        R64, B2 = fold.fold_R(R), fold.fold_cols(B, gs)
+        ib2 = fold.fold_cols(ib, 1) if act else None
+        assert (O.prism_forward(A, B2, R64, gs, 64, act, internal_bias=ib2) - C).abs().max() < 1e-12
+        gf = O.prism_backward(dC, A, B2, R64, gs, 64, act, internal_bias=ib2)
+        assert (gf[0] - grads[0]).abs().max() < 1e-12
+        assert (fold.unfold_dR(gf[1]) - grads[1]).abs().max() < 1e-12
+        if act:
+            assert (fold.unfold_cols(gf[2], gs) - grads[2]).abs().max() < 1e-12
+            assert (fold.unfold_cols(gf[3], 1) - grads[3]).abs().max() < 1e-12
+        # the fold is differentiable: autograd through it gives the same dR as the explicit unfold
+        Rq = R.clone().requires_grad_(True)
+        (fold.fold_R(Rq) * gf[1]).sum().backward()
+        assert (Rq.grad - fold.unfold_dR(gf[1])).abs().max() < 1e-12

@@ -48,6 +48,30 @@ def test_oracle_matches_reference_internal_bias(path):
         assert O.rel_err(val, _t(z[key])) < tol, key
 
 
+def test_oracle_matches_reference_input_shuffle():
+    """Input shuffle: the reference's masks and its outputs (tests/golden/shuffle_a.npz); the masks are
+    also what the package's own mask builder produces."""
+    from cute_mma_b200 import _shuffle as S
+    z = np.load(os.path.join(GOLD, "shuffle_a.npz"))
+    M, K, N, gs, rs = [int(v) for v in z["meta"]]
+    A, B, R, dC, ib, masks = (_t(z[k]) for k in ("A", "B", "R", "dC", "ib", "masks"))
+    mine, deltas = S.build_shuffle_masks(K, N, gs, rs, 64)
+    assert torch.equal(mine, masks) and deltas == [int(v) for v in z["deltas"]]
+    assert int(masks[0].abs().sum()) == 0 and int(masks[1:].abs().sum()) > 0
+    for act, tag in ((None, "plain"), ("silu_gate", "gated"), ("sigmoid_gate", "sgate")):
+        ibx = ib if act else None
+        C = O.prism_forward(A, B, R, gs, rs, act, internal_bias=ibx, shuffle_masks=masks)
+        grads = O.prism_backward(dC, A, B, R, gs, rs, act, internal_bias=ibx, shuffle_masks=masks)
+        assert O.rel_err(C, _t(z[f"C_{tag}"])) < 1e-12
+        assert O.rel_err(grads[0], _t(z[f"dA_{tag}"])) < 1e-12
+        assert O.rel_err(grads[1], _t(z[f"dR_{tag}"])) < 1e-12
+        if act:
+            assert O.rel_err(grads[2], _t(z[f"dB_{tag}"])) < 1e-12
+            assert O.rel_err(grads[3], _t(z[f"dib_{tag}"])) < 1e-12
+        # the shuffle really changes the result
+        assert O.rel_err(O.prism_forward(A, B, R, gs, rs, act, internal_bias=ibx), _t(z[f"C_{tag}"])) > 1e-2
+
+
 @pytest.mark.parametrize("seed", [0, 1])
 def test_oracle_matches_reference_config0(seed):
     z = np.load(os.path.join(GOLD, f"config0_seed{seed}.npz"))
