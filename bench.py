@@ -398,6 +398,27 @@ def run_e2e(args, w, dev, world, A, B, R, dC, step_flops):
     dC_full.copy_(dC_h, non_blocking=True)
     h2d_gbs = copy_rate(dC_full, dC_h)
     d2h_gbs = copy_rate(C_h, dC_full)
+    # the step copies in both directions at once: the two rates with both directions busy (two streams,
+    # in the step's byte ratio: the shorter direction is repeated until the longer one is done)
+    def both_rates(reps=3):
+        up = torch.empty_like(dC)
+        sa, sb = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        torch.cuda.synchronize()
+        with torch.cuda.stream(sa):
+            e[0].record(sa)
+            for _ in range(reps):
+                up.copy_(dC_h, non_blocking=True)
+            e[1].record(sa)
+        with torch.cuda.stream(sb):
+            e[2].record(sb)
+            for _ in range(reps):
+                C_h.copy_(dC_full, non_blocking=True)
+            e[3].record(sb)
+        torch.cuda.synchronize()
+        nbytes = dC.numel() * dC.element_size() * reps
+        return nbytes / (e[0].elapsed_time(e[1]) * 1e-3) / 1e9, nbytes / (e[2].elapsed_time(e[3]) * 1e-3) / 1e9
+    h2d_gbs_both, d2h_gbs_both = both_rates()
     del dC_full
 
     def e2e_steps(n_steps):
@@ -460,12 +481,16 @@ def run_e2e(args, w, dev, world, A, B, R, dC, step_flops):
     h2d = int((A_h.numel() + dC_h.numel()) * 2)
     d2h = int(C_h.numel() * 2 + dA_h.numel() * 2 + dR_h.numel() * 2 + (dB_h.numel() * 2 if gate else 0))
     copy_bound_ms = max(h2d / h2d_gbs, d2h / d2h_gbs) / 1e6
+    copy_bound_both_ms = max(h2d / h2d_gbs_both, d2h / d2h_gbs_both) / 1e6
     return {"value": world * step_flops / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e_ms, "steps": e_steps,
             "micro_batches": n_mb,
             "h2d_gbs_achieved": h2d / (e_ms * 1e-3) / 1e9, "d2h_gbs_achieved": d2h / (e_ms * 1e-3) / 1e9,
             "h2d_gbs_plain_copy": h2d_gbs, "d2h_gbs_plain_copy": d2h_gbs,
             "copy_bound_ms": copy_bound_ms, "ms_over_copy_bound": e_ms / copy_bound_ms,
+            "h2d_gbs_plain_copy_both_directions": h2d_gbs_both, "d2h_gbs_plain_copy_both_directions": d2h_gbs_both,
+            "copy_bound_both_directions_ms": copy_bound_both_ms,
+            "ms_over_copy_bound_both_directions": e_ms / copy_bound_both_ms,
             "note": "cute_mma_b200.forward/backward per micro-batch with A, dC from pinned host memory; C, dA "
                     "copied back per micro-batch, dR, dB (accumulated in fp32, cast to 16 bit) once per step; copies "
                     "and kernels of neighbouring micro-batches and steps overlap on three streams, one host wait after "
