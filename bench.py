@@ -292,7 +292,7 @@ def make_inputs(w, dev, rank, M=None):
     return A, B, R, dC
 
 
-def make_step(w, A, B, R, dC, world):
+def make_step(w, A, B, R, dC, world, exchange="nccl"):
     """One step on resident inputs: forward, dB (its all-reduce starts at once), dA+dR, all-reduce(dR)."""
     import cute_mma_b200 as cp
     from cute_mma_b200 import _functional as F
@@ -308,6 +308,35 @@ def make_step(w, A, B, R, dC, world):
             runs = max(1, pairs // n_ft)
             extra = pairs - n_ft * runs
             dadr_cfg = [runs, 0 if extra > 0 else -1, max(extra, 0)]
+
+    if world > 1 and exchange == "peer":
+        # the gradient sums over peer memory: the reduce kernels write their fp32 sums straight into buffers all
+        # ranks can address, one kernel per rank adds its slice over the ranks in rank order (bit-identical on
+        # every rank) and stores it everywhere; the dB exchange runs on a side stream beside the dA+dR kernel
+        red_b = cp.PeerGradReducer([tuple(B.shape)], out_dtype=A.dtype, ctas=NCCL_CTAS) if gate else None
+        red_r = cp.PeerGradReducer([tuple(R.shape)], out_dtype=A.dtype, ctas=NCCL_CTAS)
+        side = torch.cuda.Stream()
+
+        def step_peer(ev=None):
+            if ev: ev[0].record()
+            C, _ = cp.forward(A, B, R, gs, rs, activation=act)
+            if ev: ev[1].record()
+            dB = None
+            if gate:
+                F._backward_db(dC, A, R, gs, rs, gate, out_dtype=torch.float32, dB_out=red_b.inputs()[0])
+                ready = torch.cuda.Event()
+                ready.record()
+                with torch.cuda.stream(side):
+                    side.wait_event(ready)
+                    dB = red_b.reduce()[0]
+            if ev: ev[2].record()
+            dA, _ = F._backward_dadr(dC, A, B, R, gs, rs, gate, tile_cfg=dadr_cfg, dR_dtype=torch.float32,
+                                     dR_out=red_r.inputs()[0])
+            if ev: ev[3].record()
+            dR = red_r.reduce()[0]
+            torch.cuda.current_stream().wait_stream(side)
+            return C, dA, dR, dB
+        return step_peer
 
     def step(ev=None):
         if ev: ev[0].record()
@@ -570,7 +599,7 @@ def run_small_m(w, dev, B, R, peaks):
             "hbm_peak_gbs": peaks["hbm_gbs"], "calls": small}
 
 
-def run_train_cfg3(dev, rank, world, local_rank):
+def run_train_cfg3(dev, rank, world, local_rank, exchange="nccl"):
     """The 65536-token fp16 training step (K=1024, N=16384, gs=256, rs=8, silu_gate) with its token rows
     split evenly over the ranks: forward, dB, all-reduce(dB) beside dA+dR, all-reduce(dR).  Strong
     scaling: tokens/s of the whole job; rank 0 also times the unsplit step on its own GPU, which gives
@@ -580,7 +609,7 @@ def run_train_cfg3(dev, rank, world, local_rank):
     rows = w["M"] // world
     wl = dict(w, M=rows)
     A, B, R, dC = make_inputs(wl, dev, rank)
-    step = make_step(wl, A, B, R, dC, world)
+    step = make_step(wl, A, B, R, dC, world, exchange)
     for _ in range(3):
         step()
     n = 6
@@ -588,7 +617,8 @@ def run_train_cfg3(dev, rank, world, local_rank):
     out = {"workload": "cfg3 (M=65536 split over the ranks)", "rows_per_gpu": rows, "ms_per_step": ms,
            "tokens_per_s": w["M"] / (ms * 1e-3), "tflops": sum(flops(w).values()) / (ms * 1e-3) / 1e12,
            "kernels_ms": parts, "scaling": "strong",
-           "exchange": "NCCL all-reduce of dB (33.5 MB fp16) beside the dA+dR kernel, then of dR (1 MB)"}
+           "exchange": ("NCCL all-reduce of dB (33.5 MB fp16) beside the dA+dR kernel, then of dR (1 MB)" if exchange == "nccl" else
+                        "prism_peer_reduce over peer memory: fp32 dB sums (67 MB) added in rank order beside the dA+dR kernel, then dR")}
     del A, dC, step
     torch.cuda.empty_cache()
     if world > 1:
@@ -812,6 +842,9 @@ def main():
     ap.add_argument("--no-train-cfg3", action="store_true")
     ap.add_argument("--small-m-sweep", action="store_true",
                     help="only time the few-token forward, streaming against general kernel, and print the table")
+    ap.add_argument("--grad-exchange", default="nccl", choices=["nccl", "peer"],
+                    help="N > 1: how dB / dR are summed over the ranks: NCCL all-reduce (default) or this library's "
+                         "kernel over peer memory (cute_mma_b200.PeerGradReducer: fp32 sums added in rank order)")
     ap.add_argument("--no-cuda-graph", action="store_true", help="cfg4: issue the step eagerly")
     ap.add_argument("--cfg4-sequences", type=int, default=64, help="cfg4: global batch in sequences (64 = the configuration)")
     args = ap.parse_args()
@@ -859,7 +892,7 @@ def main():
     A, B, R, dC = make_inputs(w, dev, rank)
     fl = flops(w)
     step_flops = sum(fl.values())
-    step = make_step(w, A, B, R, dC, world)
+    step = make_step(w, A, B, R, dC, world, args.grad_exchange)
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
@@ -882,7 +915,7 @@ def main():
     train_cfg3 = None
     if not args.no_train_cfg3 and wname == "cfg2_m16384":
         del step
-        train_cfg3 = run_train_cfg3(dev, rank, world, local_rank)
+        train_cfg3 = run_train_cfg3(dev, rank, world, local_rank, args.grad_exchange)
 
     if rank != 0:
         if world > 1:
@@ -925,6 +958,8 @@ def main():
         "frac_of_measured_sustained": value / world / sust,
         "roofline": roofline, "clocks": clocks, "gpu_launches": int(launches), "host": placement,
     }
+    if world > 1:
+        line["grad_exchange"] = args.grad_exchange
     if sustained:
         sustained["frac_of_measured_sustained"] = sustained["value"] / world / sust
         sustained["frac_of_nominal_peak"] = sustained["value"] / world / NOMINAL_TFLOPS

@@ -344,14 +344,24 @@ def cayley_backward(M, dR, reconn_sz: int):
     return dM
 
 
+def _out_buffer(out, shape, dtype, device, name):
+    """``out`` if given (a contiguous tensor of that shape and dtype, e.g. a view of a gradient staging
+    buffer that other GPUs read), else a new tensor."""
+    if out is None:
+        return torch.empty(shape, dtype=dtype, device=device)
+    if tuple(out.shape) != tuple(shape) or out.dtype != dtype or out.device != device or not out.is_contiguous():
+        raise ValueError(f"{name} must be a contiguous {tuple(shape)} tensor of {dtype} on {device}")
+    return out
+
+
 def _backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=None, out_dtype=None,
-                 internal_bias=None, dropout_seeds=None, dropout_p=0.0):
+                 internal_bias=None, dropout_seeds=None, dropout_p=0.0, dB_out=None):
     """dB = dc_scale * dC^T . H  through ``prism_bwd_db`` (H recomputed on chip); with
-    ``out_dtype=torch.float32`` the kernel's fp32 sums are returned unrounded."""
+    ``out_dtype=torch.float32`` the kernel's fp32 sums are returned unrounded.  ``dB_out``: write there."""
     M, K = A.shape
     N = dC.shape[1]
     out_dtype, out_code = _grad_dtype(out_dtype, A.dtype, "dB_dtype")
-    dB = torch.empty(N, K, dtype=out_dtype, device=A.device)
+    dB = _out_buffer(dB_out, (N, K), out_dtype, A.device, "dB_out")
     L = _lib.lib()
     cfg = tile_cfg if tile_cfg is not None else _tile_lookup("bwd_db", A.dtype, gate, M, N, K, group_size, reconn_sz)
     cfg_arr = _cfg_array(cfg)
@@ -368,7 +378,7 @@ def _backward_db(dC, A, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=N
 
 
 def _backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_cfg=None, dR_dtype=None,
-                   internal_bias=None, dropout_seeds=None, dropout_p=0.0):
+                   internal_bias=None, dropout_seeds=None, dropout_p=0.0, dR_out=None):
     """(dA, dR), both scaled by ``dc_scale``, through ``prism_bwd_dadr``; with
     ``dR_dtype=torch.float32`` the fp32 sums of the dR reduction are returned unrounded.  With an
     ``internal_bias`` the result is ``(dA, dR, d_internal_bias)``."""
@@ -376,7 +386,7 @@ def _backward_dadr(dC, A, B, R, group_size, reconn_sz, gate, dc_scale=1.0, tile_
     N = B.shape[0]
     dR_dtype, dr_code = _grad_dtype(dR_dtype, A.dtype, "dR_dtype")
     dA = torch.empty(M, K, dtype=A.dtype, device=A.device)
-    dR = torch.empty(R.shape, dtype=dR_dtype, device=A.device)
+    dR = _out_buffer(dR_out, R.shape, dR_dtype, A.device, "dR_out")
     d_ib = torch.empty_like(internal_bias) if internal_bias is not None else None
     L = _lib.lib()
     cfg = tile_cfg if tile_cfg is not None else _tile_lookup("bwd_dadr", A.dtype, gate, M, N, K, group_size, reconn_sz)

@@ -15,7 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.environ.get("PRISM_B200_LIB", os.path.join(_HERE, "libprism_b200.so"))
 SOURCES = ["prism_abi.cu", "prism_fwd.cu", "prism_fwd_small.cu", "prism_bwd_db.cu", "prism_bwd_dadr.cu",
-           "prism_bwd_dadr_f16.cu", "prism_bwd_dadr_bf16.cu", "prism_fwd_noalloc.cu", "prism_cayley.cu"]
+           "prism_bwd_dadr_f16.cu", "prism_bwd_dadr_bf16.cu", "prism_fwd_noalloc.cu", "prism_cayley.cu", "prism_peer_reduce.cu"]
 HEADERS = ["prism_common.cuh", "prism_host.cuh", "prism_kernels.cuh", "prism_bwd_dadr_kernel.cuh"]
 PUBLIC_HEADER = os.path.join(os.path.dirname(_HERE), "include", "prism_b200.h")
 
@@ -26,7 +26,7 @@ NVCC_FLAGS = [
 
 # every symbol include/prism_b200.h declares
 EXPORTS = [
-    "prism_fwd", "prism_fwd_dropout", "prism_fwd_noalloc", "prism_bwd_dadr", "prism_bwd_db", "prism_dbias", "prism_fold_weight", "prism_cayley", "prism_cayley_bwd", "prism_workspace_bytes",
+    "prism_fwd", "prism_fwd_dropout", "prism_fwd_noalloc", "prism_bwd_dadr", "prism_bwd_db", "prism_dbias", "prism_fold_weight", "prism_cayley", "prism_cayley_bwd", "prism_peer_reduce", "prism_workspace_bytes",
     "prism_status",
     "prism_last_error_string", "prism_abi_version", "prism_launch_count",
 ]
@@ -130,6 +130,8 @@ def lib() -> ctypes.CDLL:
             L.prism_cayley.argtypes = [vp, vp, i, i, i, i, ll, ll, vp]
             L.prism_cayley_bwd.restype = i
             L.prism_cayley_bwd.argtypes = [vp, vp, vp, i, i, i, i, ll, ll, ll, vp]
+            L.prism_peer_reduce.restype = i
+            L.prism_peer_reduce.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(vp), i, i, ll, i, ctypes.c_float, i, vp]
             L.prism_workspace_bytes.restype = sz
             L.prism_workspace_bytes.argtypes = [i, i, i, i, i, i, i, ip]
             L.prism_status.restype = i

@@ -165,6 +165,18 @@ int prism_cayley(const void* M, void* R, int n_groups, int K, int reconn_sz, int
 int prism_cayley_bwd(const void* M, const void* dR, void* dM, int n_groups, int K, int reconn_sz, int dtype,
                      long long ldm, long long lddr, long long lddm, void* stream);
 
+/* Sum of gradient buffers over the GPUs of one box, over peer memory: the exchange step of token-sharded
+ * training (the reference leaves it to DistributedDataParallel's all-reduce, integration/train.py:130-145,
+ * 299-300).  in_ptrs / out_ptrs: HOST arrays of `world` device pointers -- every rank's fp32 buffer of n
+ * elements and every rank's result buffer (out_dtype: PRISM_DTYPE_F16 / BF16 / F32), as this process maps
+ * them (symmetric memory, CUDA IPC).  Rank `rank` sums its n / world slice over the ranks in rank order
+ * (bit-identical on every rank and run), multiplies by `scale`, and stores the result into every rank's
+ * result buffer.  The kernel does not wait for anybody: call it between two barriers over the ranks
+ * (all inputs written; nobody reads a result or rewrites an input before all ranks are done).
+ * n: a multiple of 4; buffers 16-byte aligned; ctas: grid size (0 = 16). */
+int prism_peer_reduce(const void* const* in_ptrs, void* const* out_ptrs, int world, int rank, long long n,
+                      int out_dtype, float scale, int ctas, void* stream);
+
 /* Bytes of workspace the given call needs (kind = PRISM_KIND_*), header included. */
 size_t prism_workspace_bytes(int kind, int M, int N, int K, int group_size, int reconn_sz,
                              int dtype, const int* cfg);
