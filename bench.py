@@ -292,7 +292,7 @@ def make_inputs(w, dev, rank, M=None):
     return A, B, R, dC
 
 
-def make_step(w, A, B, R, dC, world, exchange="nccl"):
+def make_step(w, A, B, R, dC, world, exchange="auto"):
     """One step on resident inputs: forward, dB (its all-reduce starts at once), dA+dR, all-reduce(dR)."""
     import cute_mma_b200 as cp
     from cute_mma_b200 import _functional as F
@@ -309,12 +309,28 @@ def make_step(w, A, B, R, dC, world, exchange="nccl"):
             extra = pairs - n_ft * runs
             dadr_cfg = [runs, 0 if extra > 0 else -1, max(extra, 0)]
 
-    if world > 1 and exchange == "peer":
+    red_b = red_r = None
+    if world > 1 and exchange in ("peer", "auto"):
         # the gradient sums over peer memory: the reduce kernels write their fp32 sums straight into buffers all
         # ranks can address, one kernel per rank adds its slice over the ranks in rank order (bit-identical on
-        # every rank) and stores it everywhere; the dB exchange runs on a side stream beside the dA+dR kernel
-        red_b = cp.PeerGradReducer([tuple(B.shape)], out_dtype=A.dtype, ctas=NCCL_CTAS) if gate else None
-        red_r = cp.PeerGradReducer([tuple(R.shape)], out_dtype=A.dtype, ctas=NCCL_CTAS)
+        # every rank) and stores it everywhere; the dB exchange runs on a side stream beside the dA+dR kernel.
+        # "auto": if the symmetric buffers cannot be set up on some rank, all ranks agree on NCCL instead.
+        import torch.distributed as dist
+        ok = 1
+        try:
+            red_b = cp.PeerGradReducer([tuple(B.shape)], out_dtype=A.dtype, ctas=NCCL_CTAS) if gate else None
+            red_r = cp.PeerGradReducer([tuple(R.shape)], out_dtype=A.dtype, ctas=NCCL_CTAS)
+        except Exception as e:   # noqa: BLE001 -- any set-up failure means "use NCCL", on every rank
+            if exchange == "peer":
+                raise
+            print(f"[bench] peer exchange not available on rank {dist.get_rank()}: {e}", file=sys.stderr, flush=True)
+            ok = 0
+        flag = torch.tensor([ok], device=A.device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            red_b = red_r = None
+    make_step.last_exchange = "peer" if red_r is not None else ("nccl" if world > 1 else None)
+    if red_r is not None:
         side = torch.cuda.Stream()
 
         def step_peer(ev=None):
@@ -599,7 +615,7 @@ def run_small_m(w, dev, B, R, peaks):
             "hbm_peak_gbs": peaks["hbm_gbs"], "calls": small}
 
 
-def run_train_cfg3(dev, rank, world, local_rank, exchange="nccl"):
+def run_train_cfg3(dev, rank, world, local_rank, exchange="auto"):
     """The 65536-token fp16 training step (K=1024, N=16384, gs=256, rs=8, silu_gate) with its token rows
     split evenly over the ranks: forward, dB, all-reduce(dB) beside dA+dR, all-reduce(dR).  Strong
     scaling: tokens/s of the whole job; rank 0 also times the unsplit step on its own GPU, which gives
@@ -617,7 +633,8 @@ def run_train_cfg3(dev, rank, world, local_rank, exchange="nccl"):
     out = {"workload": "cfg3 (M=65536 split over the ranks)", "rows_per_gpu": rows, "ms_per_step": ms,
            "tokens_per_s": w["M"] / (ms * 1e-3), "tflops": sum(flops(w).values()) / (ms * 1e-3) / 1e12,
            "kernels_ms": parts, "scaling": "strong",
-           "exchange": ("NCCL all-reduce of dB (33.5 MB fp16) beside the dA+dR kernel, then of dR (1 MB)" if exchange == "nccl" else
+           "exchange": ("NCCL all-reduce of dB (33.5 MB fp16) beside the dA+dR kernel, then of dR (1 MB)"
+                        if make_step.last_exchange != "peer" else
                         "prism_peer_reduce over peer memory: fp32 dB sums (67 MB) added in rank order beside the dA+dR kernel, then dR")}
     del A, dC, step
     torch.cuda.empty_cache()
@@ -842,9 +859,10 @@ def main():
     ap.add_argument("--no-train-cfg3", action="store_true")
     ap.add_argument("--small-m-sweep", action="store_true",
                     help="only time the few-token forward, streaming against general kernel, and print the table")
-    ap.add_argument("--grad-exchange", default="nccl", choices=["nccl", "peer"],
-                    help="N > 1: how dB / dR are summed over the ranks: NCCL all-reduce (default) or this library's "
-                         "kernel over peer memory (cute_mma_b200.PeerGradReducer: fp32 sums added in rank order)")
+    ap.add_argument("--grad-exchange", default="auto", choices=["auto", "nccl", "peer"],
+                    help="N > 1: how dB / dR are summed over the ranks: this library's kernel over peer memory "
+                         "(cute_mma_b200.PeerGradReducer: fp32 sums added in rank order), NCCL all-reduce, or auto: "
+                         "peer memory if every rank can set it up, else NCCL")
     ap.add_argument("--no-cuda-graph", action="store_true", help="cfg4: issue the step eagerly")
     ap.add_argument("--cfg4-sequences", type=int, default=64, help="cfg4: global batch in sequences (64 = the configuration)")
     args = ap.parse_args()
@@ -893,6 +911,7 @@ def main():
     fl = flops(w)
     step_flops = sum(fl.values())
     step = make_step(w, A, B, R, dC, world, args.grad_exchange)
+    exchange_used = make_step.last_exchange
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
@@ -959,7 +978,7 @@ def main():
         "roofline": roofline, "clocks": clocks, "gpu_launches": int(launches), "host": placement,
     }
     if world > 1:
-        line["grad_exchange"] = args.grad_exchange
+        line["grad_exchange"] = exchange_used
     if sustained:
         sustained["frac_of_measured_sustained"] = sustained["value"] / world / sust
         sustained["frac_of_nominal_peak"] = sustained["value"] / world / NOMINAL_TFLOPS
