@@ -63,10 +63,19 @@ def allreduce_grads(grads, group=None, average: bool = False, async_op: bool = F
     return None
 
 
-def sync_module_grads(module: torch.nn.Module, group=None, average: bool = True) -> None:
-    """All-reduce the ``.grad`` of every trainable parameter of ``module`` (DDP semantics)."""
-    allreduce_grads([p.grad for p in module.parameters() if p.requires_grad and p.grad is not None],
-                    group=group, average=average)
+def sync_module_grads(module: torch.nn.Module, group=None, average: bool = True, reducer=None) -> None:
+    """Sum (``average``: mean) the ``.grad`` of every trainable parameter of ``module`` over the ranks (DDP
+    semantics): an NCCL / gloo all-reduce, or with ``reducer`` (``PeerGradReducer.for_module(module)``) the
+    library's rank-order fp32 sum over peer memory."""
+    params = [p for p in module.parameters() if p.requires_grad and p.grad is not None]
+    if reducer is None:
+        allreduce_grads([p.grad for p in params], group=group, average=average)
+        return
+    if [tuple(p.shape) for p in params] != reducer.shapes:
+        raise ValueError("the reducer was built for another set of parameters")
+    torch._foreach_copy_(reducer.inputs(), [p.grad for p in params])
+    outs = reducer.reduce()
+    torch._foreach_copy_([p.grad for p in params], outs)
 
 
 class PeerGradReducer:
@@ -115,6 +124,15 @@ class PeerGradReducer:
         vp = ctypes.c_void_p
         self._in_ptrs = (vp * self.world)(*[vp(int(p)) for p in self._h_in.buffer_ptrs])
         self._out_ptrs = (vp * self.world)(*[vp(int(p)) for p in self._h_out.buffer_ptrs])
+
+    @classmethod
+    def for_module(cls, module: torch.nn.Module, average: bool = True, **kw):
+        """A reducer for the gradients of ``module``'s trainable parameters (``sync_module_grads(reducer=...)``);
+        results in fp32, ``average`` as in DistributedDataParallel."""
+        params = [p for p in module.parameters() if p.requires_grad]
+        kw.setdefault("out_dtype", torch.float32)
+        kw.setdefault("device", params[0].device)
+        return cls([tuple(p.shape) for p in params], average=average, **kw)
 
     def _views(self, flat):
         out = []

@@ -76,6 +76,17 @@ def _worker(rank, world, port, q):
             for t in parts[1:]:
                 exact += t
             ok = ok and torch.equal(o, exact.to(torch.bfloat16))
+    # a module's gradients through the same exchange, averaged like DistributedDataParallel
+    torch.manual_seed(7)
+    lin = torch.nn.Linear(64, 32).to(dev)
+    lin(torch.randn(16, 64, device=dev, generator=torch.Generator(device=dev).manual_seed(rank))).square().sum().backward()
+    want = [p.grad.clone() for p in lin.parameters()]
+    for w_ in want:
+        dist.all_reduce(w_)
+        w_ /= world
+    cp.sync_module_grads(lin, reducer=cp.PeerGradReducer.for_module(lin, ctas=4))
+    torch.cuda.synchronize()
+    ok = ok and all(torch.allclose(p.grad, w_, rtol=1e-5, atol=1e-6) for p, w_ in zip(lin.parameters(), want))
     q.put((rank, ok))
     dist.barrier()
     dist.destroy_process_group()
